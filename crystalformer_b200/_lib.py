@@ -1,0 +1,74 @@
+"""ctypes binding of ``libcrystalformer_b200.so`` (the C ABI declared in include/crystalformer_b200.h).
+
+There is no CPU or PyTorch fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_double, c_int, c_int64, c_void_p
+from typing import Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcrystalformer_b200.so")
+_lib: Optional[ctypes.CDLL] = None
+
+P, I64, I32, F64 = c_void_p, c_int64, c_int, c_double
+
+# name -> argument types, in the order of include/crystalformer_b200.h
+SIGNATURES = {
+    "cf_crystal_offsets": [P, I64, P, P, P],
+    "cf_batch_prepare": [P, P, P, P, P, I64, I64, I64, P, P, P, P, P, P, P, P],
+    "cf_lattice_box": [P, I32, P, P, I64, I64, I64, P, F64, I32, I32, P, P],
+    "cf_lattice_sum_fwd": [P, I32, P, P, P, P, I64, I64, I64, I64, F64, F64, P, I64, I64, P, F64, I32, I32, P, P, P],
+    "cf_lattice_sum_bwd": [P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, F64, F64, P, I64, I64, P, F64, I32, I32, P, P,
+                           P, P],
+    "cf_fused_attn_fwd": [P, P, P, P, P, P, P, I64, I64, I64, I64, P, P, P],
+    "cf_fused_attn_bwd": [P, P, P, P, P, P, I64, I64, I64, I64, P, P, P, P, P, P, P, P, P],
+    "cf_segment_mean_fwd": [P, P, I64, I64, P, P],
+    "cf_infinite_attn_fwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32, I32, P,
+                             P, P, P, P],
+    "cf_infinite_attn_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32, I32, P,
+                             P, P, P, P, P, P, P, P, P],
+    "cf_pipe_probe": [I32, I32, I32, I64, P, P],
+}
+
+
+class CrystalformerB200Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, name: str, code: int, message: str):
+        super().__init__(f"{name} failed with code {code}: {message}")
+        self.code = code
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library once; raises if it has not been built (python -m crystalformer_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m crystalformer_b200.build`; "
+                "crystalformer_b200 has no CPU fallback")
+        lib = ctypes.CDLL(LIB_PATH)
+        lib.cf_version.restype = c_int
+        lib.cf_last_error.restype = c_char_p
+        lib.cf_set_weight_floor_log2.argtypes = [c_double]
+        lib.cf_set_weight_floor_log2.restype = None
+        lib.cf_get_weight_floor_log2.restype = c_double
+        lib.cf_lattice_sum_bwd_scratch_bytes.argtypes = [I64, I64, I64, I64]
+        lib.cf_lattice_sum_bwd_scratch_bytes.restype = c_int64
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _lib = lib
+    return _lib
+
+
+def call(name: str, *args) -> None:
+    """Calls one entry point and raises CrystalformerB200Error on a negative status."""
+    lib = load()
+    code = getattr(lib, name)(*args)
+    if code != 0:
+        raise CrystalformerB200Error(name, code, lib.cf_last_error().decode())

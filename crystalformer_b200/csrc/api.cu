@@ -1,0 +1,65 @@
+// Host-side plumbing shared by every entry point: error reporting, tuning knobs, device queries.
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace cf {
+
+static thread_local char g_error[512] = "";
+static std::atomic<double> g_floor_log2{-40.0};
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int launch_status(const char *what)
+{
+    cudaError_t err = cudaPeekAtLastError();
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(CF_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+    }
+    return CF_OK;
+}
+
+float weight_floor()
+{
+    const double f = g_floor_log2.load();
+    return f <= -150.0 ? 0.0f : (float)std::exp2(f);
+}
+
+int sm_count()
+{
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached = n;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+}  // namespace cf
+
+extern "C" {
+
+int cf_version(void) { return 100; }
+
+const char *cf_last_error(void) { return cf::g_error; }
+
+void cf_set_weight_floor_log2(double log2_floor) { cf::g_floor_log2.store(log2_floor); }
+
+double cf_get_weight_floor_log2(void) { return cf::g_floor_log2.load(); }
+
+}  // extern "C"

@@ -1,0 +1,160 @@
+// Batch preparation on the device: crystal offsets, the all-pairs edge list, its CSR, relative positions and the
+// reciprocal-lattice quantities the cut-off rule needs.  Replaces the host loop over crystals and the tolist()
+// synchronisations of the reference (models/indexed_latticeformer_encoder.py:15-32, 183-253).
+#include "common.cuh"
+
+namespace cf {
+namespace {
+
+constexpr int SCAN_THREADS = 1024;
+
+// Exclusive prefix sums of sizes and sizes^2 with one block: each thread scans a contiguous chunk.
+__global__ void __launch_bounds__(SCAN_THREADS) crystal_offsets_kernel(const int64_t *__restrict__ sizes, long long B,
+                                                                       int64_t *__restrict__ atom_start,
+                                                                       int64_t *__restrict__ edge_start)
+{
+    __shared__ long long part_n[SCAN_THREADS], part_e[SCAN_THREADS];
+    const int t = threadIdx.x;
+    const long long chunk = (B + SCAN_THREADS - 1) / SCAN_THREADS;
+    const long long lo = min((long long)t * chunk, B), hi = min(lo + chunk, B);
+    long long sn = 0, se = 0;
+    for (long long b = lo; b < hi; ++b) {
+        const long long n = sizes[b];
+        sn += n;
+        se += n * n;
+    }
+    part_n[t] = sn;
+    part_e[t] = se;
+    __syncthreads();
+    // Hillis-Steele inclusive scan over the 1024 partials
+    for (int off = 1; off < SCAN_THREADS; off <<= 1) {
+        long long vn = 0, ve = 0;
+        if (t >= off) {
+            vn = part_n[t - off];
+            ve = part_e[t - off];
+        }
+        __syncthreads();
+        part_n[t] += vn;
+        part_e[t] += ve;
+        __syncthreads();
+    }
+    long long on = part_n[t] - sn, oe = part_e[t] - se;
+    for (long long b = lo; b < hi; ++b) {
+        atom_start[b] = on;
+        edge_start[b] = oe;
+        const long long n = sizes[b];
+        on += n;
+        oe += n * n;
+    }
+    if (t == SCAN_THREADS - 1) {
+        atom_start[B] = part_n[t];
+        edge_start[B] = part_e[t];
+    }
+}
+
+// Largest b in [0, B) with start[b] <= x  (start is non-decreasing, start[0] = 0; empty crystals are skipped over).
+__device__ __forceinline__ long long find_segment(const int64_t *__restrict__ start, long long B, long long x)
+{
+    long long lo = 0, hi = B;  // invariant: start[lo] <= x < start[hi]
+    while (hi - lo > 1) {
+        const long long mid = (lo + hi) >> 1;
+        if (start[mid] <= x) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__global__ void cell_kernel(const float *__restrict__ trans, long long B, float *__restrict__ rvecs,
+                            float *__restrict__ vcell, float *__restrict__ rvlen)
+{
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    const float *m = trans + 9 * b;
+    // determinant by the rule of Sarrus, term order as models/indexed_latticeformer_encoder.py:34-44
+    const float v = __fadd_rn(__fadd_rn(__fmul_rn(__fmul_rn(m[0], m[4]), m[8]), __fmul_rn(__fmul_rn(m[1], m[5]), m[6])),
+                              __fmul_rn(__fmul_rn(m[2], m[3]), m[7]))
+                  - __fmul_rn(__fmul_rn(m[2], m[4]), m[6]) - __fmul_rn(__fmul_rn(m[0], m[5]), m[7])
+                  - __fmul_rn(__fmul_rn(m[1], m[3]), m[8]);
+    if (vcell) vcell[b] = v;
+    const float scale = __fmul_rn(__frcp_rn(v), 6.283185307179586f);
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+        const float *u = m + 3 * ((r + 1) % 3), *w = m + 3 * ((r + 2) % 3);
+        const float cx = __fsub_rn(__fmul_rn(u[1], w[2]), __fmul_rn(u[2], w[1]));
+        const float cy = __fsub_rn(__fmul_rn(u[2], w[0]), __fmul_rn(u[0], w[2]));
+        const float cz = __fsub_rn(__fmul_rn(u[0], w[1]), __fmul_rn(u[1], w[0]));
+        const float x = __fmul_rn(cx, scale), y = __fmul_rn(cy, scale), z = __fmul_rn(cz, scale);
+        if (rvecs) {
+            rvecs[9 * b + 3 * r + 0] = x;
+            rvecs[9 * b + 3 * r + 1] = y;
+            rvecs[9 * b + 3 * r + 2] = z;
+        }
+        if (rvlen) rvlen[3 * b + r] = __fsqrt_rn(__fadd_rn(__fadd_rn(__fmul_rn(x, x), __fmul_rn(y, y)), __fmul_rn(z, z)));
+    }
+}
+
+__global__ void atom_kernel(const int64_t *__restrict__ atom_start, const int64_t *__restrict__ edge_start,
+                            long long B, long long N, int64_t *__restrict__ batch, int64_t *__restrict__ row_start,
+                            long long E)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i > N) return;
+    if (i == N) {
+        if (row_start) row_start[N] = E;
+        return;
+    }
+    const long long c = find_segment(atom_start, B, i);
+    if (batch) batch[i] = c;
+    if (row_start) row_start[i] = edge_start[c] + (i - atom_start[c]) * (atom_start[c + 1] - atom_start[c]);
+}
+
+__global__ void edge_kernel(const float *__restrict__ pos, const int64_t *__restrict__ atom_start,
+                            const int64_t *__restrict__ edge_start, long long B, long long E,
+                            int64_t *__restrict__ edges, float *__restrict__ pos_ij)
+{
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= E) return;
+    const long long c = find_segment(edge_start, B, e);
+    const long long n = atom_start[c + 1] - atom_start[c];
+    const long long local = e - edge_start[c];
+    const long long i = atom_start[c] + local / n, j = atom_start[c] + local % n;
+    if (edges) {
+        edges[e] = i;
+        edges[E + e] = j;
+    }
+    if (pos_ij) {
+        pos_ij[3 * e + 0] = __fsub_rn(pos[3 * j + 0], pos[3 * i + 0]);
+        pos_ij[3 * e + 1] = __fsub_rn(pos[3 * j + 1], pos[3 * i + 1]);
+        pos_ij[3 * e + 2] = __fsub_rn(pos[3 * j + 2], pos[3 * i + 2]);
+    }
+}
+
+}  // namespace
+}  // namespace cf
+
+extern "C" int cf_crystal_offsets(const int64_t *sizes, int64_t B, int64_t *atom_start, int64_t *edge_start,
+                                  void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(B >= 0 && B <= (1 << 20), CF_ERR_RANGE, "cf_crystal_offsets: B=%lld outside [0, 2^20]", (long long)B);
+    CF_REQUIRE(atom_start && edge_start && (sizes || B == 0), CF_ERR_INVALID, "cf_crystal_offsets: null pointer");
+    crystal_offsets_kernel<<<1, SCAN_THREADS, 0, as_stream(stream)>>>(sizes, B, atom_start, edge_start);
+    return launch_status("cf_crystal_offsets");
+}
+
+extern "C" int cf_batch_prepare(const float *pos, const float *trans, const int64_t *sizes, const int64_t *atom_start,
+                                const int64_t *edge_start, int64_t B, int64_t N, int64_t E, int64_t *batch,
+                                int64_t *edges, int64_t *row_start, float *pos_ij, float *rvecs, float *vcell,
+                                float *rvlen, void *stream)
+{
+    using namespace cf;
+    (void)sizes;
+    CF_REQUIRE(B >= 0 && N >= 0 && E >= 0, CF_ERR_INVALID, "cf_batch_prepare: negative size");
+    CF_REQUIRE(atom_start && edge_start, CF_ERR_INVALID, "cf_batch_prepare: offsets are null");
+    CF_REQUIRE(!pos_ij || pos, CF_ERR_INVALID, "cf_batch_prepare: pos_ij requested without pos");
+    CF_REQUIRE(!(rvecs || vcell || rvlen) || trans, CF_ERR_INVALID, "cf_batch_prepare: cell outputs requested without trans");
+    cudaStream_t s = as_stream(stream);
+    if (B > 0 && (rvecs || vcell || rvlen)) cell_kernel<<<(unsigned)((B + 127) / 128), 128, 0, s>>>(trans, B, rvecs, vcell, rvlen);
+    if (B > 0 && (batch || row_start)) atom_kernel<<<(unsigned)((N + 1 + 255) / 256), 256, 0, s>>>(atom_start, edge_start, B, N, batch, row_start, E);
+    if (B > 0 && E > 0 && (edges || pos_ij)) edge_kernel<<<(unsigned)((E + 255) / 256), 256, 0, s>>>(pos, atom_start, edge_start, B, E, edges, pos_ij);
+    return launch_status("cf_batch_prepare");
+}

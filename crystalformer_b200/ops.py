@@ -1,0 +1,207 @@
+"""Thin torch-tensor front end of the C ABI: checks tensors, allocates outputs with torch and passes raw pointers.
+
+Every function launches on ``torch.cuda.current_stream`` of the tensors' device and returns without synchronising.
+These are the building blocks of the drop-in autograd functions in ``crystalformer_b200.cuda_funcs`` and of the
+fused attention module; they have no CPU path.
+"""
+from __future__ import annotations
+
+from ctypes import c_double, c_int, c_int64, c_void_p
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+HEADS = 8
+HEAD_DIM = 16
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+
+
+def _stream(device) -> c_void_p:
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _want(t: Optional[torch.Tensor], dtype, name: str, device=None) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: crystalformer_b200 has no CPU path")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if device is not None and t.device != device:
+        raise RuntimeError(f"{name} is on {t.device}, expected {device}")
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def set_weight_floor_log2(value: float) -> None:
+    _lib.load().cf_set_weight_floor_log2(c_double(value))
+
+
+def get_weight_floor_log2() -> float:
+    return float(_lib.load().cf_get_weight_floor_log2())
+
+
+def crystal_offsets(sizes: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(atom_start, edge_start), each (B+1) int64: exclusive prefix sums of sizes and sizes^2."""
+    sizes = _want(sizes, torch.int64, "sizes")
+    B = sizes.shape[0]
+    atom_start = torch.empty(B + 1, dtype=torch.int64, device=sizes.device)
+    edge_start = torch.empty(B + 1, dtype=torch.int64, device=sizes.device)
+    with torch.cuda.device(sizes.device):
+        _lib.call("cf_crystal_offsets", _ptr(sizes), c_int64(B), _ptr(atom_start), _ptr(edge_start), _stream(sizes.device))
+    return atom_start, edge_start
+
+
+def batch_prepare(pos, trans, sizes, atom_start, edge_start, N: int, E: int, want_edges=True, want_pos_ij=True):
+    """Device-side replacement of get_edge_index + compute_lattice_distances_for_cuda.  N and E are host integers
+    (sum of sizes and of sizes^2) known to the caller.  Returns a dict of tensors."""
+    dev = pos.device
+    pos = _want(pos, torch.float32, "pos")
+    trans = _want(trans, torch.float32, "trans", dev)
+    sizes = _want(sizes, torch.int64, "sizes", dev)
+    B = sizes.shape[0]
+    o = dict(
+        batch=torch.empty(N, dtype=torch.int64, device=dev),
+        row_start=torch.empty(N + 1, dtype=torch.int64, device=dev),
+        edges=torch.empty((2, E), dtype=torch.int64, device=dev) if want_edges else None,
+        pos_ij=torch.empty((E, 3), dtype=torch.float32, device=dev) if want_pos_ij else None,
+        rvecs=torch.empty((B, 3, 3), dtype=torch.float32, device=dev),
+        vcell=torch.empty((B,), dtype=torch.float32, device=dev),
+        rvlen=torch.empty((B, 3), dtype=torch.float32, device=dev),
+    )
+    with torch.cuda.device(dev):
+        _lib.call("cf_batch_prepare", _ptr(pos), _ptr(trans), _ptr(sizes), _ptr(atom_start), _ptr(edge_start),
+                  c_int64(B), c_int64(N), c_int64(E), _ptr(o["batch"]), _ptr(o["edges"]), _ptr(o["row_start"]),
+                  _ptr(o["pos_ij"]), _ptr(o["rvecs"]), _ptr(o["vcell"]), _ptr(o["rvlen"]), _stream(dev))
+    return o
+
+
+def lattice_box(a, batch, edges, rvlen, cutoff_radius, lattice_range, minimum_range, a_per_edge=False):
+    """(E,H,3) int32 half-widths of the translation box of every (edge, head)."""
+    dev = a.device
+    a = _want(a, torch.float32, "a")
+    batch, edges = _want(batch, torch.int64, "batch", dev), _want(edges, torch.int64, "edges", dev)
+    rvlen = _want(rvlen, torch.float32, "rvlen", dev)
+    E, H, N = edges.shape[1], a.shape[1], batch.shape[0]
+    box = torch.empty((E, H, 3), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_lattice_box", _ptr(a), c_int(int(a_per_edge)), _ptr(batch), _ptr(edges), c_int64(N), c_int64(H),
+                  c_int64(E), _ptr(rvlen), c_double(cutoff_radius), c_int(lattice_range), c_int(minimum_range),
+                  _ptr(box), _stream(dev))
+    return box
+
+
+def lattice_sum_fwd(a, pos_ij, tvecs, batch, edges, K, dist_max, wscale, W=None, rvlen=None, cutoff_radius=0.0,
+                    lattice_range=2, minimum_range=2, a_per_edge=False, z=None, v=None):
+    """phi (E,H) and psi (E,H,K) or W psi (E,H,Dv).  W: (H,Dv,K) or (W_num,H,Dv,K).  z / v may be preallocated."""
+    dev = a.device
+    a = _want(a, torch.float32, "a")
+    pos_ij = _want(pos_ij, torch.float32, "pos_ij", dev)
+    tvecs = _want(tvecs, torch.float32, "tvecs", dev)
+    batch, edges = _want(batch, torch.int64, "batch", dev), _want(edges, torch.int64, "edges", dev)
+    W, rvlen = _want(W, torch.float32, "W", dev), _want(rvlen, torch.float32, "rvlen", dev)
+    E, H, N = edges.shape[1], a.shape[1], batch.shape[0]
+    if W is not None:
+        W_num = 1 if W.dim() == 3 else W.shape[0]
+        Dv = W.shape[-2]
+    else:
+        W_num, Dv = 0, 0
+    if z is None:
+        z = torch.empty((E, H), dtype=torch.float32, device=dev)
+    if K > 0 and v is None:
+        v = torch.empty((E, H, Dv if W is not None else K), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_lattice_sum_fwd", _ptr(a), c_int(int(a_per_edge)), _ptr(pos_ij), _ptr(tvecs), _ptr(batch),
+                  _ptr(edges), c_int64(N), c_int64(H), c_int64(E), c_int64(K), c_double(dist_max), c_double(wscale),
+                  _ptr(W), c_int64(W_num), c_int64(Dv), _ptr(rvlen), c_double(cutoff_radius or 0.0),
+                  c_int(lattice_range), c_int(minimum_range), _ptr(z), _ptr(v if K > 0 else None), _stream(dev))
+    return z, (v if K > 0 else None)
+
+
+def lattice_sum_bwd(a, pos_ij, tvecs, batch, edges, row_start, z, gz, gv, K, dist_max, wscale, W=None, rvlen=None,
+                    cutoff_radius=0.0, lattice_range=2, minimum_range=2):
+    """ga (N,H) and gW (W_num,H,Dv,K) (None without W)."""
+    dev = a.device
+    a = _want(a, torch.float32, "a")
+    pos_ij = _want(pos_ij, torch.float32, "pos_ij", dev)
+    tvecs = _want(tvecs, torch.float32, "tvecs", dev)
+    batch, edges = _want(batch, torch.int64, "batch", dev), _want(edges, torch.int64, "edges", dev)
+    row_start = _want(row_start, torch.int64, "row_start", dev)
+    z, gz, gv = (_want(t, torch.float32, n, dev) for t, n in ((z, "z"), (gz, "gz"), (gv, "gv")))
+    W, rvlen = _want(W, torch.float32, "W", dev), _want(rvlen, torch.float32, "rvlen", dev)
+    E, H, N = edges.shape[1], a.shape[1], batch.shape[0]
+    ga = torch.empty((N, H), dtype=torch.float32, device=dev)
+    gW = scratch = None
+    W_num = Dv = 0
+    if W is not None and K > 0:
+        W_num = 1 if W.dim() == 3 else W.shape[0]
+        Dv = W.shape[-2]
+        gW = torch.empty((W_num, H, Dv, K), dtype=torch.float32, device=dev)
+        nbytes = int(_lib.load().cf_lattice_sum_bwd_scratch_bytes(N, H, Dv, K)) if W_num == 1 else 0
+        if nbytes:
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_lattice_sum_bwd", _ptr(a), _ptr(pos_ij), _ptr(tvecs), _ptr(batch), _ptr(edges), _ptr(row_start),
+                  _ptr(z), _ptr(gz), _ptr(gv if K > 0 else None), c_int64(N), c_int64(H), c_int64(E), c_int64(K),
+                  c_double(dist_max), c_double(wscale), _ptr(W), c_int64(W_num), c_int64(Dv), _ptr(rvlen),
+                  c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(ga), _ptr(gW),
+                  _ptr(scratch), _stream(dev))
+    return ga, gW
+
+
+def fused_attn_fwd(q, k, v, aij, bij, edges, row_start):
+    """prob (E,H), out (N,H,D); q already divided by sqrt(D)."""
+    dev = q.device
+    q, k, v = (_want(t, torch.float32, n, dev) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+    aij, bij = _want(aij, torch.float32, "aij", dev), _want(bij, torch.float32, "bij", dev)
+    edges, row_start = _want(edges, torch.int64, "edges", dev), _want(row_start, torch.int64, "row_start", dev)
+    N, H, D = q.shape
+    E = edges.shape[1]
+    prob = torch.empty((E, H), dtype=torch.float32, device=dev)
+    out = torch.empty((N, H, D), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_fused_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(aij), _ptr(bij), _ptr(edges), _ptr(row_start),
+                  c_int64(N), c_int64(H), c_int64(D), c_int64(E), _ptr(prob), _ptr(out), _stream(dev))
+    return prob, out
+
+
+def fused_attn_bwd(q, k, v, bij, edges, row_start, prob, out, gout):
+    """(gq, gk, gv, gaij, gbij); gq is with respect to the pre-scaled q."""
+    dev = q.device
+    q, k, v, prob, out, gout = (_want(t, torch.float32, n, dev) for t, n in
+                                ((q, "q"), (k, "k"), (v, "v"), (prob, "prob"), (out, "out"), (gout, "gout")))
+    bij = _want(bij, torch.float32, "bij", dev)
+    edges, row_start = _want(edges, torch.int64, "edges", dev), _want(row_start, torch.int64, "row_start", dev)
+    N, H, D = q.shape
+    E = edges.shape[1]
+    gq, gk, gv = (torch.empty_like(q) for _ in range(3))
+    gaij = torch.empty((E, H), dtype=torch.float32, device=dev)
+    gbij = torch.empty((E, H, D), dtype=torch.float32, device=dev) if bij is not None else None
+    with torch.cuda.device(dev):
+        _lib.call("cf_fused_attn_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(bij), _ptr(edges), _ptr(row_start), c_int64(N),
+                  c_int64(H), c_int64(D), c_int64(E), _ptr(prob), _ptr(out), _ptr(gout), _ptr(gq), _ptr(gk), _ptr(gv),
+                  _ptr(gaij), _ptr(gbij), _stream(dev))
+    return gq, gk, gv, gaij, gbij
+
+
+def segment_mean(x, start):
+    """Per-crystal mean: x (N,D) float32, start (B+1) int64 atom offsets -> (B,D)."""
+    dev = x.device
+    x = _want(x, torch.float32, "x")
+    start = _want(start, torch.int64, "start", dev)
+    B = start.shape[0] - 1
+    D = x.numel() // max(x.shape[0], 1)
+    out = torch.empty((B,) + tuple(x.shape[1:]), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_segment_mean_fwd", _ptr(x), _ptr(start), c_int64(B), c_int64(D), _ptr(out), _stream(dev))
+    return out
+
+
+def pipe_probe(kind: int, blocks: int, threads: int, iters: int, sink: torch.Tensor) -> None:
+    with torch.cuda.device(sink.device):
+        _lib.call("cf_pipe_probe", c_int(kind), c_int(blocks), c_int(threads), c_int64(iters), _ptr(sink),
+                  _stream(sink.device))

@@ -1,0 +1,184 @@
+/*
+ * crystalformer_b200 - C ABI of the sm_100a kernels for Crystalformer's infinitely connected attention.
+ *
+ * This library replaces the reference project's run-time compiled CuPy kernels (models/kernels/ *.cu, loaded by
+ * models/cuda_funcs/kernel_manager.py) and the launch code of its autograd wrappers (models/cuda_funcs/ *.py).
+ * Every entry point
+ *   - takes raw DEVICE pointers to contiguous arrays (float32 data, int64 indices, as the reference kernels do),
+ *     plain sizes and scalars, and the CUDA stream to launch on (a cudaStream_t passed as void*; NULL = default),
+ *   - launches asynchronously on that stream of the CURRENT device; it never synchronises, never allocates and
+ *     never frees device memory (outputs and scratch are the caller's, as with the reference wrappers, which
+ *     allocate with torch.empty and hand pointers to the kernels),
+ *   - returns CF_OK or a negative CF_ERR_* code and never throws; cf_last_error() gives the message of the last
+ *     failure on the calling thread.
+ * The library keeps no per-call state, so it may be called concurrently from one host thread per GPU (the
+ * reference's multi-GPU path does that: models/latticeformer.py:274).
+ *
+ * Compile-time constants of the reference (HEAD_NUM, K_HEAD_DIM, V_HEAD_DIM, VPE_DIM, LATTICE_RANGE, MINIMUM_RANGE;
+ * kernel_manager.py:110-126) are run-time arguments here.  Supported shapes: H = 8 heads, head dim D = 16,
+ * K = value_pe_dist_real in {0, 64}; anything else returns CF_ERR_UNSUPPORTED.
+ *
+ * Shapes: N atoms, E edges (all ordered pairs inside each crystal, row-major per crystal:
+ * models/indexed_latticeformer_encoder.py:15-32), B crystals, H heads, D head dim, K radial-basis bins.
+ */
+#ifndef CRYSTALFORMER_B200_H
+#define CRYSTALFORMER_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CF_OK 0
+#define CF_ERR_INVALID (-1)     /* null pointer, negative size, inconsistent arguments */
+#define CF_ERR_UNSUPPORTED (-2) /* shape outside the compiled set (H, D, K) */
+#define CF_ERR_CUDA (-3)        /* a CUDA runtime call failed; message in cf_last_error() */
+#define CF_ERR_RANGE (-4)       /* a size exceeds a documented limit */
+
+/* Largest half-width of the translation box in any direction.  The reference loops over whatever the cut-off rule
+ * yields; here a box wider than this is clamped so that a degenerate width (a -> 0) cannot stall the GPU. */
+#define CF_MAX_RANGE 32
+
+/* Library version as major*10000 + minor*100 + patch. */
+int cf_version(void);
+
+/* Message of the last error raised on the calling thread ("" if none). The pointer stays valid until the next
+ * failing call on the same thread. */
+const char *cf_last_error(void);
+
+/* Terms of the lattice sum whose Gaussian weight exp(a (d^2 - d^2_min)) is below 2^log2_floor for every head are
+ * left out of the radial-basis accumulation (never out of the log-sum-exp itself).  Default -40 (a relative error
+ * below 1e-10); pass -1000 to accumulate every term.  Process-wide tuning knob, read at launch time. */
+void cf_set_weight_floor_log2(double log2_floor);
+double cf_get_weight_floor_log2(void);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Batch preparation.  Replaces get_edge_index and compute_lattice_distances_for_cuda
+ * (models/indexed_latticeformer_encoder.py:15-32, 183-253) and the CSR construction repeated in every wrapper
+ * (models/cuda_funcs/fused_dpa.py:24-26), without the host loop over crystals and without device->host syncs.
+ *
+ * cf_crystal_offsets: atom_start (B+1), edge_start (B+1) int64 exclusive prefix sums of sizes and sizes^2.
+ *                     One block; B <= 2^20.
+ * cf_batch_prepare  : from pos (N,3), trans (B,3,3), sizes (B) and the two offset arrays writes any of (NULL = skip)
+ *     batch     (N)   int64  crystal of each atom
+ *     edges     (2,E) int64  all-pairs edge list, bit-identical to get_edge_index
+ *     row_start (N+1) int64  first edge of each source atom (CSR of edges[0])
+ *     pos_ij    (E,3) f32    pos[j] - pos[i]
+ *     rvecs (B,3,3), vcell (B), rvlen (B,3) f32: reciprocal rows 2 pi (t_b x t_c)/V, cell volume, |rvecs rows|
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_crystal_offsets(const int64_t *sizes, int64_t B, int64_t *atom_start, int64_t *edge_start, void *stream);
+int cf_batch_prepare(const float *pos, const float *trans, const int64_t *sizes, const int64_t *atom_start,
+                     const int64_t *edge_start, int64_t B, int64_t N, int64_t E, int64_t *batch, int64_t *edges,
+                     int64_t *row_start, float *pos_ij, float *rvecs, float *vcell, float *rvlen, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Translation box of every (edge, head): box (E,H,3) int32 = (R1,R2,R3) of the reference's cut-off rule
+ * (models/kernels/real_enc_fwd.cu:63-85), reproduced bit for bit:
+ *   cutoff_radius == 0 or rvlen == NULL : R = lattice_range            (the fixed box of the PyTorch path)
+ *   cutoff_radius <  0 : radius = sqrt(-0.5/a) * |cutoff_radius|       (per atom and head)
+ *   cutoff_radius >  0 : radius = cutoff_radius
+ *   R_d = ceil((radius + 0.01) * rvlen_d / 2pi), raised to minimum_range, clamped to CF_MAX_RANGE.
+ * a is (N,H), or (E,H) when a_per_edge != 0.  Diagnostic / test entry; the kernels below apply the same rule.
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_lattice_box(const float *a, int a_per_edge, const int64_t *batch, const int64_t *edges, int64_t N, int64_t H,
+                   int64_t E, const float *rvlen, double cutoff_radius, int lattice_range, int minimum_range,
+                   int32_t *box, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Real-space lattice sum, forward.  Replaces real_enc_fwd / real_enc_proj_fwd (and their _v2 variants)
+ * (models/kernels/real_enc_fwd.cu:4-144, real_enc_proj_fwd.cu:4-169) as launched by
+ * RealPeriodicEncodingFuncCUDA.forward / RealPeriodicEncodingWithProjFuncCUDA.forward
+ * (models/cuda_funcs/real_space_enc.py:19-138, real_space_enc_proj.py:20-97).
+ *   z (E,H)   = log sum_n exp(a |r_ij + n.T|^2)
+ *   v         = psi (E,H,K) when W == NULL, else W psi (E,H,Dv) with W (W_num,H,Dv,K), W_num in {1, N, E}
+ *   psi[k]    = softmax_n-weighted Gaussian radial basis, centres (k+1) dist_max/K, width wscale dist_max/K
+ * K == 0 writes z only (v may be NULL).  a_per_edge != 0 reads a as (E,H) instead of (N,H) (kernel benchmark).
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_lattice_sum_fwd(const float *a, int a_per_edge, const float *pos_ij, const float *tvecs, const int64_t *batch,
+                       const int64_t *edges, int64_t N, int64_t H, int64_t E, int64_t K, double dist_max,
+                       double wscale, const float *W, int64_t W_num, int64_t Dv, const float *rvlen,
+                       double cutoff_radius, int lattice_range, int minimum_range, float *z, float *v, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Real-space lattice sum, backward.  Replaces real_enc_bwd / real_enc_proj_bwd
+ * (models/kernels/real_enc_bwd.cu:4-157, real_enc_proj_bwd.cu:4-221) as launched by the wrappers' backward
+ * (models/cuda_funcs/real_space_enc.py:141-247, real_space_enc_proj.py:100-178).  phi and psi are recomputed.
+ *   in : z (E,H) from the forward, gz (E,H), gv = d/d psi (E,H,K) when W == NULL else d/d (W psi) (E,H,Dv)
+ *   out: ga (N,H); gW (W_num,H,Dv,K) when W != NULL and gW != NULL.  For W_num == 1 the sum over all edges is
+ *        written (the reference writes one block per atom and lets autograd add them up).
+ * row_start (N+1) is the CSR of edges[0].  gW_scratch: W_num == 1 needs cf_lattice_sum_bwd_scratch_bytes() bytes of
+ * device scratch (partial sums per thread block, reduced in a fixed order so that results are run-to-run identical).
+ * ---------------------------------------------------------------------------------------------------------- */
+int64_t cf_lattice_sum_bwd_scratch_bytes(int64_t N, int64_t H, int64_t Dv, int64_t K);
+int cf_lattice_sum_bwd(const float *a, const float *pos_ij, const float *tvecs, const int64_t *batch,
+                       const int64_t *edges, const int64_t *row_start, const float *z, const float *gz,
+                       const float *gv, int64_t N, int64_t H, int64_t E, int64_t K, double dist_max, double wscale,
+                       const float *W, int64_t W_num, int64_t Dv, const float *rvlen, double cutoff_radius,
+                       int lattice_range, int minimum_range, float *ga, float *gW, void *gW_scratch, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Edge-indexed softmax attention with given position terms.  Replaces fused_dpa_fwd[_v3], fused_dpa_bwd[_v3],
+ * fused_dpa_bwd_q[_v3] and irregular_transpose (models/kernels/fused_dpa_fwd.cu, fused_dpa_bwd.cu,
+ * fused_dpa_bwd_q.cu, irregular_transpose.cu) as launched by FusedDotProductAttentionCUDA
+ * (models/cuda_funcs/fused_dpa.py:17-208).  q is already divided by sqrt(D) by the caller.
+ *   fwd: prob (E,H) = softmax_j(q_i.k_j + aij), out (N,H,D) = sum_j prob (v_j + bij); aij, bij may be NULL
+ *   bwd: gq, gk, gv (N,H,D), gaij (E,H), gbij (E,H,D) (NULL when bij is NULL); no transposed copies are made.
+ * No limit on atoms per crystal (the reference stops at 320, kernel_manager.py:55).
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_fused_attn_fwd(const float *q, const float *k, const float *v, const float *aij, const float *bij,
+                      const int64_t *edges, const int64_t *row_start, int64_t N, int64_t H, int64_t D, int64_t E,
+                      float *prob, float *out, void *stream);
+int cf_fused_attn_bwd(const float *q, const float *k, const float *v, const float *bij, const int64_t *edges,
+                      const int64_t *row_start, int64_t N, int64_t H, int64_t D, int64_t E, const float *prob,
+                      const float *out, const float *gout, float *gq, float *gk, float *gv, float *gaij,
+                      float *gbij, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Per-crystal mean of atom features.  Replaces irregular_mean_fwd (models/kernels/irregular_mean_fwd.cu) as
+ * launched by IrregularMeanCUDA.forward (models/cuda_funcs/irregular_mean.py:21-58); same fixed summation tree.
+ * x (N,D) -> out (B,D); start (B+1) int64 atom offsets.  Crystals of up to 1024 atoms.
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_segment_mean_fwd(const float *x, const int64_t *start, int64_t B, int64_t D, float *out, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Fully fused infinitely connected attention (what the reference computes with real_enc_proj_fwd followed by
+ * fused_dpa_fwd, models/indexed_lattice_multi_head_attention_cuda.py:393-421,181-185), without materialising any
+ * per-edge tensor except the logits:
+ *   out_i = sum_j softmax_j(q_i.k_j + phi_ij) (v_j + W psi_ij)
+ * computed as  sum_j p_ij v_j + W_h (sum_j p_ij psi_ij)  (W is shared by all edges, W (H,D,K)).
+ *   in : q (pre-scaled), k, v (N,H,D); a (N,H); pos (N,3); tvecs (B,3,3); rvlen (B,3) or NULL; batch (N);
+ *        atom_start (B+1); row_start (N+1); E total edges
+ *   out: out (N,H,D)
+ *        logit (E,H)  q.k + phi, kept for the backward
+ *        lse (N,H)    log sum_j exp(logit)
+ *        psi_row (N,H,K) = sum_j p_ij psi_ij (NULL to skip; needed for the gradient of W)
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                         const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *atom_start,
+                         const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D, int64_t E, int64_t K,
+                         double dist_max, double wscale, const float *W, double cutoff_radius, int lattice_range,
+                         int minimum_range, float *out, float *logit, float *lse, float *psi_row, void *stream);
+
+/* Backward of cf_infinite_attn_fwd; phi and psi are recomputed from the geometry.
+ *   in : everything the forward read, plus logit, lse, out and gout (N,H,D)
+ *   out: gq (w.r.t. the pre-scaled q), gk, gv (N,H,D); ga (N,H); glogit (E,H) scratch/diagnostic
+ * The gradient of W is sum_i gout_i (x) psi_row_i, a plain GEMM the caller does from psi_row. */
+int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                         const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *atom_start,
+                         const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D, int64_t E, int64_t K,
+                         double dist_max, double wscale, const float *W, double cutoff_radius, int lattice_range,
+                         int minimum_range, const float *logit, const float *lse, const float *out,
+                         const float *gout, float *gq, float *gk, float *gv, float *ga, float *glogit, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Pipe-throughput probes for the roofline denominators: `iters` dependent-free FFMA (kind 0) or MUFU.EX2 (kind 1)
+ * instructions per thread over a full grid; sink (>= 1 float) receives a value so the loop is not elided.
+ * Work per launch = blocks * threads * iters * 8 instructions.
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_pipe_probe(int kind, int blocks, int threads, int64_t iters, float *sink, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CRYSTALFORMER_B200_H */
