@@ -30,10 +30,10 @@ int launch_status(const char *what)
     return CF_OK;
 }
 
-float weight_floor()
+float weight_floor_log2()
 {
     const double f = g_floor_log2.load();
-    return f <= -150.0 ? 0.0f : (float)std::exp2(f);
+    return f < -1e30 ? -1e30f : (float)f;
 }
 
 int sm_count()

@@ -16,7 +16,7 @@ constexpr float LN2 = 0.6931471805599453f;
 // ---- host-side error plumbing (api.cu) --------------------------------------------------------------------
 int fail(int code, const char *fmt, ...);
 int launch_status(const char *what);
-float weight_floor();  // 2^floor as a float, 0 when every term is to be accumulated
+float weight_floor_log2();  // log2 of the weight below which a term is left out of the basis accumulation
 
 #define CF_REQUIRE(cond, code, ...) \
     do {                            \

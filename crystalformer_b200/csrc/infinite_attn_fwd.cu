@@ -1,0 +1,272 @@
+// Fused infinitely connected attention, forward:
+//     out_i = sum_j softmax_j(q_i.k_j + phi_ij) (v_j + W psi_ij)
+// with phi and psi computed from the geometry on the fly.  No per-edge tensor other than the logits exists.
+//
+// Because W is shared by every edge, sum_j p_ij W psi_ij = W (sum_j p_ij psi_ij): the 8 x 64 radial-basis histogram
+// of a row is accumulated over ALL its (key, translation) terms with the final joint weight
+//     p_ij p(n | ij) = exp(q_i.k_j - lse_i + a_i d2_ijn)
+// and projected once per atom instead of once per edge.
+//
+// Launch sequence (one stream, no host synchronisation):
+//   lattice_phi_kernel        thread per edge : phi_ij for all heads (lattice_core.cuh), written into `logit`
+//   infinite_attn_rows_kernel CTA per atom i  : logits q.k + phi, their log-sum-exp, p_ij; then the row's
+//                             n_i x (2R1+1)(2R2+1)(2R3+1) terms are split over the four warps, each running the
+//                             lane<->term / lane<->bins turn-around of BinAccumulator; the four partial histograms are
+//                             added in a fixed order (deterministic), projected with W and added to sum_j p_ij v_j.
+#include "lattice_core.cuh"
+
+namespace cf {
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int WARPS = THREADS / 32;
+constexpr int KBINS = 64;
+
+struct RowArgs {
+    const float *q, *k, *v, *a, *pos, *pos_ij, *tvecs, *rvlen, *W;
+    const int64_t *batch, *edges, *row_start;
+    long long E;
+    float *out, *logit, *lse, *psi_row;
+    long long N;
+    int max_atoms;
+    BoxRule rule;
+    BasisParams basis;
+};
+
+__host__ __device__ inline size_t row_smem_floats(int max_atoms, bool with_basis)
+{
+    // rel (4) + c (8) + p (8) per atom, then per-warp staging and partial histograms, then 8 lse values
+    return (size_t)max_atoms * 20 + (with_basis ? WARPS * (STAGE_FLOATS + HEADS * KBINS) : 0) + 16;
+}
+
+template <int K>
+__global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowArgs p)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float4 *rel = reinterpret_cast<float4 *>(smem);                    // [max_atoms]
+    float *cj = smem + (size_t)p.max_atoms * 4;                        // [max_atoms][8]
+    float *pj = cj + (size_t)p.max_atoms * 8;                          // [max_atoms][8]
+    float *stage = pj + (size_t)p.max_atoms * 8;                       // [WARPS][STAGE_FLOATS]
+    float *part = stage + (K > 0 ? WARPS * STAGE_FLOATS : 0);          // [WARPS][8][64]
+    float *lse_s = part + (K > 0 ? WARPS * HEADS * KBINS : 0);         // [8]
+
+    BinAccumulator<KBINS> bins;
+    if (K > 0) bins.init(stage + warp * STAGE_FLOATS, lane, p.basis);
+
+    for (long long i = blockIdx.x; i < p.N; i += gridDim.x) {
+        const long long c = p.batch[i];
+        const long long e0 = p.row_start[i];
+        const int n = (int)(p.row_start[i + 1] - e0);  // keys of the row = atoms of the crystal
+        const long long a0 = n > 0 ? p.edges[p.E + e0] : 0;  // first atom of the crystal
+        if (n > p.max_atoms) {  // the caller understated max_atoms: poison the row instead of overrunning shared memory
+            p.out[i * HEADS * HEAD_DIM + tid] = __int_as_float(0x7fc00000);
+            continue;
+        }
+
+        // ---- relative positions of the keys
+        if (p.pos_ij) {
+            for (int j = tid; j < n; j += THREADS) {
+                const float *pp = p.pos_ij + 3 * (e0 + j);
+                rel[j] = make_float4(pp[0], pp[1], pp[2], 0.f);
+            }
+        } else {
+            const float pix = p.pos[3 * i], piy = p.pos[3 * i + 1], piz = p.pos[3 * i + 2];
+            for (int j = tid; j < n; j += THREADS) {
+                const float *pp = p.pos + 3 * (a0 + j);
+                rel[j] = make_float4(__fsub_rn(pp[0], pix), __fsub_rn(pp[1], piy), __fsub_rn(pp[2], piz), 0.f);
+            }
+        }
+        // ---- logits and soft-max statistics: warp w owns heads 2w and 2w+1
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int h = 2 * warp + hh;
+            float4 qv[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) qv[t] = __ldg(reinterpret_cast<const float4 *>(p.q + (i * HEADS + h) * HEAD_DIM) + t);
+            float mx = -INFINITY;
+            for (int j = lane; j < n; j += 32) {
+                const float4 *kp = reinterpret_cast<const float4 *>(p.k + ((a0 + j) * HEADS + h) * HEAD_DIM);
+                float s = 0.f;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float4 kv = __ldg(kp + t);
+                    s = fmaf(qv[t].x, kv.x, s); s = fmaf(qv[t].y, kv.y, s); s = fmaf(qv[t].z, kv.z, s); s = fmaf(qv[t].w, kv.w, s);
+                }
+                const float lg = s + p.logit[(e0 + j) * HEADS + h];  // phi was left here by the phi kernel
+                p.logit[(e0 + j) * HEADS + h] = lg;
+                cj[j * 8 + h] = s;
+                pj[j * 8 + h] = lg;
+                mx = fmaxf(mx, lg);
+            }
+            mx = warp_max(mx);
+            float den = 0.f;
+            for (int j = lane; j < n; j += 32) den += ex2((pj[j * 8 + h] - mx) * LOG2E);
+            den = warp_sum(den);
+            const float lse = mx + logf(den);
+            if (lane == 0) {
+                lse_s[h] = lse;
+                p.lse[i * HEADS + h] = lse;
+            }
+            for (int j = lane; j < n; j += 32) {
+                cj[j * 8 + h] = (cj[j * 8 + h] - lse) * LOG2E;
+                pj[j * 8 + h] = ex2((pj[j * 8 + h] - lse) * LOG2E);
+            }
+        }
+        __syncthreads();
+
+        if (K > 0) {
+            // ---- boxes of the row's heads (they depend on the atom and the head, not on the key)
+            const float a_own = p.a[i * HEADS + (lane & 7)];
+            const int pk_own = packed_box(p.rule, a_own, p.rvlen ? p.rvlen + 3 * c : nullptr);
+            int uni = pk_own;
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) uni = box_union(uni, __shfl_xor_sync(FULL, uni, o));
+            const bool masked = !__all_sync(FULL, pk_own == uni);
+            float a2[8];
+            int pk[8];
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                a2[h] = __shfl_sync(FULL, a_own, h) * LOG2E;
+                pk[h] = __shfl_sync(FULL, pk_own, h);
+            }
+            const int R1 = box_r1(uni), R2 = box_r2(uni), R3 = box_r3(uni);
+            const unsigned per_key = (unsigned)((2 * R1 + 1) * (2 * R2 + 1) * (2 * R3 + 1));
+            const unsigned total = per_key * (unsigned)n;
+            const unsigned chunk = ((total + WARPS * 32 - 1) / (WARPS * 32)) * 32;  // multiple of 32 per warp
+            const unsigned begin = min(warp * chunk, total), end = min(begin + chunk, total);
+            Cell cell;
+            cell.load(p.tvecs + 9 * c);
+            const float F1 = (float)R1, F2 = (float)R2, F3 = (float)R3;
+            TermWalker walk;
+            walk.init(R1, R2, R3, begin + lane);
+            bins.clear();
+            for (unsigned base = begin; base < end; base += 32) {
+                const bool valid = base + lane < end;
+                const int j = valid ? walk.row : 0;
+                const float4 r = rel[j];
+                const float4 ca = *reinterpret_cast<const float4 *>(cj + j * 8);
+                const float4 cb = *reinterpret_cast<const float4 *>(cj + j * 8 + 4);
+                const float off[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+                const float f1 = walk.u1 - F1, f2 = walk.u2 - F2, f3 = walk.u3 - F3;
+                const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
+                const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
+                const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
+                const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                int i1 = 0, i2 = 0, i3 = 0;
+                if (masked) {
+                    i1 = abs(__float2int_rn(f1)); i2 = abs(__float2int_rn(f2)); i3 = abs(__float2int_rn(f3));
+                }
+                float w[8];
+                float emax = -INFINITY;
+#pragma unroll
+                for (int h = 0; h < 8; ++h) {
+                    float eh = fmaf(a2[h], d2, off[h]);
+                    if (masked && !(i1 <= box_r1(pk[h]) && i2 <= box_r2(pk[h]) && i3 <= box_r3(pk[h]))) eh = -INFINITY;
+                    w[h] = ex2(eh);
+                    emax = fmaxf(emax, eh);
+                }
+                const float x = sqrtf(d2) * p.basis.bin_scale;
+                bins.push(valid && emax > p.basis.floor_log2 && d2 < p.basis.d2_cut, x, w);
+                walk.step();
+            }
+            // ---- partial histograms -> shared memory, fixed-order sum over the four warps
+            float *mine = part + warp * HEADS * KBINS;
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                mine[h * KBINS + lane] = bins.acc[h][0];
+                mine[h * KBINS + lane + 32] = bins.acc[h][1];
+            }
+            __syncthreads();
+            for (int idx = tid; idx < HEADS * KBINS; idx += THREADS) {
+                const float s = (part[idx] + part[HEADS * KBINS + idx]) + (part[2 * HEADS * KBINS + idx] + part[3 * HEADS * KBINS + idx]);
+                part[idx] = s;
+                if (p.psi_row) p.psi_row[i * HEADS * KBINS + idx] = s;
+            }
+            __syncthreads();
+        }
+
+        // ---- out[h][m] = sum_j p_ij v_j[h][m] + sum_k W[h][m][k] Psi[h][k]; thread = (h, m)
+        {
+            const int h = tid >> 4;
+            float acc = 0.f;
+            const float *vp = p.v + a0 * HEADS * HEAD_DIM + tid;
+            for (int j = 0; j < n; ++j) acc = fmaf(pj[j * 8 + h], __ldg(vp + (size_t)j * HEADS * HEAD_DIM), acc);
+            if (K > 0) {
+                const float4 *wp = reinterpret_cast<const float4 *>(p.W + (size_t)tid * KBINS);
+                const float4 *pp = reinterpret_cast<const float4 *>(part + h * KBINS);
+                float o = 0.f;
+#pragma unroll 4
+                for (int k4 = 0; k4 < KBINS / 4; ++k4) {
+                    const float4 wv = __ldg(wp + k4), ps = pp[k4];
+                    o = fmaf(wv.x, ps.x, o); o = fmaf(wv.y, ps.y, o); o = fmaf(wv.z, ps.z, o); o = fmaf(wv.w, ps.w, o);
+                }
+                acc += o;
+            }
+            p.out[i * HEADS * HEAD_DIM + tid] = acc;
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace
+}  // namespace cf
+
+extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                                    const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                                    const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
+                                    int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
+                                    const float *W, double cutoff_radius, int lattice_range, int minimum_range,
+                                    float *out, float *logit, float *lse, float *psi_row, void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_fwd: negative size");
+    CF_REQUIRE(H == HEADS && D == HEAD_DIM, CF_ERR_UNSUPPORTED, "cf_infinite_attn_fwd: H=%lld D=%lld, only H=8 D=16 is compiled",
+               (long long)H, (long long)D);
+    CF_REQUIRE(K == 0 || K == 64, CF_ERR_UNSUPPORTED, "cf_infinite_attn_fwd: K=%lld, only K in {0,64} is compiled", (long long)K);
+    CF_REQUIRE(lattice_range >= 0 && lattice_range <= CF_MAX_RANGE && minimum_range >= 0, CF_ERR_RANGE,
+               "cf_infinite_attn_fwd: lattice_range %d outside [0,%d]", lattice_range, CF_MAX_RANGE);
+    CF_REQUIRE(max_atoms >= 1 && max_atoms <= 2048, CF_ERR_RANGE, "cf_infinite_attn_fwd: max_atoms=%lld outside [1,2048]",
+               (long long)max_atoms);
+    if (N == 0) return CF_OK;
+    CF_REQUIRE(q && k && v && a && (pos || pos_ij) && tvecs && batch && edges && row_start && out && logit && lse,
+               CF_ERR_INVALID, "cf_infinite_attn_fwd: null pointer");
+    CF_REQUIRE(K == 0 || (W != nullptr && dist_max > 0 && wscale > 0), CF_ERR_INVALID,
+               "cf_infinite_attn_fwd: K > 0 needs W and positive dist_max, wscale");
+    cudaStream_t s = as_stream(stream);
+    PhiArgs phi{};
+    phi.a = a; phi.pos = pos; phi.pos_ij = pos_ij; phi.tvecs = tvecs; phi.batch = batch; phi.edges = edges; phi.rvlen = rvlen; phi.z = logit;
+    phi.E = E; phi.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
+    int rc = launch_lattice_phi(phi, s);
+    if (rc != CF_OK) return rc;
+
+    RowArgs p{};
+    p.q = q; p.k = k; p.v = v; p.a = a; p.pos = pos; p.pos_ij = pos_ij; p.tvecs = tvecs; p.rvlen = rvlen; p.W = W;
+    p.batch = batch; p.edges = edges; p.row_start = row_start; p.E = E;
+    p.out = out; p.logit = logit; p.lse = lse; p.psi_row = psi_row; p.N = N; p.max_atoms = (int)max_atoms;
+    p.rule = phi.rule;
+    p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
+    const size_t smem = sizeof(float) * row_smem_floats((int)max_atoms, K > 0);
+    auto kernel = K > 0 ? infinite_attn_rows_kernel<64> : infinite_attn_rows_kernel<0>;
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(CF_ERR_RANGE, "cf_infinite_attn_fwd: %zu bytes of shared memory for max_atoms=%lld not available",
+                        smem, (long long)max_atoms);
+        }
+    }
+    static thread_local size_t cached_smem[2] = {0, 0};
+    static thread_local int cached_occ[2] = {0, 0};
+    const int slot = K > 0 ? 1 : 0;
+    if (cached_occ[slot] == 0 || cached_smem[slot] != smem) {
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, THREADS, smem) != cudaSuccess || occ <= 0) occ = 1;
+        cached_occ[slot] = occ;
+        cached_smem[slot] = smem;
+    }
+    const int occ = cached_occ[slot];
+    const long long cap = (long long)sm_count() * occ;
+    const int blocks = (int)(N < cap ? N : cap);
+    kernel<<<blocks, THREADS, smem, s>>>(p);
+    return launch_status("cf_infinite_attn_fwd");
+}

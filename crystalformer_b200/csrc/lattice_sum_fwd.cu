@@ -1,20 +1,14 @@
 // Real-space lattice sum, forward: phi (E,H) and psi (E,H,K) or W psi (E,H,16) per edge.
 //
-// One warp owns one edge (i,j) and all eight heads.  The reference gives every (edge, head) its own thread, which
-// repeats the geometry and the 64 radial-basis exponentials eight times; here they are computed once per
-// (edge, translation) and shared by the heads.
-//
-//   pass 0  lanes <-> translations : d^2 of every translation in the box, running minimum per head
-//   pass 1  lanes <-> translations : the eight Gaussian weights w_h = 2^(a_h log2e (d^2 - d^2_min,h)), partial sums
-//           for the log-sum-exp; translations whose weights all fall below the floor, or whose distance is so far
-//           beyond the last bin that every basis value underflows, are dropped, the rest are compacted with a ballot
-//           into a small per-warp staging area in shared memory (x = scaled distance, w_0..7)
-//   pass 2  lanes <-> bins : each lane owns bins (lane, lane+32) of all eight heads = 16 accumulators in
-//           registers; per staged translation it evaluates its two basis values (2 MUFU) and does 16 FMAs
-//
-// The box of a head follows the reference rule exactly (common.cuh); heads of one edge may have different boxes,
-// in which case the union box is enumerated and each head masks the translations outside its own.
-#include "common.cuh"
+// Two kernels (building blocks in lattice_core.cuh):
+//   lattice_phi_kernel   one thread per edge, all eight heads: z = log sum_n exp(a |r + n.T|^2).  MUFU-bound.
+//   lattice_psi_kernel   one warp per edge: the radial-basis expansion psi, with the Gaussian weights already
+//                        normalised by z, so no second reduction is needed.  The reference gives every (edge, head)
+//                        its own thread and so repeats the geometry and the 64 basis exponentials eight times; here
+//                        they are evaluated once per (edge, translation) and shared by the heads.
+// The box of a head follows the reference rule exactly; heads of one edge may have different boxes, in which case
+// the union box is enumerated and each head masks the translations outside its own.
+#include "lattice_core.cuh"
 
 namespace cf {
 
@@ -24,7 +18,7 @@ constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
 constexpr int PSI_STRIDE = 68;                            // floats per head row of the per-warp psi tile (bank skew)
 constexpr int WT_HEAD_STRIDE = 64 * HEAD_DIM + 16;        // floats per head of the transposed projection (bank skew)
-constexpr int WARP_SMEM_FLOATS = 32 * 8 + 32 + 8 * PSI_STRIDE;
+constexpr int WARP_SMEM_FLOATS = STAGE_FLOATS + 8 * PSI_STRIDE;
 
 struct FwdArgs {
     const float *a;
@@ -38,20 +32,10 @@ struct FwdArgs {
     float *v;
     long long N, E, W_num;
     BoxRule rule;
-    float bin_step;   // spacing of bin centres in basis units: sqrt(log2 e) / (sqrt2 wscale)
-    float bin_scale;  // bin_step / mu0: distance -> basis units
-    float x_cut;      // beyond this scaled distance every basis value underflows
-    float w_floor;
+    BasisParams basis;
     int a_per_edge;
     int stage_w;      // 1: W (1,H,16,K) is staged transposed in shared memory
 };
-
-template <bool MASKED>
-__device__ __forceinline__ bool in_box(int packed, int n1, int n2, int n3)
-{
-    if (!MASKED) return true;
-    return abs(n1) <= (packed & 0xff) && abs(n2) <= ((packed >> 8) & 0xff) && abs(n3) <= ((packed >> 16) & 0xff);
-}
 
 // out[h][4 mq .. 4 mq + 3] = sum_k W[h][m][k] psi[h][k] for the lane's (h, mq); psi in shared memory.
 template <int K, bool STAGED>
@@ -92,114 +76,53 @@ __device__ __forceinline__ float4 project(const float *__restrict__ Wsrc, const 
     return make_float4(o0, o1, o2, o3);
 }
 
-template <int K, bool MASKED>
-__device__ __forceinline__ void edge_sums(const FwdArgs &p, const TermGrid &grid, const Cell &cell, float rx, float ry,
-                                          float rz, const float (&a2)[8], const int (&pk)[8], float (&dmin)[8],
-                                          float (&sum)[8], float (&acc)[8][2], float *sw, float *sx, int lane)
+
+__global__ void __launch_bounds__(128) lattice_phi_kernel(const PhiArgs p)
 {
-    // pass 0: minimum squared distance, per head when the boxes differ
-#pragma unroll
-    for (int h = 0; h < 8; ++h) dmin[h] = 1e10f;
-    for (int base = 0; base < grid.count; base += 32) {
-        const int t = base + lane;
-        int n1, n2, n3;
-        grid.decode(min(t, grid.count - 1), n1, n2, n3);
-        const float d2 = cell.dist2(rx, ry, rz, n1, n2, n3);
-        if (MASKED) {
-#pragma unroll
-            for (int h = 0; h < 8; ++h)
-                if (in_box<true>(pk[h], n1, n2, n3)) dmin[h] = fminf(dmin[h], d2);
-        } else {
-            dmin[0] = fminf(dmin[0], d2);
-        }
-    }
-    if (MASKED) {
-#pragma unroll
-        for (int h = 0; h < 8; ++h) dmin[h] = warp_min(dmin[h]);
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= p.E) return;
+    const long long i = p.edges[e];
+    const long long c = p.batch[i];
+    Cell cell;
+    cell.load(p.tvecs + 9 * c);
+    const float4 *ap = reinterpret_cast<const float4 *>(p.a + (p.a_per_edge ? e : i) * HEADS);
+    const float4 a_lo = __ldg(ap), a_hi = __ldg(ap + 1);
+    const float a[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+    float rx, ry, rz;
+    if (p.pos_ij) {
+        rx = p.pos_ij[3 * e]; ry = p.pos_ij[3 * e + 1]; rz = p.pos_ij[3 * e + 2];
     } else {
-        const float m = warp_min(dmin[0]);
-#pragma unroll
-        for (int h = 0; h < 8; ++h) dmin[h] = m;
+        const long long j = p.edges[p.E + e];
+        rx = __fsub_rn(p.pos[3 * j], p.pos[3 * i]);
+        ry = __fsub_rn(p.pos[3 * j + 1], p.pos[3 * i + 1]);
+        rz = __fsub_rn(p.pos[3 * j + 2], p.pos[3 * i + 2]);
     }
-
-    const float c0 = (float)(lane + 1) * p.bin_step, c1 = (float)(lane + 33) * p.bin_step;
-#pragma unroll
-    for (int h = 0; h < 8; ++h) {
-        sum[h] = 0.f;
-        acc[h][0] = acc[h][1] = 0.f;
-    }
-
-    for (int base = 0; base < grid.count; base += 32) {
-        // pass 1: one translation per lane
-        const int t = base + lane;
-        const bool valid = t < grid.count;
-        int n1, n2, n3;
-        grid.decode(valid ? t : 0, n1, n2, n3);
-        const float d2 = cell.dist2(rx, ry, rz, n1, n2, n3);
-        float w[8];
-        float wmax = 0.f;
-#pragma unroll
-        for (int h = 0; h < 8; ++h) {
-            float wh = ex2(a2[h] * (d2 - dmin[h]));
-            if (!valid || !in_box<MASKED>(pk[h], n1, n2, n3)) wh = 0.f;
-            w[h] = wh;
-            sum[h] += wh;
-            wmax = fmaxf(wmax, wh);
-        }
-        if (K > 0) {
-            const float x = sqrtf(d2) * p.bin_scale;
-            const bool keep = wmax > p.w_floor && x < p.x_cut;
-            const unsigned mask = __ballot_sync(FULL, keep);
-            if (keep) {
-                const int slot = __popc(mask & ((1u << lane) - 1u));
-                sx[slot] = x;
-                reinterpret_cast<float4 *>(sw)[2 * slot] = make_float4(w[0], w[1], w[2], w[3]);
-                reinterpret_cast<float4 *>(sw)[2 * slot + 1] = make_float4(w[4], w[5], w[6], w[7]);
-            }
-            __syncwarp();
-            // pass 2: two bins per lane, all heads
-            const int cnt = __popc(mask);
-#pragma unroll 2
-            for (int m = 0; m < cnt; ++m) {
-                const float x_m = sx[m];
-                const float4 wa = reinterpret_cast<const float4 *>(sw)[2 * m];
-                const float4 wb = reinterpret_cast<const float4 *>(sw)[2 * m + 1];
-                const float t0 = c0 - x_m, t1 = c1 - x_m;
-                const float g0 = ex2(-t0 * t0), g1 = ex2(-t1 * t1);
-                acc[0][0] = fmaf(wa.x, g0, acc[0][0]); acc[0][1] = fmaf(wa.x, g1, acc[0][1]);
-                acc[1][0] = fmaf(wa.y, g0, acc[1][0]); acc[1][1] = fmaf(wa.y, g1, acc[1][1]);
-                acc[2][0] = fmaf(wa.z, g0, acc[2][0]); acc[2][1] = fmaf(wa.z, g1, acc[2][1]);
-                acc[3][0] = fmaf(wa.w, g0, acc[3][0]); acc[3][1] = fmaf(wa.w, g1, acc[3][1]);
-                acc[4][0] = fmaf(wb.x, g0, acc[4][0]); acc[4][1] = fmaf(wb.x, g1, acc[4][1]);
-                acc[5][0] = fmaf(wb.y, g0, acc[5][0]); acc[5][1] = fmaf(wb.y, g1, acc[5][1]);
-                acc[6][0] = fmaf(wb.z, g0, acc[6][0]); acc[6][1] = fmaf(wb.z, g1, acc[6][1]);
-                acc[7][0] = fmaf(wb.w, g0, acc[7][0]); acc[7][1] = fmaf(wb.w, g1, acc[7][1]);
-            }
-            __syncwarp();
-        }
-    }
-#pragma unroll
-    for (int h = 0; h < 8; ++h) sum[h] = warp_sum(sum[h]);
+    float z[8];
+    edge_phi(p.rule, a, p.rvlen ? p.rvlen + 3 * c : nullptr, cell, rx, ry, rz, z);
+    float4 *zp = reinterpret_cast<float4 *>(p.z + e * HEADS);
+    zp[0] = make_float4(z[0], z[1], z[2], z[3]);
+    zp[1] = make_float4(z[4], z[5], z[6], z[7]);
 }
 
 template <int K>
-__global__ void __launch_bounds__(THREADS) lattice_sum_fwd_kernel(const FwdArgs p)
+__global__ void __launch_bounds__(THREADS) lattice_psi_kernel(const FwdArgs p)
 {
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float *wt = smem;
     float *mine = smem + (p.stage_w ? HEADS * WT_HEAD_STRIDE : 0) + warp * WARP_SMEM_FLOATS;
-    float *sw = mine, *sx = mine + 32 * 8, *psi = mine + 32 * 8 + 32;
+    float *psi = mine + STAGE_FLOATS;
 
-    if (K > 0 && p.stage_w) {
+    if (p.stage_w) {
         // W[h][m][k] -> wt[h][k][m] so that a lane reads its four outputs' weights as one float4
-        constexpr int KK = K > 0 ? K : 1;
         for (int idx = threadIdx.x; idx < HEADS * HEAD_DIM * K; idx += THREADS) {
-            const int h = idx / (HEAD_DIM * KK), m = (idx / KK) % HEAD_DIM, k = idx % KK;
+            const int h = idx / (HEAD_DIM * K), m = (idx / K) % HEAD_DIM, k = idx % K;
             wt[h * WT_HEAD_STRIDE + k * HEAD_DIM + m] = p.W[idx];
         }
         __syncthreads();
     }
+    BinAccumulator<K> bins;
+    bins.init(mine, lane, p.basis);
 
     for (long long e = (long long)blockIdx.x * WARPS + warp; e < p.E; e += (long long)gridDim.x * WARPS) {
         const long long i = p.edges[e];
@@ -208,57 +131,76 @@ __global__ void __launch_bounds__(THREADS) lattice_sum_fwd_kernel(const FwdArgs 
         Cell cell;
         cell.load(p.tvecs + 9 * c);
 
+        // lanes 0..7 (and their copies) hold head (lane & 7): its width, its box and the log-normaliser from phi
         const float a_own = p.a[(p.a_per_edge ? e : i) * HEADS + (lane & 7)];
-        int R1, R2, R3;
-        box_half_widths(p.rule, a_own, p.rvlen ? p.rvlen + 3 * c : nullptr, R1, R2, R3);
-        const int M1 = warp_max_int(R1), M2 = warp_max_int(R2), M3 = warp_max_int(R3);
-        const bool uniform = __all_sync(FULL, R1 == M1 && R2 == M2 && R3 == M3);
-        const int packed = R1 | (R2 << 8) | (R3 << 16);
-        float a2[8];
+        const float z_own = p.z[e * HEADS + (lane & 7)];
+        const int pk_own = packed_box(p.rule, a_own, p.rvlen ? p.rvlen + 3 * c : nullptr);
+        int uni = pk_own;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) uni = box_union(uni, __shfl_xor_sync(FULL, uni, o));
+        const bool masked = !__all_sync(FULL, pk_own == uni);
+        float a2[8], off[8];
         int pk[8];
 #pragma unroll
         for (int h = 0; h < 8; ++h) {
             a2[h] = __shfl_sync(FULL, a_own, h) * LOG2E;
-            pk[h] = __shfl_sync(FULL, packed, h);
+            off[h] = -__shfl_sync(FULL, z_own, h) * LOG2E;
+            pk[h] = __shfl_sync(FULL, pk_own, h);
         }
-        TermGrid grid;
-        grid.set(M1, M2, M3);
-
-        float dmin[8], sum[8], acc[8][2];
-        if (uniform) edge_sums<K, false>(p, grid, cell, rx, ry, rz, a2, pk, dmin, sum, acc, sw, sx, lane);
-        else edge_sums<K, true>(p, grid, cell, rx, ry, rz, a2, pk, dmin, sum, acc, sw, sx, lane);
-
-        if (lane < 8) {
-            const float s = pick8(sum, lane), dm = pick8(dmin, lane);
-            p.z[e * HEADS + lane] = fmaf(dm, a_own, logf(s));
-        }
-        if (K > 0) {
-            if (p.W == nullptr) {
-                float *dst = p.v + (size_t)e * HEADS * K + lane;
-#pragma unroll
-                for (int h = 0; h < 8; ++h) {
-                    const float inv = __frcp_rn(sum[h]);
-                    dst[h * K] = acc[h][0] * inv;
-                    dst[h * K + 32] = acc[h][1] * inv;
-                }
-            } else {
-#pragma unroll
-                for (int h = 0; h < 8; ++h) {
-                    const float inv = __frcp_rn(sum[h]);
-                    psi[h * PSI_STRIDE + lane] = acc[h][0] * inv;
-                    psi[h * PSI_STRIDE + lane + 32] = acc[h][1] * inv;
-                }
-                __syncwarp();
-                float4 o;
-                if (p.stage_w) {
-                    o = project<(K > 0 ? K : 4), true>(wt, psi, lane);
-                } else {
-                    const long long wi = (p.W_num == 1) ? 0 : (p.W_num == p.E ? e : i);
-                    o = project<(K > 0 ? K : 4), false>(p.W + (size_t)wi * HEADS * HEAD_DIM * K, psi, lane);
-                }
-                reinterpret_cast<float4 *>(p.v + (size_t)e * HEADS * HEAD_DIM)[lane] = o;
-                __syncwarp();
+        const int R1 = box_r1(uni), R2 = box_r2(uni), R3 = box_r3(uni);
+        const int count = (2 * R1 + 1) * (2 * R2 + 1) * (2 * R3 + 1);
+        TermWalker walk;
+        walk.init(R1, R2, R3, (unsigned)lane);
+        const float F1 = (float)R1, F2 = (float)R2, F3 = (float)R3;
+        bins.clear();
+        for (int base = 0; base < count; base += 32) {
+            const bool valid = base + lane < count;
+            const float f1 = walk.u1 - F1, f2 = walk.u2 - F2, f3 = walk.u3 - F3;
+            const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, rx)));
+            const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, ry)));
+            const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, rz)));
+            const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+            int i1 = 0, i2 = 0, i3 = 0;
+            if (masked) {
+                i1 = abs(__float2int_rn(f1)); i2 = abs(__float2int_rn(f2)); i3 = abs(__float2int_rn(f3));
             }
+            float w[8];
+            float emax = -INFINITY;
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                float eh = fmaf(a2[h], d2, off[h]);
+                if (masked && !(i1 <= box_r1(pk[h]) && i2 <= box_r2(pk[h]) && i3 <= box_r3(pk[h]))) eh = -INFINITY;
+                w[h] = ex2(eh);
+                emax = fmaxf(emax, eh);
+            }
+            const float x = sqrtf(d2) * p.basis.bin_scale;
+            bins.push(valid && emax > p.basis.floor_log2 && d2 < p.basis.d2_cut, x, w);
+            walk.step();
+        }
+
+        if (p.W == nullptr) {
+            float *dst = p.v + (size_t)e * HEADS * K + lane;
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                dst[h * K] = bins.acc[h][0];
+                dst[h * K + 32] = bins.acc[h][1];
+            }
+        } else {
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                psi[h * PSI_STRIDE + lane] = bins.acc[h][0];
+                psi[h * PSI_STRIDE + lane + 32] = bins.acc[h][1];
+            }
+            __syncwarp();
+            float4 o;
+            if (p.stage_w) {
+                o = project<K, true>(wt, psi, lane);
+            } else {
+                const long long wi = (p.W_num == 1) ? 0 : (p.W_num == p.E ? e : i);
+                o = project<K, false>(p.W + (size_t)wi * HEADS * HEAD_DIM * K, psi, lane);
+            }
+            reinterpret_cast<float4 *>(p.v + (size_t)e * HEADS * HEAD_DIM)[lane] = o;
+            __syncwarp();
         }
     }
 }
@@ -279,25 +221,37 @@ __global__ void lattice_box_kernel(const float *a, int a_per_edge, const int64_t
     box[3 * tid + 2] = R3;
 }
 
-template <int K>
-int launch_fwd(const FwdArgs &p, cudaStream_t stream)
+
+int launch_fwd(const FwdArgs &p, long long K, cudaStream_t stream)
 {
-    const size_t smem = sizeof(float) * ((p.stage_w ? HEADS * WT_HEAD_STRIDE : 0) + WARPS * WARP_SMEM_FLOATS);
-    static thread_local int per_sm[2] = {0, 0};
-    int &occ = per_sm[p.stage_w ? 1 : 0];
-    if (occ == 0) {
-        cudaFuncSetAttribute(lattice_sum_fwd_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(float) * (HEADS * WT_HEAD_STRIDE + WARPS * WARP_SMEM_FLOATS)));
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, lattice_sum_fwd_kernel<K>, THREADS, smem) != cudaSuccess || occ <= 0)
-            occ = 4;
+    PhiArgs phi{};
+    phi.a = p.a; phi.pos_ij = p.pos_ij; phi.tvecs = p.tvecs; phi.batch = p.batch; phi.edges = p.edges;
+    phi.rvlen = p.rvlen; phi.z = p.z; phi.E = p.E; phi.rule = p.rule; phi.a_per_edge = p.a_per_edge;
+    launch_lattice_phi(phi, stream);
+    if (K > 0) {
+        const size_t smem = sizeof(float) * ((p.stage_w ? HEADS * WT_HEAD_STRIDE : 0) + WARPS * WARP_SMEM_FLOATS);
+        static thread_local int per_sm[2] = {0, 0};
+        int &occ = per_sm[p.stage_w ? 1 : 0];
+        if (occ == 0) {
+            cudaFuncSetAttribute(lattice_psi_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(sizeof(float) * (HEADS * WT_HEAD_STRIDE + WARPS * WARP_SMEM_FLOATS)));
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, lattice_psi_kernel<64>, THREADS, smem) != cudaSuccess || occ <= 0)
+                occ = 4;
+        }
+        const long long want = (p.E + WARPS - 1) / WARPS;
+        const long long cap = (long long)sm_count() * occ;
+        lattice_psi_kernel<64><<<(int)(want < cap ? want : cap), THREADS, smem, stream>>>(p);
     }
-    const long long want = (p.E + WARPS - 1) / WARPS;
-    const long long cap = (long long)sm_count() * occ;
-    const int blocks = (int)(want < cap ? want : cap);
-    lattice_sum_fwd_kernel<K><<<blocks, THREADS, smem, stream>>>(p);
     return launch_status("cf_lattice_sum_fwd");
 }
 
 }  // namespace
+
+int launch_lattice_phi(const PhiArgs &p, cudaStream_t stream)
+{
+    if (p.E > 0) lattice_phi_kernel<<<(unsigned)((p.E + 127) / 128), 128, 0, stream>>>(p);
+    return launch_status("lattice_phi_kernel");
+}
 
 }  // namespace cf
 
@@ -347,14 +301,7 @@ extern "C" int cf_lattice_sum_fwd(const float *a, int a_per_edge, const float *p
     p.N = N; p.E = E; p.W_num = W_num;
     p.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
     p.a_per_edge = a_per_edge;
-    p.w_floor = weight_floor();
+    p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
     p.stage_w = (p.W != nullptr && W_num == 1) ? 1 : 0;
-    if (K > 0) {
-        const double step = sqrt(1.4426950408889634) / (sqrt(2.0) * (double)(float)wscale);
-        const double mu0 = (double)(float)dist_max / (double)K;
-        p.bin_step = (float)step;
-        p.bin_scale = (float)(step / mu0);
-        p.x_cut = (float)((double)K * step + 11.3);  // (x - K step)^2 > 126 => every 2^-(..)^2 < 2^-126
-    }
-    return K == 0 ? launch_fwd<0>(p, as_stream(stream)) : launch_fwd<64>(p, as_stream(stream));
+    return launch_fwd(p, K, as_stream(stream));
 }

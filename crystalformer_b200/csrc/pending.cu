@@ -11,17 +11,11 @@ extern "C" int cf_lattice_sum_bwd(const float *, const float *, const float *, c
     return cf::fail(CF_ERR_UNSUPPORTED, "cf_lattice_sum_bwd: not built yet");
 }
 
-extern "C" int cf_infinite_attn_fwd(const float *, const float *, const float *, const float *, const float *,
-                                    const float *, const float *, const int64_t *, const int64_t *, const int64_t *,
-                                    int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, double, double, const float *,
-                                    double, int, int, float *, float *, float *, float *, void *)
-{
-    return cf::fail(CF_ERR_UNSUPPORTED, "cf_infinite_attn_fwd: not built yet");
-}
-
 extern "C" int cf_infinite_attn_bwd(const float *, const float *, const float *, const float *, const float *,
-                                    const float *, const float *, const int64_t *, const int64_t *, const int64_t *,
-                                    int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, double, double, const float *,
+                                    const float *, const float *, const float *, const int64_t *, const int64_t *,
+                                    const int64_t *,
+                                    int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
+                                    double, double, const float *,
                                     double, int, int, const float *, const float *, const float *, const float *,
                                     float *, float *, float *, float *, float *, void *)
 {

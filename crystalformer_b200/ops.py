@@ -188,6 +188,32 @@ def fused_attn_bwd(q, k, v, bij, edges, row_start, prob, out, gout):
     return gq, gk, gv, gaij, gbij
 
 
+def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W,
+                      cutoff_radius, lattice_range, minimum_range, want_psi_row=False, pos=None):
+    """Fused attention forward.  Geometry as pos_ij (E,3), or pos (N,3) when pos_ij is None.
+    Returns (out (N,H,D), logit (E,H), lse (N,H), psi_row (N,H,K) or None)."""
+    dev = q.device
+    q, k, v, a, tvecs = (_want(t, torch.float32, n, dev) for t, n in
+                         ((q, "q"), (k, "k"), (v, "v"), (a, "a"), (tvecs, "tvecs")))
+    pos_ij, pos = _want(pos_ij, torch.float32, "pos_ij", dev), _want(pos, torch.float32, "pos", dev)
+    rvlen, W = _want(rvlen, torch.float32, "rvlen", dev), _want(W, torch.float32, "W", dev)
+    batch, edges, row_start = (_want(t, torch.int64, n, dev) for t, n in
+                               ((batch, "batch"), (edges, "edges"), (row_start, "row_start")))
+    N, H, D = q.shape
+    E, B = edges.shape[1], tvecs.shape[0]
+    out = torch.empty((N, H, D), dtype=torch.float32, device=dev)
+    logit = torch.empty((E, H), dtype=torch.float32, device=dev)
+    lse = torch.empty((N, H), dtype=torch.float32, device=dev)
+    psi_row = torch.empty((N, H, K), dtype=torch.float32, device=dev) if (want_psi_row and K > 0) else None
+    with torch.cuda.device(dev):
+        _lib.call("cf_infinite_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(pos), _ptr(pos_ij), _ptr(tvecs),
+                  _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),
+                  c_int64(D), c_int64(E), c_int64(K), c_int64(max_atoms), c_double(dist_max), c_double(wscale), _ptr(W),
+                  c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(out), _ptr(logit),
+                  _ptr(lse), _ptr(psi_row), _stream(dev))
+    return out, logit, lse, psi_row
+
+
 def segment_mean(x, start):
     """Per-crystal mean: x (N,D) float32, start (B+1) int64 atom offsets -> (B,D)."""
     dev = x.device

@@ -147,29 +147,34 @@ int cf_segment_mean_fwd(const float *x, const int64_t *start, int64_t B, int64_t
  * per-edge tensor except the logits:
  *   out_i = sum_j softmax_j(q_i.k_j + phi_ij) (v_j + W psi_ij)
  * computed as  sum_j p_ij v_j + W_h (sum_j p_ij psi_ij)  (W is shared by all edges, W (H,D,K)).
- *   in : q (pre-scaled), k, v (N,H,D); a (N,H); pos (N,3); tvecs (B,3,3); rvlen (B,3) or NULL; batch (N);
- *        atom_start (B+1); row_start (N+1); E total edges
+ *   in : q (pre-scaled), k, v (N,H,D); a (N,H); the geometry either as pos_ij (E,3) (what the reference hands its
+ *        kernels) or, when pos_ij is NULL, as pos (N,3) from which pos[j]-pos[i] is taken; tvecs (B,3,3);
+ *        rvlen (B,3) or NULL; batch (N); edges (2,E); row_start (N+1);
+ *        max_atoms >= the largest number of atoms in one crystal
+ *        (it sizes the shared memory of a thread block; crystals of up to 2048 atoms)
  *   out: out (N,H,D)
  *        logit (E,H)  q.k + phi, kept for the backward
  *        lse (N,H)    log sum_j exp(logit)
  *        psi_row (N,H,K) = sum_j p_ij psi_ij (NULL to skip; needed for the gradient of W)
  * ---------------------------------------------------------------------------------------------------------- */
 int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
-                         const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *atom_start,
-                         const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D, int64_t E, int64_t K,
-                         double dist_max, double wscale, const float *W, double cutoff_radius, int lattice_range,
-                         int minimum_range, float *out, float *logit, float *lse, float *psi_row, void *stream);
+                         const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                         const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
+                         int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
+                         const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out,
+                         float *logit, float *lse, float *psi_row, void *stream);
 
 /* Backward of cf_infinite_attn_fwd; phi and psi are recomputed from the geometry.
  *   in : everything the forward read, plus logit, lse, out and gout (N,H,D)
  *   out: gq (w.r.t. the pre-scaled q), gk, gv (N,H,D); ga (N,H); glogit (E,H) scratch/diagnostic
  * The gradient of W is sum_i gout_i (x) psi_row_i, a plain GEMM the caller does from psi_row. */
 int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
-                         const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *atom_start,
-                         const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D, int64_t E, int64_t K,
-                         double dist_max, double wscale, const float *W, double cutoff_radius, int lattice_range,
-                         int minimum_range, const float *logit, const float *lse, const float *out,
-                         const float *gout, float *gq, float *gk, float *gv, float *ga, float *glogit, void *stream);
+                         const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                         const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
+                         int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
+                         const float *W, double cutoff_radius, int lattice_range, int minimum_range,
+                         const float *logit, const float *lse, const float *out, const float *gout, float *gq,
+                         float *gk, float *gv, float *ga, float *glogit, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Pipe-throughput probes for the roofline denominators: `iters` dependent-free FFMA (kind 0) or MUFU.EX2 (kind 1)
