@@ -21,8 +21,7 @@ SIGNATURES = {
     "cf_batch_prepare": [P, P, P, P, P, I64, I64, I64, P, P, P, P, P, P, P, P],
     "cf_lattice_box": [P, I32, P, P, I64, I64, I64, P, F64, I32, I32, P, P],
     "cf_lattice_sum_fwd": [P, I32, P, P, P, P, I64, I64, I64, I64, F64, F64, P, I64, I64, P, F64, I32, I32, P, P, P],
-    "cf_lattice_sum_bwd": [P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, F64, F64, P, I64, I64, P, F64, I32, I32, P, P,
-                           P, P],
+    "cf_lattice_sum_bwd": [P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, F64, F64, P, F64, I32, I32, P, P, P, P],
     "cf_fused_attn_fwd": [P, P, P, P, P, P, P, I64, I64, I64, I64, P, P, P],
     "cf_fused_attn_bwd": [P, P, P, P, P, P, I64, I64, I64, I64, P, P, P, P, P, P, P, P, P],
     "cf_segment_mean_fwd": [P, P, I64, I64, P, P],
@@ -56,8 +55,6 @@ def load() -> ctypes.CDLL:
         lib.cf_set_weight_floor_log2.argtypes = [c_double]
         lib.cf_set_weight_floor_log2.restype = None
         lib.cf_get_weight_floor_log2.restype = c_double
-        lib.cf_lattice_sum_bwd_scratch_bytes.argtypes = [I64, I64, I64, I64]
-        lib.cf_lattice_sum_bwd_scratch_bytes.restype = c_int64
         for name, argtypes in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes

@@ -1,0 +1,316 @@
+"""Infinitely connected multi-head attention module with the reference's interface.
+
+``CrystalformerMultiheadAttentionCUDA`` has the constructor, ``forward`` signature, parameter names (hence state_dict
+keys) and initialisation of the reference class of the same name
+(models/indexed_lattice_multi_head_attention_cuda.py:790-1016; the pure-PyTorch twin is
+models/indexed_lattice_multi_head_attention.py:1501-1727).  The host-side steps - in-projection, the Gaussian width
+``a`` per (atom, head), out-projection - follow ``crystalformer_multi_head_attention_forward_cuda`` (:462-788).  The
+position encodings and the attention itself run in one fused operator (``InfiniteAttentionFunction``) instead of the
+reference's ``RealPeriodicEncodingWithProjFuncCUDA`` + ``FusedDotProductAttentionCUDA`` pair; the pair is still
+available (``fused=False`` or ``need_weights=True``) through ``crystalformer_b200.cuda_funcs``.
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+from torch.nn import Module, Parameter
+from torch.nn.init import constant_, normal_, xavier_uniform_
+from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
+
+from . import ops
+from .cuda_funcs import FusedDotProductAttentionCUDA, RealPeriodicEncodingWithProjFuncCUDA
+from .cuda_funcs.kernel_manager import KernelManager
+from .params import LatticeformerParams
+
+# ---------------------------------------------------------------------------------------------------------------
+# Per-batch quantities derived from the edge list: CSR offsets and the largest crystal.  The reference rebuilds the
+# CSR inside every wrapper call; here it is cached per edge tensor so that the layers of one forward share it.
+# ---------------------------------------------------------------------------------------------------------------
+_EDGE_CACHE: "OrderedDict[tuple, tuple]" = OrderedDict()
+
+
+def register_edge_info(edges: Tensor, row_start: Tensor, max_atoms: int) -> None:
+    """Lets a caller that already knows the CSR offsets and the largest crystal (e.g. the encoder, which builds the
+    edge list on the device) avoid the device->host read that ``edge_info`` would need."""
+    key = (edges.data_ptr(), tuple(edges.shape), edges.device, edges._version)
+    _EDGE_CACHE[key] = (row_start, int(max_atoms))
+    while len(_EDGE_CACHE) > 16:
+        _EDGE_CACHE.popitem(last=False)
+
+
+def edge_info(edges: Tensor, N: int) -> Tuple[Tensor, int]:
+    key = (edges.data_ptr(), tuple(edges.shape), edges.device, edges._version)
+    hit = _EDGE_CACHE.get(key)
+    if hit is not None:
+        return hit
+    row_start = torch.zeros(N + 1, dtype=torch.int64, device=edges.device)
+    row_start.scatter_add_(0, edges[0] + 1, torch.ones_like(edges[0]))
+    row_start = row_start.cumsum(0)
+    max_atoms = int((row_start[1:] - row_start[:-1]).max().item()) if N > 0 else 1
+    register_edge_info(edges, row_start, max_atoms)
+    return row_start, max_atoms
+
+
+class InfiniteAttentionFunction(torch.autograd.Function):
+    """out_i = sum_j softmax_j(q_i.k_j + phi_ij) (v_j + W psi_ij), phi/psi recomputed in forward and backward.
+
+    Gradients flow to q (pre-scaled), k, v, a and W; never to positions or lattice vectors, as in the reference
+    (models/cuda_funcs/real_space_enc.py:244-247 returns None for them)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, a, W, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale,
+                cutoff, lattice_range, minimum_range):
+        q, k, v, a = (t.contiguous().detach() for t in (q, k, v, a))
+        W3 = None
+        if K > 0:
+            W3 = W.detach().reshape(W.shape[-3], W.shape[-2], W.shape[-1]).contiguous()
+        need_grad = any(ctx.needs_input_grad[:5])
+        out, logit, lse, psi_row = ops.infinite_attn_fwd(
+            q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W3, cutoff,
+            lattice_range, minimum_range, want_psi_row=need_grad and K > 0)
+        if need_grad:
+            ctx.save_for_backward(q, k, v, a, W3, pos_ij, tvecs, rvlen, batch, edges, row_start, logit, lse, out, psi_row)
+            ctx.cfg = (max_atoms, K, dist_max, wscale, cutoff, lattice_range, minimum_range)
+            ctx.w_shape = None if W is None else tuple(W.shape)
+        return out
+
+    @staticmethod
+    def backward(ctx, gout):
+        q, k, v, a, W3, pos_ij, tvecs, rvlen, batch, edges, row_start, logit, lse, out, psi_row = ctx.saved_tensors
+        max_atoms, K, dist_max, wscale, cutoff, lattice_range, minimum_range = ctx.cfg
+        gout = gout.contiguous()
+        gq, gk, gv, ga = ops.infinite_attn_bwd(
+            q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W3, cutoff,
+            lattice_range, minimum_range, logit, lse, out, gout)
+        gW = None
+        if K > 0 and ctx.needs_input_grad[4]:
+            gW = torch.einsum("nhd,nhk->hdk", gout, psi_row).reshape(ctx.w_shape)
+        return (gq, gk, gv, ga, gW) + (None,) * 13
+
+
+def positive_function(name: str):
+    """The map from the normalised alpha to a positive width factor (…attention_cuda.py:675-692)."""
+    beta = float(name.split("=")[1]) if "=" in name else 1.0
+    if name == "abs":
+        return lambda x, lb: (1 - lb) * x.abs() + lb
+    if name.startswith("softplus"):
+        return lambda x, lb: F.softplus(x + 1 / beta * math.log(math.exp(beta * (1 - lb)) - 1), beta=beta) + lb
+    if name.startswith("exp"):
+        return lambda x, lb: (1.0 - lb) * torch.exp(x * (beta / (1.0 - lb))) + lb
+    if name.startswith("elu"):
+        return lambda x, lb: (1.0 - lb) * F.elu(x * (beta / (1.0 - lb))) + 1.0
+    if name.startswith("sigmoid"):
+        return lambda x, lb: (1 / lb - lb) * torch.sigmoid(x * (beta * (1 + lb) / (1.0 - lb)) + math.log(lb)) + lb
+    raise NotImplementedError(f"Unkown positive_func: {name}")
+
+
+class CrystalformerMultiheadAttentionCUDA(Module):
+    """Drop-in for the reference module of the same name; see the module docstring."""
+
+    def __init__(self, embed_dim, num_heads, dropout=0., bias=True, kdim=None, vdim=None,
+                 params=LatticeformerParams(), device=None, dtype=None, fused: bool = True) -> None:
+        factory_kwargs = {"device": device, "dtype": dtype}
+        super().__init__()
+        self.embed_dim = embed_dim
+        self.kdim = kdim * num_heads if kdim is not None and kdim > 0 else embed_dim
+        self.vdim = vdim * num_heads if vdim is not None and vdim > 0 else embed_dim
+        if params.domain != "real":
+            raise NotImplementedError(f"crystalformer_b200 implements domain='real' only, got {params.domain!r}")
+        if params.gauss_state not in ("q", "q-headdim", "q-kdim", "1", "x", "x-norm", "x-xavier"):
+            raise NotImplementedError(f"gauss_state {params.gauss_state!r} is not supported")
+        if params.value_pe_wave_real > 0:
+            raise NotImplementedError("value_pe_wave_real > 0 is not supported")
+        self.params = params
+        self.fused = fused
+        self.gauss_scale = Parameter(torch.zeros(2, **factory_kwargs), requires_grad=False)
+        self.atten_scale = Parameter(torch.zeros(1, **factory_kwargs), requires_grad=False)
+        self.num_heads = num_heads
+        self.dropout = dropout
+        self.head_dim = embed_dim // num_heads
+        assert self.head_dim * num_heads == self.embed_dim, "embed_dim must be divisible by num_heads"
+
+        self.q_proj_weight = Parameter(torch.empty((self.kdim, embed_dim), **factory_kwargs))
+        self.k_proj_weight = Parameter(torch.empty((self.kdim, embed_dim), **factory_kwargs))
+        self.v_proj_weight = Parameter(torch.empty((self.vdim, embed_dim), **factory_kwargs))
+        if bias:
+            self.in_proj_bias = Parameter(torch.empty(self.kdim * 2 + self.vdim, **factory_kwargs))
+        else:
+            self.register_parameter("in_proj_bias", None)
+        self.out_proj = NonDynamicallyQuantizableLinear(self.vdim, embed_dim, bias=bias, **factory_kwargs)
+
+        if params.gauss_state.startswith("q") or params.gauss_state == "1":
+            self.lattice_pos_weights = Parameter(torch.empty((self.kdim), **factory_kwargs))
+        else:
+            self.lattice_pos_weights = Parameter(torch.empty((self.num_heads, embed_dim), **factory_kwargs))
+
+        self.ATOM_NUM = 98
+        head = self.num_heads if params.value_pe_headed else 1
+        cond = 1 if params.value_pe_condproj == "no" else self.ATOM_NUM
+        self.pe_dist_proj = Parameter(torch.empty(cond, head, self.head_dim, params.value_pe_dist_real, **factory_kwargs)) \
+            if params.value_pe_dist_real > 0 else None
+        self.pe_wave_proj = None
+        self._scale_known = False
+        self._reset_parameters()
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._scale_known = False
+        return super()._load_from_state_dict(*args, **kwargs)
+
+    def _reset_parameters(self):
+        # …attention_cuda.py:882-948
+        xavier_uniform_(self.q_proj_weight)
+        xavier_uniform_(self.k_proj_weight)
+        xavier_uniform_(self.v_proj_weight)
+        xavier_uniform_(self.out_proj.weight)
+        if self.in_proj_bias is not None:
+            constant_(self.in_proj_bias, 0.)
+            constant_(self.out_proj.bias, 0.)
+        state = self.params.gauss_state
+        if state in ("q", "q-headdim", "1"):
+            normal_(self.lattice_pos_weights, 0., (self.kdim // self.num_heads) ** -0.5)
+        elif state == "q-kdim":
+            normal_(self.lattice_pos_weights, 0., (self.kdim) ** -0.5)
+        elif state in ("x", "x-norm"):
+            normal_(self.lattice_pos_weights, 0., (self.embed_dim) ** -0.5)
+        elif state == "x-xavier":
+            xavier_uniform_(self.lattice_pos_weights)
+        if self.pe_dist_proj is not None:
+            with torch.no_grad():
+                for i, W in enumerate(self.pe_dist_proj):
+                    if i != 0 and self.params.value_pe_condproj in ("I", "J", "IJ"):
+                        W.set_(self.pe_dist_proj[0])
+                    else:
+                        W = W.view(-1, W.shape[-1])
+                        xavier_uniform_(W, (W.shape[1]) ** -0.5)
+
+    # -----------------------------------------------------------------------------------------------------------
+    def _widths(self, query: Tensor, q: Tensor) -> Tensor:
+        """a (N,H) < 0: the Gaussian parameter of every (atom, head) (…attention_cuda.py:640-722)."""
+        P = self.params
+        N, H, Dq = q.shape
+        w = self.lattice_pos_weights
+        if P.gauss_state.startswith("q"):
+            alpha = q.reshape(N, H, 1, Dq) @ w.reshape(H, Dq, 1)
+        elif P.gauss_state == "1":
+            alpha = torch.ones_like(q).reshape(N, H, 1, Dq) @ w.reshape(H, Dq, 1)
+        else:
+            alpha = F.linear(query, w)
+        alpha = alpha.view(N, H)
+        if P.normalize_gauss:
+            # The reference tests the stored scale on every call, a device->host read per layer; once the scale is
+            # known to be set it cannot become unset except by loading a state_dict, so the answer is remembered.
+            if not self._scale_known:
+                self._scale_known = bool(self.gauss_scale[0] > 0)
+            scale_available = self._scale_known
+            if scale_available:
+                scale, shift = self.gauss_scale[0], self.gauss_scale[1]
+            else:
+                scale = torch.reciprocal(alpha.detach().std())
+                shift = -alpha.detach().mean()
+            alpha = (alpha + shift) * scale
+            if self.training and not scale_available:
+                # saved once, in the first training step (…attention_cuda.py:669-673)
+                torch.nn.init.constant_(self.gauss_scale[0], scale)
+                torch.nn.init.constant_(self.gauss_scale[1], shift)
+                self._scale_known = True
+        func = positive_function(P.positive_func)
+        return func(alpha, P.gauss_lb_real) * (-0.5 * P.scale_real ** -2)
+
+    def forward(self, query: Tensor, key: Tensor, value: Tensor, batch_q: Tensor, batch_kv: Tensor, edges: Tensor,
+                points: Tensor, dist2_min: Tensor, tvecs: Tensor,
+                kr_base: Optional[Tensor] = None, rvecs: Optional[Tensor] = None, vcell: Optional[Tensor] = None,
+                onehot: Tensor = None, need_weights: bool = True, rvlen: Optional[Tensor] = None
+                ) -> Tuple[Tensor, Optional[Tensor]]:
+        """Same arguments as the reference (…attention_cuda.py:950-955): ``points`` is pos_ij (E,3), ``tvecs`` the
+        lattice rows (B,3,3), ``rvecs`` the reciprocal rows (needed by the adaptive cut-off).  ``rvlen`` optionally
+        passes the row norms of ``rvecs`` if the caller has them already."""
+        P = self.params
+        H = self.num_heads
+        N = query.shape[0]
+        if P.value_pe_condproj != "no":
+            raise NotImplementedError("value_pe_condproj other than 'no' is not supported")
+        if P.norm_func_mode != 0:
+            raise NotImplementedError("norm_func_mode other than 0 is not supported")
+        if batch_q is not batch_kv and not torch.equal(batch_q, batch_kv):
+            raise NotImplementedError("only self-attention (batch_q == batch_kv) is supported")
+        if self.training and self.dropout > 0.0:
+            raise NotImplementedError("attention dropout is not supported by the fused kernels")
+
+        # in-projection (…attention_cuda.py:582-596): one GEMM when q, k and v come from the same tensor
+        if query is key and key is value:
+            w_in = torch.cat((self.q_proj_weight, self.k_proj_weight, self.v_proj_weight), dim=0)
+            q, k, v = F.linear(query, w_in, self.in_proj_bias).split((self.kdim, self.kdim, self.vdim), dim=1)
+        else:
+            b_q = b_k = b_v = None
+            if self.in_proj_bias is not None:
+                b_q, b_k, b_v = self.in_proj_bias.split([self.kdim, self.kdim, self.vdim])
+            q = F.linear(query, self.q_proj_weight, b_q)
+            k = F.linear(key, self.k_proj_weight, b_k)
+            v = F.linear(value, self.v_proj_weight, b_v)
+        Dq, Dv = self.kdim // H, self.vdim // H
+        q = q.reshape(N, H, Dq)
+        k = k.reshape(k.shape[0], H, Dq)
+        v = v.reshape(v.shape[0], H, Dv)
+
+        a = self._widths(query, q)
+
+        dist_max = P.value_pe_dist_max
+        if dist_max < 0:
+            dist_max = (-dist_max) * P.scale_real
+        K = P.value_pe_dist_real
+        cutoff = 0.0
+        if P.adaptive_cutoff_sigma < 0:
+            cutoff = float(P.adaptive_cutoff_sigma)
+        elif P.adaptive_cutoff_sigma > 0:
+            cutoff = P.scale_real * P.gauss_lb_real ** (-0.5) * P.adaptive_cutoff_sigma
+        if cutoff != 0.0:
+            if rvlen is None:
+                if rvecs is None:
+                    raise ValueError("the adaptive cut-off needs rvecs (reciprocal lattice rows)")
+                rvlen = torch.norm(rvecs, 2, dim=-1)
+        else:
+            rvlen = None
+        lattice_range = int(P.lattice_range)
+        minimum_range = lattice_range if P.minimum_range else 0
+        q_scaled = q / math.sqrt(Dq)
+
+        values = None
+        if self.fused and not need_weights:
+            row_start, max_atoms = edge_info(edges, N)
+            attn = InfiniteAttentionFunction.apply(
+                q_scaled, k, v, a, self.pe_dist_proj, points, tvecs, rvlen, batch_q, edges, row_start, max_atoms, K,
+                float(dist_max), float(P.value_pe_width_scale), cutoff, lattice_range, minimum_range)
+            weights = None
+        else:
+            # the reference's operator split, through the drop-in autograd functions
+            saved = (KernelManager.LATTICE_RANGE, KernelManager.MINIMUM_RANGE)
+            KernelManager.LATTICE_RANGE, KernelManager.MINIMUM_RANGE = lattice_range, minimum_range
+            try:
+                extra = (rvlen, cutoff) if cutoff != 0.0 else ()
+                res = RealPeriodicEncodingWithProjFuncCUDA.apply(
+                    a, points, dist2_min, tvecs, batch_q, edges, K, float(dist_max), float(P.value_pe_width_scale),
+                    self.pe_dist_proj, *extra)
+            finally:
+                KernelManager.LATTICE_RANGE, KernelManager.MINIMUM_RANGE = saved
+            phi = res[0]
+            values = res[1] if len(res) > 1 else None
+            attn = FusedDotProductAttentionCUDA.apply(q_scaled, k, v, phi, values, batch_q, edges)
+            weights = None
+            if need_weights:
+                with torch.no_grad():
+                    row_start, _ = edge_info(edges, N)
+                    prob, _ = ops.fused_attn_fwd(q_scaled.detach(), k.detach(), v.detach(), phi.detach(),
+                                                 None if values is None else values.detach(), edges, row_start)
+                    weights = prob.mean(dim=1)
+
+        attn_output = F.linear(attn.reshape(N, Dv * H), self.out_proj.weight, self.out_proj.bias)
+        if need_weights:
+            return attn_output, weights
+        return attn_output, values
+
+

@@ -124,7 +124,9 @@ def lattice_sum_fwd(a, pos_ij, tvecs, batch, edges, K, dist_max, wscale, W=None,
 
 def lattice_sum_bwd(a, pos_ij, tvecs, batch, edges, row_start, z, gz, gv, K, dist_max, wscale, W=None, rvlen=None,
                     cutoff_radius=0.0, lattice_range=2, minimum_range=2):
-    """ga (N,H) and gW (W_num,H,Dv,K) (None without W)."""
+    """ga (N,H) and gW (shape of W; None without W).  gv is the gradient of psi (E,H,K) when W is None, else of
+    W psi (E,H,Dv).  The projection is handled around the kernel with two GEMM-shaped torch calls:
+    gpsi = W^T gv before it, gW = sum_e gv_e (x) psi_e after it (psi recomputed by the kernel)."""
     dev = a.device
     a = _want(a, torch.float32, "a")
     pos_ij = _want(pos_ij, torch.float32, "pos_ij", dev)
@@ -135,21 +137,39 @@ def lattice_sum_bwd(a, pos_ij, tvecs, batch, edges, row_start, z, gz, gv, K, dis
     W, rvlen = _want(W, torch.float32, "W", dev), _want(rvlen, torch.float32, "rvlen", dev)
     E, H, N = edges.shape[1], a.shape[1], batch.shape[0]
     ga = torch.empty((N, H), dtype=torch.float32, device=dev)
-    gW = scratch = None
-    W_num = Dv = 0
-    if W is not None and K > 0:
-        W_num = 1 if W.dim() == 3 else W.shape[0]
-        Dv = W.shape[-2]
-        gW = torch.empty((W_num, H, Dv, K), dtype=torch.float32, device=dev)
-        nbytes = int(_lib.load().cf_lattice_sum_bwd_scratch_bytes(N, H, Dv, K)) if W_num == 1 else 0
-        if nbytes:
-            scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    scratch = torch.empty((E, H), dtype=torch.float32, device=dev)
+    gpsi = psi = None
+    if K > 0:
+        if W is None:
+            gpsi = gv
+        else:
+            W4 = W if W.dim() == 4 else W[None]
+            W_num = W4.shape[0]
+            if W_num == 1:
+                gpsi = torch.einsum("ehd,hdk->ehk", gv, W4[0]).contiguous()
+            elif W_num == E:
+                gpsi = torch.einsum("ehd,ehdk->ehk", gv, W4).contiguous()
+            elif W_num == N:
+                gpsi = torch.einsum("ehd,ehdk->ehk", gv, W4[edges[0]]).contiguous()
+            else:
+                raise ValueError(f"W_num={W_num} must be 1, E or N")
+            psi = torch.empty((E, H, K), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         _lib.call("cf_lattice_sum_bwd", _ptr(a), _ptr(pos_ij), _ptr(tvecs), _ptr(batch), _ptr(edges), _ptr(row_start),
-                  _ptr(z), _ptr(gz), _ptr(gv if K > 0 else None), c_int64(N), c_int64(H), c_int64(E), c_int64(K),
-                  c_double(dist_max), c_double(wscale), _ptr(W), c_int64(W_num), c_int64(Dv), _ptr(rvlen),
-                  c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(ga), _ptr(gW),
-                  _ptr(scratch), _stream(dev))
+                  _ptr(z), _ptr(gz), _ptr(gpsi), c_int64(N), c_int64(H), c_int64(E), c_int64(K), c_double(dist_max),
+                  c_double(wscale), _ptr(rvlen), c_double(cutoff_radius or 0.0), c_int(lattice_range),
+                  c_int(minimum_range), _ptr(ga), _ptr(psi), _ptr(scratch), _stream(dev))
+    gW = None
+    if psi is not None:
+        if W_num == 1:
+            gW = torch.einsum("ehd,ehk->hdk", gv, psi)[None]
+        elif W_num == E:
+            gW = gv[..., :, None] * psi[..., None, :]
+        else:
+            gW = torch.zeros((N,) + tuple(W4.shape[1:]), dtype=torch.float32, device=dev)
+            gW.index_add_(0, edges[0], gv[..., :, None] * psi[..., None, :])
+        if W.dim() == 3:
+            gW = gW[0]
     return ga, gW
 
 
@@ -212,6 +232,31 @@ def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
                   c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(out), _ptr(logit),
                   _ptr(lse), _ptr(psi_row), _stream(dev))
     return out, logit, lse, psi_row
+
+
+def infinite_attn_bwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W,
+                      cutoff_radius, lattice_range, minimum_range, logit, lse, out, gout, pos=None):
+    """Backward of infinite_attn_fwd: (gq, gk, gv, ga).  gq is with respect to the pre-scaled q."""
+    dev = q.device
+    q, k, v, a, tvecs, logit, lse, out, gout = (_want(t, torch.float32, n, dev) for t, n in (
+        (q, "q"), (k, "k"), (v, "v"), (a, "a"), (tvecs, "tvecs"), (logit, "logit"), (lse, "lse"), (out, "out"),
+        (gout, "gout")))
+    pos_ij, pos = _want(pos_ij, torch.float32, "pos_ij", dev), _want(pos, torch.float32, "pos", dev)
+    rvlen, W = _want(rvlen, torch.float32, "rvlen", dev), _want(W, torch.float32, "W", dev)
+    batch, edges, row_start = (_want(t, torch.int64, n, dev) for t, n in
+                               ((batch, "batch"), (edges, "edges"), (row_start, "row_start")))
+    N, H, D = q.shape
+    E, B = edges.shape[1], tvecs.shape[0]
+    gq, gk, gv = (torch.empty_like(q) for _ in range(3))
+    ga = torch.empty((N, H), dtype=torch.float32, device=dev)
+    glogit = torch.empty((E, H), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_infinite_attn_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(pos), _ptr(pos_ij), _ptr(tvecs),
+                  _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),
+                  c_int64(D), c_int64(E), c_int64(K), c_int64(max_atoms), c_double(dist_max), c_double(wscale), _ptr(W),
+                  c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(logit), _ptr(lse),
+                  _ptr(out), _ptr(gout), _ptr(gq), _ptr(gk), _ptr(gv), _ptr(ga), _ptr(glogit), _stream(dev))
+    return gq, gk, gv, ga
 
 
 def segment_mean(x, start):

@@ -104,18 +104,19 @@ int cf_lattice_sum_fwd(const float *a, int a_per_edge, const float *pos_ij, cons
  * Real-space lattice sum, backward.  Replaces real_enc_bwd / real_enc_proj_bwd
  * (models/kernels/real_enc_bwd.cu:4-157, real_enc_proj_bwd.cu:4-221) as launched by the wrappers' backward
  * (models/cuda_funcs/real_space_enc.py:141-247, real_space_enc_proj.py:100-178).  phi and psi are recomputed.
- *   in : z (E,H) from the forward, gz (E,H), gv = d/d psi (E,H,K) when W == NULL else d/d (W psi) (E,H,Dv)
- *   out: ga (N,H); gW (W_num,H,Dv,K) when W != NULL and gW != NULL.  For W_num == 1 the sum over all edges is
- *        written (the reference writes one block per atom and lets autograd add them up).
- * row_start (N+1) is the CSR of edges[0].  gW_scratch: W_num == 1 needs cf_lattice_sum_bwd_scratch_bytes() bytes of
- * device scratch (partial sums per thread block, reduced in a fixed order so that results are run-to-run identical).
+ *   in : z (E,H) from the forward, gz (E,H), gpsi (E,H,K) = gradient arriving at psi (NULL when K == 0); with a
+ *        projection W the caller forms gpsi = W^T gv first, as the reference's real_space_enc.py:196-199 does
+ *   out: ga (N,H)
+ *        psi_out (E,H,K), optional: psi recomputed, from which the caller gets the gradient of W as
+ *        sum_e gv_e (x) psi_e (one GEMM; the reference accumulates the same sum per atom inside its kernel)
+ * row_start (N+1) is the CSR of edges[0].  edge_scratch: (E,H) floats of device scratch holding the per-edge
+ * contributions, which a second kernel adds up per atom in edge order (run-to-run identical results).
  * ---------------------------------------------------------------------------------------------------------- */
-int64_t cf_lattice_sum_bwd_scratch_bytes(int64_t N, int64_t H, int64_t Dv, int64_t K);
 int cf_lattice_sum_bwd(const float *a, const float *pos_ij, const float *tvecs, const int64_t *batch,
                        const int64_t *edges, const int64_t *row_start, const float *z, const float *gz,
-                       const float *gv, int64_t N, int64_t H, int64_t E, int64_t K, double dist_max, double wscale,
-                       const float *W, int64_t W_num, int64_t Dv, const float *rvlen, double cutoff_radius,
-                       int lattice_range, int minimum_range, float *ga, float *gW, void *gW_scratch, void *stream);
+                       const float *gpsi, int64_t N, int64_t H, int64_t E, int64_t K, double dist_max, double wscale,
+                       const float *rvlen, double cutoff_radius, int lattice_range, int minimum_range, float *ga,
+                       float *psi_out, float *edge_scratch, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Edge-indexed softmax attention with given position terms.  Replaces fused_dpa_fwd[_v3], fused_dpa_bwd[_v3],
@@ -166,7 +167,8 @@ int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const f
 
 /* Backward of cf_infinite_attn_fwd; phi and psi are recomputed from the geometry.
  *   in : everything the forward read, plus logit, lse, out and gout (N,H,D)
- *   out: gq (w.r.t. the pre-scaled q), gk, gv (N,H,D); ga (N,H); glogit (E,H) scratch/diagnostic
+ *   out: gq (w.r.t. the pre-scaled q), gk, gv (N,H,D); ga (N,H); glogit (E,H) = gradient of the logits (also the
+ *        hand-over between the two kernels of this call); crystals of up to 1024 atoms
  * The gradient of W is sum_i gout_i (x) psi_row_i, a plain GEMM the caller does from psi_row. */
 int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
                          const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
