@@ -1,0 +1,441 @@
+#!/usr/bin/env python
+"""Benchmark of the infinitely-connected-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload cfg0|cfg2|cfg4]
+
+One "step" is one forward pass of the Crystalformer model (4 layers, model_dim 128, 8 heads, 64 radial-basis bins for
+cfg0/cfg4; 7 layers without the value encoding for cfg2) over one batch of seeded synthetic crystals.  Per GPU the batch
+has the configuration's crystal count; with N GPUs a batch of N times that many crystals is drawn, split over the ranks
+by the reference's greedy rule on n^2 (crystalformer_b200.sharding.lpt_assign) and only the per-crystal outputs are
+all-gathered (weak scaling).  Rank 0 prints ONE JSON line:
+
+  value            crystals / s over all ranks, inputs already resident in HBM, device-timed (CUDA events), max over ranks
+  e2e              the same through the public model call with HOST inputs: pinned host -> device copies of the step's
+                   inputs and the device -> host read of the outputs are inside the timed region
+  roofline         the dominant operator (lattice_phi_kernel + infinite_attn_rows_kernel of every layer), timed live
+                   with CUDA events on the launch stream during the timed steps; work = (edge, translation) terms of the
+                   batch x FP32-pipe instructions per term; peak = FP32 FMA issue rate measured by cf_pipe_probe
+  lattice_sum_microbench   the 2,000,000 (i,j,head) lattice-sum kernel benchmark (phi + 64-bin psi, forward), same units
+  cpu_baseline     (N = 1) the CPU oracle's model forward on a bounded sample of the same batch, on the host cores
+
+--impl reference times the reference's CPU implementation of the path (its own kernel sources compiled for the CPU
+when oracle/_ref exists, else the C restatement) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+WORKLOADS = {
+    "cfg0": dict(config="cfg0", layers=4, K=64, crystals=128),
+    "cfg2": dict(config="cfg2", layers=7, K=0, crystals=256),
+    "cfg4": dict(config="cfg4", layers=4, K=64, crystals=64),
+}
+FIXED_BOX_TERMS = 125  # (2 R + 1)^3 with the default lattice_range R = 2
+
+
+def fp32_instr_per_term(K, H=8):
+    """FP32-pipe instructions per (edge, translation) term with the basis shared by the heads: geometry and minimum
+    pass 25, two per bin, (2 + K) per head."""
+    return 25 + 2 * K + H * (2 + K)
+
+
+def sfu_per_term(K, H=8):
+    return (1 if K > 0 else 0) + K + H
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False).name
+        self.proc = None
+        self.gpu = gpu_index
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return None
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_model(layers, K, seed=0):
+    import torch
+    from crystalformer_b200.model import Latticeformer, default_params
+    torch.manual_seed(seed)
+    params = default_params(num_layers=layers, value_pe_dist_real=K)
+    return Latticeformer(params), params
+
+
+def fix_gauss_scale(model, data):
+    """One training-mode forward stores the batch statistics of alpha in gauss_scale (as the reference's first training
+    step does, models/indexed_lattice_multi_head_attention_cuda.py:669-673); afterwards the model is shard-invariant."""
+    import torch
+    model.train()
+    with torch.no_grad():
+        model(data)
+    model.eval()
+
+
+def to_device_batch(cb, device, pinned=False):
+    import torch
+    import types
+    host = dict(x=torch.from_numpy(cb.x), pos=torch.from_numpy(cb.pos), trans_vec=torch.from_numpy(cb.trans_vec),
+                sizes=torch.from_numpy(cb.sizes))
+    if pinned:
+        return types.SimpleNamespace(**{k: v.pin_memory() for k, v in host.items()})
+    return types.SimpleNamespace(**{k: v.to(device) for k, v in host.items()})
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    import types
+    from crystalformer_b200 import ops
+    from crystalformer_b200.encoder import BatchGeometry
+    from crystalformer_b200.sharding import gather_outputs, lpt_assign, shard_balance
+    from crystalformer_b200.synthetic import make_config
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+
+    wl = WORKLOADS[args.workload]
+    global_batch = make_config(wl["config"], num_crystals=wl["crystals"] * world)
+    shards = lpt_assign(global_batch.sizes, world)
+    mine = global_batch.select(shards[rank])
+    n_atoms, n_edges, max_atoms = mine.num_atoms, mine.num_edges, int(mine.sizes.max())
+
+    model, params = make_model(wl["layers"], wl["K"])
+    model = model.to(device)
+    # gauss_scale from the statistics of rank 0's shard, shared by every rank (broadcast once, outside the timed region)
+    resident = to_device_batch(mine, device)
+    fix_gauss_scale(model, resident)
+    if world > 1:
+        for layer in model.encoder.layers:
+            dist.broadcast(layer.self_attn.gauss_scale.data, src=0)
+
+    # instrument the fused operator: CUDA events around every call, on the launching stream
+    op_events = []
+    raw_fwd = ops.infinite_attn_fwd
+    record = {"on": False}
+
+    def timed_fwd(*a, **kw):
+        if not record["on"]:
+            return raw_fwd(*a, **kw)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = raw_fwd(*a, **kw)
+        e.record()
+        op_events.append((s, e))
+        return r
+
+    ops.infinite_attn_fwd = timed_fwd
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)  # > 126 MB L2
+
+    def step_resident():
+        g = BatchGeometry(resident.pos, resident.trans_vec, resident.sizes, n_atoms, n_edges, max_atoms)
+        with torch.no_grad():
+            y = model(resident, geometry=g)
+        return gather_outputs(y, shards) if world > 1 else y
+
+    pinned = to_device_batch(mine, device, pinned=True)
+    h2d_bytes = sum(t.numel() * t.element_size() for t in vars(pinned).values())
+    out_host = torch.empty((global_batch.num_crystals if world > 1 else mine.num_crystals, 1)).pin_memory()
+
+    def step_e2e():
+        d = types.SimpleNamespace(**{k: v.to(device, non_blocking=True) for k, v in vars(pinned).items()})
+        g = BatchGeometry(d.pos, d.trans_vec, d.sizes, n_atoms, n_edges, max_atoms)
+        with torch.no_grad():
+            y = model(d, geometry=g)
+        y = gather_outputs(y, shards) if world > 1 else y
+        out_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller has its result on the host
+        return out_host
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step, steps, warmup, instrument=False):
+        for _ in range(warmup):
+            step()
+        barrier()
+        total = 0.0
+        record["on"] = instrument
+        for _ in range(steps):
+            flush.zero_()  # L2 flush between timed iterations, outside the event pair
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            step()
+            e.record()
+            e.synchronize()
+            total += s.elapsed_time(e)
+        record["on"] = False
+        barrier()
+        t = torch.tensor([total], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())  # ms for all steps, max over ranks
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms_total = timed(step_resident, args.steps, args.warmup, instrument=True)
+    clocks = sampler.stop() if sampler else None
+    op_ms = sum(s.elapsed_time(e) for s, e in op_events)
+    op_calls = len(op_events)
+    ms_e2e = timed(step_e2e, args.steps, args.warmup)
+
+    total_crystals = global_batch.num_crystals
+    value = total_crystals * args.steps / (ms_total * 1e-3)
+    e2e_value = total_crystals * args.steps / (ms_e2e * 1e-3)
+
+    result = None
+    if rank == 0:
+        # ---- roofline of the dominant operator
+        K = wl["K"]
+        sink = torch.zeros(4, device=device)
+        peaks = {}
+        for kind, name in ((0, "fp32"), (1, "sfu")):
+            blocks, threads, iters = ops_sm_count(device) * 8, 256, 1 << 13
+            best = 1e30
+            for _ in range(5):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(); ops.pipe_probe(kind, blocks, threads, iters, sink); e.record(); e.synchronize()
+                best = min(best, s.elapsed_time(e))
+            peaks[name] = blocks * threads * iters * 8 / (best * 1e-3)  # lane-instructions / s
+        terms_per_call = n_edges * FIXED_BOX_TERMS  # lower bound: the adaptive rule never shrinks the minimum box
+        t_call = op_ms * 1e-3 / max(op_calls, 1)
+        achieved = terms_per_call * fp32_instr_per_term(K) / t_call
+        achieved_sfu = terms_per_call * sfu_per_term(K) / t_call
+        roofline = {
+            "kernel": "lattice_phi_kernel + infinite_attn_rows_kernel (one fused-attention call)",
+            "bound": "fp32_simt", "achieved": achieved / 1e9, "peak": peaks["fp32"] / 1e9, "unit": "G lane-instr/s",
+            "frac": achieved / peaks["fp32"], "peak_source": "cf_pipe_probe FFMA, measured in this run",
+            "sfu": {"achieved": achieved_sfu / 1e9, "peak": peaks["sfu"] / 1e9, "frac": achieved_sfu / peaks["sfu"]},
+            "terms_per_launch": terms_per_call, "launches": op_calls, "avg_launch_us": t_call * 1e6,
+            "share_of_step": op_ms / ms_total,
+            "traffic": None,
+            "note": "work counted for EVERY (edge, translation) term; terms whose weights fall below 2^-40 are skipped "
+                    "by the kernel, so frac may exceed the executed-instruction utilisation",
+        }
+        micro = lattice_microbench(ops, device, peaks)
+        cpu = cpu_baseline(model, params, mine) if (world == 1 and not args.no_cpu_baseline) else None
+        per_step_launches = 4 + 2 * wl["layers"] + 1
+        result = {
+            "metric": "crystals/sec (4-layer, fwd)" if wl["layers"] == 4 else f"crystals/sec ({wl['layers']}-layer, fwd)",
+            "value": value, "unit": "crystals/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {wl['layers']}-layer Crystalformer forward, K={K}, "
+                                   f"{wl['crystals']} crystals per GPU per step", "global_batch": total_crystals,
+                       "atoms_this_rank": n_atoms, "edges_this_rank": n_edges, "cutoff": "adaptive -3.5 sigma, minimum box R=2",
+                       "l2": "flushed between timed steps (256 MB write outside the event pair)",
+                       "parallelism": f"dp{world} (LPT on n^2, all-gather of outputs)",
+                       "shard_balance": shard_balance(global_batch.sizes, shards)},
+            "e2e": {"value": e2e_value, "unit": "crystals/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": out_host.numel() * 4},
+            "gpu_launches": per_step_launches * args.steps,
+            "roofline": roofline, "lattice_sum_microbench": micro, "cpu_baseline": cpu, "clocks": clocks,
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return result
+
+
+def ops_sm_count(device):
+    import torch
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def lattice_microbench(ops, device, peaks):
+    """2,000,000 (i,j,head) items = 250,000 pairs x 8 heads from 4096 crystals, one width per item, phi + 64-bin psi."""
+    import torch
+    from crystalformer_b200.synthetic import microbench_edges
+    cb, edges, pos_ij, a = microbench_edges()
+    d = lambda x: torch.as_tensor(np.ascontiguousarray(x)).to(device)
+    sizes = d(cb.sizes)
+    atom_start, edge_start = ops.crystal_offsets(sizes)
+    geo = ops.batch_prepare(d(cb.pos), d(cb.trans_vec), sizes, atom_start, edge_start, cb.num_atoms, 0, want_edges=False,
+                            want_pos_ij=False)
+    A, P, T, Bt, Ed = d(a), d(pos_ij), d(cb.trans_vec), d(cb.batch), d(edges)
+    box = ops.lattice_box(A, Bt, Ed, geo["rvlen"], -3.5, 2, 2, a_per_edge=True).max(dim=1).values.long()
+    terms = int(((2 * box[:, 0] + 1) * (2 * box[:, 1] + 1) * (2 * box[:, 2] + 1)).sum())
+    E = edges.shape[1]
+    z = torch.empty((E, 8), device=device)
+    v = torch.empty((E, 8, 64), device=device)
+    run = lambda: ops.lattice_sum_fwd(A, P, T, Bt, Ed, 64, 14.0, 1.0, rvlen=geo["rvlen"], cutoff_radius=-3.5,
+                                      lattice_range=2, minimum_range=2, a_per_edge=True, z=z, v=v)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(10):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); run(); e.record(); e.synchronize()
+        times.append(s.elapsed_time(e) * 1e-3)
+    t = float(np.median(times))
+    work = terms * fp32_instr_per_term(64)
+    out_bytes = E * 8 * 65 * 4
+    return {"items": E * 8, "edges": E, "terms": terms, "ms": t * 1e3, "items_per_s": E * 8 / t,
+            "fp32_frac": work / t / peaks["fp32"], "sfu_frac": terms * sfu_per_term(64) / t / peaks["sfu"],
+            "hbm_gbs": out_bytes / t / 1e9, "kernels": "lattice_phi_kernel + lattice_psi_kernel",
+            "l2": "output 520 MB per launch exceeds L2"}
+
+
+def cpu_baseline(model, params, cb, seconds_budget=20.0):
+    """The CPU oracle's model forward on the first crystals of the batch (about 10-30 s of CPU work)."""
+    from oracle.model_cpu import forward_cpu
+    import oracle as _oracle
+    state = {k: v.detach().cpu() for k, v in model.state_dict().items()}
+    use_ref = _oracle.have_ref() and params.value_pe_dist_real in (0, 64)
+    sample = min(8, cb.num_crystals)
+    t0 = time.time(); forward_cpu(state, params, cb.select(range(sample)), use_ref=use_ref); dt = time.time() - t0
+    rate = sample / dt
+    sample2 = int(min(cb.num_crystals, max(sample, rate * seconds_budget)))
+    if sample2 > sample:
+        t0 = time.time(); forward_cpu(state, params, cb.select(range(sample2)), use_ref=use_ref); dt = time.time() - t0
+        sample = sample2
+    return {"value": sample / dt, "unit": "crystals/s", "cores": os.cpu_count(),
+            "kind": "reference" if use_ref else "port",
+            "sample": f"first {sample} crystals of the batch, one forward pass, {dt:.1f} s, OpenMP over all host cores"}
+
+
+def run_reference(args):
+    """The reference arm: the reference's CPU implementation of the path on the host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    import torch
+    import oracle as _oracle
+    from oracle.model_cpu import forward_cpu
+    from crystalformer_b200.synthetic import make_config
+    torch.set_num_threads(os.cpu_count())
+    wl = WORKLOADS[args.workload]
+    world = args.gpus
+    cb = make_config(wl["config"], num_crystals=wl["crystals"] * world)
+    # a CPU-only model with the same architecture and random init; no kernels of this repository are involved
+    params, state = reference_state(wl["layers"], wl["K"])
+    use_ref = _oracle.have_ref()
+    sample = cb.select(range(min(cb.num_crystals, args.reference_sample)))
+    for _ in range(min(args.warmup, 1)):
+        forward_cpu(state, params, sample.select(range(min(2, sample.num_crystals))), use_ref=use_ref)
+    t0 = time.time()
+    for _ in range(args.steps):
+        forward_cpu(state, params, sample, use_ref=use_ref)
+    dt = time.time() - t0
+    value = sample.num_crystals * args.steps / dt
+    return {
+        "impl": "reference", "metric": "crystals/sec (4-layer, fwd)" if wl["layers"] == 4 else f"crystals/sec ({wl['layers']}-layer, fwd)",
+        "value": value, "unit": "crystals/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {wl['layers']}-layer Crystalformer forward, K={wl['K']}, "
+                               f"{wl['crystals']} crystals per GPU per step"},
+        "cpu_baseline": {"value": value, "unit": "crystals/s", "cores": os.cpu_count(),
+                         "kind": "reference" if use_ref else "port",
+                         "sample": f"first {sample.num_crystals} crystals of the batch per step"},
+        "e2e": {"value": value, "unit": "crystals/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def reference_state(layers, K, seed=0):
+    """Random-init weights with the model's shapes, drawn on the CPU without constructing any CUDA-backed module."""
+    import torch
+    import types
+    from crystalformer_b200.params import DEFAULT_MODEL_PARAMS
+    p = dict(DEFAULT_MODEL_PARAMS); p.update(num_layers=layers, value_pe_dist_real=K)
+    params = types.SimpleNamespace(**p)
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s, std=0.05: torch.randn(*s, generator=g) * std
+    st = {"input_embeddings.weight": r(128, 98)}
+    for l in range(layers):
+        pre = f"encoder.layers.{l}.self_attn."
+        for n in "qkv":
+            st[pre + f"{n}_proj_weight"] = r(128, 128, std=0.1)
+        st[pre + "in_proj_bias"] = torch.zeros(384)
+        st[pre + "lattice_pos_weights"] = r(128, std=0.25)
+        st[pre + "gauss_scale"] = torch.tensor([20.0, 0.0])
+        if K > 0:
+            st[pre + "pe_dist_proj"] = r(1, 8, 16, K, std=0.1)
+        st[pre + "out_proj.weight"] = r(128, 128, std=0.1)
+        st[pre + "out_proj.bias"] = torch.zeros(128)
+        st[f"encoder.layers.{l}.linear1.weight"] = r(512, 128); st[f"encoder.layers.{l}.linear1.bias"] = torch.zeros(512)
+        st[f"encoder.layers.{l}.linear2.weight"] = r(128, 512); st[f"encoder.layers.{l}.linear2.bias"] = torch.zeros(128)
+    st["mlp.0.weight"] = r(128, 128); st["mlp.0.bias"] = torch.zeros(128)
+    st["mlp.3.weight"] = r(1, 128); st["mlp.3.bias"] = torch.zeros(1)
+    return params, st
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="cfg0", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reference-sample", type=int, default=24, help="crystals per step of the reference arm")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = min(args.steps, 5)
+        result = run_reference(args)
+    else:
+        args.warmup = max(args.warmup, 3)
+        result = run_b200(args)
+    if result is not None:
+        print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()
