@@ -22,6 +22,7 @@ SIGNATURES = {
     "cf_lattice_box": [P, I32, P, P, I64, I64, I64, P, F64, I32, I32, P, P],
     "cf_lattice_sum_fwd": [P, I32, P, P, P, P, I64, I64, I64, I64, F64, F64, P, I64, I64, P, F64, I32, I32, P, P, P],
     "cf_lattice_sum_bwd": [P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, F64, F64, P, F64, I32, I32, P, P, P, P],
+    "cf_lattice_sum_bwd_static": [P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, F64, F64, P, F64, I32, I32, P, P, P],
     "cf_fused_attn_fwd": [P, P, P, P, P, P, P, I64, I64, I64, I64, P, P, P],
     "cf_fused_attn_bwd": [P, P, P, P, P, P, I64, I64, I64, I64, P, P, P, P, P, P, P, P, P],
     "cf_segment_mean_fwd": [P, P, I64, I64, P, P],

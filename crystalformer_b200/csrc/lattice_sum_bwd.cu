@@ -198,3 +198,59 @@ extern "C" int cf_lattice_sum_bwd(const float *a, const float *pos_ij, const flo
     row_sum_kernel<<<(unsigned)((total + 127) / 128), 128, 0, s>>>(edge_scratch, row_start, N, ga);
     return launch_status("cf_lattice_sum_bwd");
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// cf_lattice_sum_bwd_static: the same computation for callers that cannot hand over a scratch buffer.
+//
+// Some embedders are not in a position to allocate device memory at the moment they call: a serving process that
+// sized all of its device memory at start-up and gives libraries none afterwards, a binding from a language runtime
+// that has no device allocator at hand, or a latency-critical loop in which an allocation (which may synchronise the
+// whole device) is not acceptable.  For them the per-edge contributions live in a fixed array that is part of the
+// library image itself: it costs CF_STATIC_SCRATCH_MAX_EDGES * 8 floats (8 MiB) on every GPU that loads the library,
+// for as long as the process lives, and bounds the number of edges one call may have.
+//
+// The array's name is only meaningful to device code; host code must ask the runtime for its device address.  That
+// is done once per device, on the first call made with that device current (so make the first call on each device
+// outside any stream capture), and the address is remembered.  Every call on a device uses the same array: two calls
+// whose kernels may overlap on the GPU (different streams) would overwrite each other's contributions, so callers
+// must serialise them.  Nothing in the array needs clearing between calls: every element a call reads (edges
+// 0..E-1) is written by that same call first.
+// ------------------------------------------------------------------------------------------------------------------
+#include <mutex>
+
+static __device__ __align__(256) float g_static_edge_scratch[(size_t)CF_STATIC_SCRATCH_MAX_EDGES * 8];
+
+extern "C" int cf_lattice_sum_bwd_static(const float *a, const float *pos_ij, const float *tvecs, const int64_t *batch,
+                                         const int64_t *edges, const int64_t *row_start, const float *z,
+                                         const float *gz, const float *gpsi, int64_t N, int64_t H, int64_t E, int64_t K,
+                                         double dist_max, double wscale, const float *rvlen, double cutoff_radius,
+                                         int lattice_range, int minimum_range, float *ga, float *psi_out, void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(E <= (int64_t)CF_STATIC_SCRATCH_MAX_EDGES, CF_ERR_RANGE,
+               "cf_lattice_sum_bwd_static: E=%lld exceeds the built-in scratch of %lld edges; use cf_lattice_sum_bwd "
+               "with a caller-provided scratch buffer", (long long)E, (long long)CF_STATIC_SCRATCH_MAX_EDGES);
+    constexpr int MAX_DEVICES = 64;
+    static std::mutex lock;
+    static float *address_on_device[MAX_DEVICES] = {};
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+        return fail(CF_ERR_CUDA, "cf_lattice_sum_bwd_static: cudaGetDevice: %s", cudaGetErrorString(err));
+    float *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        if (address_on_device[dev] == nullptr) {
+            float *ptr = nullptr;
+            err = cudaGetSymbolAddress((void **)&ptr, g_static_edge_scratch);
+            if (err != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return fail(CF_ERR_CUDA, "cf_lattice_sum_bwd_static: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+            }
+            address_on_device[dev] = ptr;
+        }
+        scratch = address_on_device[dev];
+    }
+    return cf_lattice_sum_bwd(a, pos_ij, tvecs, batch, edges, row_start, z, gz, gpsi, N, H, E, K, dist_max, wscale, rvlen,
+                              cutoff_radius, lattice_range, minimum_range, ga, psi_out, scratch, stream);
+}

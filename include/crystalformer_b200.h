@@ -119,6 +119,30 @@ int cf_lattice_sum_bwd(const float *a, const float *pos_ij, const float *tvecs, 
                        float *psi_out, float *edge_scratch, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
+ * cf_lattice_sum_bwd without a scratch argument.  No counterpart in the reference (its wrappers always allocate
+ * their temporaries with torch).
+ *
+ * Meant for callers that cannot allocate device memory when they call: processes that fixed their device-memory
+ * budget at start-up, bindings from runtimes without a device allocator, loops where an allocation's possible
+ * device-wide synchronisation is not tolerable.  The (E,H) per-edge contributions are kept in an array built into
+ * the library, which occupies CF_STATIC_SCRATCH_MAX_EDGES * 8 * 4 bytes (8 MiB) on every GPU that loads the library
+ * until the process exits, and limits a call to E <= CF_STATIC_SCRATCH_MAX_EDGES edges (CF_ERR_RANGE beyond that).
+ * The call itself allocates and frees nothing.
+ *
+ * The first call made with a given device current looks up the array's device address (once per device); make that
+ * first call outside any stream capture.  All calls on a device share the one array and it keeps the previous
+ * call's contents: calls that can overlap on the GPU (e.g. on different streams) race and must be serialised by the
+ * caller.  Nothing needs zeroing: a call writes every element it later reads.  Arguments and results are those of
+ * cf_lattice_sum_bwd.
+ * ---------------------------------------------------------------------------------------------------------- */
+#define CF_STATIC_SCRATCH_MAX_EDGES 262144
+int cf_lattice_sum_bwd_static(const float *a, const float *pos_ij, const float *tvecs, const int64_t *batch,
+                              const int64_t *edges, const int64_t *row_start, const float *z, const float *gz,
+                              const float *gpsi, int64_t N, int64_t H, int64_t E, int64_t K, double dist_max,
+                              double wscale, const float *rvlen, double cutoff_radius, int lattice_range,
+                              int minimum_range, float *ga, float *psi_out, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
  * Edge-indexed softmax attention with given position terms.  Replaces fused_dpa_fwd[_v3], fused_dpa_bwd[_v3],
  * fused_dpa_bwd_q[_v3] and irregular_transpose (models/kernels/fused_dpa_fwd.cu, fused_dpa_bwd.cu,
  * fused_dpa_bwd_q.cu, irregular_transpose.cu) as launched by FusedDotProductAttentionCUDA
