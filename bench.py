@@ -57,7 +57,7 @@ def sfu_per_term(K, H=8):
 class ClockSampler:
     """nvidia-smi sampling of SM clocks and throttle reasons while the timed region runs."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
@@ -67,35 +67,46 @@ class ClockSampler:
         self.gpu = gpu_index
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples taken between the two wall-clock times (all samples if none fall inside)."""
+        import datetime
         if self.proc is None:
             return None
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []
         for line in open(self.path):
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                stamp = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((stamp, float(f[1]), float(f[2]), float(f[3]), f[5:9]))
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+        os.unlink(self.path)
+        if not rows:
+            return None
+        inside = [r for r in rows if t_begin is not None and t_begin <= r[0] <= t_end]
+        used = inside if inside else rows
+        reasons = set()
+        for r in used:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        os.unlink(self.path)
-        if not sm:
-            return None
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "samples": len(sm), "reasons": sorted(reasons)}
+        return {"sm_mhz": float(np.median([r[1] for r in used])), "sm_max_mhz": float(max(r[2] for r in used)),
+                "power_w_max": float(max(r[3] for r in used)), "samples": len(used),
+                "window": "timed region" if inside else "whole run (timed region shorter than the sampling period)",
+                "reasons": sorted(reasons)}
 
 
 def make_model(layers, K, seed=0):
@@ -229,8 +240,12 @@ def run_b200(args):
         return float(t.item())  # ms for all steps, max over ranks
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        time.sleep(0.3)  # let nvidia-smi start sampling
+    t_begin = time.time()
     ms_total = timed(step_resident, args.steps, args.warmup, instrument=True)
-    clocks = sampler.stop() if sampler else None
+    t_end = time.time()
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
     op_ms = sum(s.elapsed_time(e) for s, e in op_events)
     op_calls = len(op_events)
     ms_e2e = timed(step_e2e, args.steps, args.warmup)
@@ -298,11 +313,46 @@ def ops_sm_count(device):
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
-def lattice_microbench(ops, device, peaks):
+def run_kernel_case(args):
+    """--only microbench : the lattice-sum kernels on --pairs pairs (3 warm-up + 10 timed launches).
+    --only attention  : the fused attention forward on the workload's crystals (3 warm-up + 10 timed calls)."""
+    import torch
+    from crystalformer_b200 import ops
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    if args.only == "microbench":
+        return lattice_microbench(ops, device, None, pairs=args.pairs)
+    from crystalformer_b200.encoder import BatchGeometry
+    from crystalformer_b200.synthetic import make_config
+    wl = WORKLOADS[args.workload]
+    cb = make_config(wl["config"], num_crystals=args.crystals or wl["crystals"])
+    d = lambda x: torch.as_tensor(np.ascontiguousarray(x)).to(device)
+    g = BatchGeometry(d(cb.pos), d(cb.trans_vec), d(cb.sizes), cb.num_atoms, cb.num_edges, int(cb.sizes.max()))
+    gen = torch.Generator(device=device).manual_seed(0)
+    N, K = cb.num_atoms, wl["K"]
+    q = torch.randn((N, 8, 16), device=device, generator=gen) * 0.3
+    k, v = (torch.randn((N, 8, 16), device=device, generator=gen) for _ in range(2))
+    a = -0.5 / (1.4 * (1 + 0.1 * torch.randn((N, 8), device=device, generator=gen)).clamp(0.75, 1.4)) ** 2
+    W = torch.randn((8, 16, 64), device=device, generator=gen) * 0.1 if K else None
+    run = lambda: ops.infinite_attn_fwd(q, k, v, a, g.pos_ij, d(cb.trans_vec), g.rvlen, g.batch, g.edges, g.row_start,
+                                        g.max_atoms, K, 14.0, 1.0, W, -3.5, 2, 2)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(10):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); run(); e.record(); e.synchronize()
+        times.append(s.elapsed_time(e))
+    return {"case": "attention", "workload": args.workload, "crystals": cb.num_crystals, "atoms": N, "edges": cb.num_edges,
+            "K": K, "ms_median": float(np.median(times)), "ms_min": float(min(times))}
+
+
+def lattice_microbench(ops, device, peaks, pairs=250000):
     """2,000,000 (i,j,head) items = 250,000 pairs x 8 heads from 4096 crystals, one width per item, phi + 64-bin psi."""
     import torch
     from crystalformer_b200.synthetic import microbench_edges
-    cb, edges, pos_ij, a = microbench_edges()
+    cb, edges, pos_ij, a = microbench_edges(num_pairs=pairs)
     d = lambda x: torch.as_tensor(np.ascontiguousarray(x)).to(device)
     sizes = d(cb.sizes)
     atom_start, edge_start = ops.crystal_offsets(sizes)
@@ -327,6 +377,8 @@ def lattice_microbench(ops, device, peaks):
     t = float(np.median(times))
     work = terms * fp32_instr_per_term(64)
     out_bytes = E * 8 * 65 * 4
+    if peaks is None:
+        return {"case": "microbench", "items": E * 8, "edges": E, "terms": terms, "ms": t * 1e3}
     return {"items": E * 8, "edges": E, "terms": terms, "ms": t * 1e3, "items_per_s": E * 8 / t,
             "fp32_frac": work / t / peaks["fp32"], "sfu_frac": terms * sfu_per_term(64) / t / peaks["sfu"],
             "hbm_gbs": out_bytes / t / 1e9, "kernels": "lattice_phi_kernel + lattice_psi_kernel",
@@ -426,7 +478,14 @@ def main():
     ap.add_argument("--workload", default="cfg0", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--reference-sample", type=int, default=24, help="crystals per step of the reference arm")
+    ap.add_argument("--only", default=None, choices=["microbench", "attention"],
+                    help="run one kernel case a few times and exit (small, fixed work: meant for profiler captures)")
+    ap.add_argument("--pairs", type=int, default=250000, help="(i,j) pairs of the lattice-sum microbenchmark")
+    ap.add_argument("--crystals", type=int, default=None, help="crystals of the --only attention case")
     args = ap.parse_args()
+    if args.only:
+        print(json.dumps(run_kernel_case(args)))
+        return
     if args.impl == "reference":
         args.steps = min(args.steps, 5)
         result = run_reference(args)
