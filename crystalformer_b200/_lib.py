@@ -31,6 +31,7 @@ SIGNATURES = {
     "cf_infinite_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                              I32, P, P, P, P, P, P, P, P, P, P],
     "cf_pipe_probe": [I32, I32, I32, I64, P, P],
+    "cf_encoder_forward": [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, F64, F64, I32, I32, P, P, P],
 }
 
 
@@ -56,6 +57,8 @@ def load() -> ctypes.CDLL:
         lib.cf_set_weight_floor_log2.argtypes = [c_double]
         lib.cf_set_weight_floor_log2.restype = None
         lib.cf_get_weight_floor_log2.restype = c_double
+        lib.cf_encoder_workspace_floats.argtypes = [I64, I64, I64]
+        lib.cf_encoder_workspace_floats.restype = c_int64
         for name, argtypes in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes

@@ -1,0 +1,209 @@
+// Inference forward of the whole encoder stack in ONE host call.
+//
+// The reference runs an encoder layer as ~30 framework operators (in-projection, the Gaussian-width pipeline of
+// models/indexed_lattice_multi_head_attention_cuda.py:640-722, q scaling, attention, out-projection, residual,
+// feed-forward, residual; models/indexed_latticeformer_encoder.py:848-890 with LayerNorm = Identity under T-Fixup).
+// At the sizes of a crystal batch each of them is launch-bound, and the host cannot issue them as fast as the GPU
+// retires them.  Here a layer is eight launches issued back to back from C++:
+//
+//   SGEMM   qkv = x Wqkv^T                                   (cuBLAS, fp32)
+//   qkv_post    + bias, alpha = q.w -> normalise -> elu -> a, q / sqrt(D); also x += out_proj.bias (used later)
+//   lattice_phi_kernel, infinite_attn_rows_kernel           (cf_infinite_attn_fwd)
+//   SGEMM   x += attn Wo^T                                   (beta = 1: the residual is the accumulator)
+//   SGEMM   h = x W1^T
+//   ffn_post    h = relu(h + b1); x += b2
+//   SGEMM   x += h W2^T
+//
+// cuBLAS is resolved at run time from the copy already loaded in the process (the caller passes its handle), so that
+// the handle and the functions come from the same library.  No training support: the autograd path stays in Python.
+#include <cublas_v2.h>
+#include <dlfcn.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace cf {
+namespace {
+
+using SgemmFn = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const float *,
+                                   const float *, int, const float *, int, const float *, float *, int);
+using SetStreamFn = cublasStatus_t (*)(cublasHandle_t, cudaStream_t);
+using GetStreamFn = cublasStatus_t (*)(cublasHandle_t, cudaStream_t *);
+using SetMathFn = cublasStatus_t (*)(cublasHandle_t, cublasMath_t);
+using GetMathFn = cublasStatus_t (*)(cublasHandle_t, cublasMath_t *);
+
+struct Blas {
+    SgemmFn sgemm = nullptr;
+    SetStreamFn set_stream = nullptr;
+    GetStreamFn get_stream = nullptr;
+    SetMathFn set_math = nullptr;
+    GetMathFn get_math = nullptr;
+    bool ok = false;
+};
+
+const Blas &blas()
+{
+    static Blas b;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_NOLOAD);
+        if (!lib) lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
+        if (!lib) lib = dlopen("libcublas.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!lib) return;
+        b.sgemm = (SgemmFn)dlsym(lib, "cublasSgemm_v2");
+        b.set_stream = (SetStreamFn)dlsym(lib, "cublasSetStream_v2");
+        b.get_stream = (GetStreamFn)dlsym(lib, "cublasGetStream_v2");
+        b.set_math = (SetMathFn)dlsym(lib, "cublasSetMathMode");
+        b.get_math = (GetMathFn)dlsym(lib, "cublasGetMathMode");
+        b.ok = b.sgemm && b.set_stream && b.get_stream && b.set_math && b.get_math;
+    });
+    return b;
+}
+
+// Y (rows x out) = [beta] Y + X (rows x in) W^T, W (out x in), all row-major.
+inline cublasStatus_t linear(const Blas &b, cublasHandle_t h, const float *X, const float *W, float *Y, int rows, int in,
+                             int out, float beta)
+{
+    const float one = 1.0f;
+    return b.sgemm(h, CUBLAS_OP_T, CUBLAS_OP_N, out, rows, in, &one, W, in, X, in, &beta, Y, out);
+}
+
+struct LayerScalars {
+    float gauss_scale, gauss_shift;  // alpha <- (alpha + shift) * scale
+    float a_factor;                  // -0.5 / scale_real^2
+    float elu_beta, lower_bound;     // positive_func 'elu=beta', gauss_lb_real
+};
+
+// One thread per (atom, head): bias, width parameter, scaled query, and the deferred out-projection bias.
+__global__ void qkv_post_kernel(const float *__restrict__ qkv, const float *__restrict__ bias,
+                                const float *__restrict__ w_pos, const float *__restrict__ out_bias, LayerScalars sc,
+                                long long N, float *__restrict__ q, float *__restrict__ k, float *__restrict__ v,
+                                float *__restrict__ a, float *__restrict__ x)
+{
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= N * HEADS) return;
+    const long long i = tid / HEADS;
+    const int h = (int)(tid % HEADS);
+    const int col = h * HEAD_DIM;
+    const float4 *src = reinterpret_cast<const float4 *>(qkv + i * 384 + col);
+    const float4 *bq = reinterpret_cast<const float4 *>(bias + col);
+    const float4 *wp = reinterpret_cast<const float4 *>(w_pos + col);
+    float4 *qd = reinterpret_cast<float4 *>(q + i * 128 + col);
+    float4 *kd = reinterpret_cast<float4 *>(k + i * 128 + col);
+    float4 *vd = reinterpret_cast<float4 *>(v + i * 128 + col);
+    float4 *xd = reinterpret_cast<float4 *>(x + i * 128 + col);
+    const float4 *ob = reinterpret_cast<const float4 *>(out_bias + col);
+    float alpha = 0.f;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        float4 qv = src[t];
+        const float4 b0 = __ldg(bq + t), w = __ldg(wp + t);
+        qv.x += b0.x; qv.y += b0.y; qv.z += b0.z; qv.w += b0.w;
+        alpha = fmaf(qv.x, w.x, alpha); alpha = fmaf(qv.y, w.y, alpha); alpha = fmaf(qv.z, w.z, alpha); alpha = fmaf(qv.w, w.w, alpha);
+        qd[t] = make_float4(qv.x * 0.25f, qv.y * 0.25f, qv.z * 0.25f, qv.w * 0.25f);  // 1/sqrt(16)
+        float4 kv = src[32 + t];
+        const float4 b1 = __ldg(bq + 32 + t);
+        kd[t] = make_float4(kv.x + b1.x, kv.y + b1.y, kv.z + b1.z, kv.w + b1.w);
+        float4 vv = src[64 + t];
+        const float4 b2 = __ldg(bq + 64 + t);
+        vd[t] = make_float4(vv.x + b2.x, vv.y + b2.y, vv.z + b2.z, vv.w + b2.w);
+        float4 xv = xd[t];
+        const float4 o = __ldg(ob + t);
+        xd[t] = make_float4(xv.x + o.x, xv.y + o.y, xv.z + o.z, xv.w + o.w);
+    }
+    // (1 - lb) elu(x beta / (1 - lb)) + 1, x the normalised alpha
+    const float xn = (alpha + sc.gauss_shift) * sc.gauss_scale;
+    const float t = xn * (sc.elu_beta / (1.0f - sc.lower_bound));
+    const float elu = t > 0.f ? t : expm1f(t);
+    a[tid] = ((1.0f - sc.lower_bound) * elu + 1.0f) * sc.a_factor;
+}
+
+__global__ void ffn_post_kernel(float *__restrict__ h, const float *__restrict__ b1, long long N, int ff,
+                                float *__restrict__ x, const float *__restrict__ b2)
+{
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total_h = N * (long long)(ff / 4);
+    if (tid < total_h) {
+        const int c = (int)(tid % (ff / 4));
+        float4 hv = reinterpret_cast<float4 *>(h)[tid];
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(b1) + c);
+        hv.x = fmaxf(hv.x + b.x, 0.f); hv.y = fmaxf(hv.y + b.y, 0.f); hv.z = fmaxf(hv.z + b.z, 0.f); hv.w = fmaxf(hv.w + b.w, 0.f);
+        reinterpret_cast<float4 *>(h)[tid] = hv;
+    }
+    if (tid < N * 32) {
+        const int c = (int)(tid % 32);
+        float4 xv = reinterpret_cast<float4 *>(x)[tid];
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(b2) + c);
+        xv.x += b.x; xv.y += b.y; xv.z += b.z; xv.w += b.w;
+        reinterpret_cast<float4 *>(x)[tid] = xv;
+    }
+}
+
+}  // namespace
+}  // namespace cf
+
+extern "C" int64_t cf_encoder_workspace_floats(int64_t N, int64_t E, int64_t ff_dim)
+{
+    // qkv (384) + q,k,v (3 x 128) + attention output (128) + a (8) + lse (8) + hidden (ff) per atom, logits per edge
+    return N * (384 + 384 + 128 + 8 + 8 + ff_dim) + E * 8 + 64;
+}
+
+extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars,
+                                  float *x, const float *pos_ij, const float *tvecs, const float *rvlen,
+                                  const int64_t *batch, const int64_t *edges, const int64_t *row_start, int64_t N,
+                                  int64_t B, int64_t E, int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale,
+                                  double cutoff_radius, int lattice_range, int minimum_range, float *workspace,
+                                  void *const *attn_events, void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(N >= 0 && E >= 0 && num_layers >= 0, CF_ERR_INVALID, "cf_encoder_forward: negative size");
+    CF_REQUIRE(ff_dim > 0 && ff_dim % 4 == 0, CF_ERR_UNSUPPORTED, "cf_encoder_forward: ff_dim must be a positive multiple of 4");
+    CF_REQUIRE(N < (1ll << 31) / 512, CF_ERR_RANGE, "cf_encoder_forward: N=%lld too large for 32-bit GEMM sizes", (long long)N);
+    if (N == 0 || num_layers == 0) return CF_OK;
+    CF_REQUIRE(cublas_handle && weights && scalars && x && workspace, CF_ERR_INVALID, "cf_encoder_forward: null pointer");
+    const Blas &bl = blas();
+    CF_REQUIRE(bl.ok, CF_ERR_CUDA, "cf_encoder_forward: libcublas.so.12 could not be resolved in this process");
+    cublasHandle_t handle = reinterpret_cast<cublasHandle_t>(cublas_handle);
+    cudaStream_t s = as_stream(stream);
+    cudaStream_t old_stream = nullptr;
+    cublasMath_t old_math = CUBLAS_DEFAULT_MATH;
+    bl.get_stream(handle, &old_stream);
+    bl.get_math(handle, &old_math);
+    bl.set_stream(handle, s);
+    bl.set_math(handle, CUBLAS_DEFAULT_MATH);  // plain fp32 (no TF32), as the reference's train.py:61-62 asks
+
+    float *qkv = workspace;
+    float *q = qkv + N * 384, *k = q + N * 128, *v = k + N * 128, *attn = v + N * 128;
+    float *a = attn + N * 128, *lse = a + N * 8, *hidden = lse + N * 8, *logit = hidden + N * ff_dim;
+    const int rows = (int)N, ff = (int)ff_dim;
+    int rc = CF_OK;
+    cublasStatus_t st = CUBLAS_STATUS_SUCCESS;
+    for (int l = 0; l < num_layers && rc == CF_OK && st == CUBLAS_STATUS_SUCCESS; ++l) {
+        const float *const *w = weights + 11 * l;  // Wqkv, bqkv, w_pos, Wpe, Wo, bo, W1, b1, W2, b2, (reserved)
+        const double *sc = scalars + 6 * l;        // gauss_scale, gauss_shift, a_factor, elu_beta, lower_bound, dist_max
+        LayerScalars ls{(float)sc[0], (float)sc[1], (float)sc[2], (float)sc[3], (float)sc[4]};
+        st = linear(bl, handle, x, w[0], qkv, rows, 128, 384, 0.0f);
+        if (st != CUBLAS_STATUS_SUCCESS) break;
+        const long long nh = N * HEADS;
+        qkv_post_kernel<<<(unsigned)((nh + 127) / 128), 128, 0, s>>>(qkv, w[1], w[2], w[5], ls, N, q, k, v, a, x);
+        if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
+        rc = cf_infinite_attn_fwd(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS, HEAD_DIM,
+                                  E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range, minimum_range, attn,
+                                  logit, lse, nullptr, s);
+        if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
+        if (rc != CF_OK) break;
+        st = linear(bl, handle, attn, w[4], x, rows, 128, 128, 1.0f);
+        if (st != CUBLAS_STATUS_SUCCESS) break;
+        st = linear(bl, handle, x, w[6], hidden, rows, 128, ff, 0.0f);
+        if (st != CUBLAS_STATUS_SUCCESS) break;
+        const long long work = N * (long long)(ff / 4 > 32 ? ff / 4 : 32);
+        ffn_post_kernel<<<(unsigned)((work + 255) / 256), 256, 0, s>>>(hidden, w[7], N, ff, x, w[9]);
+        st = linear(bl, handle, hidden, w[8], x, rows, ff, 128, 1.0f);
+    }
+    bl.set_math(handle, old_math);
+    bl.set_stream(handle, old_stream);
+    if (st != CUBLAS_STATUS_SUCCESS) return fail(CF_ERR_CUDA, "cf_encoder_forward: cuBLAS SGEMM failed with status %d", (int)st);
+    if (rc != CF_OK) return rc;
+    return launch_status("cf_encoder_forward");
+}

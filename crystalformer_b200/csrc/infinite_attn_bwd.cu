@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_bwd_rows_kernel(const B
                 G[h] = fmaf(w[h] * d2, gj[h], G[h]);
             }
             if (K > 0) {
-                const float x = sqrtf(d2) * p.basis.bin_scale;
+                const float x = fast_sqrt(d2) * p.basis.bin_scale;
                 const bool keep = emax > p.basis.floor_log2 && d2 < p.basis.d2_cut;
                 const int cnt = stage_terms(stage, lane, keep, x, d2, j, w);
                 if (cnt > 0) {

@@ -166,17 +166,12 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                     w[h] = ex2(eh);
                     emax = fmaxf(emax, eh);
                 }
-                const float x = sqrtf(d2) * p.basis.bin_scale;
+                const float x = fast_sqrt(d2) * p.basis.bin_scale;
                 bins.push(valid && emax > p.basis.floor_log2 && d2 < p.basis.d2_cut, x, w);
                 walk.step();
             }
             // ---- partial histograms -> shared memory, fixed-order sum over the four warps
-            float *mine = part + warp * HEADS * KBINS;
-#pragma unroll
-            for (int h = 0; h < 8; ++h) {
-                mine[h * KBINS + lane] = bins.acc[h][0];
-                mine[h * KBINS + lane + 32] = bins.acc[h][1];
-            }
+            bins.flush(part + warp * HEADS * KBINS, KBINS);
             __syncthreads();
             for (int idx = tid; idx < HEADS * KBINS; idx += THREADS) {
                 const float s = (part[idx] + part[HEADS * KBINS + idx]) + (part[2 * HEADS * KBINS + idx] + part[3 * HEADS * KBINS + idx]);
@@ -237,6 +232,7 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     PhiArgs phi{};
     phi.a = a; phi.pos = pos; phi.pos_ij = pos_ij; phi.tvecs = tvecs; phi.batch = batch; phi.edges = edges; phi.rvlen = rvlen; phi.z = logit;
     phi.E = E; phi.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
+    phi.floor_log2 = weight_floor_log2();
     int rc = launch_lattice_phi(phi, s);
     if (rc != CF_OK) return rc;
 

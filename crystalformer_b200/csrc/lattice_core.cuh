@@ -94,46 +94,66 @@ static __device__ __noinline__ float head_phi_own_min(const Cell &cell, float rx
     return fmaf(m, a, logf(sum));
 }
 
+// TPE threads (a power of two, consecutive lanes) share one edge: thread `sub` takes the (n1,n2) columns
+// sub, sub + TPE, ... of the box and the partial minimum / sums are combined with shuffles.  More threads per edge
+// give small batches enough warps to hide the latency of the per-term dependency chain.
+template <int TPE>
 __device__ __forceinline__ void edge_phi(const BoxRule &rule, const float (&a)[8], const float *__restrict__ rvlen3,
-                                         const Cell &cell, float rx, float ry, float rz, float (&z)[8])
+                                         const Cell &cell, float rx, float ry, float rz, float floor_log2, int sub,
+                                         float (&z)[8])
 {
     int pk[8];
     float a2[8], r1[8], r2[8], r3[8];
     int uni = 0;
+    float a2max = -INFINITY;  // the widest Gaussian of the eight: bounds every head's weight from above
 #pragma unroll
     for (int h = 0; h < 8; ++h) {
         pk[h] = packed_box(rule, a[h], rvlen3);
         a2[h] = a[h] * LOG2E;
+        a2max = fmaxf(a2max, a2[h]);
         uni = box_union(uni, pk[h]);
         r1[h] = (float)box_r1(pk[h]);
         r2[h] = (float)box_r2(pk[h]);
         r3[h] = (float)box_r3(pk[h]);
     }
     const float F1 = (float)box_r1(uni), F2 = (float)box_r2(uni), F3 = (float)box_r3(uni);
+    const float S2 = 2.0f * F2 + 1.0f;
+    // column walk: (f1, f2) advances by TPE columns per step, f2 fastest
+    float start1 = -F1, start2 = -F2 + (float)sub, step1 = 0.f, step2 = (float)TPE;
+    while (start2 > F2) { start2 -= S2; start1 += 1.0f; }
+    while (step2 >= S2) { step2 -= S2; step1 += 1.0f; }
+
     float m = 1e10f;
-    for (float f1 = -F1; f1 <= F1; f1 += 1.0f) {
-        const float ax = fmaf(cell.t1x, f1, rx), ay = fmaf(cell.t1y, f1, ry), az = fmaf(cell.t1z, f1, rz);
-        for (float f2 = -F2; f2 <= F2; f2 += 1.0f) {
-            const float bx = fmaf(cell.t2x, f2, ax), by = fmaf(cell.t2y, f2, ay), bz = fmaf(cell.t2z, f2, az);
-            for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
-                const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
-                m = fminf(m, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
-            }
+    for (float f1 = start1, f2 = start2; f1 <= F1;) {
+        const float bx = fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, rx));
+        const float by = fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, ry));
+        const float bz = fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, rz));
+        for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
+            const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
+            m = fminf(m, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
         }
+        f2 += step2; f1 += step1;
+        if (f2 > F2) { f2 -= S2; f1 += 1.0f; }
     }
+#pragma unroll
+    for (int o = TPE / 2; o > 0; o >>= 1) m = fminf(m, __shfl_xor_sync(FULL, m, o));
+
     float sum[8];
 #pragma unroll
     for (int h = 0; h < 8; ++h) sum[h] = 0.f;
-    for (float f1 = -F1; f1 <= F1; f1 += 1.0f) {
-        const float ax = fmaf(cell.t1x, f1, rx), ay = fmaf(cell.t1y, f1, ry), az = fmaf(cell.t1z, f1, rz);
-        for (float f2 = -F2; f2 <= F2; f2 += 1.0f) {
-            const float bx = fmaf(cell.t2x, f2, ax), by = fmaf(cell.t2y, f2, ay), bz = fmaf(cell.t2z, f2, az);
-            float lim[8];
+    for (float f1 = start1, f2 = start2; f1 <= F1;) {
+        const float bx = fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, rx));
+        const float by = fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, ry));
+        const float bz = fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, rz));
+        float lim[8];
 #pragma unroll
-            for (int h = 0; h < 8; ++h) lim[h] = (fabsf(f1) <= r1[h] && fabsf(f2) <= r2[h]) ? r3[h] : -1.0f;
-            for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
-                const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
-                const float rel = fmaf(dz, dz, fmaf(dy, dy, dx * dx)) - m;
+        for (int h = 0; h < 8; ++h) lim[h] = (fabsf(f1) <= r1[h] && fabsf(f2) <= r2[h]) ? r3[h] : -1.0f;
+        for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
+            const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
+            const float rel = fmaf(dz, dz, fmaf(dy, dy, dx * dx)) - m;
+            // the term with d2 = m contributes 1 to every sum it belongs to, so a term whose largest weight is
+            // below the floor (2^-40 by default) changes no sum by more than that fraction: skip its eight ex2
+            if (a2max * rel > floor_log2) {
                 const float af3 = fabsf(f3);
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
@@ -142,13 +162,20 @@ __device__ __forceinline__ void edge_phi(const BoxRule &rule, const float (&a)[8
                 }
             }
         }
+        f2 += step2; f1 += step1;
+        if (f2 > F2) { f2 -= S2; f1 += 1.0f; }
     }
 #pragma unroll
     for (int h = 0; h < 8; ++h) {
+#pragma unroll
+        for (int o = TPE / 2; o > 0; o >>= 1) sum[h] += __shfl_xor_sync(FULL, sum[h], o);
         z[h] = fmaf(m, a[h], logf(sum[h]));
         if (!(sum[h] > 1e-30f)) z[h] = head_phi_own_min(cell, rx, ry, rz, a[h], pk[h]);
     }
 }
+
+// d = sqrt(d2) by one rsqrt and one multiply (2 ulp), exact zero for d2 = 0.
+__device__ __forceinline__ float fast_sqrt(float d2) { return d2 * rsqrt_fast(fmaxf(d2, 1e-35f)); }
 
 // ---- lane <-> term ------------------------------------------------------------------------------------------------
 // Walks flat term indices t, t+32, t+64, ... of a (rows x S1 x S2 x S3) mixed-radix space, S3 fastest, keeping the
@@ -164,17 +191,30 @@ struct TermWalker {
     {
         const unsigned s1 = 2 * R1 + 1, s2 = 2 * R2 + 1, s3 = 2 * R3 + 1;
         S1 = (float)s1; S2 = (float)s2; S3 = (float)s3;
-        // digits of the stride 32
-        unsigned q = 32u;
-        d3 = (float)(q % s3); q /= s3;
-        d2 = (float)(q % s2); q /= s2;
-        d1 = (float)(q % s1); q /= s1;
-        drow = (int)q;
-        unsigned t = start;
-        u3 = (float)(t % s3); t /= s3;
-        u2 = (float)(t % s2); t /= s2;
-        u1 = (float)(t % s1); t /= s1;
-        row = (int)t;
+        // digits of the stride 32 (same reciprocal trick: exact for these small integers)
+        const unsigned q3s = (unsigned)__float2int_rd(32.5f * __frcp_rn(S3));
+        d3 = (float)(32u - q3s * s3);
+        const unsigned q2s = (unsigned)__float2int_rd(((float)q3s + 0.5f) * __frcp_rn(S2));
+        d2 = (float)(q3s - q2s * s2);
+        const unsigned q1s = (unsigned)__float2int_rd(((float)q2s + 0.5f) * __frcp_rn(S1));
+        d1 = (float)(q2s - q1s * s1);
+        drow = (int)q1s;
+        if (start < 32u) {  // a lane index: at most two quotient digits are non-zero and they are tiny
+            unsigned t = start;
+            const unsigned q3 = (unsigned)__float2int_rd(((float)t + 0.5f) * __frcp_rn(S3));
+            u3 = (float)(t - q3 * s3);
+            const unsigned q2 = (unsigned)__float2int_rd(((float)q3 + 0.5f) * __frcp_rn(S2));
+            u2 = (float)(q3 - q2 * s2);
+            const unsigned q1 = (unsigned)__float2int_rd(((float)q2 + 0.5f) * __frcp_rn(S1));
+            u1 = (float)(q2 - q1 * s1);
+            row = (int)q1;
+        } else {
+            unsigned t = start;
+            u3 = (float)(t % s3); t /= s3;
+            u2 = (float)(t % s2); t /= s2;
+            u1 = (float)(t % s1); t /= s1;
+            row = (int)t;
+        }
     }
     __device__ __forceinline__ void step()
     {
@@ -197,64 +237,153 @@ struct BasisParams {
     float bin_scale;   // bin_step / mu0: distance -> basis units
     float d2_cut;      // squared distance beyond which every basis value underflows
     float floor_log2;  // terms whose largest log2-weight is below this are not accumulated
+    int windowed;      // 1: basis narrow enough for the three-window accumulation (see BinAccumulator)
 };
 
 constexpr int STAGE_FLOATS = 32 * 12;  // per warp: 32 entries x (x, pad[3], w0..7); 16-byte aligned rows
 
-// Accumulates sum_n w_h(n) g_k(d_n) for one warp.  Protocol per batch of 32 terms:
-//   push(keep, x, w[8])    every lane offers its term; survivors are compacted into shared memory with a ballot,
-//                          then all lanes sweep the staged entries (lanes <-> bins)
+// Packed FP32 pair arithmetic of sm_100 (fma.rn.f32x2): one issue slot for two FMAs.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+
+// Accumulates sum_n w_h(n) g_k(d_n) for one warp.  Per batch of 32 terms, push(keep, x, w[8]): every lane offers its
+// term; survivors are compacted into shared memory with ballots; then all lanes sweep the staged entries, each lane
+// evaluating the basis at ITS bins and updating ITS accumulators for all eight heads (heads paired in f32x2 FMAs).
+//
+// Two bin layouts:
+//   dense     lane owns bins (lane, lane+32): per entry 2 ex2 + 8 packed FMAs.
+//   windowed  the basis is a Gaussian of one bin width, so at 8 bins from its centre it is below 2^-46.  The 64 bins
+//             are covered by three overlapping 32-bin windows [0,32), [16,48), [32,64); an entry centred at bin xi
+//             goes to the window that contains [xi-8, xi+8] (always one of the three), and a lane owns bin
+//             16 w + lane in window w: per entry 1 ex2 + 4 packed FMAs, with 12 packed accumulators per lane.
+//             Used when (8 bin_step)^2 >= 40, i.e. value_pe_width_scale <= 1.07; otherwise the dense layout.
+// flush() adds the accumulators into a per-warp shared-memory tile [8][stride] of per-bin totals.
 template <int K>
 struct BinAccumulator {
-    float acc[8][2];
-    float c0, c1;
-    float *stage;  // STAGE_FLOATS floats of this warp
+    float2 acc[12];  // dense: [hp][bin slot] = acc[2 hp + slot]; windowed: [window][hp] = acc[4 window + hp]
+    float c0, c1, c2;
+    float *stage;    // STAGE_FLOATS floats of this warp
     int lane;
+    bool windowed;
+    float inv_step;
 
     __device__ __forceinline__ void init(float *stage_, int lane_, const BasisParams &bp)
     {
         stage = stage_;
         lane = lane_;
-        c0 = (float)(lane + 1) * bp.bin_step;
-        c1 = (float)(lane + 33) * bp.bin_step;
-#pragma unroll
-        for (int h = 0; h < 8; ++h) acc[h][0] = acc[h][1] = 0.f;
+        windowed = bp.windowed != 0;
+        inv_step = __frcp_rn(bp.bin_step);
+        if (windowed) {
+            c0 = (float)(lane + 1) * bp.bin_step;
+            c1 = (float)(lane + 17) * bp.bin_step;
+            c2 = (float)(lane + 33) * bp.bin_step;
+        } else {
+            c0 = (float)(lane + 1) * bp.bin_step;
+            c1 = (float)(lane + 33) * bp.bin_step;
+            c2 = 0.f;
+        }
+        clear();
     }
     __device__ __forceinline__ void clear()
     {
 #pragma unroll
-        for (int h = 0; h < 8; ++h) acc[h][0] = acc[h][1] = 0.f;
+        for (int t = 0; t < 12; ++t) acc[t] = make_float2(0.f, 0.f);
     }
 
     // x = basis coordinate of the lane's term, w = its eight weights
     __device__ __forceinline__ void push(bool keep, float x, const float (&w)[8])
     {
-        const unsigned mask = __ballot_sync(FULL, keep);
-        if (mask == 0u) return;
-        if (keep) {
-            const int slot = __popc(mask & ((1u << lane) - 1u));
-            float4 *row = reinterpret_cast<float4 *>(stage + 12 * slot);
-            row[0] = make_float4(x, 0.f, 0.f, 0.f);
-            row[1] = make_float4(w[0], w[1], w[2], w[3]);
-            row[2] = make_float4(w[4], w[5], w[6], w[7]);
-        }
-        __syncwarp();
-        const int cnt = __popc(mask);
+        const unsigned lt = (1u << lane) - 1u;
+        if (windowed) {
+            // window of the term: bin coordinate xi = x / step - 1; [xi-8, xi+8] lies in window 0 below 24, 1 below 40
+            const float xi = fmaf(x, inv_step, -1.0f);
+            const int win = (xi >= 24.0f) + (xi >= 40.0f);
+            const unsigned m0 = __ballot_sync(FULL, keep && win == 0);
+            const unsigned m1 = __ballot_sync(FULL, keep && win == 1);
+            const unsigned m2 = __ballot_sync(FULL, keep && win == 2);
+            if ((m0 | m1 | m2) == 0u) return;
+            const int n0 = __popc(m0), n1 = __popc(m1), n2 = __popc(m2);
+            if (keep) {
+                const int slot = win == 0 ? __popc(m0 & lt) : (win == 1 ? n0 + __popc(m1 & lt) : n0 + n1 + __popc(m2 & lt));
+                float4 *row = reinterpret_cast<float4 *>(stage + 12 * slot);
+                row[0] = make_float4(x, 0.f, 0.f, 0.f);
+                row[1] = make_float4(w[0], w[1], w[2], w[3]);
+                row[2] = make_float4(w[4], w[5], w[6], w[7]);
+            }
+            __syncwarp();
+            sweep_window(0, n0, c0, 0);
+            sweep_window(n0, n0 + n1, c1, 4);
+            sweep_window(n0 + n1, n0 + n1 + n2, c2, 8);
+            __syncwarp();
+        } else {
+            const unsigned mask = __ballot_sync(FULL, keep);
+            if (mask == 0u) return;
+            if (keep) {
+                const int slot = __popc(mask & lt);
+                float4 *row = reinterpret_cast<float4 *>(stage + 12 * slot);
+                row[0] = make_float4(x, 0.f, 0.f, 0.f);
+                row[1] = make_float4(w[0], w[1], w[2], w[3]);
+                row[2] = make_float4(w[4], w[5], w[6], w[7]);
+            }
+            __syncwarp();
+            const int cnt = __popc(mask);
 #pragma unroll 2
-        for (int m = 0; m < cnt; ++m) {
+            for (int m = 0; m < cnt; ++m) {
+                const float4 *row = reinterpret_cast<const float4 *>(stage + 12 * m);
+                const float x_m = row[0].x;
+                const float4 wa = row[1], wb = row[2];
+                const float t0 = c0 - x_m, t1 = c1 - x_m;
+                const float g0 = ex2(-t0 * t0), g1 = ex2(-t1 * t1);
+                const float2 G0 = make_float2(g0, g0), G1 = make_float2(g1, g1);
+                acc[0] = fma2(make_float2(wa.x, wa.y), G0, acc[0]); acc[1] = fma2(make_float2(wa.x, wa.y), G1, acc[1]);
+                acc[2] = fma2(make_float2(wa.z, wa.w), G0, acc[2]); acc[3] = fma2(make_float2(wa.z, wa.w), G1, acc[3]);
+                acc[4] = fma2(make_float2(wb.x, wb.y), G0, acc[4]); acc[5] = fma2(make_float2(wb.x, wb.y), G1, acc[5]);
+                acc[6] = fma2(make_float2(wb.z, wb.w), G0, acc[6]); acc[7] = fma2(make_float2(wb.z, wb.w), G1, acc[7]);
+            }
+            __syncwarp();
+        }
+    }
+
+    __device__ __forceinline__ void sweep_window(int begin, int end, float centre, int base)
+    {
+#pragma unroll 2
+        for (int m = begin; m < end; ++m) {
             const float4 *row = reinterpret_cast<const float4 *>(stage + 12 * m);
-            const float x = row[0].x;
+            const float t = centre - row[0].x;
             const float4 wa = row[1], wb = row[2];
-            const float t0 = c0 - x, t1 = c1 - x;
-            const float g0 = ex2(-t0 * t0), g1 = ex2(-t1 * t1);
-            acc[0][0] = fmaf(wa.x, g0, acc[0][0]); acc[0][1] = fmaf(wa.x, g1, acc[0][1]);
-            acc[1][0] = fmaf(wa.y, g0, acc[1][0]); acc[1][1] = fmaf(wa.y, g1, acc[1][1]);
-            acc[2][0] = fmaf(wa.z, g0, acc[2][0]); acc[2][1] = fmaf(wa.z, g1, acc[2][1]);
-            acc[3][0] = fmaf(wa.w, g0, acc[3][0]); acc[3][1] = fmaf(wa.w, g1, acc[3][1]);
-            acc[4][0] = fmaf(wb.x, g0, acc[4][0]); acc[4][1] = fmaf(wb.x, g1, acc[4][1]);
-            acc[5][0] = fmaf(wb.y, g0, acc[5][0]); acc[5][1] = fmaf(wb.y, g1, acc[5][1]);
-            acc[6][0] = fmaf(wb.z, g0, acc[6][0]); acc[6][1] = fmaf(wb.z, g1, acc[6][1]);
-            acc[7][0] = fmaf(wb.w, g0, acc[7][0]); acc[7][1] = fmaf(wb.w, g1, acc[7][1]);
+            const float g = ex2(-t * t);
+            const float2 G = make_float2(g, g);
+            acc[base + 0] = fma2(make_float2(wa.x, wa.y), G, acc[base + 0]);
+            acc[base + 1] = fma2(make_float2(wa.z, wa.w), G, acc[base + 1]);
+            acc[base + 2] = fma2(make_float2(wb.x, wb.y), G, acc[base + 2]);
+            acc[base + 3] = fma2(make_float2(wb.z, wb.w), G, acc[base + 3]);
+        }
+    }
+
+    // Writes the per-bin totals of this warp into tile[h * stride + k] (shared memory, overwritten).
+    __device__ __forceinline__ void flush(float *tile, int stride)
+    {
+        if (windowed) {
+#pragma unroll
+            for (int hp = 0; hp < 4; ++hp) {
+                tile[(2 * hp) * stride + lane] = acc[hp].x;
+                tile[(2 * hp + 1) * stride + lane] = acc[hp].y;
+                tile[(2 * hp) * stride + lane + 32] = acc[8 + hp].x;
+                tile[(2 * hp + 1) * stride + lane + 32] = acc[8 + hp].y;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int hp = 0; hp < 4; ++hp) {
+                tile[(2 * hp) * stride + lane + 16] += acc[4 + hp].x;
+                tile[(2 * hp + 1) * stride + lane + 16] += acc[4 + hp].y;
+            }
+        } else {
+#pragma unroll
+            for (int hp = 0; hp < 4; ++hp) {
+                tile[(2 * hp) * stride + lane] = acc[2 * hp].x;
+                tile[(2 * hp + 1) * stride + lane] = acc[2 * hp].y;
+                tile[(2 * hp) * stride + lane + 32] = acc[2 * hp + 1].x;
+                tile[(2 * hp + 1) * stride + lane + 32] = acc[2 * hp + 1].y;
+            }
         }
         __syncwarp();
     }
@@ -272,6 +401,7 @@ struct PhiArgs {
     float *z;                // (E,H) out
     long long E;
     BoxRule rule;
+    float floor_log2;        // weights below 2^floor_log2 of the nearest image's are not summed
     int a_per_edge;
 };
 int launch_lattice_phi(const PhiArgs &p, cudaStream_t stream);
@@ -288,6 +418,7 @@ inline BasisParams make_basis_params(long long K, double dist_max, double wscale
         bp.bin_scale = (float)(step / mu0);
         const double x_cut = (double)K * step + 11.3;  // (x - K step)^2 > 126  =>  every basis value < 2^-126
         bp.d2_cut = (float)((x_cut / (step / mu0)) * (x_cut / (step / mu0)));
+        bp.windowed = (K == 64 && (8.0 * step) * (8.0 * step) >= 40.0) ? 1 : 0;
     }
     bp.floor_log2 = floor_log2;
     return bp;

@@ -16,7 +16,7 @@ namespace {
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
 constexpr int KBINS = 64;
-constexpr int WARP_SMEM_FLOATS = HEADS * U_STRIDE + (STAGE_FLOATS > BWD_STAGE_FLOATS ? STAGE_FLOATS : BWD_STAGE_FLOATS);
+constexpr int WARP_SMEM_FLOATS = HEADS * U_STRIDE + HEADS * KBINS + (STAGE_FLOATS > BWD_STAGE_FLOATS ? STAGE_FLOATS : BWD_STAGE_FLOATS);
 
 struct BwdArgs {
     const float *a, *pos_ij, *tvecs, *rvlen, *z, *gz, *gpsi;
@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(THREADS) lattice_bwd_edges_kernel(const BwdArg
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float *u = smem + warp * WARP_SMEM_FLOATS;
-    float *stage = u + HEADS * U_STRIDE;
+    float *tile = u + HEADS * U_STRIDE;      // per-bin totals of the recomputed psi
+    float *stage = tile + HEADS * KBINS;
     BinAccumulator<KBINS> bins;
     if (K > 0) bins.init(stage, lane, p.basis);
 
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(THREADS) lattice_bwd_edges_kernel(const BwdArg
                     w[h] = ex2(eh);
                     emax = fmaxf(emax, eh);
                 }
-                const float x = sqrtf(d2) * p.basis.bin_scale;
+                const float x = fast_sqrt(d2) * p.basis.bin_scale;
                 const bool keep = K > 0 && emax > p.basis.floor_log2 && d2 < p.basis.d2_cut;
                 if (pass == 0) {
                     bins.push(keep, x, w);
@@ -126,12 +127,15 @@ __global__ void __launch_bounds__(THREADS) lattice_bwd_edges_kernel(const BwdArg
                 walk.step();
             }
             if (pass == 0) {
+                // per-bin totals go through the warp's own tile (u must stay intact for the second pass)
                 float *dst = p.psi_out + (size_t)e * HEADS * KBINS + lane;
+                bins.flush(tile, KBINS);
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
-                    dst[h * KBINS] = bins.acc[h][0];
-                    dst[h * KBINS + 32] = bins.acc[h][1];
+                    dst[h * KBINS] = tile[h * KBINS + lane];
+                    dst[h * KBINS + 32] = tile[h * KBINS + lane + 32];
                 }
+                __syncwarp();
             }
         }
 #pragma unroll

@@ -77,10 +77,14 @@ __device__ __forceinline__ float4 project(const float *__restrict__ Wsrc, const 
 }
 
 
+template <int TPE>
 __global__ void __launch_bounds__(128) lattice_phi_kernel(const PhiArgs p)
 {
-    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= p.E) return;
+    const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long e_raw = gtid / TPE;
+    const int sub = (int)(gtid % TPE);
+    const bool live = e_raw < p.E;
+    const long long e = live ? e_raw : p.E - 1;  // idle tail threads shadow the last edge so that shuffles stay full
     const long long i = p.edges[e];
     const long long c = p.batch[i];
     Cell cell;
@@ -98,14 +102,16 @@ __global__ void __launch_bounds__(128) lattice_phi_kernel(const PhiArgs p)
         rz = __fsub_rn(p.pos[3 * j + 2], p.pos[3 * i + 2]);
     }
     float z[8];
-    edge_phi(p.rule, a, p.rvlen ? p.rvlen + 3 * c : nullptr, cell, rx, ry, rz, z);
-    float4 *zp = reinterpret_cast<float4 *>(p.z + e * HEADS);
-    zp[0] = make_float4(z[0], z[1], z[2], z[3]);
-    zp[1] = make_float4(z[4], z[5], z[6], z[7]);
+    edge_phi<TPE>(p.rule, a, p.rvlen ? p.rvlen + 3 * c : nullptr, cell, rx, ry, rz, p.floor_log2, sub, z);
+    if (live && sub == 0) {
+        float4 *zp = reinterpret_cast<float4 *>(p.z + e * HEADS);
+        zp[0] = make_float4(z[0], z[1], z[2], z[3]);
+        zp[1] = make_float4(z[4], z[5], z[6], z[7]);
+    }
 }
 
 template <int K>
-__global__ void __launch_bounds__(THREADS) lattice_psi_kernel(const FwdArgs p)
+__global__ void __launch_bounds__(THREADS, 5) lattice_psi_kernel(const FwdArgs p)
 {
     extern __shared__ __align__(16) float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -173,25 +179,21 @@ __global__ void __launch_bounds__(THREADS) lattice_psi_kernel(const FwdArgs p)
                 w[h] = ex2(eh);
                 emax = fmaxf(emax, eh);
             }
-            const float x = sqrtf(d2) * p.basis.bin_scale;
+            const float x = fast_sqrt(d2) * p.basis.bin_scale;
             bins.push(valid && emax > p.basis.floor_log2 && d2 < p.basis.d2_cut, x, w);
             walk.step();
         }
 
+        bins.flush(psi, PSI_STRIDE);
         if (p.W == nullptr) {
             float *dst = p.v + (size_t)e * HEADS * K + lane;
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
-                dst[h * K] = bins.acc[h][0];
-                dst[h * K + 32] = bins.acc[h][1];
-            }
-        } else {
-#pragma unroll
-            for (int h = 0; h < 8; ++h) {
-                psi[h * PSI_STRIDE + lane] = bins.acc[h][0];
-                psi[h * PSI_STRIDE + lane + 32] = bins.acc[h][1];
+                dst[h * K] = psi[h * PSI_STRIDE + lane];
+                dst[h * K + 32] = psi[h * PSI_STRIDE + lane + 32];
             }
             __syncwarp();
+        } else {
             float4 o;
             if (p.stage_w) {
                 o = project<K, true>(wt, psi, lane);
@@ -227,6 +229,7 @@ int launch_fwd(const FwdArgs &p, long long K, cudaStream_t stream)
     PhiArgs phi{};
     phi.a = p.a; phi.pos_ij = p.pos_ij; phi.tvecs = p.tvecs; phi.batch = p.batch; phi.edges = p.edges;
     phi.rvlen = p.rvlen; phi.z = p.z; phi.E = p.E; phi.rule = p.rule; phi.a_per_edge = p.a_per_edge;
+    phi.floor_log2 = p.basis.floor_log2;
     launch_lattice_phi(phi, stream);
     if (K > 0) {
         const size_t smem = sizeof(float) * ((p.stage_w ? HEADS * WT_HEAD_STRIDE : 0) + WARPS * WARP_SMEM_FLOATS);
@@ -249,7 +252,19 @@ int launch_fwd(const FwdArgs &p, long long K, cudaStream_t stream)
 
 int launch_lattice_phi(const PhiArgs &p, cudaStream_t stream)
 {
-    if (p.E > 0) lattice_phi_kernel<<<(unsigned)((p.E + 127) / 128), 128, 0, stream>>>(p);
+    if (p.E > 0) {
+        // enough threads to give every SM about 24 warps: small batches split each edge over up to 8 threads
+        const long long target = (long long)sm_count() * 24 * 32;
+        int tpe = 1;
+        while (tpe < 8 && p.E * tpe < target) tpe *= 2;
+        const unsigned blocks = (unsigned)((p.E * tpe + 127) / 128);
+        switch (tpe) {
+            case 1: lattice_phi_kernel<1><<<blocks, 128, 0, stream>>>(p); break;
+            case 2: lattice_phi_kernel<2><<<blocks, 128, 0, stream>>>(p); break;
+            case 4: lattice_phi_kernel<4><<<blocks, 128, 0, stream>>>(p); break;
+            default: lattice_phi_kernel<8><<<blocks, 128, 0, stream>>>(p); break;
+        }
+    }
     return launch_status("lattice_phi_kernel");
 }
 

@@ -14,7 +14,9 @@ from torch import Tensor
 from torch.nn import Dropout, Identity, LayerNorm, Linear, Module, ModuleList
 from torch.nn.init import constant_, xavier_uniform_
 
-from . import ops
+import ctypes
+
+from . import _lib, ops
 from .attention import CrystalformerMultiheadAttentionCUDA, register_edge_info
 from .cuda_funcs import compile_kernels
 from .params import LatticeformerParams
@@ -125,10 +127,97 @@ class CrystalformerEncoderCUDA(Module):
         self.norm = LayerNorm(d_model, eps=layer_norm_eps) if not no_layer_norm else None
         self.d_model = d_model
         self.nhead = nhead
+        self.native = True  # use the one-call inference path whenever it applies
         v_head_dim = v_dim if v_dim > 0 else d_model // nhead
         k_head_dim = k_dim if k_dim > 0 else d_model // nhead
         compile_kernels(lattice_params.lattice_range, nhead, k_head_dim, lattice_params.value_pe_dist_real, v_head_dim,
                         lattice_params.minimum_range)
+
+    # -----------------------------------------------------------------------------------------------------------
+    # Inference fast path: the whole stack in one call into the library (cf_encoder_forward).
+    # -----------------------------------------------------------------------------------------------------------
+    def _native_ok(self) -> bool:
+        if self.training or torch.is_grad_enabled() or self.norm is not None or self.d_model != 128 or self.nhead != 8:
+            return False
+        for layer in self.layers:
+            att, P = layer.self_attn, layer.self_attn.params
+            if not (P.positive_func.startswith("elu") and P.gauss_state == "q" and P.normalize_gauss and att.fused
+                    and P.value_pe_condproj == "no" and P.norm_func_mode == 0 and att.kdim == 128 and att.vdim == 128
+                    and att.in_proj_bias is not None and layer.activation is F.relu and not layer.norm_first
+                    and isinstance(layer.norm1, Identity)):
+                return False
+            if not att._scale_known:
+                att._scale_known = bool(att.gauss_scale[0] > 0)
+                if not att._scale_known:
+                    return False
+        return True
+
+    def _packed_weights(self, device):
+        """Device pointers and scalars of every layer in the layout cf_encoder_forward expects; rebuilt only when a
+        parameter changed (in-place updates bump ``_version``)."""
+        params = [p for p in self.parameters()]
+        key = (device, tuple(p._version for p in params), tuple(p.data_ptr() for p in params))
+        cache = getattr(self, "_native_cache", None)
+        if cache is not None and cache[0] == key:
+            return cache[1]
+        keep, ptrs, scalars = [], [], []
+        for layer in self.layers:
+            att, P = layer.self_attn, layer.self_attn.params
+            wqkv = torch.cat((att.q_proj_weight, att.k_proj_weight, att.v_proj_weight), 0).detach().float().contiguous()
+            tensors = [wqkv, att.in_proj_bias, att.lattice_pos_weights,
+                       att.pe_dist_proj if att.pe_dist_proj is not None else None, att.out_proj.weight, att.out_proj.bias,
+                       layer.linear1.weight, layer.linear1.bias, layer.linear2.weight, layer.linear2.bias, None]
+            tensors = [None if t is None else t.detach().float().contiguous() for t in tensors]
+            keep.append(tensors)
+            ptrs += [0 if t is None else t.data_ptr() for t in tensors]
+            beta = float(P.positive_func.split("=")[1]) if "=" in P.positive_func else 1.0
+            dist_max = P.value_pe_dist_max
+            if dist_max < 0:
+                dist_max = (-dist_max) * P.scale_real
+            gs = att.gauss_scale.detach().cpu().tolist()
+            scalars += [gs[0], gs[1], -0.5 * P.scale_real ** -2, beta, P.gauss_lb_real, dist_max]
+        packed = dict(keep=keep, ptrs=(ctypes.c_void_p * len(ptrs))(*ptrs), scalars=(ctypes.c_double * len(scalars))(*scalars),
+                      ff=self.layers[0].linear1.weight.shape[0])
+        self._native_cache = (key, packed)
+        return packed
+
+    def _forward_native(self, src: Tensor, trans: Tensor, g: "BatchGeometry") -> Tensor:
+        P = self.lattice_params
+        dev = src.device
+        w = self._packed_weights(dev)
+        N, E, B = src.shape[0], g.edges.shape[1], trans.shape[0]
+        x = src.detach().float().contiguous().clone()
+        lib = _lib.load()
+        work = torch.empty(int(lib.cf_encoder_workspace_floats(N, E, w["ff"])), dtype=torch.float32, device=dev)
+        cutoff = 0.0
+        if P.adaptive_cutoff_sigma < 0:
+            cutoff = float(P.adaptive_cutoff_sigma)
+        elif P.adaptive_cutoff_sigma > 0:
+            sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
+            cutoff = sr * P.gauss_lb_real ** (-0.5) * P.adaptive_cutoff_sigma
+        with torch.cuda.device(dev):
+            _lib.call("cf_encoder_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()), len(self.layers),
+                      w["ptrs"], w["scalars"], x.data_ptr(), g.pos_ij.data_ptr(), trans.data_ptr(),
+                      g.rvlen.data_ptr() if cutoff != 0.0 else None, g.batch.data_ptr(), g.edges.data_ptr(),
+                      g.row_start.data_ptr(), N, B, E, g.max_atoms, int(P.value_pe_dist_real), w["ff"],
+                      float(P.value_pe_width_scale), cutoff, int(P.lattice_range),
+                      int(P.lattice_range) if P.minimum_range else 0, work.data_ptr(), self._attention_events(),
+                      torch.cuda.current_stream(dev).cuda_stream)
+        return x
+
+    def _attention_events(self):
+        """When ``self.attention_event_log`` is a list, every native forward appends one (start, end) pair of timing
+        events per layer, recorded by the library around that layer's attention kernels."""
+        log = getattr(self, "attention_event_log", None)
+        if log is None:
+            return None
+        pairs = []
+        for _ in self.layers:
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); e.record()  # creates the underlying CUDA events; they are re-recorded by the library
+            pairs += [s, e]
+        log.extend(zip(pairs[0::2], pairs[1::2]))
+        return (ctypes.c_void_p * len(pairs))(*[p.cuda_event for p in pairs])
 
     def forward(self, src: Tensor, pos: Tensor, batch: Tensor, trans: Tensor, sizes: Tensor, onehot: Tensor = None,
                 geometry: Optional[BatchGeometry] = None) -> Tensor:
@@ -136,6 +225,8 @@ class CrystalformerEncoderCUDA(Module):
         if src.size(-1) != self.d_model:
             raise RuntimeError("the feature number of src and tgt must be equal to d_model")
         g = geometry if geometry is not None else BatchGeometry(pos, trans, sizes)
+        if self.native and self._native_ok():
+            return self._forward_native(src, trans.float().contiguous(), g)
         output = src
         for mod in self.layers:
             output = mod(output, g.batch, g.edges, g.pos_ij, None, trans, None, g.rvecs, g.vcell, onehot, rvlen=g.rvlen)

@@ -203,6 +203,34 @@ int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const f
                          float *gk, float *gv, float *ga, float *glogit, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
+ * Inference forward of the encoder stack (every layer of CrystalformerEncoderCUDA,
+ * models/indexed_latticeformer_encoder.py:699-742 and :848-890, post-norm with LayerNorm = Identity) in one call:
+ * per layer  x <- x + out_proj(attention(x)) ;  x <- x + W2 relu(W1 x + b1) + b2, with the attention of
+ * cf_infinite_attn_fwd and the Gaussian-width pipeline of
+ * models/indexed_lattice_multi_head_attention_cuda.py:640-722 (gauss_state 'q', normalised alpha with a stored
+ * gauss_scale, positive_func 'elu=beta').  model_dim 128, 8 heads; dense products by cuBLAS SGEMM in plain fp32 on the
+ * caller's handle (cublasHandle_t passed as void*; the library resolves cuBLAS from the copy loaded in the process).
+ *   weights : HOST array of num_layers x 11 device pointers:
+ *             Wqkv (384,128) [q,k,v rows stacked], bqkv (384), lattice_pos_weights (128), pe_dist_proj (8,16,K) or
+ *             NULL, out_proj.weight (128,128), out_proj.bias (128), linear1.weight (ff,128), linear1.bias (ff),
+ *             linear2.weight (128,ff), linear2.bias (128), reserved
+ *   scalars : HOST array of num_layers x 6 doubles: gauss_scale, gauss_shift, -0.5/scale_real^2, elu beta,
+ *             gauss_lb_real, dist_max
+ *   x       : (N,128) atom features, updated in place
+ *   workspace: cf_encoder_workspace_floats(N, E, ff_dim) floats of device scratch
+ *   attn_events: NULL, or a HOST array of 2 x num_layers cudaEvent_t recorded on `stream` immediately before and
+ *             after each layer's attention kernels (lets a caller time them without splitting the call)
+ * Geometry arguments as in cf_infinite_attn_fwd.  No gradient support (training uses the autograd path).
+ * ---------------------------------------------------------------------------------------------------------- */
+int64_t cf_encoder_workspace_floats(int64_t N, int64_t E, int64_t ff_dim);
+int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars, float *x,
+                       const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                       const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
+                       int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                       int lattice_range, int minimum_range, float *workspace, void *const *attn_events,
+                       void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
  * Pipe-throughput probes for the roofline denominators: `iters` dependent-free FFMA (kind 0) or MUFU.EX2 (kind 1)
  * instructions per thread over a full grid; sink (>= 1 float) receives a value so the loop is not elided.
  * Work per launch = blocks * threads * iters * 8 instructions.

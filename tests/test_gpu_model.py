@@ -62,6 +62,27 @@ def test_training_step_gradients_match_reference_model(golden_model, fused):
     assert checked >= 8
 
 
+def test_one_call_encoder_forward_equals_the_operator_by_operator_path(golden_model):
+    """Inference takes the single-call path (cf_encoder_forward); it must agree with the torch-operator path that
+    training uses, and with the reference's output."""
+    model = build(golden_model).eval()
+    data = batch_of(golden_model)
+    calls = []
+    enc = model.encoder
+    original = enc._forward_native
+    enc._forward_native = lambda *a, **k: (calls.append(1), original(*a, **k))[1]
+    with torch.no_grad():
+        y_native = model(data)
+        enc.native = False
+        y_ops = model(data)
+    assert len(calls) == 1
+    assert rel_err(y_native.cpu().numpy(), y_ops.cpu().numpy()) < 1e-5
+    assert rel_err(y_native.cpu().numpy(), golden_model["y_f64"]) < TOL
+    enc.native = True
+    y_grad = model(data)  # gradients enabled: must not take the inference path
+    assert len(calls) == 1 and y_grad.requires_grad
+
+
 def test_state_dict_keys_are_the_reference_keys(golden_model):
     model = build(golden_model)
     ref_keys = sorted(k[len("state:"):] for k in golden_model if k.startswith("state:"))
