@@ -36,7 +36,7 @@ struct RowArgs {
 __host__ __device__ inline size_t row_smem_floats(int max_atoms, bool with_basis)
 {
     // rel (4) + c (8) + p (8) per atom, then per-warp staging and partial histograms, then 8 lse values
-    return (size_t)max_atoms * 20 + (with_basis ? WARPS * (STAGE_FLOATS + HEADS * KBINS) : 0) + 16;
+    return (size_t)max_atoms * 20 + (with_basis ? WARPS * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + 16 + WARPS * 128;
 }
 
 template <int K>
@@ -49,10 +49,16 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
     float *pj = cj + (size_t)p.max_atoms * 8;                          // [max_atoms][8]
     float *stage = pj + (size_t)p.max_atoms * 8;                       // [WARPS][STAGE_FLOATS]
     float *part = stage + (K > 0 ? WARPS * STAGE_FLOATS : 0);          // [WARPS][8][64]
-    float *lse_s = part + (K > 0 ? WARPS * HEADS * KBINS : 0);         // [8]
+    float *rings = part + (K > 0 ? WARPS * HEADS * KBINS : 0);         // [WARPS][RING_FLOATS]
+    float *lse_s = rings + (K > 0 ? WARPS * RING_FLOATS : 0);          // [8] (+ padding to 16)
+    float *vsum = lse_s + 16;                                          // [WARPS][128] partial sum_j p v
 
     BinAccumulator<KBINS> bins;
-    if (K > 0) bins.init(stage + warp * STAGE_FLOATS, lane, p.basis);
+    CandidateRing ring;
+    if (K > 0) {
+        bins.init(stage + warp * STAGE_FLOATS, lane, p.basis);
+        ring.init(rings + warp * RING_FLOATS, lane);
+    }
 
     for (long long i = blockIdx.x; i < p.N; i += gridDim.x) {
         const long long c = p.batch[i];
@@ -116,6 +122,13 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
         __syncthreads();
 
         if (K > 0) {
+            // ---- per key: the largest of the eight offsets, kept in the spare component of rel
+            for (int j = tid; j < n; j += THREADS) {
+                const float4 ca = *reinterpret_cast<const float4 *>(cj + j * 8);
+                const float4 cb = *reinterpret_cast<const float4 *>(cj + j * 8 + 4);
+                rel[j].w = fmaxf(fmaxf(fmaxf(ca.x, ca.y), fmaxf(ca.z, ca.w)), fmaxf(fmaxf(cb.x, cb.y), fmaxf(cb.z, cb.w)));
+            }
+            __syncthreads();
             // ---- boxes of the row's heads (they depend on the atom and the head, not on the key)
             const float a_own = p.a[i * HEADS + (lane & 7)];
             const int pk_own = packed_box(p.rule, a_own, p.rvlen ? p.rvlen + 3 * c : nullptr);
@@ -125,51 +138,77 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             const bool masked = !__all_sync(FULL, pk_own == uni);
             float a2[8];
             int pk[8];
+            float a2max = -INFINITY;
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
                 a2[h] = __shfl_sync(FULL, a_own, h) * LOG2E;
                 pk[h] = __shfl_sync(FULL, pk_own, h);
+                a2max = fmaxf(a2max, a2[h]);
             }
             const int R1 = box_r1(uni), R2 = box_r2(uni), R3 = box_r3(uni);
-            const unsigned per_key = (unsigned)((2 * R1 + 1) * (2 * R2 + 1) * (2 * R3 + 1));
-            const unsigned total = per_key * (unsigned)n;
-            const unsigned chunk = ((total + WARPS * 32 - 1) / (WARPS * 32)) * 32;  // multiple of 32 per warp
-            const unsigned begin = min(warp * chunk, total), end = min(begin + chunk, total);
+            const int S2 = 2 * R2 + 1, S3 = 2 * R3 + 1;
+            const int translations = (2 * R1 + 1) * S2 * S3;
+            // the four warps split the TRANSLATIONS (balanced for any number of keys); lanes run over the keys, so a
+            // translation vector is warp-uniform and a lane's key stays in registers
+            const int per_warp = (translations + WARPS - 1) / WARPS;
+            const int t_begin = min(warp * per_warp, translations), t_end = min(t_begin + per_warp, translations);
             Cell cell;
             cell.load(p.tvecs + 9 * c);
-            const float F1 = (float)R1, F2 = (float)R2, F3 = (float)R3;
-            TermWalker walk;
-            walk.init(R1, R2, R3, begin + lane);
             bins.clear();
-            for (unsigned base = begin; base < end; base += 32) {
-                const bool valid = base + lane < end;
-                const int j = valid ? walk.row : 0;
-                const float4 r = rel[j];
+            // candidates of the ring -> eight weights each -> accumulation
+            auto consume = [&]() {
+                float d2;
+                int key;
+                const bool got = ring.take(d2, key);
+                const int j = got ? (key & 2047) : 0;
                 const float4 ca = *reinterpret_cast<const float4 *>(cj + j * 8);
                 const float4 cb = *reinterpret_cast<const float4 *>(cj + j * 8 + 4);
                 const float off[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
-                const float f1 = walk.u1 - F1, f2 = walk.u2 - F2, f3 = walk.u3 - F3;
-                const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
-                const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
-                const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
-                const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
-                int i1 = 0, i2 = 0, i3 = 0;
-                if (masked) {
-                    i1 = abs(__float2int_rn(f1)); i2 = abs(__float2int_rn(f2)); i3 = abs(__float2int_rn(f3));
-                }
                 float w[8];
                 float emax = -INFINITY;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
                     float eh = fmaf(a2[h], d2, off[h]);
-                    if (masked && !(i1 <= box_r1(pk[h]) && i2 <= box_r2(pk[h]) && i3 <= box_r3(pk[h]))) eh = -INFINITY;
+                    if (!got || (masked && !key_in_box(key, pk[h]))) eh = -INFINITY;
                     w[h] = ex2(eh);
                     emax = fmaxf(emax, eh);
                 }
-                const float x = fast_sqrt(d2) * p.basis.bin_scale;
-                bins.push(valid && emax > p.basis.floor_log2 && d2 < p.basis.d2_cut, x, w);
-                walk.step();
+                bins.push(emax > p.basis.floor_log2, fast_sqrt(d2) * p.basis.bin_scale, w);
+            };
+            for (int j0 = 0; j0 < n; j0 += 32) {
+                const int j = j0 + lane;
+                const bool live = j < n;
+                const float4 r = rel[live ? j : 0];  // r.w: the key's largest offset
+                // reach of this chunk of keys: no key farther than `far` from the origin, no candidate beyond `reach`
+                // from its key; a translation longer than reach + far cannot produce a candidate (triangle inequality)
+                const float far2 = warp_max(live ? fmaf(r.z, r.z, fmaf(r.y, r.y, r.x * r.x)) : 0.f);
+                const float cmax = warp_max(live ? r.w : -INFINITY);
+                const float reach2 = fminf(__fdividef(p.basis.floor_log2 - cmax, a2max), p.basis.d2_cut);
+                const float bound = sqrtf(fmaxf(reach2, 0.f)) + sqrtf(far2);
+                const float tau2_max = bound * bound * 1.0001f + 1e-4f;
+                // warp-uniform translation counters, n3 fastest as in the reference's loops
+                int n1 = t_begin / (S2 * S3) - R1, n2 = (t_begin / S3) % S2 - R2, n3 = t_begin % S3 - R3;
+                for (int t = t_begin; t < t_end; ++t) {
+                    const float f1 = (float)n1, f2 = (float)n2, f3 = (float)n3;
+                    const float tx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, cell.t1x * f1));
+                    const float ty = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, cell.t1y * f1));
+                    const float tz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, cell.t1z * f1));
+                    if (fmaf(tz, tz, fmaf(ty, ty, tx * tx)) <= tau2_max) {  // warp-uniform
+                        const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
+                        const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
+                        const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
+                        const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                        const int key = masked ? pack_key(j, abs(n1), abs(n2), abs(n3)) : j;
+                        ring.offer(live && fmaf(a2max, d2, r.w) > p.basis.floor_log2 && d2 < p.basis.d2_cut, d2, key);
+                        if (ring.ready()) consume();
+                    }
+                    if (++n3 > R3) {
+                        n3 = -R3;
+                        if (++n2 > R2) { n2 = -R2; ++n1; }
+                    }
+                }
             }
+            if (ring.count > 0) consume();
             // ---- partial histograms -> shared memory, fixed-order sum over the four warps
             bins.flush(part + warp * HEADS * KBINS, KBINS);
             __syncthreads();
@@ -181,12 +220,35 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             __syncthreads();
         }
 
-        // ---- out[h][m] = sum_j p_ij v_j[h][m] + sum_k W[h][m][k] Psi[h][k]; thread = (h, m)
+        // ---- sum_j p_ij v_j: warp w takes keys w, w+4, ...; a lane owns four consecutive channels (one float4 load
+        //      per key); the four partial rows meet in shared memory (the staging area is free by now)
+        {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int hh = lane >> 2;  // head of the lane's channels 4 lane .. 4 lane + 3
+            const float4 *vp = reinterpret_cast<const float4 *>(p.v + a0 * HEADS * HEAD_DIM) + lane;
+            int j = warp;
+            for (; j + 3 * WARPS < n; j += 4 * WARPS) {
+                const float4 v0 = __ldg(vp + (size_t)(j) * 32), v1 = __ldg(vp + (size_t)(j + WARPS) * 32);
+                const float4 v2 = __ldg(vp + (size_t)(j + 2 * WARPS) * 32), v3 = __ldg(vp + (size_t)(j + 3 * WARPS) * 32);
+                const float p0 = pj[j * 8 + hh], p1 = pj[(j + WARPS) * 8 + hh];
+                const float p2 = pj[(j + 2 * WARPS) * 8 + hh], p3 = pj[(j + 3 * WARPS) * 8 + hh];
+                acc.x = fmaf(p0, v0.x, acc.x); acc.y = fmaf(p0, v0.y, acc.y); acc.z = fmaf(p0, v0.z, acc.z); acc.w = fmaf(p0, v0.w, acc.w);
+                acc.x = fmaf(p1, v1.x, acc.x); acc.y = fmaf(p1, v1.y, acc.y); acc.z = fmaf(p1, v1.z, acc.z); acc.w = fmaf(p1, v1.w, acc.w);
+                acc.x = fmaf(p2, v2.x, acc.x); acc.y = fmaf(p2, v2.y, acc.y); acc.z = fmaf(p2, v2.z, acc.z); acc.w = fmaf(p2, v2.w, acc.w);
+                acc.x = fmaf(p3, v3.x, acc.x); acc.y = fmaf(p3, v3.y, acc.y); acc.z = fmaf(p3, v3.z, acc.z); acc.w = fmaf(p3, v3.w, acc.w);
+            }
+            for (; j < n; j += WARPS) {
+                const float4 v0 = __ldg(vp + (size_t)j * 32);
+                const float p0 = pj[j * 8 + hh];
+                acc.x = fmaf(p0, v0.x, acc.x); acc.y = fmaf(p0, v0.y, acc.y); acc.z = fmaf(p0, v0.z, acc.z); acc.w = fmaf(p0, v0.w, acc.w);
+            }
+            reinterpret_cast<float4 *>(vsum)[warp * 32 + lane] = acc;
+        }
+        __syncthreads();
+        // ---- out[h][m] = (sum over the four partial rows) + sum_k W[h][m][k] Psi[h][k]; thread = (h, m)
         {
             const int h = tid >> 4;
-            float acc = 0.f;
-            const float *vp = p.v + a0 * HEADS * HEAD_DIM + tid;
-            for (int j = 0; j < n; ++j) acc = fmaf(pj[j * 8 + h], __ldg(vp + (size_t)j * HEADS * HEAD_DIM), acc);
+            float acc = (vsum[tid] + vsum[128 + tid]) + (vsum[256 + tid] + vsum[384 + tid]);
             if (K > 0) {
                 const float4 *wp = reinterpret_cast<const float4 *>(p.W + (size_t)tid * KBINS);
                 const float4 *pp = reinterpret_cast<const float4 *>(part + h * KBINS);

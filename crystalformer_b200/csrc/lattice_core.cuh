@@ -97,13 +97,50 @@ static __device__ __noinline__ float head_phi_own_min(const Cell &cell, float rx
 // TPE threads (a power of two, consecutive lanes) share one edge: thread `sub` takes the (n1,n2) columns
 // sub, sub + TPE, ... of the box and the partial minimum / sums are combined with shuffles.  More threads per edge
 // give small batches enough warps to hide the latency of the per-term dependency chain.
+// Inner loops over n3 for one (n1,n2) column; R3 = 2 (the usual minimum box) is fully unrolled.
+template <bool UNROLL5>
+__device__ __forceinline__ float column_min(const Cell &cell, float bx, float by, float bz, float F3, float m)
+{
+    if (UNROLL5) {
+#pragma unroll
+        for (int t = -2; t <= 2; ++t) {
+            const float f3 = (float)t;
+            const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
+            m = fminf(m, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
+        }
+    } else {
+        for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
+            const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
+            m = fminf(m, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
+        }
+    }
+    return m;
+}
+
+__device__ __forceinline__ void term_sums(const float (&a2)[8], const float (&lim)[8], float a2max, float rel, float af3,
+                                          float floor_log2, float (&sum)[8])
+{
+    // the term with d2 = m contributes 1 to every sum it belongs to, so a term whose largest weight is below the
+    // floor (2^-40 by default) changes no sum by more than that fraction: skip its eight ex2
+    if (a2max * rel > floor_log2) {
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+            const float w = ex2(a2[h] * rel);
+            if (af3 <= lim[h]) sum[h] += w;
+        }
+    }
+}
+
+// TPE threads (a power of two, consecutive lanes) share one edge: thread `sub` takes the (n1,n2) columns
+// sub, sub + TPE, ... of the box and the partial minimum / sums are combined with shuffles.  More threads per edge
+// give small batches enough warps to hide the latency of the per-term dependency chain.
 template <int TPE>
 __device__ __forceinline__ void edge_phi(const BoxRule &rule, const float (&a)[8], const float *__restrict__ rvlen3,
                                          const Cell &cell, float rx, float ry, float rz, float floor_log2, int sub,
                                          float (&z)[8])
 {
     int pk[8];
-    float a2[8], r1[8], r2[8], r3[8];
+    float a2[8];
     int uni = 0;
     float a2max = -INFINITY;  // the widest Gaussian of the eight: bounds every head's weight from above
 #pragma unroll
@@ -112,26 +149,29 @@ __device__ __forceinline__ void edge_phi(const BoxRule &rule, const float (&a)[8
         a2[h] = a[h] * LOG2E;
         a2max = fmaxf(a2max, a2[h]);
         uni = box_union(uni, pk[h]);
-        r1[h] = (float)box_r1(pk[h]);
-        r2[h] = (float)box_r2(pk[h]);
-        r3[h] = (float)box_r3(pk[h]);
     }
     const float F1 = (float)box_r1(uni), F2 = (float)box_r2(uni), F3 = (float)box_r3(uni);
+    const bool five = box_r3(uni) == 2;
     const float S2 = 2.0f * F2 + 1.0f;
     // column walk: (f1, f2) advances by TPE columns per step, f2 fastest
     float start1 = -F1, start2 = -F2 + (float)sub, step1 = 0.f, step2 = (float)TPE;
     while (start2 > F2) { start2 -= S2; start1 += 1.0f; }
     while (step2 >= S2) { step2 -= S2; step1 += 1.0f; }
 
-    float m = 1e10f;
+    // A column (n1,n2) is the line b + n3 t3; no point of it is closer to the origin than the line itself, whose
+    // squared distance is |b|^2 - (b.t3)^2 / |t3|^2.  Columns that cannot hold the minimum (pass 0) or a weight above
+    // the floor (pass 1) are skipped as a whole.  The bound is shaved by 1e-4 relative + 1e-6 so that rounding can
+    // only make it skip less.
+    const float inv_t3sq = __frcp_rn(fmaf(cell.t3z, cell.t3z, fmaf(cell.t3y, cell.t3y, cell.t3x * cell.t3x)));
+    float m = fmaf(rz, rz, fmaf(ry, ry, rx * rx));  // the n = 0 image belongs to every box
     for (float f1 = start1, f2 = start2; f1 <= F1;) {
         const float bx = fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, rx));
         const float by = fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, ry));
         const float bz = fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, rz));
-        for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
-            const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
-            m = fminf(m, fmaf(dz, dz, fmaf(dy, dy, dx * dx)));
-        }
+        const float bt = fmaf(bz, cell.t3z, fmaf(by, cell.t3y, bx * cell.t3x));
+        const float line2 = fmaf(bz, bz, fmaf(by, by, bx * bx)) - bt * bt * inv_t3sq;
+        if (line2 * 0.9999f - 1e-6f <= m)
+            m = five ? column_min<true>(cell, bx, by, bz, F3, m) : column_min<false>(cell, bx, by, bz, F3, m);
         f2 += step2; f1 += step1;
         if (f2 > F2) { f2 -= S2; f1 += 1.0f; }
     }
@@ -145,21 +185,28 @@ __device__ __forceinline__ void edge_phi(const BoxRule &rule, const float (&a)[8
         const float bx = fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, rx));
         const float by = fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, ry));
         const float bz = fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, rz));
-        float lim[8];
+        const float bt = fmaf(bz, cell.t3z, fmaf(by, cell.t3y, bx * cell.t3x));
+        const float line2 = fmaf(bz, bz, fmaf(by, by, bx * bx)) - bt * bt * inv_t3sq;
+        if (a2max * (line2 * 0.9999f - 1e-6f - m) <= floor_log2) {  // every term of the column is below the floor
+            f2 += step2; f1 += step1;
+            if (f2 > F2) { f2 -= S2; f1 += 1.0f; }
+            continue;
+        }
+        const int i1 = abs(__float2int_rn(f1)), i2 = abs(__float2int_rn(f2));
+        float lim[8];  // head h takes |n3| <= lim[h] in this column (-1: the column is outside its box)
 #pragma unroll
-        for (int h = 0; h < 8; ++h) lim[h] = (fabsf(f1) <= r1[h] && fabsf(f2) <= r2[h]) ? r3[h] : -1.0f;
-        for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
-            const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
-            const float rel = fmaf(dz, dz, fmaf(dy, dy, dx * dx)) - m;
-            // the term with d2 = m contributes 1 to every sum it belongs to, so a term whose largest weight is
-            // below the floor (2^-40 by default) changes no sum by more than that fraction: skip its eight ex2
-            if (a2max * rel > floor_log2) {
-                const float af3 = fabsf(f3);
+        for (int h = 0; h < 8; ++h) lim[h] = (i1 <= box_r1(pk[h]) && i2 <= box_r2(pk[h])) ? (float)box_r3(pk[h]) : -1.0f;
+        if (five) {
 #pragma unroll
-                for (int h = 0; h < 8; ++h) {
-                    const float w = ex2(a2[h] * rel);
-                    if (af3 <= lim[h]) sum[h] += w;
-                }
+            for (int t = -2; t <= 2; ++t) {
+                const float f3 = (float)t;
+                const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
+                term_sums(a2, lim, a2max, fmaf(dz, dz, fmaf(dy, dy, dx * dx)) - m, fabsf(f3), floor_log2, sum);
+            }
+        } else {
+            for (float f3 = -F3; f3 <= F3; f3 += 1.0f) {
+                const float dx = fmaf(cell.t3x, f3, bx), dy = fmaf(cell.t3y, f3, by), dz = fmaf(cell.t3z, f3, bz);
+                term_sums(a2, lim, a2max, fmaf(dz, dz, fmaf(dy, dy, dx * dx)) - m, fabsf(f3), floor_log2, sum);
             }
         }
         f2 += step2; f1 += step1;
@@ -228,6 +275,54 @@ struct TermWalker {
         const bool c1 = u1 >= S1;
         u1 -= c1 ? S1 : 0.f;
         row += drow + (c1 ? 1 : 0);
+    }
+};
+
+// ---- candidate ring ------------------------------------------------------------------------------------------------
+// Most (edge, translation) terms of a large cell are far beyond the reach of every head's Gaussian.  A cheap upper
+// bound on the largest log2-weight of a term (one FMA with the widest Gaussian and the key's largest offset) weeds
+// them out BEFORE the eight per-head exponentials are spent: lanes <-> terms only computes d2 and the bound, survivors
+// (d2, key) are appended to a 64-entry ring in shared memory, and the per-head work runs on full warps of 32
+// candidates taken from the ring.  `key` carries the key index in bits 0..10 and, when heads have different boxes,
+// |n1|, |n2|, |n3| in bits 11..16, 17..22, 23..28.
+constexpr int RING_ENTRIES = 64;
+constexpr int RING_FLOATS = 2 * RING_ENTRIES;
+
+__device__ __forceinline__ int pack_key(int j, int i1, int i2, int i3) { return j | (i1 << 11) | (i2 << 17) | (i3 << 23); }
+__device__ __forceinline__ bool key_in_box(int key, int pk)
+{
+    return ((key >> 11) & 63) <= box_r1(pk) && ((key >> 17) & 63) <= box_r2(pk) && ((key >> 23) & 63) <= box_r3(pk);
+}
+
+struct CandidateRing {
+    float2 *buf;
+    int head, count, lane;
+    __device__ __forceinline__ void init(float *storage, int lane_)
+    {
+        buf = reinterpret_cast<float2 *>(storage);
+        head = count = 0;
+        lane = lane_;
+    }
+    __device__ __forceinline__ void offer(bool cand, float d2, int key)
+    {
+        const unsigned mask = __ballot_sync(FULL, cand);
+        if (mask == 0u) return;  // the common case for large cells: nobody in reach
+        if (cand) buf[(head + count + __popc(mask & ((1u << lane) - 1u))) & (RING_ENTRIES - 1)] = make_float2(d2, __int_as_float(key));
+        count += __popc(mask);
+        __syncwarp();
+    }
+    __device__ __forceinline__ bool ready() const { return count >= 32; }
+    // Hands one entry to each of the first min(count, 32) lanes; returns whether this lane got one.
+    __device__ __forceinline__ bool take(float &d2, int &key)
+    {
+        const int n = min(count, 32);
+        const float2 e = buf[(head + lane) & (RING_ENTRIES - 1)];
+        d2 = e.x;
+        key = __float_as_int(e.y);
+        head = (head + n) & (RING_ENTRIES - 1);
+        count -= n;
+        __syncwarp();
+        return lane < n;
     }
 };
 
