@@ -29,6 +29,7 @@ struct RowArgs {
     float *out, *logit, *lse, *psi_row;
     long long N;
     int max_atoms;
+    int keep_logit;  // 0: inference, the logits are not written back
     BoxRule rule;
     BasisParams basis;
 };
@@ -36,7 +37,9 @@ struct RowArgs {
 __host__ __device__ inline size_t row_smem_floats(int max_atoms, bool with_basis)
 {
     // rel (4) + c (8) + p (8) per atom, then per-warp staging and partial histograms, then 8 lse values
-    return (size_t)max_atoms * 20 + (with_basis ? WARPS * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + 16 + WARPS * 128;
+    const size_t ld = ((max_atoms + 31) & ~31) + 1;
+    return (size_t)max_atoms * 4 + ((16 * ld + 3) & ~(size_t)3) +
+           (with_basis ? WARPS * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + 16 + WARPS * 128;
 }
 
 template <int K>
@@ -45,9 +48,12 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
     extern __shared__ __align__(16) float smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float4 *rel = reinterpret_cast<float4 *>(smem);                    // [max_atoms]
-    float *cj = smem + (size_t)p.max_atoms * 4;                        // [max_atoms][8]
-    float *pj = cj + (size_t)p.max_atoms * 8;                          // [max_atoms][8]
-    float *stage = pj + (size_t)p.max_atoms * 8;                       // [WARPS][STAGE_FLOATS]
+    // per-key tables are head-major with a leading dimension = 1 (mod 32): lanes over keys and lanes over heads both
+    // fall into distinct banks
+    const int ld = ((p.max_atoms + 31) & ~31) + 1;
+    float *cj = smem + (size_t)p.max_atoms * 4;                        // [8][ld] (q.k - lse) log2e
+    float *pj = cj + (size_t)8 * ld;                                   // [8][ld] p_ij
+    float *stage = cj + (((size_t)16 * ld + 3) & ~(size_t)3);          // [WARPS][STAGE_FLOATS]
     float *part = stage + (K > 0 ? WARPS * STAGE_FLOATS : 0);          // [WARPS][8][64]
     float *rings = part + (K > 0 ? WARPS * HEADS * KBINS : 0);         // [WARPS][RING_FLOATS]
     float *lse_s = rings + (K > 0 ? WARPS * RING_FLOATS : 0);          // [8] (+ padding to 16)
@@ -84,6 +90,8 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             }
         }
         // ---- logits and soft-max statistics: warp w owns heads 2w and 2w+1
+        const float *__restrict__ kmat = p.k;
+        float *__restrict__ logit_io = p.logit;
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             const int h = 2 * warp + hh;
@@ -92,22 +100,22 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             for (int t = 0; t < 4; ++t) qv[t] = __ldg(reinterpret_cast<const float4 *>(p.q + (i * HEADS + h) * HEAD_DIM) + t);
             float mx = -INFINITY;
             for (int j = lane; j < n; j += 32) {
-                const float4 *kp = reinterpret_cast<const float4 *>(p.k + ((a0 + j) * HEADS + h) * HEAD_DIM);
+                const float4 *kp = reinterpret_cast<const float4 *>(kmat + ((a0 + j) * HEADS + h) * HEAD_DIM);
                 float s = 0.f;
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
                     const float4 kv = __ldg(kp + t);
                     s = fmaf(qv[t].x, kv.x, s); s = fmaf(qv[t].y, kv.y, s); s = fmaf(qv[t].z, kv.z, s); s = fmaf(qv[t].w, kv.w, s);
                 }
-                const float lg = s + p.logit[(e0 + j) * HEADS + h];  // phi was left here by the phi kernel
-                p.logit[(e0 + j) * HEADS + h] = lg;
-                cj[j * 8 + h] = s;
-                pj[j * 8 + h] = lg;
+                const float lg = s + logit_io[(e0 + j) * HEADS + h];  // phi was left here by the phi kernel
+                if (p.keep_logit) logit_io[(e0 + j) * HEADS + h] = lg;
+                cj[h * ld + j] = s;
+                pj[h * ld + j] = lg;
                 mx = fmaxf(mx, lg);
             }
             mx = warp_max(mx);
             float den = 0.f;
-            for (int j = lane; j < n; j += 32) den += ex2((pj[j * 8 + h] - mx) * LOG2E);
+            for (int j = lane; j < n; j += 32) den += ex2((pj[h * ld + j] - mx) * LOG2E);
             den = warp_sum(den);
             const float lse = mx + logf(den);
             if (lane == 0) {
@@ -115,8 +123,8 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 p.lse[i * HEADS + h] = lse;
             }
             for (int j = lane; j < n; j += 32) {
-                cj[j * 8 + h] = (cj[j * 8 + h] - lse) * LOG2E;
-                pj[j * 8 + h] = ex2((pj[j * 8 + h] - lse) * LOG2E);
+                cj[h * ld + j] = (cj[h * ld + j] - lse) * LOG2E;
+                pj[h * ld + j] = ex2((pj[h * ld + j] - lse) * LOG2E);
             }
         }
         __syncthreads();
@@ -124,9 +132,10 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
         if (K > 0) {
             // ---- per key: the largest of the eight offsets, kept in the spare component of rel
             for (int j = tid; j < n; j += THREADS) {
-                const float4 ca = *reinterpret_cast<const float4 *>(cj + j * 8);
-                const float4 cb = *reinterpret_cast<const float4 *>(cj + j * 8 + 4);
-                rel[j].w = fmaxf(fmaxf(fmaxf(ca.x, ca.y), fmaxf(ca.z, ca.w)), fmaxf(fmaxf(cb.x, cb.y), fmaxf(cb.z, cb.w)));
+                float mxo = cj[j];
+#pragma unroll
+                for (int h = 1; h < 8; ++h) mxo = fmaxf(mxo, cj[h * ld + j]);
+                rel[j].w = mxo;
             }
             __syncthreads();
             // ---- boxes of the row's heads (they depend on the atom and the head, not on the key)
@@ -161,14 +170,11 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 int key;
                 const bool got = ring.take(d2, key);
                 const int j = got ? (key & 2047) : 0;
-                const float4 ca = *reinterpret_cast<const float4 *>(cj + j * 8);
-                const float4 cb = *reinterpret_cast<const float4 *>(cj + j * 8 + 4);
-                const float off[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
                 float w[8];
                 float emax = -INFINITY;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
-                    float eh = fmaf(a2[h], d2, off[h]);
+                    float eh = fmaf(a2[h], d2, cj[h * ld + j]);
                     if (!got || (masked && !key_in_box(key, pk[h]))) eh = -INFINITY;
                     w[h] = ex2(eh);
                     emax = fmaxf(emax, eh);
@@ -230,8 +236,8 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             for (; j + 3 * WARPS < n; j += 4 * WARPS) {
                 const float4 v0 = __ldg(vp + (size_t)(j) * 32), v1 = __ldg(vp + (size_t)(j + WARPS) * 32);
                 const float4 v2 = __ldg(vp + (size_t)(j + 2 * WARPS) * 32), v3 = __ldg(vp + (size_t)(j + 3 * WARPS) * 32);
-                const float p0 = pj[j * 8 + hh], p1 = pj[(j + WARPS) * 8 + hh];
-                const float p2 = pj[(j + 2 * WARPS) * 8 + hh], p3 = pj[(j + 3 * WARPS) * 8 + hh];
+                const float *pr = pj + hh * ld + j;
+                const float p0 = pr[0], p1 = pr[WARPS], p2 = pr[2 * WARPS], p3 = pr[3 * WARPS];
                 acc.x = fmaf(p0, v0.x, acc.x); acc.y = fmaf(p0, v0.y, acc.y); acc.z = fmaf(p0, v0.z, acc.z); acc.w = fmaf(p0, v0.w, acc.w);
                 acc.x = fmaf(p1, v1.x, acc.x); acc.y = fmaf(p1, v1.y, acc.y); acc.z = fmaf(p1, v1.z, acc.z); acc.w = fmaf(p1, v1.w, acc.w);
                 acc.x = fmaf(p2, v2.x, acc.x); acc.y = fmaf(p2, v2.y, acc.y); acc.z = fmaf(p2, v2.z, acc.z); acc.w = fmaf(p2, v2.w, acc.w);
@@ -239,7 +245,7 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             }
             for (; j < n; j += WARPS) {
                 const float4 v0 = __ldg(vp + (size_t)j * 32);
-                const float p0 = pj[j * 8 + hh];
+                const float p0 = pj[hh * ld + j];
                 acc.x = fmaf(p0, v0.x, acc.x); acc.y = fmaf(p0, v0.y, acc.y); acc.z = fmaf(p0, v0.z, acc.z); acc.w = fmaf(p0, v0.w, acc.w);
             }
             reinterpret_cast<float4 *>(vsum)[warp * 32 + lane] = acc;
@@ -302,6 +308,7 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     p.q = q; p.k = k; p.v = v; p.a = a; p.pos = pos; p.pos_ij = pos_ij; p.tvecs = tvecs; p.rvlen = rvlen; p.W = W;
     p.batch = batch; p.edges = edges; p.row_start = row_start; p.E = E;
     p.out = out; p.logit = logit; p.lse = lse; p.psi_row = psi_row; p.N = N; p.max_atoms = (int)max_atoms;
+    p.keep_logit = 1;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
     const size_t smem = sizeof(float) * row_smem_floats((int)max_atoms, K > 0);
