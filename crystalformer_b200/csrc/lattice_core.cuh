@@ -26,14 +26,17 @@ __device__ __forceinline__ int ceil_div_two_pi(float x)
 {
     const double two_pi = 2.0 * (double)3.141592654f;
     if (!(x > 0.0f)) return 0;  // also NaN
-    int r = (int)ceilf(x * 0.15915494f);
+    const float t = x * 0.15915494f;  // x / two_pi to within a few ulp
+    int r = (int)ceilf(t);
     r = min(r, 1 << 20);
+    // unless t is within 1e-4 (relative) of an integer the estimate is already the exact ceiling
+    if ((float)r - t > 1e-4f * t + 1e-6f && t - (float)(r - 1) > 1e-4f * t + 1e-6f) return r;
     while ((double)r * two_pi < (double)x) ++r;
     while (r > 0 && (double)(r - 1) * two_pi >= (double)x) --r;
     return r;
 }
 
-// Half-widths of the box of one (atom, head); same rule and rounding as box_half_widths in common.cuh.
+// Half-widths of the box of one (atom, head), packed as R1 | R2 << 8 | R3 << 16.
 __device__ __forceinline__ int packed_box(const BoxRule &rule, float a, const float *__restrict__ rvlen3)
 {
     int R1 = rule.lattice_range, R2 = R1, R3 = R1;
@@ -143,9 +146,14 @@ __device__ __forceinline__ void edge_phi(const BoxRule &rule, const float (&a)[8
     float a2[8];
     int uni = 0;
     float a2max = -INFINITY;  // the widest Gaussian of the eight: bounds every head's weight from above
+    // the TPE threads of an edge split the eight box computations and exchange the results
+    constexpr int PER = 8 / TPE;
+    int mine[PER];
+#pragma unroll
+    for (int t = 0; t < PER; ++t) mine[t] = packed_box(rule, pick8(a, sub * PER + t), rvlen3);
 #pragma unroll
     for (int h = 0; h < 8; ++h) {
-        pk[h] = packed_box(rule, a[h], rvlen3);
+        pk[h] = TPE == 1 ? mine[h % PER] : __shfl_sync(FULL, mine[h % PER], h / PER, TPE);
         a2[h] = a[h] * LOG2E;
         a2max = fmaxf(a2max, a2[h]);
         uni = box_union(uni, pk[h]);

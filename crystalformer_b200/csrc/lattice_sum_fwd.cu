@@ -216,11 +216,11 @@ __global__ void lattice_box_kernel(const float *a, int a_per_edge, const int64_t
     const int h = (int)(tid % HEADS);
     const long long i = edges[e];
     const long long c = batch[i];
-    int R1, R2, R3;
-    box_half_widths(rule, a[(a_per_edge ? e : i) * HEADS + h], rvlen ? rvlen + 3 * c : nullptr, R1, R2, R3);
-    box[3 * tid + 0] = R1;
-    box[3 * tid + 1] = R2;
-    box[3 * tid + 2] = R3;
+    // the very function the lattice-sum kernels call, so that the bit-exactness test covers what they enumerate
+    const int pk = packed_box(rule, a[(a_per_edge ? e : i) * HEADS + h], rvlen ? rvlen + 3 * c : nullptr);
+    box[3 * tid + 0] = box_r1(pk);
+    box[3 * tid + 1] = box_r2(pk);
+    box[3 * tid + 2] = box_r3(pk);
 }
 
 
