@@ -338,8 +338,9 @@ def run_kernel_case(args):
     k, v = (torch.randn((N, 8, 16), device=device, generator=gen) for _ in range(2))
     a = -0.5 / (1.4 * (1 + 0.1 * torch.randn((N, 8), device=device, generator=gen)).clamp(0.75, 1.4)) ** 2
     W = torch.randn((8, 16, 64), device=device, generator=gen) * 0.1 if K else None
-    run = lambda: ops.infinite_attn_fwd(q, k, v, a, g.pos_ij, d(cb.trans_vec), g.rvlen, g.batch, g.edges, g.row_start,
-                                        g.max_atoms, K, 14.0, 1.0, W, -3.5, 2, 2)
+    tvecs = d(cb.trans_vec)
+    run = lambda: ops.infinite_attn_fwd(q, k, v, a, g.pos_ij, tvecs, g.rvlen, g.batch, g.edges, g.row_start,
+                                        g.max_atoms, K, 14.0, 1.0, W, -3.5, 2, 2, row_order=g.row_order)
     for _ in range(3):
         run()
     torch.cuda.synchronize()
@@ -348,7 +349,7 @@ def run_kernel_case(args):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record(); run(); e.record(); e.synchronize()
         times.append(s.elapsed_time(e))
-    phi_only = lambda: ops.lattice_sum_fwd(a, g.pos_ij, d(cb.trans_vec), g.batch, g.edges, 0, 14.0, 1.0, rvlen=g.rvlen,
+    phi_only = lambda: ops.lattice_sum_fwd(a, g.pos_ij, tvecs, g.batch, g.edges, 0, 14.0, 1.0, rvlen=g.rvlen,
                                            cutoff_radius=-3.5)
     for _ in range(3):
         phi_only()
@@ -358,9 +359,30 @@ def run_kernel_case(args):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record(); phi_only(); e.record(); e.synchronize()
         phi_times.append(s.elapsed_time(e))
+    def graph_ms(fn, reps=20):
+        """Device time per call with the host out of the way: `reps` calls captured in one CUDA graph."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(reps):
+                    fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            best = 1e30
+            for _ in range(5):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(); graph.replay(); e.record(); e.synchronize()
+                best = min(best, s.elapsed_time(e) / reps)
+        torch.cuda.current_stream().wait_stream(side)
+        return best
+
     return {"case": "attention", "workload": args.workload, "crystals": cb.num_crystals, "atoms": N, "edges": cb.num_edges,
             "K": K, "ms_median": float(np.median(times)), "ms_min": float(min(times)),
-            "phi_kernel_alone_ms": float(np.median(phi_times))}
+            "phi_kernel_alone_ms": float(np.median(phi_times)),
+            "device_ms_per_call_graph": graph_ms(run), "device_ms_phi_graph": graph_ms(phi_only)}
 
 
 def lattice_microbench(ops, device, peaks, pairs=250000):

@@ -27,11 +27,12 @@ SIGNATURES = {
     "cf_fused_attn_bwd": [P, P, P, P, P, P, I64, I64, I64, I64, P, P, P, P, P, P, P, P, P],
     "cf_segment_mean_fwd": [P, P, I64, I64, P, P],
     "cf_infinite_attn_fwd": [P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
-                             I32, P, P, P, P, P],
+                             I32, P, P, P, P, P, P],
     "cf_infinite_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
-                             I32, P, P, P, P, P, P, P, P, P, P],
+                             I32, P, P, P, P, P, P, P, P, P, P, P],
     "cf_pipe_probe": [I32, I32, I32, I64, P, P],
-    "cf_encoder_forward": [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, F64, F64, I32, I32, P, P, P],
+    "cf_encoder_forward": [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, F64, F64, I32, I32, P, P, P,
+                           P],
 }
 
 

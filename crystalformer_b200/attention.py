@@ -34,16 +34,24 @@ from .params import LatticeformerParams
 _EDGE_CACHE: "OrderedDict[tuple, tuple]" = OrderedDict()
 
 
-def register_edge_info(edges: Tensor, row_start: Tensor, max_atoms: int) -> None:
+def heaviest_first(row_start: Tensor) -> Tensor:
+    """Atoms sorted by the number of their keys, descending (stable): the order in which the row kernels pick them up."""
+    keys = row_start[1:] - row_start[:-1]
+    return torch.argsort(keys, descending=True, stable=True).to(torch.int32)
+
+
+def register_edge_info(edges: Tensor, row_start: Tensor, max_atoms: int, row_order: Optional[Tensor] = None) -> None:
     """Lets a caller that already knows the CSR offsets and the largest crystal (e.g. the encoder, which builds the
     edge list on the device) avoid the device->host read that ``edge_info`` would need."""
     key = (edges.data_ptr(), tuple(edges.shape), edges.device, edges._version)
-    _EDGE_CACHE[key] = (row_start, int(max_atoms))
+    if row_order is None:
+        row_order = heaviest_first(row_start)
+    _EDGE_CACHE[key] = (row_start, int(max_atoms), row_order)
     while len(_EDGE_CACHE) > 16:
         _EDGE_CACHE.popitem(last=False)
 
 
-def edge_info(edges: Tensor, N: int) -> Tuple[Tensor, int]:
+def edge_info(edges: Tensor, N: int) -> Tuple[Tensor, int, Tensor]:
     key = (edges.data_ptr(), tuple(edges.shape), edges.device, edges._version)
     hit = _EDGE_CACHE.get(key)
     if hit is not None:
@@ -53,7 +61,7 @@ def edge_info(edges: Tensor, N: int) -> Tuple[Tensor, int]:
     row_start = row_start.cumsum(0)
     max_atoms = int((row_start[1:] - row_start[:-1]).max().item()) if N > 0 else 1
     register_edge_info(edges, row_start, max_atoms)
-    return row_start, max_atoms
+    return _EDGE_CACHE[key]
 
 
 class InfiniteAttentionFunction(torch.autograd.Function):
@@ -64,7 +72,7 @@ class InfiniteAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, a, W, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale,
-                cutoff, lattice_range, minimum_range):
+                cutoff, lattice_range, minimum_range, row_order=None):
         q, k, v, a = (t.contiguous().detach() for t in (q, k, v, a))
         W3 = None
         if K > 0:
@@ -72,8 +80,9 @@ class InfiniteAttentionFunction(torch.autograd.Function):
         need_grad = any(ctx.needs_input_grad[:5])
         out, logit, lse, psi_row = ops.infinite_attn_fwd(
             q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W3, cutoff,
-            lattice_range, minimum_range, want_psi_row=need_grad and K > 0)
+            lattice_range, minimum_range, want_psi_row=need_grad and K > 0, row_order=row_order)
         if need_grad:
+            ctx.row_order = row_order
             ctx.save_for_backward(q, k, v, a, W3, pos_ij, tvecs, rvlen, batch, edges, row_start, logit, lse, out, psi_row)
             ctx.cfg = (max_atoms, K, dist_max, wscale, cutoff, lattice_range, minimum_range)
             ctx.w_shape = None if W is None else tuple(W.shape)
@@ -86,11 +95,11 @@ class InfiniteAttentionFunction(torch.autograd.Function):
         gout = gout.contiguous()
         gq, gk, gv, ga = ops.infinite_attn_bwd(
             q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W3, cutoff,
-            lattice_range, minimum_range, logit, lse, out, gout)
+            lattice_range, minimum_range, logit, lse, out, gout, row_order=ctx.row_order)
         gW = None
         if K > 0 and ctx.needs_input_grad[4]:
             gW = torch.einsum("nhd,nhk->hdk", gout, psi_row).reshape(ctx.w_shape)
-        return (gq, gk, gv, ga, gW) + (None,) * 13
+        return (gq, gk, gv, ga, gW) + (None,) * 14
 
 
 def positive_function(name: str):
@@ -281,10 +290,10 @@ class CrystalformerMultiheadAttentionCUDA(Module):
 
         values = None
         if self.fused and not need_weights:
-            row_start, max_atoms = edge_info(edges, N)
+            row_start, max_atoms, row_order = edge_info(edges, N)
             attn = InfiniteAttentionFunction.apply(
                 q_scaled, k, v, a, self.pe_dist_proj, points, tvecs, rvlen, batch_q, edges, row_start, max_atoms, K,
-                float(dist_max), float(P.value_pe_width_scale), cutoff, lattice_range, minimum_range)
+                float(dist_max), float(P.value_pe_width_scale), cutoff, lattice_range, minimum_range, row_order)
             weights = None
         else:
             # the reference's operator split, through the drop-in autograd functions
@@ -303,7 +312,7 @@ class CrystalformerMultiheadAttentionCUDA(Module):
             weights = None
             if need_weights:
                 with torch.no_grad():
-                    row_start, _ = edge_info(edges, N)
+                    row_start = edge_info(edges, N)[0]
                     prob, _ = ops.fused_attn_fwd(q_scaled.detach(), k.detach(), v.detach(), phi.detach(),
                                                  None if values is None else values.detach(), edges, row_start)
                     weights = prob.mean(dim=1)

@@ -154,7 +154,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
                                   const int64_t *batch, const int64_t *edges, const int64_t *row_start, int64_t N,
                                   int64_t B, int64_t E, int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale,
                                   double cutoff_radius, int lattice_range, int minimum_range, float *workspace,
-                                  void *const *attn_events, void *stream)
+                                  const int32_t *row_order, void *const *attn_events, void *stream)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && E >= 0 && num_layers >= 0, CF_ERR_INVALID, "cf_encoder_forward: negative size");
@@ -190,7 +190,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
         rc = cf_infinite_attn_fwd(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS, HEAD_DIM,
                                   E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range, minimum_range, attn,
-                                  logit, lse, nullptr, s);
+                                  logit, lse, nullptr, row_order, s);
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
         if (rc != CF_OK) break;
         st = linear(bl, handle, attn, w[4], x, rows, 128, 128, 1.0f);

@@ -27,6 +27,7 @@ constexpr int KBINS = 64;
 struct BwdRowArgs {
     const float *q, *k, *v, *a, *pos, *pos_ij, *tvecs, *rvlen, *W, *logit, *lse, *out, *gout;
     const int64_t *batch, *edges, *row_start;
+    const int32_t *row_order;
     float *gq, *gk, *gv, *ga, *glogit;
     long long N, E;
     int max_atoms;
@@ -56,7 +57,8 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_bwd_rows_kernel(const B
     float *ga_part = u + (K > 0 ? HEADS * U_STRIDE + WARPS * (BWD_STAGE_FLOATS + 32 * 8) : 0);  // [WARPS][8]
     float *delta_s = ga_part + WARPS * 8;                              // [8]
 
-    for (long long i = blockIdx.x; i < p.N; i += gridDim.x) {
+    for (long long slot = blockIdx.x; slot < p.N; slot += gridDim.x) {
+        const long long i = p.row_order ? p.row_order[slot] : slot;
         const long long c = p.batch[i];
         const long long e0 = p.row_start[i];
         const int n = (int)(p.row_start[i + 1] - e0);
@@ -285,7 +287,8 @@ extern "C" int cf_infinite_attn_bwd(const float *q, const float *k, const float 
                                     int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
                                     const float *W, double cutoff_radius, int lattice_range, int minimum_range,
                                     const float *logit, const float *lse, const float *out, const float *gout, float *gq,
-                                    float *gk, float *gv, float *ga, float *glogit, void *stream)
+                                    float *gk, float *gv, float *ga, float *glogit, const int32_t *row_order,
+                                    void *stream)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_bwd: negative size");
@@ -305,7 +308,7 @@ extern "C" int cf_infinite_attn_bwd(const float *q, const float *k, const float 
     BwdRowArgs p{};
     p.q = q; p.k = k; p.v = v; p.a = a; p.pos = pos; p.pos_ij = pos_ij; p.tvecs = tvecs; p.rvlen = rvlen; p.W = W;
     p.logit = logit; p.lse = lse; p.out = out; p.gout = gout; p.batch = batch; p.edges = edges; p.row_start = row_start;
-    p.gq = gq; p.gk = gk; p.gv = gv; p.ga = ga; p.glogit = glogit; p.N = N; p.E = E; p.max_atoms = (int)max_atoms;
+    p.gq = gq; p.gk = gk; p.gv = gv; p.ga = ga; p.glogit = glogit; p.row_order = row_order; p.N = N; p.E = E; p.max_atoms = (int)max_atoms;
     p.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
     const size_t smem = sizeof(float) * bwd_row_smem_floats((int)max_atoms, K > 0);

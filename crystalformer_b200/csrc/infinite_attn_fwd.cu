@@ -25,6 +25,7 @@ constexpr int KBINS = 64;
 struct RowArgs {
     const float *q, *k, *v, *a, *pos, *pos_ij, *tvecs, *rvlen, *W;
     const int64_t *batch, *edges, *row_start;
+    const int32_t *row_order;  // optional: atoms in the order they are to be processed (heaviest first)
     long long E;
     float *out, *logit, *lse, *psi_row;
     long long N;
@@ -34,67 +35,77 @@ struct RowArgs {
     BasisParams basis;
 };
 
-__host__ __device__ inline size_t row_smem_floats(int max_atoms, bool with_basis)
+// Shared-memory floats of ONE row group (the ROW_WARPS warps that work on one atom).
+__host__ __device__ inline size_t row_group_floats(int max_atoms, bool with_basis, int row_warps)
 {
-    // rel (4) + c (8) + p (8) per atom, then per-warp staging and partial histograms, then 8 lse values
     const size_t ld = ((max_atoms + 31) & ~31) + 1;
     return (size_t)max_atoms * 4 + ((16 * ld + 3) & ~(size_t)3) +
-           (with_basis ? WARPS * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + 16 + WARPS * 128;
+           (with_basis ? row_warps * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + row_warps * 128;
 }
 
-template <int K>
+// ROW_WARPS = 4: one thread block per atom (large crystals: the four warps split the translations).
+// ROW_WARPS = 1: one warp per atom, four atoms per thread block (small crystals: a row is a few thousand terms and
+//                its cost is dominated by the latency of its phases, so four rows progress independently per block
+//                and only warp-level synchronisation is needed).
+template <int K, int ROW_WARPS>
 __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowArgs p)
 {
-    extern __shared__ __align__(16) float smem[];
+    extern __shared__ __align__(16) float smem_all[];
+    constexpr int GROUPS = WARPS / ROW_WARPS;        // row groups per block
+    constexpr int RT = 32 * ROW_WARPS;               // threads per row group
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int group = warp / ROW_WARPS, wr = warp % ROW_WARPS, rt = tid % RT;
+    auto row_sync = [&]() {
+        if (ROW_WARPS == 1) __syncwarp(); else __syncthreads();
+    };
+    float *smem = smem_all + (size_t)group * row_group_floats(p.max_atoms, K > 0, ROW_WARPS);
     float4 *rel = reinterpret_cast<float4 *>(smem);                    // [max_atoms]
     // per-key tables are head-major with a leading dimension = 1 (mod 32): lanes over keys and lanes over heads both
     // fall into distinct banks
     const int ld = ((p.max_atoms + 31) & ~31) + 1;
     float *cj = smem + (size_t)p.max_atoms * 4;                        // [8][ld] (q.k - lse) log2e
     float *pj = cj + (size_t)8 * ld;                                   // [8][ld] p_ij
-    float *stage = cj + (((size_t)16 * ld + 3) & ~(size_t)3);          // [WARPS][STAGE_FLOATS]
-    float *part = stage + (K > 0 ? WARPS * STAGE_FLOATS : 0);          // [WARPS][8][64]
-    float *rings = part + (K > 0 ? WARPS * HEADS * KBINS : 0);         // [WARPS][RING_FLOATS]
-    float *lse_s = rings + (K > 0 ? WARPS * RING_FLOATS : 0);          // [8] (+ padding to 16)
-    float *vsum = lse_s + 16;                                          // [WARPS][128] partial sum_j p v
+    float *stage = cj + (((size_t)16 * ld + 3) & ~(size_t)3);          // [ROW_WARPS][STAGE_FLOATS]
+    float *part = stage + (K > 0 ? ROW_WARPS * STAGE_FLOATS : 0);      // [ROW_WARPS][8][64]
+    float *rings = part + (K > 0 ? ROW_WARPS * HEADS * KBINS : 0);     // [ROW_WARPS][RING_FLOATS]
+    float *vsum = rings + (K > 0 ? ROW_WARPS * RING_FLOATS : 0);       // [ROW_WARPS][128] partial sum_j p v
 
     BinAccumulator<KBINS> bins;
     CandidateRing ring;
     if (K > 0) {
-        bins.init(stage + warp * STAGE_FLOATS, lane, p.basis);
-        ring.init(rings + warp * RING_FLOATS, lane);
+        bins.init(stage + wr * STAGE_FLOATS, lane, p.basis);
+        ring.init(rings + wr * RING_FLOATS, lane);
     }
+    const float *__restrict__ kmat = p.k;
+    float *__restrict__ logit_io = p.logit;
 
-    for (long long i = blockIdx.x; i < p.N; i += gridDim.x) {
+    for (long long slot = (long long)blockIdx.x * GROUPS + group; slot < p.N; slot += (long long)gridDim.x * GROUPS) {
+        const long long i = p.row_order ? p.row_order[slot] : slot;
         const long long c = p.batch[i];
         const long long e0 = p.row_start[i];
         const int n = (int)(p.row_start[i + 1] - e0);  // keys of the row = atoms of the crystal
         const long long a0 = n > 0 ? p.edges[p.E + e0] : 0;  // first atom of the crystal
         if (n > p.max_atoms) {  // the caller understated max_atoms: poison the row instead of overrunning shared memory
-            p.out[i * HEADS * HEAD_DIM + tid] = __int_as_float(0x7fc00000);
+            for (int idx = rt; idx < HEADS * HEAD_DIM; idx += RT) p.out[i * HEADS * HEAD_DIM + idx] = __int_as_float(0x7fc00000);
             continue;
         }
 
         // ---- relative positions of the keys
         if (p.pos_ij) {
-            for (int j = tid; j < n; j += THREADS) {
+            for (int j = rt; j < n; j += RT) {
                 const float *pp = p.pos_ij + 3 * (e0 + j);
                 rel[j] = make_float4(pp[0], pp[1], pp[2], 0.f);
             }
         } else {
             const float pix = p.pos[3 * i], piy = p.pos[3 * i + 1], piz = p.pos[3 * i + 2];
-            for (int j = tid; j < n; j += THREADS) {
+            for (int j = rt; j < n; j += RT) {
                 const float *pp = p.pos + 3 * (a0 + j);
                 rel[j] = make_float4(__fsub_rn(pp[0], pix), __fsub_rn(pp[1], piy), __fsub_rn(pp[2], piz), 0.f);
             }
         }
-        // ---- logits and soft-max statistics: warp w owns heads 2w and 2w+1
-        const float *__restrict__ kmat = p.k;
-        float *__restrict__ logit_io = p.logit;
+        // ---- logits and soft-max statistics: warp wr of the group owns heads wr, wr + ROW_WARPS, ...
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            const int h = 2 * warp + hh;
+        for (int h = wr; h < HEADS; h += ROW_WARPS) {
             float4 qv[4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) qv[t] = __ldg(reinterpret_cast<const float4 *>(p.q + (i * HEADS + h) * HEAD_DIM) + t);
@@ -118,26 +129,23 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             for (int j = lane; j < n; j += 32) den += ex2((pj[h * ld + j] - mx) * LOG2E);
             den = warp_sum(den);
             const float lse = mx + logf(den);
-            if (lane == 0) {
-                lse_s[h] = lse;
-                p.lse[i * HEADS + h] = lse;
-            }
+            if (lane == 0) p.lse[i * HEADS + h] = lse;
             for (int j = lane; j < n; j += 32) {
                 cj[h * ld + j] = (cj[h * ld + j] - lse) * LOG2E;
                 pj[h * ld + j] = ex2((pj[h * ld + j] - lse) * LOG2E);
             }
         }
-        __syncthreads();
+        row_sync();
 
         if (K > 0) {
             // ---- per key: the largest of the eight offsets, kept in the spare component of rel
-            for (int j = tid; j < n; j += THREADS) {
+            for (int j = rt; j < n; j += RT) {
                 float mxo = cj[j];
 #pragma unroll
                 for (int h = 1; h < 8; ++h) mxo = fmaxf(mxo, cj[h * ld + j]);
                 rel[j].w = mxo;
             }
-            __syncthreads();
+            row_sync();
             // ---- boxes of the row's heads (they depend on the atom and the head, not on the key)
             const float a_own = p.a[i * HEADS + (lane & 7)];
             const int pk_own = packed_box(p.rule, a_own, p.rvlen ? p.rvlen + 3 * c : nullptr);
@@ -157,10 +165,10 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             const int R1 = box_r1(uni), R2 = box_r2(uni), R3 = box_r3(uni);
             const int S2 = 2 * R2 + 1, S3 = 2 * R3 + 1;
             const int translations = (2 * R1 + 1) * S2 * S3;
-            // the four warps split the TRANSLATIONS (balanced for any number of keys); lanes run over the keys, so a
-            // translation vector is warp-uniform and a lane's key stays in registers
-            const int per_warp = (translations + WARPS - 1) / WARPS;
-            const int t_begin = min(warp * per_warp, translations), t_end = min(t_begin + per_warp, translations);
+            // the warps of the group split the TRANSLATIONS (balanced for any number of keys); lanes run over the keys,
+            // so a translation vector is warp-uniform and a lane's key stays in registers
+            const int per_warp = (translations + ROW_WARPS - 1) / ROW_WARPS;
+            const int t_begin = min(wr * per_warp, translations), t_end = min(t_begin + per_warp, translations);
             Cell cell;
             cell.load(p.tvecs + 9 * c);
             bins.clear();
@@ -215,48 +223,51 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 }
             }
             if (ring.count > 0) consume();
-            // ---- partial histograms -> shared memory, fixed-order sum over the four warps
-            bins.flush(part + warp * HEADS * KBINS, KBINS);
-            __syncthreads();
-            for (int idx = tid; idx < HEADS * KBINS; idx += THREADS) {
-                const float s = (part[idx] + part[HEADS * KBINS + idx]) + (part[2 * HEADS * KBINS + idx] + part[3 * HEADS * KBINS + idx]);
+            // ---- partial histograms -> shared memory, fixed-order sum over the warps of the group
+            bins.flush(part + wr * HEADS * KBINS, KBINS);
+            row_sync();
+            for (int idx = rt; idx < HEADS * KBINS; idx += RT) {
+                float s = part[idx];
+                if (ROW_WARPS == 4)
+                    s = (part[idx] + part[HEADS * KBINS + idx]) + (part[2 * HEADS * KBINS + idx] + part[3 * HEADS * KBINS + idx]);
                 part[idx] = s;
                 if (p.psi_row) p.psi_row[i * HEADS * KBINS + idx] = s;
             }
-            __syncthreads();
+            row_sync();
         }
 
-        // ---- sum_j p_ij v_j: warp w takes keys w, w+4, ...; a lane owns four consecutive channels (one float4 load
-        //      per key); the four partial rows meet in shared memory (the staging area is free by now)
+        // ---- sum_j p_ij v_j: warp wr takes keys wr, wr + ROW_WARPS, ...; a lane owns four consecutive channels (one
+        //      float4 load per key); the partial rows of the group meet in shared memory
         {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             const int hh = lane >> 2;  // head of the lane's channels 4 lane .. 4 lane + 3
             const float4 *vp = reinterpret_cast<const float4 *>(p.v + a0 * HEADS * HEAD_DIM) + lane;
-            int j = warp;
-            for (; j + 3 * WARPS < n; j += 4 * WARPS) {
-                const float4 v0 = __ldg(vp + (size_t)(j) * 32), v1 = __ldg(vp + (size_t)(j + WARPS) * 32);
-                const float4 v2 = __ldg(vp + (size_t)(j + 2 * WARPS) * 32), v3 = __ldg(vp + (size_t)(j + 3 * WARPS) * 32);
+            int j = wr;
+            for (; j + 3 * ROW_WARPS < n; j += 4 * ROW_WARPS) {
+                const float4 v0 = __ldg(vp + (size_t)(j) * 32), v1 = __ldg(vp + (size_t)(j + ROW_WARPS) * 32);
+                const float4 v2 = __ldg(vp + (size_t)(j + 2 * ROW_WARPS) * 32), v3 = __ldg(vp + (size_t)(j + 3 * ROW_WARPS) * 32);
                 const float *pr = pj + hh * ld + j;
-                const float p0 = pr[0], p1 = pr[WARPS], p2 = pr[2 * WARPS], p3 = pr[3 * WARPS];
+                const float p0 = pr[0], p1 = pr[ROW_WARPS], p2 = pr[2 * ROW_WARPS], p3 = pr[3 * ROW_WARPS];
                 acc.x = fmaf(p0, v0.x, acc.x); acc.y = fmaf(p0, v0.y, acc.y); acc.z = fmaf(p0, v0.z, acc.z); acc.w = fmaf(p0, v0.w, acc.w);
                 acc.x = fmaf(p1, v1.x, acc.x); acc.y = fmaf(p1, v1.y, acc.y); acc.z = fmaf(p1, v1.z, acc.z); acc.w = fmaf(p1, v1.w, acc.w);
                 acc.x = fmaf(p2, v2.x, acc.x); acc.y = fmaf(p2, v2.y, acc.y); acc.z = fmaf(p2, v2.z, acc.z); acc.w = fmaf(p2, v2.w, acc.w);
                 acc.x = fmaf(p3, v3.x, acc.x); acc.y = fmaf(p3, v3.y, acc.y); acc.z = fmaf(p3, v3.z, acc.z); acc.w = fmaf(p3, v3.w, acc.w);
             }
-            for (; j < n; j += WARPS) {
+            for (; j < n; j += ROW_WARPS) {
                 const float4 v0 = __ldg(vp + (size_t)j * 32);
                 const float p0 = pj[hh * ld + j];
                 acc.x = fmaf(p0, v0.x, acc.x); acc.y = fmaf(p0, v0.y, acc.y); acc.z = fmaf(p0, v0.z, acc.z); acc.w = fmaf(p0, v0.w, acc.w);
             }
-            reinterpret_cast<float4 *>(vsum)[warp * 32 + lane] = acc;
+            reinterpret_cast<float4 *>(vsum)[wr * 32 + lane] = acc;
         }
-        __syncthreads();
-        // ---- out[h][m] = (sum over the four partial rows) + sum_k W[h][m][k] Psi[h][k]; thread = (h, m)
-        {
-            const int h = tid >> 4;
-            float acc = (vsum[tid] + vsum[128 + tid]) + (vsum[256 + tid] + vsum[384 + tid]);
+        row_sync();
+        // ---- out[h][m] = (sum over the partial rows) + sum_k W[h][m][k] Psi[h][k]; one output (h, m) per thread and turn
+        for (int idx = rt; idx < HEADS * HEAD_DIM; idx += RT) {
+            const int h = idx >> 4;
+            float acc = vsum[idx];
+            if (ROW_WARPS == 4) acc = (vsum[idx] + vsum[128 + idx]) + (vsum[256 + idx] + vsum[384 + idx]);
             if (K > 0) {
-                const float4 *wp = reinterpret_cast<const float4 *>(p.W + (size_t)tid * KBINS);
+                const float4 *wp = reinterpret_cast<const float4 *>(p.W + (size_t)idx * KBINS);
                 const float4 *pp = reinterpret_cast<const float4 *>(part + h * KBINS);
                 float o = 0.f;
 #pragma unroll 4
@@ -266,9 +277,9 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 }
                 acc += o;
             }
-            p.out[i * HEADS * HEAD_DIM + tid] = acc;
+            p.out[i * HEADS * HEAD_DIM + idx] = acc;
         }
-        __syncthreads();
+        row_sync();
     }
 }
 
@@ -280,7 +291,8 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
                                     const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
                                     int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
                                     const float *W, double cutoff_radius, int lattice_range, int minimum_range,
-                                    float *out, float *logit, float *lse, float *psi_row, void *stream)
+                                    float *out, float *logit, float *lse, float *psi_row, const int32_t *row_order,
+                                    void *stream)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_fwd: negative size");
@@ -306,13 +318,19 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
 
     RowArgs p{};
     p.q = q; p.k = k; p.v = v; p.a = a; p.pos = pos; p.pos_ij = pos_ij; p.tvecs = tvecs; p.rvlen = rvlen; p.W = W;
-    p.batch = batch; p.edges = edges; p.row_start = row_start; p.E = E;
+    p.batch = batch; p.edges = edges; p.row_start = row_start; p.row_order = row_order; p.E = E;
     p.out = out; p.logit = logit; p.lse = lse; p.psi_row = psi_row; p.N = N; p.max_atoms = (int)max_atoms;
     p.keep_logit = 1;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
-    const size_t smem = sizeof(float) * row_smem_floats((int)max_atoms, K > 0);
-    auto kernel = K > 0 ? infinite_attn_rows_kernel<64> : infinite_attn_rows_kernel<0>;
+    // crystals of up to 12 atoms: one warp per atom, four atoms per block; larger ones: one block per atom
+    const bool small = max_atoms <= 12;
+    const int row_warps = small ? 1 : WARPS;
+    const int groups = WARPS / row_warps;
+    const size_t smem = sizeof(float) * groups * row_group_floats((int)max_atoms, K > 0, row_warps);
+    void (*kernel)(const RowArgs) =
+        K > 0 ? (small ? infinite_attn_rows_kernel<64, 1> : infinite_attn_rows_kernel<64, 4>)
+              : (small ? infinite_attn_rows_kernel<0, 1> : infinite_attn_rows_kernel<0, 4>);
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
@@ -320,18 +338,18 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
                         smem, (long long)max_atoms);
         }
     }
-    static thread_local size_t cached_smem[2] = {0, 0};
-    static thread_local int cached_occ[2] = {0, 0};
-    const int slot = K > 0 ? 1 : 0;
+    static thread_local size_t cached_smem[4] = {0, 0, 0, 0};
+    static thread_local int cached_occ[4] = {0, 0, 0, 0};
+    const int slot = (K > 0 ? 2 : 0) + (small ? 1 : 0);
     if (cached_occ[slot] == 0 || cached_smem[slot] != smem) {
         int occ = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, THREADS, smem) != cudaSuccess || occ <= 0) occ = 1;
         cached_occ[slot] = occ;
         cached_smem[slot] = smem;
     }
-    const int occ = cached_occ[slot];
-    const long long cap = (long long)sm_count() * occ;
-    const int blocks = (int)(N < cap ? N : cap);
+    const long long want = (N + groups - 1) / groups;
+    const long long cap = (long long)sm_count() * cached_occ[slot];
+    const int blocks = (int)(want < cap ? want : cap);
     kernel<<<blocks, THREADS, smem, s>>>(p);
     return launch_status("cf_infinite_attn_fwd");
 }

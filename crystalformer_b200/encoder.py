@@ -17,7 +17,7 @@ from torch.nn.init import constant_, xavier_uniform_
 import ctypes
 
 from . import _lib, ops
-from .attention import CrystalformerMultiheadAttentionCUDA, register_edge_info
+from .attention import CrystalformerMultiheadAttentionCUDA, heaviest_first, register_edge_info
 from .cuda_funcs import compile_kernels
 from .params import LatticeformerParams
 
@@ -44,7 +44,8 @@ class BatchGeometry:
         self.batch, self.edges, self.row_start = prep["batch"], prep["edges"], prep["row_start"]
         self.pos_ij, self.rvecs, self.vcell, self.rvlen = prep["pos_ij"], prep["rvecs"], prep["vcell"], prep["rvlen"]
         self.sizes, self.max_atoms = sizes, int(max_atoms)
-        register_edge_info(self.edges, self.row_start, self.max_atoms)
+        self.row_order = heaviest_first(self.row_start)
+        register_edge_info(self.edges, self.row_start, self.max_atoms, self.row_order)
 
 
 class CrystalformerEncoderLayerCUDA(Module):
@@ -201,7 +202,8 @@ class CrystalformerEncoderCUDA(Module):
                       g.rvlen.data_ptr() if cutoff != 0.0 else None, g.batch.data_ptr(), g.edges.data_ptr(),
                       g.row_start.data_ptr(), N, B, E, g.max_atoms, int(P.value_pe_dist_real), w["ff"],
                       float(P.value_pe_width_scale), cutoff, int(P.lattice_range),
-                      int(P.lattice_range) if P.minimum_range else 0, work.data_ptr(), self._attention_events(),
+                      int(P.lattice_range) if P.minimum_range else 0, work.data_ptr(), g.row_order.data_ptr(),
+                      self._attention_events(),
                       torch.cuda.current_stream(dev).cuda_stream)
         return x
 

@@ -209,7 +209,7 @@ def fused_attn_bwd(q, k, v, bij, edges, row_start, prob, out, gout):
 
 
 def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W,
-                      cutoff_radius, lattice_range, minimum_range, want_psi_row=False, pos=None):
+                      cutoff_radius, lattice_range, minimum_range, want_psi_row=False, pos=None, row_order=None):
     """Fused attention forward.  Geometry as pos_ij (E,3), or pos (N,3) when pos_ij is None.
     Returns (out (N,H,D), logit (E,H), lse (N,H), psi_row (N,H,K) or None)."""
     dev = q.device
@@ -230,12 +230,12 @@ def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
                   _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),
                   c_int64(D), c_int64(E), c_int64(K), c_int64(max_atoms), c_double(dist_max), c_double(wscale), _ptr(W),
                   c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(out), _ptr(logit),
-                  _ptr(lse), _ptr(psi_row), _stream(dev))
+                  _ptr(lse), _ptr(psi_row), _ptr(_want(row_order, torch.int32, "row_order", dev)), _stream(dev))
     return out, logit, lse, psi_row
 
 
 def infinite_attn_bwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W,
-                      cutoff_radius, lattice_range, minimum_range, logit, lse, out, gout, pos=None):
+                      cutoff_radius, lattice_range, minimum_range, logit, lse, out, gout, pos=None, row_order=None):
     """Backward of infinite_attn_fwd: (gq, gk, gv, ga).  gq is with respect to the pre-scaled q."""
     dev = q.device
     q, k, v, a, tvecs, logit, lse, out, gout = (_want(t, torch.float32, n, dev) for t, n in (
@@ -255,7 +255,8 @@ def infinite_attn_bwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
                   _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),
                   c_int64(D), c_int64(E), c_int64(K), c_int64(max_atoms), c_double(dist_max), c_double(wscale), _ptr(W),
                   c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(logit), _ptr(lse),
-                  _ptr(out), _ptr(gout), _ptr(gq), _ptr(gk), _ptr(gv), _ptr(ga), _ptr(glogit), _stream(dev))
+                  _ptr(out), _ptr(gout), _ptr(gq), _ptr(gk), _ptr(gv), _ptr(ga), _ptr(glogit),
+                  _ptr(_want(row_order, torch.int32, "row_order", dev)), _stream(dev))
     return gq, gk, gv, ga
 
 

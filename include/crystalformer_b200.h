@@ -181,13 +181,16 @@ int cf_segment_mean_fwd(const float *x, const int64_t *start, int64_t B, int64_t
  *        logit (E,H)  q.k + phi, kept for the backward
  *        lse (N,H)    log sum_j exp(logit)
  *        psi_row (N,H,K) = sum_j p_ij psi_ij (NULL to skip; needed for the gradient of W)
+ *   row_order (N) int32, optional (NULL = 0..N-1): a permutation of the atoms giving the order in which thread blocks
+ *        pick them up.  Atoms of large crystals cost more; listing them first (descending atoms per crystal) balances
+ *        the load.  The results do not depend on it.
  * ---------------------------------------------------------------------------------------------------------- */
 int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
                          const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
                          const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
                          int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
                          const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out,
-                         float *logit, float *lse, float *psi_row, void *stream);
+                         float *logit, float *lse, float *psi_row, const int32_t *row_order, void *stream);
 
 /* Backward of cf_infinite_attn_fwd; phi and psi are recomputed from the geometry.
  *   in : everything the forward read, plus logit, lse, out and gout (N,H,D)
@@ -200,7 +203,7 @@ int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const f
                          int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
                          const float *W, double cutoff_radius, int lattice_range, int minimum_range,
                          const float *logit, const float *lse, const float *out, const float *gout, float *gq,
-                         float *gk, float *gv, float *ga, float *glogit, void *stream);
+                         float *gk, float *gv, float *ga, float *glogit, const int32_t *row_order, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Inference forward of the encoder stack (every layer of CrystalformerEncoderCUDA,
@@ -227,8 +230,8 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
                        const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
                        const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
                        int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
-                       int lattice_range, int minimum_range, float *workspace, void *const *attn_events,
-                       void *stream);
+                       int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
+                       void *const *attn_events, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Pipe-throughput probes for the roofline denominators: `iters` dependent-free FFMA (kind 0) or MUFU.EX2 (kind 1)
