@@ -9,10 +9,12 @@
 //
 // Launch sequence (one stream, no host synchronisation):
 //   lattice_phi_kernel        thread per edge : phi_ij for all heads (lattice_core.cuh), written into `logit`
-//   infinite_attn_rows_kernel CTA per atom i  : logits q.k + phi, their log-sum-exp, p_ij; then the row's
-//                             n_i x (2R1+1)(2R2+1)(2R3+1) terms are split over the four warps, each running the
-//                             lane<->term / lane<->bins turn-around of BinAccumulator; the four partial histograms are
-//                             added in a fixed order (deterministic), projected with W and added to sum_j p_ij v_j.
+//   infinite_attn_rows_kernel CTA per atom i  : logits q.k + phi (one key per thread, all heads), their log-sum-exp and
+//                             p_ij; then the row's (32-key chunk, translation column) work units are dealt round-robin
+//                             to the four warps; each warp scans its units with lanes over keys, four translations
+//                             at a time, keeps the candidates in a ring and accumulates them with the lane<->bins
+//                             turn-around of BinAccumulator; the four partial histograms are added in a fixed order
+//                             (deterministic), projected with W and added to sum_j p_ij v_j.
 #include "lattice_core.cuh"
 
 namespace cf {
@@ -103,27 +105,44 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 rel[j] = make_float4(__fsub_rn(pp[0], pix), __fsub_rn(pp[1], piy), __fsub_rn(pp[2], piz), 0.f);
             }
         }
-        // ---- logits and soft-max statistics: warp wr of the group owns heads wr, wr + ROW_WARPS, ...
+        // ---- the row's query, read back as shared-memory broadcasts (the buffer is reused for sum_j p v later)
+        float4 *qs = reinterpret_cast<float4 *>(vsum);
+        for (int idx = rt; idx < HEADS * HEAD_DIM / 4; idx += RT)
+            qs[idx] = __ldg(reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM) + idx);
+        row_sync();
+        // ---- logits: one key per thread, all eight heads; the key's 512-byte row is 32 independent 16-byte loads
+        for (int j = rt; j < n; j += RT) {
+            const float4 *kp = reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
+            float4 *lp = reinterpret_cast<float4 *>(logit_io + (e0 + j) * HEADS);  // phi was left here by the phi kernel
+            const float4 ph0 = lp[0], ph1 = lp[1];
+            const float phi[8] = {ph0.x, ph0.y, ph0.z, ph0.w, ph1.x, ph1.y, ph1.z, ph1.w};
+            float lg[8];
+#pragma unroll
+            for (int h = 0; h < HEADS; ++h) {
+                float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                for (int t = 0; t < 4; t += 2) {
+                    const float4 k0 = __ldg(kp + 4 * h + t), k1 = __ldg(kp + 4 * h + t + 1);
+                    const float4 q0 = qs[4 * h + t], q1 = qs[4 * h + t + 1];
+                    s0 = fmaf(q0.x, k0.x, s0); s0 = fmaf(q0.y, k0.y, s0); s0 = fmaf(q0.z, k0.z, s0); s0 = fmaf(q0.w, k0.w, s0);
+                    s1 = fmaf(q1.x, k1.x, s1); s1 = fmaf(q1.y, k1.y, s1); s1 = fmaf(q1.z, k1.z, s1); s1 = fmaf(q1.w, k1.w, s1);
+                }
+                const float sc = s0 + s1;
+                lg[h] = sc + phi[h];
+                cj[h * ld + j] = sc;
+                pj[h * ld + j] = lg[h];
+            }
+            if (p.keep_logit) {
+                lp[0] = make_float4(lg[0], lg[1], lg[2], lg[3]);
+                lp[1] = make_float4(lg[4], lg[5], lg[6], lg[7]);
+            }
+        }
+        row_sync();
+        // ---- soft-max statistics: warp wr of the group owns heads wr, wr + ROW_WARPS, ...
 #pragma unroll
         for (int h = wr; h < HEADS; h += ROW_WARPS) {
-            float4 qv[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) qv[t] = __ldg(reinterpret_cast<const float4 *>(p.q + (i * HEADS + h) * HEAD_DIM) + t);
             float mx = -INFINITY;
-            for (int j = lane; j < n; j += 32) {
-                const float4 *kp = reinterpret_cast<const float4 *>(kmat + ((a0 + j) * HEADS + h) * HEAD_DIM);
-                float s = 0.f;
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    const float4 kv = __ldg(kp + t);
-                    s = fmaf(qv[t].x, kv.x, s); s = fmaf(qv[t].y, kv.y, s); s = fmaf(qv[t].z, kv.z, s); s = fmaf(qv[t].w, kv.w, s);
-                }
-                const float lg = s + logit_io[(e0 + j) * HEADS + h];  // phi was left here by the phi kernel
-                if (p.keep_logit) logit_io[(e0 + j) * HEADS + h] = lg;
-                cj[h * ld + j] = s;
-                pj[h * ld + j] = lg;
-                mx = fmaxf(mx, lg);
-            }
+            for (int j = lane; j < n; j += 32) mx = fmaxf(mx, pj[h * ld + j]);
             mx = warp_max(mx);
             float den = 0.f;
             for (int j = lane; j < n; j += 32) den += ex2((pj[h * ld + j] - mx) * LOG2E);
@@ -163,14 +182,14 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 a2max = fmaxf(a2max, a2[h]);
             }
             const int R1 = box_r1(uni), R2 = box_r2(uni), R3 = box_r3(uni);
-            const int S2 = 2 * R2 + 1, S3 = 2 * R3 + 1;
-            const int translations = (2 * R1 + 1) * S2 * S3;
-            // the warps of the group split the TRANSLATIONS (balanced for any number of keys); lanes run over the keys,
-            // so a translation vector is warp-uniform and a lane's key stays in registers
-            const int per_warp = (translations + ROW_WARPS - 1) / ROW_WARPS;
-            const int t_begin = min(wr * per_warp, translations), t_end = min(t_begin + per_warp, translations);
+            const int S2 = 2 * R2 + 1;
+            const int columns = (2 * R1 + 1) * S2;  // a column = the translations (n1, n2, *)
+            const int chunks = (n + 31) >> 5;       // a chunk = 32 keys, one per lane
             Cell cell;
             cell.load(p.tvecs + 9 * c);
+            const float t3sq = fmaf(cell.t3z, cell.t3z, fmaf(cell.t3y, cell.t3y, cell.t3x * cell.t3x));
+            const bool prune = t3sq > 1e-12f;
+            const float inv_t3sq = prune ? __frcp_rn(t3sq) : 0.f;
             bins.clear();
             // candidates of the ring -> eight weights each -> accumulation
             auto consume = [&]() {
@@ -189,8 +208,11 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 }
                 bins.push(emax > p.basis.floor_log2, fast_sqrt(d2) * p.basis.bin_scale, w);
             };
-            for (int j0 = 0; j0 < n; j0 += 32) {
-                const int j = j0 + lane;
+            // Work units are (chunk, column) pairs dealt round-robin to the warps of the group, so that the few dense
+            // columns around the origin are spread over all of them whatever the number of keys.  Lanes run over the
+            // keys of the chunk: a translation is warp-uniform and a lane's key stays in registers.
+            for (int ch = 0; ch < chunks; ++ch) {
+                const int j = 32 * ch + lane;
                 const bool live = j < n;
                 const float4 r = rel[live ? j : 0];  // r.w: the key's largest offset
                 // reach of this chunk of keys: no key farther than `far` from the origin, no candidate beyond `reach`
@@ -200,29 +222,49 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 const float reach2 = fminf(__fdividef(p.basis.floor_log2 - cmax, a2max), p.basis.d2_cut);
                 const float bound = sqrtf(fmaxf(reach2, 0.f)) + sqrtf(far2);
                 const float tau2_max = bound * bound * 1.0001f + 1e-4f;
-                // warp-uniform translation counters, n3 fastest as in the reference's loops
-                int n1 = t_begin / (S2 * S3) - R1, n2 = (t_begin / S3) % S2 - R2, n3 = t_begin % S3 - R3;
-                for (int t = t_begin; t < t_end; ++t) {
-                    const float f1 = (float)n1, f2 = (float)n2, f3 = (float)n3;
-                    const float tx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, cell.t1x * f1));
-                    const float ty = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, cell.t1y * f1));
-                    const float tz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, cell.t1z * f1));
-                    if (fmaf(tz, tz, fmaf(ty, ty, tx * tx)) <= tau2_max) {  // warp-uniform
-                        const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
-                        const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
-                        const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
-                        const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
-                        const int key = masked ? pack_key(j, abs(n1), abs(n2), abs(n3)) : j;
-                        ring.offer(live && fmaf(a2max, d2, r.w) > p.basis.floor_log2 && d2 < p.basis.d2_cut, d2, key);
-                        if (ring.ready()) consume();
+                int n1 = -R1, n2 = -R2;
+                for (int col = 0; col < columns; ++col) {
+                    if ((col * chunks + ch) % ROW_WARPS == wr) {
+                        const float f1 = (float)n1, f2 = (float)n2;
+                        // the n3 of this column whose translation n1 t1 + n2 t2 + n3 t3 is no longer than the bound
+                        const float bx = fmaf(cell.t2x, f2, cell.t1x * f1), by = fmaf(cell.t2y, f2, cell.t1y * f1);
+                        const float bz = fmaf(cell.t2z, f2, cell.t1z * f1);
+                        const float bb = fmaf(bz, bz, fmaf(by, by, bx * bx));
+                        const float bt = fmaf(bz, cell.t3z, fmaf(by, cell.t3y, bx * cell.t3x));
+                        const float room = fmaf(bb, 1e-5f, tau2_max) - fmaf(-bt * bt, inv_t3sq, bb);  // slack for rounding
+                        int lo = -R3, hi = R3;
+                        if (prune) {
+                            const float half = sqrtf(fmaxf(room, 0.f) * inv_t3sq) + 1e-3f, mid = -bt * inv_t3sq;
+                            lo = max(lo, __float2int_ru(mid - half));
+                            hi = min(hi, __float2int_rd(mid + half));
+                            if (room < 0.f) hi = lo - 1;
+                        }
+                        // r + n1 t1 + n2 t2, contracted like the reference's expression
+                        const float ex = fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x));
+                        const float ey = fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y));
+                        const float ez = fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z));
+                        for (int n3 = lo; n3 <= hi; n3 += 4) {
+                            const float f3 = (float)n3;
+                            bool cand[4];
+                            float d2v[4];
+                            int key[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const float fu = f3 + (float)u;
+                                const float dx = fmaf(cell.t3x, fu, ex), dy = fmaf(cell.t3y, fu, ey), dz = fmaf(cell.t3z, fu, ez);
+                                d2v[u] = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                                cand[u] = live && n3 + u <= hi && fmaf(a2max, d2v[u], r.w) > p.basis.floor_log2 &&
+                                          d2v[u] < p.basis.d2_cut;
+                                key[u] = masked ? pack_key(j, abs(n1), abs(n2), abs(n3 + u)) : j;
+                            }
+                            ring.offer4(cand, d2v, key);
+                            while (ring.ready()) consume();
+                        }
                     }
-                    if (++n3 > R3) {
-                        n3 = -R3;
-                        if (++n2 > R2) { n2 = -R2; ++n1; }
-                    }
+                    if (++n2 > R2) { n2 = -R2; ++n1; }
                 }
             }
-            if (ring.count > 0) consume();
+            while (ring.count > 0) consume();
             // ---- partial histograms -> shared memory, fixed-order sum over the warps of the group
             bins.flush(part + wr * HEADS * KBINS, KBINS);
             row_sync();
@@ -269,13 +311,13 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             if (K > 0) {
                 const float4 *wp = reinterpret_cast<const float4 *>(p.W + (size_t)idx * KBINS);
                 const float4 *pp = reinterpret_cast<const float4 *>(part + h * KBINS);
-                float o = 0.f;
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll 4
                 for (int k4 = 0; k4 < KBINS / 4; ++k4) {
                     const float4 wv = __ldg(wp + k4), ps = pp[k4];
-                    o = fmaf(wv.x, ps.x, o); o = fmaf(wv.y, ps.y, o); o = fmaf(wv.z, ps.z, o); o = fmaf(wv.w, ps.w, o);
+                    o0 = fmaf(wv.x, ps.x, o0); o1 = fmaf(wv.y, ps.y, o1); o2 = fmaf(wv.z, ps.z, o2); o3 = fmaf(wv.w, ps.w, o3);
                 }
-                acc += o;
+                acc += (o0 + o1) + (o2 + o3);
             }
             p.out[i * HEADS * HEAD_DIM + idx] = acc;
         }

@@ -289,11 +289,11 @@ struct TermWalker {
 // ---- candidate ring ------------------------------------------------------------------------------------------------
 // Most (edge, translation) terms of a large cell are far beyond the reach of every head's Gaussian.  A cheap upper
 // bound on the largest log2-weight of a term (one FMA with the widest Gaussian and the key's largest offset) weeds
-// them out BEFORE the eight per-head exponentials are spent: lanes <-> terms only computes d2 and the bound, survivors
-// (d2, key) are appended to a 64-entry ring in shared memory, and the per-head work runs on full warps of 32
-// candidates taken from the ring.  `key` carries the key index in bits 0..10 and, when heads have different boxes,
-// |n1|, |n2|, |n3| in bits 11..16, 17..22, 23..28.
-constexpr int RING_ENTRIES = 64;
+// them out BEFORE the eight per-head exponentials are spent: lanes <-> keys only computes d2 and the bound for FOUR
+// translations at a time (independent dependency chains), survivors (d2, key) are appended to a 256-entry ring in
+// shared memory, and the per-head work runs on full warps of 32 candidates taken from the ring.  `key` carries the
+// key index in bits 0..10 and, when heads have different boxes, |n1|, |n2|, |n3| in bits 11..16, 17..22, 23..28.
+constexpr int RING_ENTRIES = 256;  // >= 31 left over + 4 x 32 offered + slack, power of two
 constexpr int RING_FLOATS = 2 * RING_ENTRIES;
 
 __device__ __forceinline__ int pack_key(int j, int i1, int i2, int i3) { return j | (i1 << 11) | (i2 << 17) | (i3 << 23); }
@@ -311,12 +311,22 @@ struct CandidateRing {
         head = count = 0;
         lane = lane_;
     }
-    __device__ __forceinline__ void offer(bool cand, float d2, int key)
+    // Appends the lanes' candidates of four translations (in translation order, lanes ascending within each).
+    // The caller keeps count < 32 before the call, so the ring cannot overflow.
+    __device__ __forceinline__ void offer4(const bool (&cand)[4], const float (&d2)[4], const int (&key)[4])
     {
-        const unsigned mask = __ballot_sync(FULL, cand);
-        if (mask == 0u) return;  // the common case for large cells: nobody in reach
-        if (cand) buf[(head + count + __popc(mask & ((1u << lane) - 1u))) & (RING_ENTRIES - 1)] = make_float2(d2, __int_as_float(key));
-        count += __popc(mask);
+        unsigned m[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) m[u] = __ballot_sync(FULL, cand[u]);
+        if ((m[0] | m[1] | m[2] | m[3]) == 0u) return;  // the common case for large cells: nobody in reach
+        const unsigned lt = (1u << lane) - 1u;
+        int at = head + count;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (cand[u]) buf[(at + __popc(m[u] & lt)) & (RING_ENTRIES - 1)] = make_float2(d2[u], __int_as_float(key[u]));
+            at += __popc(m[u]);
+        }
+        count = at - head;
         __syncwarp();
     }
     __device__ __forceinline__ bool ready() const { return count >= 32; }
@@ -446,10 +456,32 @@ struct BinAccumulator {
         }
     }
 
+    // Entries [begin, end) of the stage belong to one window; four are kept in flight so that the shared-memory
+    // loads and the ex2 of one entry overlap the FMAs of the others.
     __device__ __forceinline__ void sweep_window(int begin, int end, float centre, int base)
     {
-#pragma unroll 2
-        for (int m = begin; m < end; ++m) {
+        int m = begin;
+        for (; m + 4 <= end; m += 4) {
+            float g[4];
+            float4 wa[4], wb[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4 *row = reinterpret_cast<const float4 *>(stage + 12 * (m + u));
+                const float t = centre - row[0].x;
+                wa[u] = row[1];
+                wb[u] = row[2];
+                g[u] = ex2(-t * t);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float2 G = make_float2(g[u], g[u]);
+                acc[base + 0] = fma2(make_float2(wa[u].x, wa[u].y), G, acc[base + 0]);
+                acc[base + 1] = fma2(make_float2(wa[u].z, wa[u].w), G, acc[base + 1]);
+                acc[base + 2] = fma2(make_float2(wb[u].x, wb[u].y), G, acc[base + 2]);
+                acc[base + 3] = fma2(make_float2(wb[u].z, wb[u].w), G, acc[base + 3]);
+            }
+        }
+        for (; m < end; ++m) {
             const float4 *row = reinterpret_cast<const float4 *>(stage + 12 * m);
             const float t = centre - row[0].x;
             const float4 wa = row[1], wb = row[2];

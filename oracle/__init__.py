@@ -323,3 +323,62 @@ def ref_irregular_mean(x, sizes, K=64):
     ref_lib(K).cfref_irregular_mean_fwd(c_longlong((B * D + bsz - 1) // bsz), c_int(bsz), _p(x), _p(start),
                                         c_longlong(B), c_longlong(D), _p(out))
     return out
+
+
+# ---- reciprocal-space lattice sum ---------------------------------------------------------------------------------
+def reci_phase(pos_ij, rvecs, batch, edges):
+    """kr_base (E,3) = rvecs[crystal of the edge] . pos_ij; see cf_oracle.c cfo_reci_phase."""
+    pos_ij, rvecs, batch, edges = _f32(pos_ij), _f32(rvecs), _i64(batch), _i64(edges)
+    E = edges.shape[1]
+    kr = np.zeros((E, 3), np.float32)
+    lib().cfo_reci_phase_f32(_p(pos_ij), _p(rvecs), _p(batch), _p(edges), c_longlong(E), _p(kr))
+    return kr
+
+
+def reci_sum_fwd(a, kr_base, rvecs, vcell, batch, edges, lattice_range=2, nested=False, precision="f32"):
+    """phi (E,H) and the raw sum S (E,H); see cf_oracle.c cfo_reci_sum_fwd."""
+    dt = _np_dtype(precision)
+    a, kr_base, rvecs, vcell, batch, edges = _f32(a), _f32(kr_base), _f32(rvecs), _f32(vcell), _i64(batch), _i64(edges)
+    N, H, E = a.shape[0], a.shape[1], edges.shape[1]
+    z, s = np.zeros((E, H), dt), np.zeros((E, H), dt)
+    getattr(lib(), f"cfo_reci_sum_fwd_{precision}")(
+        _p(a), _p(kr_base), _p(rvecs), _p(vcell), _p(batch), _p(edges), c_longlong(N), c_longlong(H), c_longlong(E),
+        c_int(lattice_range), c_int(int(nested)), _p(z), _p(s))
+    return z, s
+
+
+def reci_sum_bwd(a, kr_base, rvecs, batch, edges, gz, sumexp, lattice_range=2, nested=False, precision="f32"):
+    """ga (N,H); see cf_oracle.c cfo_reci_sum_bwd."""
+    dt = _np_dtype(precision)
+    a, kr_base, rvecs, batch, edges = _f32(a), _f32(kr_base), _f32(rvecs), _i64(batch), _i64(edges)
+    gz, sumexp = _real(gz, dt), _real(sumexp, dt)
+    N, H, E = a.shape[0], a.shape[1], edges.shape[1]
+    start = row_starts(edges, N)
+    ga = np.zeros((N, H), dt)
+    getattr(lib(), f"cfo_reci_sum_bwd_{precision}")(
+        _p(a), _p(kr_base), _p(rvecs), _p(batch), _p(start), _p(gz), _p(sumexp), c_longlong(N), c_longlong(H),
+        c_longlong(E), c_int(lattice_range), c_int(int(nested)), _p(ga))
+    return ga
+
+
+def ref_reci_enc_fwd(a, kr_base, rvecs, vcell, batch, edges, K=64):
+    """The reference's reci_enc_fwd.cu compiled for the CPU (LATTICE_RANGE = 2)."""
+    a, kr_base, rvecs, vcell, batch, edges = _f32(a), _f32(kr_base), _f32(rvecs), _f32(vcell), _i64(batch), _i64(edges)
+    N, H, E = a.shape[0], a.shape[1], edges.shape[1]
+    z, s = np.zeros((E, H), np.float32), np.zeros((E, H), np.float32)
+    ref_lib(K).cfref_reci_enc_fwd(c_longlong(E), c_int(H), _p(a), _p(kr_base), _p(rvecs), _p(vcell), _p(batch),
+                                  _p(edges), c_longlong(N), c_longlong(H), c_longlong(E), _p(z), _p(s))
+    return z, s
+
+
+def ref_reci_enc_bwd(a, kr_base, rvecs, vcell, batch, edges, z, gz, sumexp, K=64):
+    """The reference's reci_enc_bwd.cu compiled for the CPU (LATTICE_RANGE = 2)."""
+    a, kr_base, rvecs, vcell, batch, edges = _f32(a), _f32(kr_base), _f32(rvecs), _f32(vcell), _i64(batch), _i64(edges)
+    z, gz, sumexp = _f32(z), _f32(gz), _f32(sumexp)
+    N, H, E = a.shape[0], a.shape[1], edges.shape[1]
+    start = row_starts(edges, N)
+    ga = np.zeros((N, H), np.float32)
+    ref_lib(K).cfref_reci_enc_bwd(c_longlong(N), c_int(H), _p(a), _p(kr_base), _p(rvecs), _p(vcell), _p(batch),
+                                  _p(edges), _p(start), _p(z), _p(gz), _p(sumexp), c_longlong(N), c_longlong(H),
+                                  c_longlong(E), _p(ga))
+    return ga

@@ -472,3 +472,90 @@ void FN(cfo_segment_mean)(const REAL *x, const i64 *start, i64 B, i64 D, REAL *o
         }
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Reciprocal-space lattice sum, forward and backward.
+ * Follows models/kernels/reci_enc_fwd.cu:16-67 and reci_enc_bwd.cu:19-70 (`nested` = the per-loop partial sums
+ * of reci_enc_fwd_v2.cu:49-58 / reci_enc_bwd_v2.cu:57-66), and the phase handed to them,
+ * kr_base = rvecs[b] . pos_ij (models/indexed_latticeformer_encoder.py:249-251).
+ *   S[e,h]   = sum over n1 in [0,R], n2,n3 in [-R,R] of w(n1) exp(a |k_n|^2) cos(kr . n),  w(0) = 1, else 2,
+ *              k_n = n1 r1 + n2 r2 + n3 r3 (rows of rvecs), a = a[i,h] < 0
+ *   phi[e,h] = log max(S, 1e-6) + 1.5 log(-4 pi a) - log V
+ *   ga[i,h]  = sum_{e of row i} gz[e,h] (S < 1e-6 ? 0 : 1/S) sum_n w |k_n|^2 exp(a |k_n|^2) cos(kr . n)
+ * (the reference's backward does not differentiate the 1.5 log(-4 pi a) term; neither does this).
+ * ---------------------------------------------------------------------------------------- */
+void FN(cfo_reci_phase)(const float *pos_ij, const float *rvecs, const i64 *batch, const i64 *edges, i64 E,
+                        float *kr_base)
+{
+    for (i64 e = 0; e < E; e++) {
+        const float *r = rvecs + 9 * batch[edges[e]], *p = pos_ij + 3 * e;
+        for (int d = 0; d < 3; d++) kr_base[3 * e + d] = r[3 * d] * p[0] + r[3 * d + 1] * p[1] + r[3 * d + 2] * p[2];
+    }
+}
+
+static REAL reci_terms(REAL a, const float *kr, const float *r, int R, int nested, int weighted)
+{
+    REAL sum = 0;
+    for (int n1 = 0; n1 <= R; n1++) {
+        const REAL scale = n1 == 0 ? 1 : 2;
+        REAL s1 = 0;
+        for (int n2 = -R; n2 <= R; n2++) {
+            REAL s2 = 0;
+            for (int n3 = -R; n3 <= R; n3++) {
+                const REAL k1 = (REAL)r[0] * n1 + (REAL)r[3] * n2 + (REAL)r[6] * n3;
+                const REAL k2 = (REAL)r[1] * n1 + (REAL)r[4] * n2 + (REAL)r[7] * n3;
+                const REAL k3 = (REAL)r[2] * n1 + (REAL)r[5] * n2 + (REAL)r[8] * n3;
+                const REAL kk = k1 * k1 + k2 * k2 + k3 * k3;
+                const REAL arg = (REAL)kr[0] * n1 + (REAL)kr[1] * n2 + (REAL)kr[2] * n3;
+                const REAL c = sizeof(REAL) == 4 ? (REAL)cosf((float)arg) : (REAL)cos((double)arg);
+                const REAL t = (weighted ? kk * r_exp(a * kk) : r_exp(a * kk)) * c * scale;
+                if (nested) s2 += t; else sum += t;
+            }
+            if (nested) s1 += s2;
+        }
+        if (nested) sum += s1;
+    }
+    return sum;
+}
+
+void FN(cfo_reci_sum_fwd)(const float *a, const float *kr_base, const float *rvecs, const float *vcell,
+                          const i64 *batch, const i64 *edges, i64 N, i64 H, i64 E, int lattice_range, int nested,
+                          REAL *z_out, REAL *sum_out)
+{
+    (void)N;
+#pragma omp parallel for schedule(dynamic, 64)
+    for (i64 e = 0; e < E; e++) {
+        const i64 i = edges[e], b = batch[i];
+        for (i64 h = 0; h < H; h++) {
+            const REAL ah = a[i * H + h];
+            const REAL s = reci_terms(ah, kr_base + 3 * e, rvecs + 9 * b, lattice_range, nested, 0);
+            const REAL c4pi = sizeof(REAL) == 4 ? (REAL)12.5663706144f : (REAL)12.5663706144;
+            const REAL log_ci = (REAL)1.5 * r_log(-c4pi * ah) - r_log((REAL)vcell[b]);
+            const REAL floor_ = sizeof(REAL) == 4 ? (REAL)1e-6f : (REAL)1e-6;
+            z_out[e * H + h] = r_log(s > floor_ ? s : floor_) + log_ci;
+            if (sum_out) sum_out[e * H + h] = s;
+        }
+    }
+}
+
+void FN(cfo_reci_sum_bwd)(const float *a, const float *kr_base, const float *rvecs, const i64 *batch,
+                          const i64 *row_start, const REAL *gz, const REAL *sum_in, i64 N, i64 H, i64 E,
+                          int lattice_range, int nested, REAL *ga)
+{
+    (void)E;
+#pragma omp parallel for schedule(dynamic, 8)
+    for (i64 i = 0; i < N; i++) {
+        const i64 b = batch[i];
+        for (i64 h = 0; h < H; h++) {
+            const REAL ah = a[i * H + h];
+            REAL acc = 0;
+            for (i64 e = row_start[i]; e < row_start[i + 1]; e++) {
+                const REAL s = reci_terms(ah, kr_base + 3 * e, rvecs + 9 * b, lattice_range, nested, 1);
+                const REAL se = sum_in[e * H + h];
+                const REAL floor_ = sizeof(REAL) == 4 ? (REAL)1e-6f : (REAL)1e-6;
+                acc += s * gz[e * H + h] * (se < floor_ ? (REAL)0 : (REAL)1 / se);
+            }
+            ga[i * H + h] = acc;
+        }
+    }
+}

@@ -3,7 +3,7 @@
  * Each `cfref_<kernel>` runs the reference kernel of that name over a 1-D grid with OpenMP across blocks and takes
  * exactly the kernel's own arguments, preceded by (grid, block) as the reference's Python wrappers compute them
  * (models/cuda_funcs/real_space_enc.py:79,99 ; real_space_enc_proj.py:53,72 ; fused_dpa.py:39-57,162-206 ;
- * irregular_mean.py:43-55).
+ * irregular_mean.py:43-55 ; reci_space_enc.py:41-56,76-95).
  */
 #include "cuda_on_cpu.h"
 
@@ -47,6 +47,10 @@ void fused_dpa_bwd(const float *, const float *, const float *, const float *, c
 void fused_dpa_bwd_q(const float *, const float *, const lli *, const lli *, const lli, const lli, const lli, float *);
 void irregular_transpose(const float *, const lli *, const lli *, const lli *, const lli, const lli, float *);
 void irregular_mean_fwd(const float *, const lli *, const lli, const lli, float *);
+void reci_enc_fwd(const float *, const float *, const float *, const float *, const lli *, const lli *, const lli,
+                  const lli, const lli, float *, float *);
+void reci_enc_bwd(const float *, const float *, const float *, const float *, const lli *, const lli *, const lli *,
+                  const float *, const float *, const float *, const lli, const lli, const lli, float *);
 
 void cfref_real_enc_fwd(lli grid, int block, const float *a, const float *rpos, const float *d2min, const float *tv,
                         const lli *batch, const lli *edges, lli N, lli H, lli E, lli K, double dist_max, double wscale,
@@ -103,5 +107,16 @@ void cfref_irregular_transpose(lli grid, int block, const float *src, const lli 
 void cfref_irregular_mean_fwd(lli grid, int block, const float *src, const lli *start, lli B, lli D, float *dst)
 {
     run_grid(grid, block, [&] { irregular_mean_fwd(src, start, B, D, dst); });
+}
+void cfref_reci_enc_fwd(lli grid, int block, const float *a, const float *kr, const float *rvecs, const float *vcell,
+                        const lli *batch, const lli *edges, lli N, lli H, lli E, float *z, float *sumexp)
+{
+    run_grid(grid, block, [&] { reci_enc_fwd(a, kr, rvecs, vcell, batch, edges, N, H, E, z, sumexp); });
+}
+void cfref_reci_enc_bwd(lli grid, int block, const float *a, const float *kr, const float *rvecs, const float *vcell,
+                        const lli *batch, const lli *edges, const lli *e_start, const float *z, const float *gz,
+                        const float *sumexp, lli N, lli H, lli E, float *ga)
+{
+    run_grid(grid, block, [&] { reci_enc_bwd(a, kr, rvecs, vcell, batch, edges, e_start, z, gz, sumexp, N, H, E, ga); });
 }
 }

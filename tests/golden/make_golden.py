@@ -5,12 +5,16 @@ Run in a container where the reference tree is mounted (default /root/reference;
     python tests/golden/make_golden.py
 
 The reference cannot travel to the GPU machines, so its outputs are committed here as small .npz files together with
-this script.  Two files are written:
+this script.  Three files are written (name them on the command line to regenerate only some):
 
 * golden_ops.npz   - operator level: phi, psi, W psi, the edge-indexed attention and all their gradients for a small
                      ragged batch, from LogSumExpXYFunc / AverageGaussiansBySoftmaxXYFunc_ /
                      _scaled_dot_product_attention (models/indexed_lattice_multi_head_attention.py:309,741,140), in
                      float32 and float64.  The PyTorch path enumerates the fixed (2R+1)^3 translation box.
+* golden_reci.npz  - the reciprocal-space lattice sum (compute_reci_domain_attn,
+                     models/indexed_lattice_multi_head_attention.py:925-950, on the cos_kr / k2 tables of
+                     compute_lattice_distances(output_rec=True), models/indexed_latticeformer_encoder.py:140-162) and
+                     its autograd gradient, float32 and float64.
 * golden_model.npz - model level: a 2-layer Latticeformer (models/latticeformer.py) with random-init weights, its
                      state_dict, inputs, per-crystal outputs and a few parameter gradients of an L1 training step.
 """
@@ -35,7 +39,7 @@ from crystalformer_b200.synthetic import make_crystals, uniform_atoms  # noqa: E
 
 from models.indexed_latticeformer_encoder import compute_lattice_distances  # noqa: E402
 from models.indexed_lattice_multi_head_attention import (  # noqa: E402
-    AverageGaussiansBySoftmaxXYFunc_, LogSumExpXYFunc, _scaled_dot_product_attention)
+    AverageGaussiansBySoftmaxXYFunc_, LogSumExpXYFunc, _scaled_dot_product_attention, compute_reci_domain_attn)
 from models.latticeformer import Latticeformer  # noqa: E402
 
 H, D, K = 8, 16, 64
@@ -80,6 +84,25 @@ def ops_case(dtype):
     return inp, {n: x.detach().numpy() for n, x in res.items()}
 
 
+def reci_case(dtype):
+    cb = make_crystals(13, 7, uniform_atoms(1, 6), length_range=(3.0, 9.0))
+    rng = np.random.default_rng(6)
+    N = cb.num_atoms
+    # a = -0.5 (scale_reci func)^2 with widths of 0.8 .. 2.4 Angstrom: the R = 2 sum is then far from its 1e-6 clamp
+    inp = dict(sizes=cb.sizes, pos=cb.pos, trans=cb.trans_vec, batch=cb.batch,
+               a=(-0.5 * (0.8 + 1.6 * rng.random((N, H))) ** 2).astype(np.float32))
+    t = {n: torch.tensor(x).to(dtype) if x.dtype.kind == "f" else torch.tensor(x) for n, x in inp.items()}
+    _, cos_kr, k2, vcell, _, edges, _ = compute_lattice_distances(t["pos"], t["batch"], t["trans"], t["sizes"],
+                                                                  LATTICE_RANGE, output_dis=False, output_rec=True)
+    a = t["a"].clone().requires_grad_(True)
+    phi = compute_reci_domain_attn(a, cos_kr, k2, vcell, edges[0], t["batch"])
+    gz = torch.tensor(rng.standard_normal((edges.shape[1], H))).to(dtype)
+    (phi * gz).sum().backward()
+    inp["gz"] = gz.numpy().astype(np.float32)
+    res = dict(edges=edges, phi=phi, g_a=a.grad, vcell=vcell)
+    return inp, {n: x.detach().numpy() for n, x in res.items()}
+
+
 def model_case():
     P = json.load(open(os.path.join(REF, "params/latticeformer/default.json")))
     P.update(num_layers=2, ff_dim=128, embedding_dim=[64])
@@ -113,18 +136,28 @@ def model_case():
 
 
 def main():
-    inp, r32 = ops_case(torch.float32)
-    _, r64 = ops_case(torch.float64)
-    blob = {f"in_{n}": x for n, x in inp.items()}
-    blob.update({f"f32_{n}": x for n, x in r32.items()})
-    blob.update({f"f64_{n}": x for n, x in r64.items()})
-    np.savez_compressed(os.path.join(HERE, "golden_ops.npz"), **blob)
-    inp, state, out = model_case()
-    blob = {f"in_{n}": x for n, x in inp.items()}
-    blob.update({f"state:{n}": x for n, x in state.items()})
-    blob.update(out)
-    np.savez_compressed(os.path.join(HERE, "golden_model.npz"), **blob)
-    for f in ("golden_ops.npz", "golden_model.npz"):
+    which = set(sys.argv[1:]) or {"golden_ops.npz", "golden_reci.npz", "golden_model.npz"}
+    if "golden_ops.npz" in which:
+        inp, r32 = ops_case(torch.float32)
+        _, r64 = ops_case(torch.float64)
+        blob = {f"in_{n}": x for n, x in inp.items()}
+        blob.update({f"f32_{n}": x for n, x in r32.items()})
+        blob.update({f"f64_{n}": x for n, x in r64.items()})
+        np.savez_compressed(os.path.join(HERE, "golden_ops.npz"), **blob)
+    if "golden_reci.npz" in which:
+        inp, r32 = reci_case(torch.float32)
+        _, r64 = reci_case(torch.float64)
+        blob = {f"in_{n}": x for n, x in inp.items()}
+        blob.update({f"f32_{n}": x for n, x in r32.items()})
+        blob.update({f"f64_{n}": x for n, x in r64.items()})
+        np.savez_compressed(os.path.join(HERE, "golden_reci.npz"), **blob)
+    if "golden_model.npz" in which:
+        inp, state, out = model_case()
+        blob = {f"in_{n}": x for n, x in inp.items()}
+        blob.update({f"state:{n}": x for n, x in state.items()})
+        blob.update(out)
+        np.savez_compressed(os.path.join(HERE, "golden_model.npz"), **blob)
+    for f in sorted(which):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 
