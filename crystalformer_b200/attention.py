@@ -7,7 +7,9 @@ models/indexed_lattice_multi_head_attention.py:1501-1727).  The host-side steps 
 ``a`` per (atom, head), out-projection - follow ``crystalformer_multi_head_attention_forward_cuda`` (:462-788).  The
 position encodings and the attention itself run in one fused operator (``InfiniteAttentionFunction``) instead of the
 reference's ``RealPeriodicEncodingWithProjFuncCUDA`` + ``FusedDotProductAttentionCUDA`` pair; the pair is still
-available (``fused=False`` or ``need_weights=True``) through ``crystalformer_b200.cuda_funcs``.
+available (``fused=False`` or ``need_weights=True``) through ``crystalformer_b200.cuda_funcs``.  The reciprocal-space
+domains (``reci``, ``RECI``, ``multihead``; :724-746) always take the operator pair, with
+``ReciPeriodicEncodingFuncCUDA`` in place of (or beside) the real-space encoding.
 """
 from __future__ import annotations
 
@@ -23,7 +25,8 @@ from torch.nn.init import constant_, normal_, xavier_uniform_
 from torch.nn.modules.linear import NonDynamicallyQuantizableLinear
 
 from . import ops
-from .cuda_funcs import FusedDotProductAttentionCUDA, RealPeriodicEncodingWithProjFuncCUDA
+from .cuda_funcs import (FusedDotProductAttentionCUDA, RealPeriodicEncodingWithProjFuncCUDA,
+                         ReciPeriodicEncodingFuncCUDA)
 from .cuda_funcs.kernel_manager import KernelManager
 from .params import LatticeformerParams
 
@@ -34,10 +37,12 @@ from .params import LatticeformerParams
 _EDGE_CACHE: "OrderedDict[tuple, tuple]" = OrderedDict()
 
 
-def heaviest_first(row_start: Tensor) -> Tensor:
-    """Atoms sorted by the number of their keys, descending (stable): the order in which the row kernels pick them up."""
-    keys = row_start[1:] - row_start[:-1]
-    return torch.argsort(keys, descending=True, stable=True).to(torch.int32)
+def heaviest_first(row_start: Tensor, cost: Optional[Tensor] = None) -> Tensor:
+    """Atoms in the order in which the row kernels pick them up: by descending scheduling weight (``ops.row_cost``)
+    or, without one, by the number of their keys."""
+    if cost is None:
+        cost = row_start[1:] - row_start[:-1]
+    return torch.argsort(cost, descending=True, stable=True).to(torch.int32)
 
 
 def register_edge_info(edges: Tensor, row_start: Tensor, max_atoms: int, row_order: Optional[Tensor] = None) -> None:
@@ -128,12 +133,14 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         self.embed_dim = embed_dim
         self.kdim = kdim * num_heads if kdim is not None and kdim > 0 else embed_dim
         self.vdim = vdim * num_heads if vdim is not None and vdim > 0 else embed_dim
-        if params.domain != "real":
-            raise NotImplementedError(f"crystalformer_b200 implements domain='real' only, got {params.domain!r}")
+        if params.domain not in ("real", "reci", "RECI", "multihead"):
+            raise NotImplementedError(f"domain {params.domain!r} is not supported")
+        if params.domain == "multihead" and num_heads != 8:
+            raise NotImplementedError("domain='multihead' needs 8 heads (4 real-space + 4 reciprocal-space)")
         if params.gauss_state not in ("q", "q-headdim", "q-kdim", "1", "x", "x-norm", "x-xavier"):
             raise NotImplementedError(f"gauss_state {params.gauss_state!r} is not supported")
-        if params.value_pe_wave_real > 0:
-            raise NotImplementedError("value_pe_wave_real > 0 is not supported")
+        if params.value_pe_wave_real > 0 or params.value_pe_wave_reci > 0:
+            raise NotImplementedError("value_pe_wave_real / value_pe_wave_reci > 0 is not supported")
         self.params = params
         self.fused = fused
         self.gauss_scale = Parameter(torch.zeros(2, **factory_kwargs), requires_grad=False)
@@ -160,8 +167,10 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         self.ATOM_NUM = 98
         head = self.num_heads if params.value_pe_headed else 1
         cond = 1 if params.value_pe_condproj == "no" else self.ATOM_NUM
-        self.pe_dist_proj = Parameter(torch.empty(cond, head, self.head_dim, params.value_pe_dist_real, **factory_kwargs)) \
-            if params.value_pe_dist_real > 0 else None
+        # …attention_cuda.py:869-878: the reciprocal-space domains size the (unused) projection by value_pe_dist_reci
+        pe_dim = params.value_pe_dist_real if params.domain in ("real", "multihead") else params.value_pe_dist_reci
+        self.pe_dist_proj = Parameter(torch.empty(cond, head, self.head_dim, pe_dim, **factory_kwargs)) \
+            if pe_dim > 0 else None
         self.pe_wave_proj = None
         self._scale_known = False
         self._reset_parameters()
@@ -199,7 +208,9 @@ class CrystalformerMultiheadAttentionCUDA(Module):
 
     # -----------------------------------------------------------------------------------------------------------
     def _widths(self, query: Tensor, q: Tensor) -> Tensor:
-        """a (N,H) < 0: the Gaussian parameter of every (atom, head) (…attention_cuda.py:640-722)."""
+        """a (N,H) < 0: the Gaussian parameter of every (atom, head) (…attention_cuda.py:640-735).  Real-space heads get
+        -0.5 f / scale_real^2 (f the positive function of the normalised alpha), reciprocal-space heads
+        -0.5 f scale_reci^2 ('reci'), -0.5 scale_reci^2 / f ('RECI'); 'multihead' = first half real, second half reci."""
         P = self.params
         N, H, Dq = q.shape
         w = self.lattice_pos_weights
@@ -228,7 +239,15 @@ class CrystalformerMultiheadAttentionCUDA(Module):
                 torch.nn.init.constant_(self.gauss_scale[1], shift)
                 self._scale_known = True
         func = positive_function(P.positive_func)
-        return func(alpha, P.gauss_lb_real) * (-0.5 * P.scale_real ** -2)
+        if P.domain == "real":
+            return func(alpha, P.gauss_lb_real) * (-0.5 * P.scale_real ** -2)
+        if P.domain == "reci":
+            return func(alpha, P.gauss_lb_reci) * (-0.5 * P.scale_reci ** 2)
+        if P.domain == "RECI":
+            return 1 / func(alpha, P.gauss_lb_reci) * (-0.5 * P.scale_reci ** 2)
+        a1, a2 = alpha.chunk(2, 1)  # multihead
+        return torch.cat((func(a1, P.gauss_lb_real) * (-0.5 * P.scale_real ** -2),
+                          func(a2, P.gauss_lb_reci) * (-0.5 * P.scale_reci ** 2)), dim=1)
 
     def forward(self, query: Tensor, key: Tensor, value: Tensor, batch_q: Tensor, batch_kv: Tensor, edges: Tensor,
                 points: Tensor, dist2_min: Tensor, tvecs: Tensor,
@@ -289,7 +308,7 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         q_scaled = q / math.sqrt(Dq)
 
         values = None
-        if self.fused and not need_weights:
+        if self.fused and not need_weights and P.domain == "real":
             row_start, max_atoms, row_order = edge_info(edges, N)
             attn = InfiniteAttentionFunction.apply(
                 q_scaled, k, v, a, self.pe_dist_proj, points, tvecs, rvlen, batch_q, edges, row_start, max_atoms, K,
@@ -300,14 +319,34 @@ class CrystalformerMultiheadAttentionCUDA(Module):
             saved = (KernelManager.LATTICE_RANGE, KernelManager.MINIMUM_RANGE)
             KernelManager.LATTICE_RANGE, KernelManager.MINIMUM_RANGE = lattice_range, minimum_range
             try:
-                extra = (rvlen, cutoff) if cutoff != 0.0 else ()
-                res = RealPeriodicEncodingWithProjFuncCUDA.apply(
-                    a, points, dist2_min, tvecs, batch_q, edges, K, float(dist_max), float(P.value_pe_width_scale),
-                    self.pe_dist_proj, *extra)
+                phi = None
+                if P.domain in ("real", "multihead"):
+                    extra = (rvlen, cutoff) if cutoff != 0.0 else ()
+                    a_real, W = a, self.pe_dist_proj
+                    if P.domain == "multihead":
+                        # the kernels are compiled for eight heads: the four real-space heads are computed twice and
+                        # the copy is dropped (…attention_cuda.py:731-746 passes half the heads to each operator)
+                        a_real = torch.cat((a[:, :H // 2], a[:, :H // 2]), dim=1)
+                        if W is not None and W.shape[1] == H:
+                            W = torch.cat((W[:, :H // 2], W[:, :H // 2]), dim=1)
+                    res = RealPeriodicEncodingWithProjFuncCUDA.apply(
+                        a_real, points, dist2_min, tvecs, batch_q, edges, K, float(dist_max),
+                        float(P.value_pe_width_scale), W, *extra)
+                    phi = res[0]
+                    values = res[1] if len(res) > 1 else None
+                if P.domain != "real":
+                    if kr_base is None or rvecs is None or vcell is None:
+                        raise ValueError("the reciprocal-space domains need kr_base, rvecs and vcell")
+                    a_reci = a if P.domain != "multihead" else torch.cat((a[:, H // 2:], a[:, H // 2:]), dim=1)
+                    phi_reci = ReciPeriodicEncodingFuncCUDA.apply(a_reci, kr_base, rvecs, vcell, batch_q, edges)
+                    if P.domain == "multihead":
+                        phi = torch.cat((phi[:, :H // 2], phi_reci[:, H // 2:]), dim=1)
+                        if values is not None:
+                            values = torch.cat((values[:, :H // 2], torch.zeros_like(values[:, H // 2:])), dim=1)
+                    else:
+                        phi = phi_reci
             finally:
                 KernelManager.LATTICE_RANGE, KernelManager.MINIMUM_RANGE = saved
-            phi = res[0]
-            values = res[1] if len(res) > 1 else None
             attn = FusedDotProductAttentionCUDA.apply(q_scaled, k, v, phi, values, batch_q, edges)
             weights = None
             if need_weights:

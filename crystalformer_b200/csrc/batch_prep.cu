@@ -128,8 +128,34 @@ __global__ void edge_kernel(const float *__restrict__ pos, const int64_t *__rest
     }
 }
 
+// Scheduling weight of an atom's row in the fused attention kernels: a fixed part plus the expected number of
+// (key, translation) pairs within `reach` of the atom, n x (volume of the reach sphere) / (cell volume).
+__global__ void row_cost_kernel(const int64_t *__restrict__ atom_start, const float *__restrict__ trans, long long B,
+                                long long N, float sphere, float *__restrict__ cost)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const long long c = find_segment(atom_start, B, i);
+    const float *m = trans + 9 * c;
+    const float v = m[0] * (m[4] * m[8] - m[5] * m[7]) - m[1] * (m[3] * m[8] - m[5] * m[6]) + m[2] * (m[3] * m[7] - m[4] * m[6]);
+    const float n = (float)(atom_start[c + 1] - atom_start[c]);
+    cost[i] = 1500.0f + n * (1.0f + sphere / fmaxf(fabsf(v), 1e-3f));
+}
+
 }  // namespace
 }  // namespace cf
+
+extern "C" int cf_row_cost(const int64_t *atom_start, const float *trans, int64_t B, int64_t N, double reach,
+                           float *cost, void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(B >= 0 && N >= 0 && reach >= 0, CF_ERR_INVALID, "cf_row_cost: negative size");
+    if (N == 0) return CF_OK;
+    CF_REQUIRE(atom_start && trans && cost, CF_ERR_INVALID, "cf_row_cost: null pointer");
+    const float sphere = (float)(4.18879020478639 * reach * reach * reach);
+    row_cost_kernel<<<(unsigned)((N + 255) / 256), 256, 0, as_stream(stream)>>>(atom_start, trans, B, N, sphere, cost);
+    return launch_status("cf_row_cost");
+}
 
 extern "C" int cf_crystal_offsets(const int64_t *sizes, int64_t B, int64_t *atom_start, int64_t *edge_start,
                                   void *stream)

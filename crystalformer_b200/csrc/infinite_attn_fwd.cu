@@ -15,10 +15,27 @@
 //                             at a time, keeps the candidates in a ring and accumulates them with the lane<->bins
 //                             turn-around of BinAccumulator; the four partial histograms are added in a fixed order
 //                             (deterministic), projected with W and added to sum_j p_ij v_j.
+#include <atomic>
+#include <cstdlib>
+
 #include "lattice_core.cuh"
+
+// Row tickets: each launch of the row kernel gets one zeroed counter out of a small pool, so that launches in flight
+// on different streams of a device do not share one.
+__device__ unsigned g_row_tickets[64];
 
 namespace cf {
 namespace {
+
+unsigned *next_ticket(cudaStream_t s)
+{
+    static std::atomic<unsigned> turn{0};
+    void *base = nullptr;
+    if (cudaGetSymbolAddress(&base, g_row_tickets) != cudaSuccess) return nullptr;
+    unsigned *t = static_cast<unsigned *>(base) + (turn.fetch_add(1) & 63u);
+    if (cudaMemsetAsync(t, 0, sizeof(unsigned), s) != cudaSuccess) return nullptr;
+    return t;
+}
 
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
@@ -28,6 +45,7 @@ struct RowArgs {
     const float *q, *k, *v, *a, *pos, *pos_ij, *tvecs, *rvlen, *W;
     const int64_t *batch, *edges, *row_start;
     const int32_t *row_order;  // optional: atoms in the order they are to be processed (heaviest first)
+    unsigned *ticket;          // zeroed before the launch: rows beyond the first wave are handed out through it
     long long E;
     float *out, *logit, *lse, *psi_row;
     long long N;
@@ -50,15 +68,23 @@ __host__ __device__ inline size_t row_group_floats(int max_atoms, bool with_basi
 //                its cost is dominated by the latency of its phases, so four rows progress independently per block
 //                and only warp-level synchronisation is needed).
 template <int K, int ROW_WARPS>
-__global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowArgs p)
+__global__ void __launch_bounds__(THREADS, ROW_WARPS == 1 ? 3 : 4) infinite_attn_rows_kernel(const RowArgs p)
 {
     extern __shared__ __align__(16) float smem_all[];
     constexpr int GROUPS = WARPS / ROW_WARPS;        // row groups per block
     constexpr int RT = 32 * ROW_WARPS;               // threads per row group
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int group = warp / ROW_WARPS, wr = warp % ROW_WARPS, rt = tid % RT;
+    // barrier of one row group: a warp barrier, or a named block barrier (one id per group) for its 32 ROW_WARPS threads
     auto row_sync = [&]() {
-        if (ROW_WARPS == 1) __syncwarp(); else __syncthreads();
+        if (ROW_WARPS == 1)
+            __syncwarp();
+        else if (ROW_WARPS == WARPS)
+            __syncthreads();
+        else if (group == 0)
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * ROW_WARPS) : "memory");
+        else
+            asm volatile("bar.sync 2, %0;" ::"n"(32 * ROW_WARPS) : "memory");
     };
     float *smem = smem_all + (size_t)group * row_group_floats(p.max_atoms, K > 0, ROW_WARPS);
     float4 *rel = reinterpret_cast<float4 *>(smem);                    // [max_atoms]
@@ -81,16 +107,38 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
     const float *__restrict__ kmat = p.k;
     float *__restrict__ logit_io = p.logit;
 
-    for (long long slot = (long long)blockIdx.x * GROUPS + group; slot < p.N; slot += (long long)gridDim.x * GROUPS) {
-        const long long i = p.row_order ? p.row_order[slot] : slot;
-        const long long c = p.batch[i];
-        const long long e0 = p.row_start[i];
-        const int n = (int)(p.row_start[i + 1] - e0);  // keys of the row = atoms of the crystal
-        const long long a0 = n > 0 ? p.edges[p.E + e0] : 0;  // first atom of the crystal
-        if (n > p.max_atoms) {  // the caller understated max_atoms: poison the row instead of overrunning shared memory
-            for (int idx = rt; idx < HEADS * HEAD_DIM; idx += RT) p.out[i * HEADS * HEAD_DIM + idx] = __int_as_float(0x7fc00000);
-            continue;
-        }
+    // Rows are handed out in the order of p.row_order: the first wave by block index, the rest through an atomic
+    // ticket, so that a block that drew a heavy row simply draws fewer rows (longest-processing-time-first).  Which
+    // block computes a row has no influence on the row's result.  The ticket and the row's indices (atom, crystal,
+    // edge range, first key) are fetched one row ahead, in stages placed where their latency is hidden.
+    __shared__ long long next_slot_sh[GROUPS];
+    const long long first_wave = (long long)gridDim.x * GROUPS;
+    long long slot = (long long)blockIdx.x * GROUPS + group;
+    if (slot >= p.N) return;
+    long long i = p.row_order ? p.row_order[slot] : slot;
+    long long c = p.batch[i];
+    long long e0 = p.row_start[i];
+    int n_raw = (int)(p.row_start[i + 1] - e0);  // keys of the row = atoms of the crystal
+    long long a0 = n_raw > 0 ? p.edges[p.E + e0] : 0;  // first atom of the crystal
+    if (rt == 0) next_slot_sh[group] = first_wave + atomicAdd(p.ticket, 1u);
+    row_sync();
+    long long nslot = next_slot_sh[group];
+
+    while (true) {
+        // stage 0 of the look-ahead: the next row's atom; thread 0 draws the ticket of the row after it
+        const bool has_next = nslot < p.N;
+        const long long i_n = has_next ? (p.row_order ? (long long)p.row_order[nslot] : nslot) : 0;
+        unsigned drawn = 0;
+        if (rt == 0) drawn = atomicAdd(p.ticket, 1u);
+        // the caller understated max_atoms: the row is poisoned instead of overrunning shared memory
+        const bool bad = n_raw > p.max_atoms;
+        const int n = bad ? 0 : n_raw;
+        // constants of the row's atom and crystal, needed after the soft-max: loaded here so that they arrive meanwhile
+        const float a_own = p.a[i * HEADS + (lane & 7)];
+        Cell cell;
+        cell.load(p.tvecs + 9 * c);
+        float rvl[3] = {0.f, 0.f, 0.f};
+        if (p.rvlen) { rvl[0] = p.rvlen[3 * c]; rvl[1] = p.rvlen[3 * c + 1]; rvl[2] = p.rvlen[3 * c + 2]; }
 
         // ---- relative positions of the keys
         if (p.pos_ij) {
@@ -110,6 +158,9 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
         for (int idx = rt; idx < HEADS * HEAD_DIM / 4; idx += RT)
             qs[idx] = __ldg(reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM) + idx);
         row_sync();
+        // stage 1 of the look-ahead: the next row's crystal and edge range
+        const long long c_n = p.batch[i_n], e0_n = p.row_start[i_n];
+        const int n_n = (int)(p.row_start[i_n + 1] - e0_n);
         // ---- logits: one key per thread, all eight heads; the key's 512-byte row is 32 independent 16-byte loads
         for (int j = rt; j < n; j += RT) {
             const float4 *kp = reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
@@ -166,8 +217,7 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             }
             row_sync();
             // ---- boxes of the row's heads (they depend on the atom and the head, not on the key)
-            const float a_own = p.a[i * HEADS + (lane & 7)];
-            const int pk_own = packed_box(p.rule, a_own, p.rvlen ? p.rvlen + 3 * c : nullptr);
+            const int pk_own = packed_box(p.rule, a_own, p.rvlen ? rvl : nullptr);
             int uni = pk_own;
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) uni = box_union(uni, __shfl_xor_sync(FULL, uni, o));
@@ -185,8 +235,6 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             const int S2 = 2 * R2 + 1;
             const int columns = (2 * R1 + 1) * S2;  // a column = the translations (n1, n2, *)
             const int chunks = (n + 31) >> 5;       // a chunk = 32 keys, one per lane
-            Cell cell;
-            cell.load(p.tvecs + 9 * c);
             const float t3sq = fmaf(cell.t3z, cell.t3z, fmaf(cell.t3y, cell.t3y, cell.t3x * cell.t3x));
             const bool prune = t3sq > 1e-12f;
             const float inv_t3sq = prune ? __frcp_rn(t3sq) : 0.f;
@@ -208,8 +256,9 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 }
                 bins.push(emax > p.basis.floor_log2, fast_sqrt(d2) * p.basis.bin_scale, w);
             };
-            // Work units are (chunk, column) pairs dealt round-robin to the warps of the group, so that the few dense
-            // columns around the origin are spread over all of them whatever the number of keys.  Lanes run over the
+            // Work units are (chunk, column) pairs dealt round-robin to the warps of the group (rotated by one warp per
+            // chunk), so that the few dense columns around the origin are spread over all of them whatever the number
+            // of keys.  Lanes run over the
             // keys of the chunk: a translation is warp-uniform and a lane's key stays in registers.
             for (int ch = 0; ch < chunks; ++ch) {
                 const int j = 32 * ch + lane;
@@ -222,9 +271,12 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 const float reach2 = fminf(__fdividef(p.basis.floor_log2 - cmax, a2max), p.basis.d2_cut);
                 const float bound = sqrtf(fmaxf(reach2, 0.f)) + sqrtf(far2);
                 const float tau2_max = bound * bound * 1.0001f + 1e-4f;
-                int n1 = -R1, n2 = -R2;
-                for (int col = 0; col < columns; ++col) {
-                    if ((col * chunks + ch) % ROW_WARPS == wr) {
+                // this warp's columns of the chunk: col = (wr - ch) mod ROW_WARPS, then every ROW_WARPS-th
+                int col = (wr - ch) & (ROW_WARPS - 1);
+                int n1 = -R1, n2 = col - R2;
+                while (n2 > R2) { n2 -= S2; ++n1; }
+                for (; col < columns; col += ROW_WARPS) {
+                    {
                         const float f1 = (float)n1, f2 = (float)n2;
                         // the n3 of this column whose translation n1 t1 + n2 t2 + n3 t3 is no longer than the bound
                         const float bx = fmaf(cell.t2x, f2, cell.t1x * f1), by = fmaf(cell.t2y, f2, cell.t1y * f1);
@@ -261,7 +313,8 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                             while (ring.ready()) consume();
                         }
                     }
-                    if (++n2 > R2) { n2 = -R2; ++n1; }
+                    n2 += ROW_WARPS;
+                    while (n2 > R2) { n2 -= S2; ++n1; }
                 }
             }
             while (ring.count > 0) consume();
@@ -270,6 +323,7 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             row_sync();
             for (int idx = rt; idx < HEADS * KBINS; idx += RT) {
                 float s = part[idx];
+                if (ROW_WARPS == 2) s = part[idx] + part[HEADS * KBINS + idx];
                 if (ROW_WARPS == 4)
                     s = (part[idx] + part[HEADS * KBINS + idx]) + (part[2 * HEADS * KBINS + idx] + part[3 * HEADS * KBINS + idx]);
                 part[idx] = s;
@@ -277,6 +331,10 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
             }
             row_sync();
         }
+
+        // stage 2 of the look-ahead: the next row's first key; thread 0 publishes the ticket it drew
+        const long long a0_n = (has_next && n_n > 0) ? p.edges[p.E + e0_n] : 0;
+        if (rt == 0) next_slot_sh[group] = first_wave + drawn;
 
         // ---- sum_j p_ij v_j: warp wr takes keys wr, wr + ROW_WARPS, ...; a lane owns four consecutive channels (one
         //      float4 load per key); the partial rows of the group meet in shared memory
@@ -307,6 +365,7 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
         for (int idx = rt; idx < HEADS * HEAD_DIM; idx += RT) {
             const int h = idx >> 4;
             float acc = vsum[idx];
+            if (ROW_WARPS == 2) acc = vsum[idx] + vsum[128 + idx];
             if (ROW_WARPS == 4) acc = (vsum[idx] + vsum[128 + idx]) + (vsum[256 + idx] + vsum[384 + idx]);
             if (K > 0) {
                 const float4 *wp = reinterpret_cast<const float4 *>(p.W + (size_t)idx * KBINS);
@@ -319,9 +378,12 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_rows_kernel(const RowAr
                 }
                 acc += (o0 + o1) + (o2 + o3);
             }
-            p.out[i * HEADS * HEAD_DIM + idx] = acc;
+            p.out[i * HEADS * HEAD_DIM + idx] = bad ? __int_as_float(0x7fc00000) : acc;
         }
         row_sync();
+        if (!has_next) break;
+        i = i_n; c = c_n; e0 = e0_n; n_raw = n_n; a0 = a0_n;
+        nslot = next_slot_sh[group];
     }
 }
 
@@ -365,14 +427,17 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     p.keep_logit = 1;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
-    // crystals of up to 12 atoms: one warp per atom, four atoms per block; larger ones: one block per atom
-    const bool small = max_atoms <= 12;
-    const int row_warps = small ? 1 : WARPS;
+    // warps per atom row: 1 for crystals of up to 12 atoms, 4 otherwise (CF_ROW_WARPS in the environment overrides)
+    static const int forced = [] { const char *e = getenv("CF_ROW_WARPS"); return e ? atoi(e) : 0; }();
+    int row_warps = max_atoms <= 12 ? 1 : WARPS;
+    if (forced == 1 || forced == 2 || forced == 4) row_warps = forced;
     const int groups = WARPS / row_warps;
     const size_t smem = sizeof(float) * groups * row_group_floats((int)max_atoms, K > 0, row_warps);
-    void (*kernel)(const RowArgs) =
-        K > 0 ? (small ? infinite_attn_rows_kernel<64, 1> : infinite_attn_rows_kernel<64, 4>)
-              : (small ? infinite_attn_rows_kernel<0, 1> : infinite_attn_rows_kernel<0, 4>);
+    void (*kernel)(const RowArgs);
+    if (K > 0)
+        kernel = row_warps == 1 ? infinite_attn_rows_kernel<64, 1> : (row_warps == 2 ? infinite_attn_rows_kernel<64, 2> : infinite_attn_rows_kernel<64, 4>);
+    else
+        kernel = row_warps == 1 ? infinite_attn_rows_kernel<0, 1> : (row_warps == 2 ? infinite_attn_rows_kernel<0, 2> : infinite_attn_rows_kernel<0, 4>);
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
@@ -380,15 +445,17 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
                         smem, (long long)max_atoms);
         }
     }
-    static thread_local size_t cached_smem[4] = {0, 0, 0, 0};
-    static thread_local int cached_occ[4] = {0, 0, 0, 0};
-    const int slot = (K > 0 ? 2 : 0) + (small ? 1 : 0);
+    static thread_local size_t cached_smem[6] = {0, 0, 0, 0, 0, 0};
+    static thread_local int cached_occ[6] = {0, 0, 0, 0, 0, 0};
+    const int slot = (K > 0 ? 3 : 0) + (row_warps == 1 ? 0 : (row_warps == 2 ? 1 : 2));
     if (cached_occ[slot] == 0 || cached_smem[slot] != smem) {
         int occ = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, THREADS, smem) != cudaSuccess || occ <= 0) occ = 1;
         cached_occ[slot] = occ;
         cached_smem[slot] = smem;
     }
+    p.ticket = next_ticket(s);
+    CF_REQUIRE(p.ticket != nullptr, CF_ERR_CUDA, "cf_infinite_attn_fwd: the row ticket could not be set up");
     const long long want = (N + groups - 1) / groups;
     const long long cap = (long long)sm_count() * cached_occ[slot];
     const int blocks = (int)(want < cap ? want : cap);

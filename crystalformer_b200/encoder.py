@@ -44,8 +44,16 @@ class BatchGeometry:
         self.batch, self.edges, self.row_start = prep["batch"], prep["edges"], prep["row_start"]
         self.pos_ij, self.rvecs, self.vcell, self.rvlen = prep["pos_ij"], prep["rvecs"], prep["vcell"], prep["rvlen"]
         self.sizes, self.max_atoms = sizes, int(max_atoms)
-        self.row_order = heaviest_first(self.row_start)
+        self.row_order = heaviest_first(self.row_start, ops.row_cost(self.atom_start, trans.float(), num_atoms))
+        self._kr_base = None
         register_edge_info(self.edges, self.row_start, self.max_atoms, self.row_order)
+
+    @property
+    def kr_base(self) -> Tensor:
+        """(E,3) phases rvecs . pos_ij of the reciprocal-space domains (…encoder.py:249-251), built on first use."""
+        if self._kr_base is None:
+            self._kr_base = ops.reci_phase(self.pos_ij, self.rvecs, self.batch, self.edges)
+        return self._kr_base
 
 
 class CrystalformerEncoderLayerCUDA(Module):
@@ -55,7 +63,7 @@ class CrystalformerEncoderLayerCUDA(Module):
                  activation: Union[str, Callable[[Tensor], Tensor]] = F.relu, layer_norm_eps: float = 1e-5,
                  norm_first: bool = False, no_layer_norm=False, params=LatticeformerParams(), k_dim=0, v_dim=0,
                  device=None, dtype=None) -> None:
-        assert params.domain in ("real",), "crystalformer_b200 implements the real-space domain only"
+        assert params.domain in ("real", "reci", "RECI", "multihead"), f"unsupported domain {params.domain!r}"
         self.domain = params.domain
         super().__init__()
         self.self_attn = CrystalformerMultiheadAttentionCUDA(d_model, nhead, dropout=dropout, kdim=k_dim, vdim=v_dim,
@@ -114,7 +122,6 @@ class CrystalformerEncoderCUDA(Module):
                  lattice_params: LatticeformerParams = LatticeformerParams(), k_dim=0, v_dim=0, device=None,
                  dtype=None) -> None:
         super().__init__()
-        assert lattice_params.domain in ("real",), "crystalformer_b200 implements the real-space domain only"
         self.lattice_params = lattice_params
         self.layers = ModuleList([
             CrystalformerEncoderLayerCUDA(d_model, nhead, dim_feedforward, dropout, activation, layer_norm_eps, norm_first,
@@ -142,7 +149,7 @@ class CrystalformerEncoderCUDA(Module):
             return False
         for layer in self.layers:
             att, P = layer.self_attn, layer.self_attn.params
-            if not (P.positive_func.startswith("elu") and P.gauss_state == "q" and P.normalize_gauss and att.fused
+            if not (P.domain == "real" and P.positive_func.startswith("elu") and P.gauss_state == "q" and P.normalize_gauss and att.fused
                     and P.value_pe_condproj == "no" and P.norm_func_mode == 0 and att.kdim == 128 and att.vdim == 128
                     and att.in_proj_bias is not None and layer.activation is F.relu and not layer.norm_first
                     and isinstance(layer.norm1, Identity)):
@@ -231,7 +238,8 @@ class CrystalformerEncoderCUDA(Module):
             return self._forward_native(src, trans.float().contiguous(), g)
         output = src
         for mod in self.layers:
-            output = mod(output, g.batch, g.edges, g.pos_ij, None, trans, None, g.rvecs, g.vcell, onehot, rvlen=g.rvlen)
+            kr_base = g.kr_base if mod.domain != "real" else None
+            output = mod(output, g.batch, g.edges, g.pos_ij, None, trans, kr_base, g.rvecs, g.vcell, onehot, rvlen=g.rvlen)
         if self.norm is not None:
             output = self.norm(output)
         return output

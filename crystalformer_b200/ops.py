@@ -260,6 +260,59 @@ def infinite_attn_bwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
     return gq, gk, gv, ga
 
 
+def row_cost(atom_start, trans, N: int, reach: float = 15.0):
+    """(N,) float32 scheduling weights of the atoms' rows (see cf_row_cost)."""
+    dev = trans.device
+    atom_start, trans = _want(atom_start, torch.int64, "atom_start", dev), _want(trans, torch.float32, "trans", dev)
+    cost = torch.empty((N,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_row_cost", _ptr(atom_start), _ptr(trans), c_int64(trans.shape[0]), c_int64(N), c_double(reach),
+                  _ptr(cost), _stream(dev))
+    return cost
+
+
+def reci_phase(pos_ij, rvecs, batch, edges):
+    """kr_base (E,3) = rvecs[crystal of the edge] . pos_ij."""
+    dev = pos_ij.device
+    pos_ij, rvecs = _want(pos_ij, torch.float32, "pos_ij", dev), _want(rvecs, torch.float32, "rvecs", dev)
+    batch, edges = _want(batch, torch.int64, "batch", dev), _want(edges, torch.int64, "edges", dev)
+    E = edges.shape[1]
+    kr = torch.empty((E, 3), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_reci_phase", _ptr(pos_ij), _ptr(rvecs), _ptr(batch), _ptr(edges), c_int64(E), _ptr(kr), _stream(dev))
+    return kr
+
+
+def reci_sum_fwd(a, kr_base, rvecs, vcell, batch, row_start, E: int, lattice_range: int):
+    """phi (E,H) and the raw sum S (E,H) of the reciprocal-space lattice sum."""
+    dev = a.device
+    a, kr_base, rvecs, vcell = (_want(t, torch.float32, n, dev) for t, n in
+                                ((a, "a"), (kr_base, "kr_base"), (rvecs, "rvecs"), (vcell, "vcell")))
+    batch, row_start = _want(batch, torch.int64, "batch", dev), _want(row_start, torch.int64, "row_start", dev)
+    N, H = a.shape
+    z = torch.empty((E, H), dtype=torch.float32, device=dev)
+    s = torch.empty((E, H), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_reci_sum_fwd", _ptr(a), _ptr(kr_base), _ptr(rvecs), _ptr(vcell), _ptr(batch), _ptr(row_start),
+                  c_int64(N), c_int64(H), c_int64(E), c_int(lattice_range), _ptr(z), _ptr(s), _stream(dev))
+    return z, s
+
+
+def reci_sum_bwd(a, kr_base, rvecs, batch, row_start, gz, sumexp, lattice_range: int):
+    """ga (N,H); the 1.5 log(-4 pi a) term of phi is not differentiated (as in the reference's kernel)."""
+    dev = a.device
+    a, kr_base, rvecs, gz, sumexp = (_want(t, torch.float32, n, dev) for t, n in
+                                     ((a, "a"), (kr_base, "kr_base"), (rvecs, "rvecs"), (gz, "gz"), (sumexp, "sumexp")))
+    batch, row_start = _want(batch, torch.int64, "batch", dev), _want(row_start, torch.int64, "row_start", dev)
+    N, H = a.shape
+    E = gz.shape[0]
+    ga = torch.empty((N, H), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_reci_sum_bwd", _ptr(a), _ptr(kr_base), _ptr(rvecs), _ptr(batch), _ptr(row_start), _ptr(gz),
+                  _ptr(sumexp), c_int64(N), c_int64(H), c_int64(E), c_int(lattice_range), _ptr(ga), _stream(dev))
+    return ga
+
+
 def segment_mean(x, start):
     """Per-crystal mean: x (N,D) float32, start (B+1) int64 atom offsets -> (B,D)."""
     dev = x.device

@@ -234,6 +234,36 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
                        void *const *attn_events, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
+ * Scheduling weight of every atom's row for the fused attention kernels (no counterpart in the reference, which
+ * launches one thread per (atom, head) in index order): cost[i] = 1500 + n (1 + (4 pi / 3) reach^3 / |det trans|),
+ * n the atom count of the atom's crystal; about the number of (key, translation) pairs within `reach` Angstrom.
+ * Sorting atoms by descending cost gives the `row_order` argument of cf_infinite_attn_fwd / cf_encoder_forward.
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_row_cost(const int64_t *atom_start, const float *trans, int64_t B, int64_t N, double reach, float *cost,
+                void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Reciprocal-space lattice sum (domains `reci`, `RECI`, `multihead` of the reference's attention module).
+ * Replace reci_enc_fwd / reci_enc_bwd (models/kernels/reci_enc_fwd.cu, reci_enc_bwd.cu) as launched by
+ * ReciPeriodicEncodingFuncCUDA (models/cuda_funcs/reci_space_enc.py:19-56, 59-99):
+ *   S[e,h]   = sum_{n1 in [0,R], n2,n3 in [-R,R]} w(n1) exp(a[i,h] |n.rvecs|^2) cos(kr_base[e].n),  w(0)=1, else 2
+ *   z[e,h]   = log max(S, 1e-6) + 1.5 log(-4 pi a[i,h]) - log vcell
+ *   ga[i,h]  = sum_{e in row i} gz[e,h] (S < 1e-6 ? 0 : 1/S) sum_n w |k_n|^2 exp(a |k_n|^2) cos(kr_base[e].n)
+ * a (N,8) < 0; kr_base (E,3); rvecs (B,3,3); vcell (B); batch (N); row_start (N+1) CSR offsets of the edge list by
+ * source atom (the reference builds it in its backward, reci_space_enc.py:64-66); R = lattice_range <= 6 (the
+ * reference compiles LATTICE_RANGE into the kernel).  sumexp (E,8) may be NULL in the forward.
+ * cf_reci_phase computes kr_base = rvecs[crystal of e] . pos_ij[e] (models/indexed_latticeformer_encoder.py:249-251).
+ * ---------------------------------------------------------------------------------------------------------- */
+int cf_reci_phase(const float *pos_ij, const float *rvecs, const int64_t *batch, const int64_t *edges, int64_t E,
+                  float *kr_base, void *stream);
+int cf_reci_sum_fwd(const float *a, const float *kr_base, const float *rvecs, const float *vcell,
+                    const int64_t *batch, const int64_t *row_start, int64_t N, int64_t H, int64_t E,
+                    int lattice_range, float *z, float *sumexp, void *stream);
+int cf_reci_sum_bwd(const float *a, const float *kr_base, const float *rvecs, const int64_t *batch,
+                    const int64_t *row_start, const float *gz, const float *sumexp, int64_t N, int64_t H, int64_t E,
+                    int lattice_range, float *ga, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
  * Pipe-throughput probes for the roofline denominators: `iters` dependent-free FFMA (kind 0) or MUFU.EX2 (kind 1)
  * instructions per thread over a full grid; sink (>= 1 float) receives a value so the loop is not elided.
  * Work per launch = blocks * threads * iters * 8 instructions.

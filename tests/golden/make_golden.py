@@ -88,9 +88,10 @@ def reci_case(dtype):
     cb = make_crystals(13, 7, uniform_atoms(1, 6), length_range=(3.0, 9.0))
     rng = np.random.default_rng(6)
     N = cb.num_atoms
-    # a = -0.5 (scale_reci func)^2 with widths of 0.8 .. 2.4 Angstrom: the R = 2 sum is then far from its 1e-6 clamp
+    # a = -0.5 s^2 with s in 2.5 .. 4.5 Angstrom: the R = 2 sum has converged for these cells, so it stays positive and
+    # well away from its 1e-6 clamp (log and 1/S would otherwise amplify float rounding beyond any fixed tolerance)
     inp = dict(sizes=cb.sizes, pos=cb.pos, trans=cb.trans_vec, batch=cb.batch,
-               a=(-0.5 * (0.8 + 1.6 * rng.random((N, H))) ** 2).astype(np.float32))
+               a=(-0.5 * (2.5 + 2.0 * rng.random((N, H))) ** 2).astype(np.float32))
     t = {n: torch.tensor(x).to(dtype) if x.dtype.kind == "f" else torch.tensor(x) for n, x in inp.items()}
     _, cos_kr, k2, vcell, _, edges, _ = compute_lattice_distances(t["pos"], t["batch"], t["trans"], t["sizes"],
                                                                   LATTICE_RANGE, output_dis=False, output_rec=True)
