@@ -27,14 +27,12 @@ __device__ unsigned g_row_tickets[64];
 namespace cf {
 namespace {
 
-unsigned *next_ticket(cudaStream_t s)
+unsigned *next_ticket()
 {
     static std::atomic<unsigned> turn{0};
     void *base = nullptr;
     if (cudaGetSymbolAddress(&base, g_row_tickets) != cudaSuccess) return nullptr;
-    unsigned *t = static_cast<unsigned *>(base) + (turn.fetch_add(1) & 63u);
-    if (cudaMemsetAsync(t, 0, sizeof(unsigned), s) != cudaSuccess) return nullptr;
-    return t;
+    return static_cast<unsigned *>(base) + (turn.fetch_add(1) & 63u);
 }
 
 constexpr int THREADS = 128;
@@ -68,7 +66,7 @@ __host__ __device__ inline size_t row_group_floats(int max_atoms, bool with_basi
 //                its cost is dominated by the latency of its phases, so four rows progress independently per block
 //                and only warp-level synchronisation is needed).
 template <int K, int ROW_WARPS>
-__global__ void __launch_bounds__(THREADS, ROW_WARPS == 1 ? 3 : 4) infinite_attn_rows_kernel(const RowArgs p)
+__global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)) infinite_attn_rows_kernel(const RowArgs p)
 {
     extern __shared__ __align__(16) float smem_all[];
     constexpr int GROUPS = WARPS / ROW_WARPS;        // row groups per block
@@ -120,102 +118,169 @@ __global__ void __launch_bounds__(THREADS, ROW_WARPS == 1 ? 3 : 4) infinite_attn
     long long e0 = p.row_start[i];
     int n_raw = (int)(p.row_start[i + 1] - e0);  // keys of the row = atoms of the crystal
     long long a0 = n_raw > 0 ? p.edges[p.E + e0] : 0;  // first atom of the crystal
-    if (rt == 0) next_slot_sh[group] = first_wave + atomicAdd(p.ticket, 1u);
-    row_sync();
-    long long nslot = next_slot_sh[group];
+    long long nslot = slot + first_wave;  // without a ticket: rows dealt round-robin
+    if (p.ticket) {
+        if (rt == 0) next_slot_sh[group] = first_wave + atomicAdd(p.ticket, 1u);
+        row_sync();
+        nslot = next_slot_sh[group];
+    }
 
     while (true) {
         // stage 0 of the look-ahead: the next row's atom; thread 0 draws the ticket of the row after it
         const bool has_next = nslot < p.N;
         const long long i_n = has_next ? (p.row_order ? (long long)p.row_order[nslot] : nslot) : 0;
         unsigned drawn = 0;
-        if (rt == 0) drawn = atomicAdd(p.ticket, 1u);
+        if (p.ticket && rt == 0) drawn = atomicAdd(p.ticket, 1u);
         // the caller understated max_atoms: the row is poisoned instead of overrunning shared memory
         const bool bad = n_raw > p.max_atoms;
         const int n = bad ? 0 : n_raw;
         // constants of the row's atom and crystal, needed after the soft-max: loaded here so that they arrive meanwhile
-        const float a_own = p.a[i * HEADS + (lane & 7)];
+        float a_own = 0.f;
         Cell cell;
-        cell.load(p.tvecs + 9 * c);
         float rvl[3] = {0.f, 0.f, 0.f};
-        if (p.rvlen) { rvl[0] = p.rvlen[3 * c]; rvl[1] = p.rvlen[3 * c + 1]; rvl[2] = p.rvlen[3 * c + 2]; }
+        if (K > 0) {
+            a_own = p.a[i * HEADS + (lane & 7)];
+            cell.load(p.tvecs + 9 * c);
+            if (p.rvlen) { rvl[0] = p.rvlen[3 * c]; rvl[1] = p.rvlen[3 * c + 1]; rvl[2] = p.rvlen[3 * c + 2]; }
+        }
 
-        // ---- relative positions of the keys
-        if (p.pos_ij) {
-            for (int j = rt; j < n; j += RT) {
-                const float *pp = p.pos_ij + 3 * (e0 + j);
-                rel[j] = make_float4(pp[0], pp[1], pp[2], 0.f);
+        if (n <= 32) {
+            // ---- up to 32 keys: the first warp of the group does the whole soft-max in registers, one key per lane
+            //      (positions, logits of all eight heads, statistics by shuffles); the other warps wait
+            if (wr == 0) {
+                const bool live = lane < n;
+                const int j = live ? lane : 0;
+                float rx, ry, rz;
+                if (p.pos_ij) {
+                    const float *pp = p.pos_ij + 3 * (e0 + j);
+                    rx = n > 0 ? pp[0] : 0.f; ry = n > 0 ? pp[1] : 0.f; rz = n > 0 ? pp[2] : 0.f;
+                } else {
+                    const float *pp = p.pos + 3 * (a0 + j), *pi = p.pos + 3 * i;
+                    rx = __fsub_rn(pp[0], pi[0]); ry = __fsub_rn(pp[1], pi[1]); rz = __fsub_rn(pp[2], pi[2]);
+                }
+                const float4 *qp = reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM);
+                const float4 *kp = reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
+                float4 *lp = reinterpret_cast<float4 *>(logit_io + (e0 + j) * HEADS);  // phi was left here by the phi kernel
+                float4 ph0 = make_float4(0.f, 0.f, 0.f, 0.f), ph1 = ph0;
+                if (live) { ph0 = lp[0]; ph1 = lp[1]; }
+                const float phi[8] = {ph0.x, ph0.y, ph0.z, ph0.w, ph1.x, ph1.y, ph1.z, ph1.w};
+                float sc[8], lg[8];
+#pragma unroll
+                for (int h = 0; h < HEADS; ++h) {
+                    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                    for (int t = 0; t < 4; t += 2) {
+                        const float4 k0 = __ldg(kp + 4 * h + t), k1 = __ldg(kp + 4 * h + t + 1);
+                        const float4 q0 = __ldg(qp + 4 * h + t), q1 = __ldg(qp + 4 * h + t + 1);
+                        s0 = fmaf(q0.x, k0.x, s0); s0 = fmaf(q0.y, k0.y, s0); s0 = fmaf(q0.z, k0.z, s0); s0 = fmaf(q0.w, k0.w, s0);
+                        s1 = fmaf(q1.x, k1.x, s1); s1 = fmaf(q1.y, k1.y, s1); s1 = fmaf(q1.z, k1.z, s1); s1 = fmaf(q1.w, k1.w, s1);
+                    }
+                    sc[h] = s0 + s1;
+                    lg[h] = live ? sc[h] + phi[h] : -INFINITY;
+                }
+                if (p.keep_logit && live) {
+                    lp[0] = make_float4(lg[0], lg[1], lg[2], lg[3]);
+                    lp[1] = make_float4(lg[4], lg[5], lg[6], lg[7]);
+                }
+                float mxo = -INFINITY, lse_mine = 0.f;
+#pragma unroll
+                for (int h = 0; h < HEADS; ++h) {
+                    const float mx = warp_max(lg[h]);
+                    const float den = warp_sum(ex2((lg[h] - mx) * LOG2E));
+                    const float lse = mx + logf(den);
+                    if (lane == h) lse_mine = lse;
+                    const float off = (sc[h] - lse) * LOG2E;
+                    if (live) {
+                        cj[h * ld + j] = off;
+                        pj[h * ld + j] = ex2((lg[h] - lse) * LOG2E);
+                    }
+                    mxo = fmaxf(mxo, off);
+                }
+                if (lane < HEADS) p.lse[i * HEADS + lane] = lse_mine;
+                if (live) rel[j] = make_float4(rx, ry, rz, mxo);  // .w: the key's largest offset
             }
+            row_sync();
         } else {
-            const float pix = p.pos[3 * i], piy = p.pos[3 * i + 1], piz = p.pos[3 * i + 2];
+            // ---- relative positions of the keys
+            if (p.pos_ij) {
+                for (int j = rt; j < n; j += RT) {
+                    const float *pp = p.pos_ij + 3 * (e0 + j);
+                    rel[j] = make_float4(pp[0], pp[1], pp[2], 0.f);
+                }
+            } else {
+                const float pix = p.pos[3 * i], piy = p.pos[3 * i + 1], piz = p.pos[3 * i + 2];
+                for (int j = rt; j < n; j += RT) {
+                    const float *pp = p.pos + 3 * (a0 + j);
+                    rel[j] = make_float4(__fsub_rn(pp[0], pix), __fsub_rn(pp[1], piy), __fsub_rn(pp[2], piz), 0.f);
+                }
+            }
+            // ---- the row's query, read back as shared-memory broadcasts (the buffer is reused for sum_j p v later)
+            float4 *qs = reinterpret_cast<float4 *>(vsum);
+            for (int idx = rt; idx < HEADS * HEAD_DIM / 4; idx += RT)
+                qs[idx] = __ldg(reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM) + idx);
+            row_sync();
+            // ---- logits: one key per thread, all eight heads; the key's 512-byte row is 32 independent 16-byte loads
             for (int j = rt; j < n; j += RT) {
-                const float *pp = p.pos + 3 * (a0 + j);
-                rel[j] = make_float4(__fsub_rn(pp[0], pix), __fsub_rn(pp[1], piy), __fsub_rn(pp[2], piz), 0.f);
+                const float4 *kp = reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
+                float4 *lp = reinterpret_cast<float4 *>(logit_io + (e0 + j) * HEADS);  // phi was left here by the phi kernel
+                const float4 ph0 = lp[0], ph1 = lp[1];
+                const float phi[8] = {ph0.x, ph0.y, ph0.z, ph0.w, ph1.x, ph1.y, ph1.z, ph1.w};
+                float lg[8];
+#pragma unroll
+                for (int h = 0; h < HEADS; ++h) {
+                    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                    for (int t = 0; t < 4; t += 2) {
+                        const float4 k0 = __ldg(kp + 4 * h + t), k1 = __ldg(kp + 4 * h + t + 1);
+                        const float4 q0 = qs[4 * h + t], q1 = qs[4 * h + t + 1];
+                        s0 = fmaf(q0.x, k0.x, s0); s0 = fmaf(q0.y, k0.y, s0); s0 = fmaf(q0.z, k0.z, s0); s0 = fmaf(q0.w, k0.w, s0);
+                        s1 = fmaf(q1.x, k1.x, s1); s1 = fmaf(q1.y, k1.y, s1); s1 = fmaf(q1.z, k1.z, s1); s1 = fmaf(q1.w, k1.w, s1);
+                    }
+                    const float sc = s0 + s1;
+                    lg[h] = sc + phi[h];
+                    cj[h * ld + j] = sc;
+                    pj[h * ld + j] = lg[h];
+                }
+                if (p.keep_logit) {
+                    lp[0] = make_float4(lg[0], lg[1], lg[2], lg[3]);
+                    lp[1] = make_float4(lg[4], lg[5], lg[6], lg[7]);
+                }
+            }
+            row_sync();
+            // ---- soft-max statistics: warp wr of the group owns heads wr, wr + ROW_WARPS, ...
+#pragma unroll
+            for (int h = wr; h < HEADS; h += ROW_WARPS) {
+                float mx = -INFINITY;
+                for (int j = lane; j < n; j += 32) mx = fmaxf(mx, pj[h * ld + j]);
+                mx = warp_max(mx);
+                float den = 0.f;
+                for (int j = lane; j < n; j += 32) den += ex2((pj[h * ld + j] - mx) * LOG2E);
+                den = warp_sum(den);
+                const float lse = mx + logf(den);
+                if (lane == 0) p.lse[i * HEADS + h] = lse;
+                for (int j = lane; j < n; j += 32) {
+                    cj[h * ld + j] = (cj[h * ld + j] - lse) * LOG2E;
+                    pj[h * ld + j] = ex2((pj[h * ld + j] - lse) * LOG2E);
+                }
+            }
+            row_sync();
+
+            if (K > 0) {
+                // ---- per key: the largest of the eight offsets, kept in the spare component of rel
+                for (int j = rt; j < n; j += RT) {
+                    float mxo = cj[j];
+#pragma unroll
+                    for (int h = 1; h < 8; ++h) mxo = fmaxf(mxo, cj[h * ld + j]);
+                    rel[j].w = mxo;
+                }
+                row_sync();
             }
         }
-        // ---- the row's query, read back as shared-memory broadcasts (the buffer is reused for sum_j p v later)
-        float4 *qs = reinterpret_cast<float4 *>(vsum);
-        for (int idx = rt; idx < HEADS * HEAD_DIM / 4; idx += RT)
-            qs[idx] = __ldg(reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM) + idx);
-        row_sync();
         // stage 1 of the look-ahead: the next row's crystal and edge range
         const long long c_n = p.batch[i_n], e0_n = p.row_start[i_n];
         const int n_n = (int)(p.row_start[i_n + 1] - e0_n);
-        // ---- logits: one key per thread, all eight heads; the key's 512-byte row is 32 independent 16-byte loads
-        for (int j = rt; j < n; j += RT) {
-            const float4 *kp = reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
-            float4 *lp = reinterpret_cast<float4 *>(logit_io + (e0 + j) * HEADS);  // phi was left here by the phi kernel
-            const float4 ph0 = lp[0], ph1 = lp[1];
-            const float phi[8] = {ph0.x, ph0.y, ph0.z, ph0.w, ph1.x, ph1.y, ph1.z, ph1.w};
-            float lg[8];
-#pragma unroll
-            for (int h = 0; h < HEADS; ++h) {
-                float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-                for (int t = 0; t < 4; t += 2) {
-                    const float4 k0 = __ldg(kp + 4 * h + t), k1 = __ldg(kp + 4 * h + t + 1);
-                    const float4 q0 = qs[4 * h + t], q1 = qs[4 * h + t + 1];
-                    s0 = fmaf(q0.x, k0.x, s0); s0 = fmaf(q0.y, k0.y, s0); s0 = fmaf(q0.z, k0.z, s0); s0 = fmaf(q0.w, k0.w, s0);
-                    s1 = fmaf(q1.x, k1.x, s1); s1 = fmaf(q1.y, k1.y, s1); s1 = fmaf(q1.z, k1.z, s1); s1 = fmaf(q1.w, k1.w, s1);
-                }
-                const float sc = s0 + s1;
-                lg[h] = sc + phi[h];
-                cj[h * ld + j] = sc;
-                pj[h * ld + j] = lg[h];
-            }
-            if (p.keep_logit) {
-                lp[0] = make_float4(lg[0], lg[1], lg[2], lg[3]);
-                lp[1] = make_float4(lg[4], lg[5], lg[6], lg[7]);
-            }
-        }
-        row_sync();
-        // ---- soft-max statistics: warp wr of the group owns heads wr, wr + ROW_WARPS, ...
-#pragma unroll
-        for (int h = wr; h < HEADS; h += ROW_WARPS) {
-            float mx = -INFINITY;
-            for (int j = lane; j < n; j += 32) mx = fmaxf(mx, pj[h * ld + j]);
-            mx = warp_max(mx);
-            float den = 0.f;
-            for (int j = lane; j < n; j += 32) den += ex2((pj[h * ld + j] - mx) * LOG2E);
-            den = warp_sum(den);
-            const float lse = mx + logf(den);
-            if (lane == 0) p.lse[i * HEADS + h] = lse;
-            for (int j = lane; j < n; j += 32) {
-                cj[h * ld + j] = (cj[h * ld + j] - lse) * LOG2E;
-                pj[h * ld + j] = ex2((pj[h * ld + j] - lse) * LOG2E);
-            }
-        }
-        row_sync();
 
         if (K > 0) {
-            // ---- per key: the largest of the eight offsets, kept in the spare component of rel
-            for (int j = rt; j < n; j += RT) {
-                float mxo = cj[j];
-#pragma unroll
-                for (int h = 1; h < 8; ++h) mxo = fmaxf(mxo, cj[h * ld + j]);
-                rel[j].w = mxo;
-            }
-            row_sync();
             // ---- boxes of the row's heads (they depend on the atom and the head, not on the key)
             const int pk_own = packed_box(p.rule, a_own, p.rvlen ? rvl : nullptr);
             int uni = pk_own;
@@ -334,7 +399,7 @@ __global__ void __launch_bounds__(THREADS, ROW_WARPS == 1 ? 3 : 4) infinite_attn
 
         // stage 2 of the look-ahead: the next row's first key; thread 0 publishes the ticket it drew
         const long long a0_n = (has_next && n_n > 0) ? p.edges[p.E + e0_n] : 0;
-        if (rt == 0) next_slot_sh[group] = first_wave + drawn;
+        if (p.ticket && rt == 0) next_slot_sh[group] = first_wave + drawn;
 
         // ---- sum_j p_ij v_j: warp wr takes keys wr, wr + ROW_WARPS, ...; a lane owns four consecutive channels (one
         //      float4 load per key); the partial rows of the group meet in shared memory
@@ -383,7 +448,7 @@ __global__ void __launch_bounds__(THREADS, ROW_WARPS == 1 ? 3 : 4) infinite_attn
         row_sync();
         if (!has_next) break;
         i = i_n; c = c_n; e0 = e0_n; n_raw = n_n; a0 = a0_n;
-        nslot = next_slot_sh[group];
+        nslot = p.ticket ? next_slot_sh[group] : nslot + first_wave;
     }
 }
 
@@ -417,6 +482,11 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     phi.a = a; phi.pos = pos; phi.pos_ij = pos_ij; phi.tvecs = tvecs; phi.batch = batch; phi.edges = edges; phi.rvlen = rvlen; phi.z = logit;
     phi.E = E; phi.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
     phi.floor_log2 = weight_floor_log2();
+    // rows with a basis expansion differ widely in cost and are drawn through a ticket, which the phi launch zeroes;
+    // without one (K = 0) rows are cheap and uniform and are dealt round-robin
+    unsigned *ticket = K > 0 ? next_ticket() : nullptr;
+    CF_REQUIRE(K == 0 || ticket != nullptr, CF_ERR_CUDA, "cf_infinite_attn_fwd: the row ticket could not be set up");
+    phi.zero_word = ticket;
     int rc = launch_lattice_phi(phi, s);
     if (rc != CF_OK) return rc;
 
@@ -425,6 +495,7 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     p.batch = batch; p.edges = edges; p.row_start = row_start; p.row_order = row_order; p.E = E;
     p.out = out; p.logit = logit; p.lse = lse; p.psi_row = psi_row; p.N = N; p.max_atoms = (int)max_atoms;
     p.keep_logit = 1;
+    p.ticket = ticket;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
     // warps per atom row: 1 for crystals of up to 12 atoms, 4 otherwise (CF_ROW_WARPS in the environment overrides)
@@ -454,8 +525,6 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
         cached_occ[slot] = occ;
         cached_smem[slot] = smem;
     }
-    p.ticket = next_ticket(s);
-    CF_REQUIRE(p.ticket != nullptr, CF_ERR_CUDA, "cf_infinite_attn_fwd: the row ticket could not be set up");
     const long long want = (N + groups - 1) / groups;
     const long long cap = (long long)sm_count() * cached_occ[slot];
     const int blocks = (int)(want < cap ? want : cap);

@@ -583,6 +583,7 @@ struct PhiArgs {
     BoxRule rule;
     float floor_log2;        // weights below 2^floor_log2 of the nearest image's are not summed
     int a_per_edge;
+    unsigned *zero_word;  // optional: a word this launch sets to zero (the row ticket of the kernel that follows)
 };
 int launch_lattice_phi(const PhiArgs &p, cudaStream_t stream);
 

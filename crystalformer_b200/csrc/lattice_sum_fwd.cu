@@ -81,6 +81,7 @@ template <int TPE>
 __global__ void __launch_bounds__(128) lattice_phi_kernel(const PhiArgs p)
 {
     const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gtid == 0 && p.zero_word) *p.zero_word = 0u;
     const long long e_raw = gtid / TPE;
     const int sub = (int)(gtid % TPE);
     const bool live = e_raw < p.E;

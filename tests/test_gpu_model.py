@@ -102,3 +102,29 @@ def test_sharded_batches_give_identical_outputs(golden_model):
         a, b = model(to_data(cb.select([4, 0, 2]))), model(to_data(cb.select([1, 5, 3])))
     assert rel_err(a.cpu().numpy(), full[[4, 0, 2]].cpu().numpy()) < 1e-5
     assert rel_err(b.cpu().numpy(), full[[1, 5, 3]].cpu().numpy()) < 1e-5
+
+
+def test_pipelined_predictor_equals_direct_calls(golden_model):
+    """Batches streamed through PipelinedPredictor (copies on a second stream, several batches in flight, results in
+    pinned ring buffers) give exactly what model(batch) gives, in submission order."""
+    from crystalformer_b200.serving import PipelinedPredictor
+    model = build(golden_model).eval()
+    batches = [make_crystals(40 + s, 5 + s, uniform_atoms(1, 8), length_range=(3.0, 10.0)) for s in range(5)]
+    host = [types.SimpleNamespace(x=torch.from_numpy(b.x).pin_memory(), pos=torch.from_numpy(b.pos).pin_memory(),
+                                  trans_vec=torch.from_numpy(b.trans_vec).pin_memory(),
+                                  sizes=torch.from_numpy(b.sizes).pin_memory()) for b in batches]
+    with torch.no_grad():
+        direct = [model(types.SimpleNamespace(**{k: v.cuda() for k, v in vars(h).items()})).cpu() for h in host]
+    runner = PipelinedPredictor(model, depth=2)
+    got, tickets = [], []
+    for h in host:
+        if runner.pending() == runner.depth:
+            got.append(runner.result(tickets.pop(0)).clone())
+        tickets.append(runner.submit(h))
+    while tickets:
+        got.append(runner.result(tickets.pop(0)).clone())
+    assert len(got) == len(direct)
+    for y, ref in zip(got, direct):
+        assert torch.equal(y, ref)
+    with pytest.raises(RuntimeError):
+        runner.result(123)
