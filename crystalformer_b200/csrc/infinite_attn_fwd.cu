@@ -498,10 +498,10 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     p.ticket = ticket;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
-    // warps per atom row: 4 (CF_ROW_WARPS = 1, 2 or 4 in the environment overrides; fewer warps per row keep more rows
-    // in flight but stretch the heaviest rows, which bound the kernel: measured slower on every workload tried)
+    // warps per atom row: 1 for crystals of up to 12 atoms, else 4 (CF_ROW_WARPS = 1, 2 or 4 in the environment
+    // overrides; fewer warps per row keep more rows in flight but stretch the heaviest rows, which bound the kernel)
     static const int forced = [] { const char *e = getenv("CF_ROW_WARPS"); return e ? atoi(e) : 0; }();
-    int row_warps = WARPS;
+    int row_warps = max_atoms <= 12 ? 1 : WARPS;
     if (forced == 1 || forced == 2 || forced == 4) row_warps = forced;
     const int groups = WARPS / row_warps;
     const size_t smem = sizeof(float) * groups * row_group_floats((int)max_atoms, K > 0, row_warps);
