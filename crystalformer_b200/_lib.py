@@ -32,6 +32,7 @@ SIGNATURES = {
                              I32, P, P, P, P, P, P, P, P, P, P, P],
     "cf_pipe_probe": [I32, I32, I32, I64, P, P],
     "cf_row_cost": [P, P, I64, I64, F64, P, P],
+    "cf_row_order": [P, P, I64, I64, F64, P, P],
     "cf_reci_phase": [P, P, P, P, I64, P, P],
     "cf_reci_sum_fwd": [P, P, P, P, P, P, I64, I64, I64, I32, P, P, P],
     "cf_reci_sum_bwd": [P, P, P, P, P, P, P, I64, I64, I64, I32, P, P],

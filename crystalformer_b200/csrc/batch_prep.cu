@@ -142,8 +142,99 @@ __global__ void row_cost_kernel(const int64_t *__restrict__ atom_start, const fl
     cost[i] = 1500.0f + n * (1.0f + sphere / fmaxf(fabsf(v), 1e-3f));
 }
 
+// Atoms in descending order of their row cost, ties by atom index (what a stable descending sort of cf_row_cost gives).
+// All rows of a crystal have the same cost, so it is the crystals that are sorted: one thread block, bitonic sort of
+// (cost, crystal) keys in shared memory, exclusive scan of the sorted atom counts, then every crystal's atoms are
+// written as one run.
+constexpr int ORDER_THREADS = 1024;
+constexpr int ORDER_MAX_CRYSTALS = 2048;
+
+__global__ void __launch_bounds__(ORDER_THREADS) row_order_kernel(const int64_t *__restrict__ atom_start,
+                                                                  const float *__restrict__ trans, int B, int padded,
+                                                                  float sphere, int32_t *__restrict__ order)
+{
+    __shared__ unsigned long long key[ORDER_MAX_CRYSTALS];
+    __shared__ int offset[ORDER_MAX_CRYSTALS];
+    __shared__ int warp_tot[ORDER_THREADS / 32];
+    const int tid = threadIdx.x;
+    for (int c = tid; c < padded; c += ORDER_THREADS) {
+        unsigned long long k = 0ull;  // padding sorts last
+        if (c < B) {
+            const float *m = trans + 9 * c;
+            const float v = m[0] * (m[4] * m[8] - m[5] * m[7]) - m[1] * (m[3] * m[8] - m[5] * m[6]) + m[2] * (m[3] * m[7] - m[4] * m[6]);
+            const float n = (float)(atom_start[c + 1] - atom_start[c]);
+            const float cost = 1500.0f + n * (1.0f + sphere / fmaxf(fabsf(v), 1e-3f));
+            // positive floats order like their bit patterns; the complemented index breaks ties towards low indices
+            k = ((unsigned long long)__float_as_uint(cost) << 32) | (unsigned)(0x7fffffff - c);
+        }
+        key[c] = k;
+    }
+    __syncthreads();
+    for (int size = 2; size <= padded; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = tid; t < (padded >> 1); t += ORDER_THREADS) {
+                const int lo = 2 * t - (t & (stride - 1));  // index of the pair's first element
+                const int hi = lo + stride;
+                const bool descending = (lo & size) == 0;
+                const unsigned long long a = key[lo], b = key[hi];
+                if ((a < b) == descending) { key[lo] = b; key[hi] = a; }
+            }
+            __syncthreads();
+        }
+    }
+    // exclusive scan of the sorted crystals' atom counts (chunks of ORDER_THREADS, carried over)
+    int carry = 0;
+    for (int base = 0; base < padded; base += ORDER_THREADS) {
+        const int k = base + tid;
+        int n = 0;
+        if (k < padded && key[k] != 0ull) {
+            const int c = 0x7fffffff - (int)(unsigned)(key[k] & 0xffffffffu);
+            n = (int)(atom_start[c + 1] - atom_start[c]);
+        }
+        int incl = n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(FULL, incl, o);
+            if ((tid & 31) >= o) incl += up;
+        }
+        if ((tid & 31) == 31) warp_tot[tid >> 5] = incl;
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < (tid >> 5); ++w) before += warp_tot[w];
+        int total = 0;
+        for (int w = 0; w < ORDER_THREADS / 32; ++w) total += warp_tot[w];
+        if (k < padded) offset[k] = carry + before + incl - n;
+        carry += total;
+        __syncthreads();
+    }
+    // every sorted crystal's atoms as one run; a warp per crystal, lanes over its atoms
+    for (int k = tid >> 5; k < padded; k += ORDER_THREADS / 32) {
+        if (key[k] == 0ull) continue;
+        const int c = 0x7fffffff - (int)(unsigned)(key[k] & 0xffffffffu);
+        const int first = (int)atom_start[c], n = (int)(atom_start[c + 1] - atom_start[c]);
+        for (int r = tid & 31; r < n; r += 32) order[offset[k] + r] = first + r;
+    }
+}
+
 }  // namespace
 }  // namespace cf
+
+extern "C" int cf_row_order(const int64_t *atom_start, const float *trans, int64_t B, int64_t N, double reach,
+                            int32_t *row_order, void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(B >= 0 && N >= 0 && reach >= 0, CF_ERR_INVALID, "cf_row_order: negative size");
+    CF_REQUIRE(B <= ORDER_MAX_CRYSTALS, CF_ERR_RANGE, "cf_row_order: B=%lld above %d crystals (sort cf_row_cost instead)",
+               (long long)B, ORDER_MAX_CRYSTALS);
+    CF_REQUIRE(N < (1ll << 31), CF_ERR_RANGE, "cf_row_order: N=%lld does not fit 32-bit atom indices", (long long)N);
+    if (N == 0 || B == 0) return CF_OK;
+    CF_REQUIRE(atom_start && trans && row_order, CF_ERR_INVALID, "cf_row_order: null pointer");
+    int padded = 2;
+    while (padded < B) padded <<= 1;
+    const float sphere = (float)(4.18879020478639 * reach * reach * reach);
+    row_order_kernel<<<1, ORDER_THREADS, 0, as_stream(stream)>>>(atom_start, trans, (int)B, padded, sphere, row_order);
+    return launch_status("cf_row_order");
+}
 
 extern "C" int cf_row_cost(const int64_t *atom_start, const float *trans, int64_t B, int64_t N, double reach,
                            float *cost, void *stream)

@@ -44,7 +44,7 @@ class BatchGeometry:
         self.batch, self.edges, self.row_start = prep["batch"], prep["edges"], prep["row_start"]
         self.pos_ij, self.rvecs, self.vcell, self.rvlen = prep["pos_ij"], prep["rvecs"], prep["vcell"], prep["rvlen"]
         self.sizes, self.max_atoms = sizes, int(max_atoms)
-        self.row_order = heaviest_first(self.row_start, ops.row_cost(self.atom_start, trans.float(), num_atoms))
+        self.row_order = ops.row_order(self.atom_start, trans.float(), num_atoms)
         self._kr_base = None
         register_edge_info(self.edges, self.row_start, self.max_atoms, self.row_order)
 

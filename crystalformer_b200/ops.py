@@ -271,6 +271,23 @@ def row_cost(atom_start, trans, N: int, reach: float = 15.0):
     return cost
 
 
+ROW_ORDER_MAX_CRYSTALS = 2048
+
+
+def row_order(atom_start, trans, N: int, reach: float = 15.0):
+    """(N,) int32: the atoms by descending scheduling weight, ties by index (see cf_row_order / cf_row_cost)."""
+    dev = trans.device
+    atom_start, trans = _want(atom_start, torch.int64, "atom_start", dev), _want(trans, torch.float32, "trans", dev)
+    B = trans.shape[0]
+    if B > ROW_ORDER_MAX_CRYSTALS:
+        return torch.argsort(row_cost(atom_start, trans, N, reach), descending=True, stable=True).to(torch.int32)
+    order = torch.empty((N,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_row_order", _ptr(atom_start), _ptr(trans), c_int64(B), c_int64(N), c_double(reach), _ptr(order),
+                  _stream(dev))
+    return order
+
+
 def reci_phase(pos_ij, rvecs, batch, edges):
     """kr_base (E,3) = rvecs[crystal of the edge] . pos_ij."""
     dev = pos_ij.device

@@ -40,25 +40,43 @@ def shard_balance(sizes: Sequence[int], shards: List[List[int]]) -> dict:
             "atoms_max_over_mean": float(a.max() / max(a.mean(), 1.0))}
 
 
+_GATHER_INDEX: dict = {}
+
+
+def _gather_index(shards: List[List[int]], longest: int, device) -> torch.Tensor:
+    """Row of the gathered (world * longest, T) buffer that holds crystal g of the unsharded batch, for every g.
+    Built once per (sharding, device): a host list turned into a device tensor is a synchronous copy, which must not
+    sit on the per-step path."""
+    key = (tuple(tuple(s) for s in shards), longest, str(device))
+    hit = _GATHER_INDEX.get(key)
+    if hit is None:
+        total = sum(len(s) for s in shards)
+        src = np.zeros(total, dtype=np.int64)
+        for r, s in enumerate(shards):
+            src[np.asarray(s, dtype=np.int64)] = r * longest + np.arange(len(s), dtype=np.int64)
+        hit = torch.from_numpy(src).to(device)
+        if len(_GATHER_INDEX) > 8:
+            _GATHER_INDEX.clear()
+        _GATHER_INDEX[key] = hit
+    return hit
+
+
 def gather_outputs(local: torch.Tensor, shards: List[List[int]], group=None) -> torch.Tensor:
     """All-gathers the per-crystal outputs of every rank and puts them back in the order of the unsharded batch.
 
     ``local`` is (len(shards[rank]), T) on this rank's device (CPU tensors with the gloo backend).  Shards are padded
     to the largest one so that a single fixed-size all-gather suffices."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    total = sum(len(s) for s in shards)
-    T = local.shape[1]
-    if world == 1:
-        out = local.new_empty((total, T))
-        out[torch.as_tensor(shards[0], device=local.device, dtype=torch.long)] = local
-        return out
     longest = max(len(s) for s in shards)
-    padded = local.new_zeros((longest, T))
-    padded[: local.shape[0]] = local
+    index = _gather_index(shards, longest, local.device)
+    if world == 1:
+        return local.index_select(0, index)
+    T = local.shape[1]
+    if local.shape[0] == longest:
+        padded = local.contiguous()
+    else:
+        padded = local.new_zeros((longest, T))
+        padded[: local.shape[0]] = local
     gathered = local.new_empty((world * longest, T))
     dist.all_gather_into_tensor(gathered, padded, group=group)
-    out = local.new_empty((total, T))
-    for r, s in enumerate(shards):
-        if s:
-            out[torch.as_tensor(s, device=local.device, dtype=torch.long)] = gathered[r * longest: r * longest + len(s)]
-    return out
+    return gathered.index_select(0, index)

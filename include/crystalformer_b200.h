@@ -241,6 +241,10 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
  * ---------------------------------------------------------------------------------------------------------- */
 int cf_row_cost(const int64_t *atom_start, const float *trans, int64_t B, int64_t N, double reach, float *cost,
                 void *stream);
+/* The atoms in descending order of cf_row_cost, ties by index (a stable descending sort of the costs), computed in
+ * one launch for batches of up to 2048 crystals (CF_ERR_RANGE beyond: sort the costs instead).  row_order (N) int32. */
+int cf_row_order(const int64_t *atom_start, const float *trans, int64_t B, int64_t N, double reach,
+                 int32_t *row_order, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Reciprocal-space lattice sum (domains `reci`, `RECI`, `multihead` of the reference's attention module).

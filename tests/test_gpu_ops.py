@@ -200,3 +200,20 @@ def test_errors_are_reported_not_thrown_away(ops):
     with pytest.raises(RuntimeError):
         ops.lattice_sum_fwd(torch.zeros((4, 8)), torch.zeros((4, 3)), torch.zeros((1, 3, 3)),
                             torch.zeros(4, dtype=torch.int64), torch.zeros((2, 4), dtype=torch.int64), K, DIST_MAX, WSCALE)
+
+
+@pytest.mark.parametrize("crystals,nmax", [(1, 5), (37, 9), (128, 30), (1500, 4)])
+def test_row_order_is_the_stable_descending_sort_of_the_row_costs(ops, crystals, nmax):
+    """The single-launch ordering kernel against torch's stable sort of cf_row_cost; integers, so bit exact."""
+    cb = make_crystals(50 + crystals, crystals, uniform_atoms(1, nmax))
+    sizes, trans = dev(cb.sizes), dev(cb.trans_vec)
+    atom_start, _ = ops.crystal_offsets(sizes)
+    cost = ops.row_cost(atom_start, trans, cb.num_atoms)
+    # the cost model itself: 1500 + n (1 + sphere / |det T|)
+    n = cb.sizes[cb.batch].astype(np.float64)
+    vol = np.abs(np.linalg.det(cb.trans_vec.astype(np.float64)))[cb.batch]
+    ref_cost = 1500.0 + n * (1.0 + 4.18879020478639 * 15.0 ** 3 / vol)
+    assert rel_err(cost.cpu().numpy(), ref_cost) < 1e-5
+    want = torch.argsort(cost, descending=True, stable=True).to(torch.int32)
+    got = ops.row_order(atom_start, trans, cb.num_atoms)
+    assert torch.equal(got, want)
