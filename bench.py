@@ -194,9 +194,8 @@ def run_b200(args):
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)  # > 126 MB L2
 
     def step_resident():
-        g = BatchGeometry(resident.pos, resident.trans_vec, resident.sizes, n_atoms, n_edges, max_atoms)
         with torch.no_grad():
-            y = model(resident, geometry=g)
+            y = model(resident, counts=(n_atoms, n_edges, max_atoms))
         return gather_outputs(y, shards) if world > 1 else y
 
     pinned = to_device_batch(mine, device, pinned=True)

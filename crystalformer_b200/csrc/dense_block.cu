@@ -1,0 +1,413 @@
+// The dense part of an encoder layer boundary in ONE kernel (inference):
+//
+//     tail of layer l      y  = x + attn Wo^T + bo
+//                          x' = y + relu(y W1^T + b1) W2^T + b2            (hidden units in chunks of 128, never stored)
+//     head of layer l+1    q|k|v = x' Wqkv^T + bqkv ;  a = width(q . w_pos) ;  q <- q / sqrt(16)
+//
+// (models/indexed_latticeformer_encoder.py:848-890 without LayerNorm, and the in-projection and Gaussian-width
+// pipeline of models/indexed_lattice_multi_head_attention_cuda.py:582-722.)  The reference - and the cuBLAS path of
+// cf_encoder_forward - runs this as four GEMMs and two element-wise passes per layer, each a separate launch over a
+// few thousand rows.  Here a thread block owns a tile of 16 MT atom rows and carries it through all four
+// products; only x', q, k, v and a are written.
+//
+// Arithmetic: fp32 accuracy on the tensor cores by the three-product TF32 split,
+//     a b ~ a_hi b_hi + a_lo b_hi + a_hi b_lo,   a_hi = tf32(a), a_lo = tf32(a - a_hi)      (relative error ~2^-21),
+// with warp-level mma.m16n8k8 (a 16-row tile per instruction fits the ragged, few-thousand-row batches; the
+// 64/128-row tiles of the block-level tensor instructions would leave most SMs idle at these sizes).  Weights are
+// pre-split and stored in fragment order by the host (pack order documented at DensePacked below), so a B fragment is
+// one 16-byte load per lane; activations are split when they are written to shared memory.
+#include "common.cuh"
+#include "dense_block.cuh"
+
+namespace cf {
+namespace {
+
+constexpr int DB_THREADS = 256;           // 8 warps; warp w owns output columns 16 w .. 16 w + 15 of every 128-wide product
+constexpr int DB_WARPS = DB_THREADS / 32;
+constexpr int LDA = 132;                  // row stride of the operand tiles (words): 528 bytes, so the eight 16-byte rows
+                                          // of an ldmatrix fall into distinct bank groups
+
+__device__ __forceinline__ unsigned tf32_hi(float x)
+{
+    unsigned r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const unsigned *row)
+{
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// ---- weight stream ---------------------------------------------------------------------------------------------------
+// A warp consumes its B fragments in an order that is fixed in advance: panel after panel (a panel = the 16 k steps of
+// one 128-deep product for the warp's two column tiles), the same sequence for every row tile.  The packed layout
+// makes a fragment lane-private (a lane reads back exactly the 16 bytes it fetched), so each warp runs its own
+// cp.async ring, DEPTH items (k steps) ahead, across product, barrier and tile boundaries alike, with no block-level
+// synchronisation: weights stream from L2 continuously while the tensor cores work.
+constexpr int DEPTH = 8;                  // k steps in flight per warp: 8 x 1 KB
+constexpr int RING_WORDS = DEPTH * 2 * 32 * 4;
+
+struct Panel {
+    const float4 *base;   // fragments of the warp's first column tile at k step 0
+    size_t tile_stride;   // float4 between the warp's two column tiles
+};
+
+struct WeightStream {
+    float4 *ring;         // this warp's [DEPTH][2][32] float4
+    int lane;
+    int panels;           // panels per row tile
+    long long produced, consumed, limit;  // items; limit = tiles of this block x panels x 16
+    struct { const float4 *Wo, *W1, *W2, *Wqkv; int ff, tail; } d;
+    int warp;
+    int p_panel, p_ks;    // producer position within the row tile's sequence
+    Panel cur;            // the producer's current panel
+
+    __device__ __forceinline__ Panel panel(int idx) const
+    {
+        const int chunks = d.ff / 128;
+        Panel r;
+        if (d.tail && idx == 0) {
+            r.base = d.Wo + (size_t)(2 * warp) * 16 * 32;
+            r.tile_stride = 16 * 32;
+        } else if (d.tail && idx <= 2 * chunks) {
+            const int ch = (idx - 1) >> 1;
+            if ((idx - 1) & 1) {  // W2, k steps 16 ch .. 16 ch + 15 of column tiles 2 warp, 2 warp + 1
+                r.base = d.W2 + ((size_t)(2 * warp) * (d.ff / 8) + 16 * ch) * 32;
+                r.tile_stride = (size_t)(d.ff / 8) * 32;
+            } else {              // W1, column tiles of the chunk's hidden units
+                r.base = d.W1 + (size_t)(16 * ch + 2 * warp) * 16 * 32;
+                r.tile_stride = 16 * 32;
+            }
+        } else {                  // Wqkv, group 0..2 of the warp's 48 output columns
+            const int grp = idx - (d.tail ? 1 + 2 * chunks : 0);
+            r.base = d.Wqkv + (size_t)((48 * warp + 16 * grp) / 8) * 16 * 32;
+            r.tile_stride = 16 * 32;
+        }
+        return r;
+    }
+    __device__ __forceinline__ void produce()
+    {
+        if (produced < limit) {
+            float4 *dst = ring + (size_t)(produced & (DEPTH - 1)) * 64 + lane;
+            const float4 *src = cur.base + (size_t)p_ks * 32 + lane;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const unsigned saddr = (unsigned)__cvta_generic_to_shared(dst + 32 * nt);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + nt * cur.tile_stride));
+            }
+            if (++p_ks == 16) {  // next panel of the sequence (wrapping to the next row tile's first)
+                p_ks = 0;
+                if (++p_panel == panels) p_panel = 0;
+                cur = panel(p_panel);
+            }
+        }
+        asm volatile("cp.async.commit_group;");  // always commit, so that the group count stays in step
+        ++produced;
+    }
+    __device__ __forceinline__ void start()
+    {
+        p_panel = p_ks = 0;
+        cur = panel(0);
+        for (int i = 0; i < DEPTH; ++i) produce();
+    }
+    // the next item's two fragments; refills the slot it frees
+    __device__ __forceinline__ void consume(float4 (&b)[2])
+    {
+        asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+        const float4 *src = ring + (size_t)(consumed & (DEPTH - 1)) * 64 + lane;
+        b[0] = src[0];
+        b[1] = src[32];
+        ++consumed;
+        produce();
+    }
+};
+
+// acc[mt][nt] += A (rows of the tile x 128, split in shared memory) . B (the next panel of the weight stream).
+template <int MT>
+__device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsigned *__restrict__ a_hi,
+                                            const unsigned *__restrict__ a_lo, WeightStream &ws, int lane)
+{
+    // ldmatrix hands a lane the 32-bit words (row lane/4, word lane%4) of four 8-row x 16-byte matrices, which for
+    // 32-bit elements are exactly the a0..a3 of the m16n8k8 A fragment: rows 0-7 / 8-15 of the m tile, words 0-3 / 4-7
+    // of the k step.  Lane l supplies the address of row l%8 of matrix l/8.
+    const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8, lcol = (lane >> 4) * 4;
+    // the three partial products go to separate accumulators: three independent dependency chains per tile instead of
+    // one of triple length
+    float lo1[MT][2][4], lo2[MT][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) lo1[mt][nt][u] = lo2[mt][nt][u] = 0.f;
+#pragma unroll 2
+    for (int ks = 0; ks < 16; ++ks) {
+        float4 b[2];
+        ws.consume(b);
+        unsigned ah[MT][4], al[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const int off = (16 * mt + lrow) * LDA + 8 * ks + lcol;
+            ldmatrix_x4(ah[mt], a_hi + off);
+            ldmatrix_x4(al[mt], a_lo + off);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const unsigned bh0 = __float_as_uint(b[nt].x), bh1 = __float_as_uint(b[nt].y);
+            const unsigned bl0 = __float_as_uint(b[nt].z), bl1 = __float_as_uint(b[nt].w);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_tf32(lo1[mt][nt], al[mt], bh0, bh1);
+                mma_tf32(lo2[mt][nt], ah[mt], bl0, bl1);
+                mma_tf32(acc[mt][nt], ah[mt], bh0, bh1);
+            }
+        }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[mt][nt][u] += lo1[mt][nt][u] + lo2[mt][nt][u];
+}
+
+// Writes this lane's accumulator entries of a 128-wide product (columns 16 warp + 8 nt + 2 t + {0,1}) into an operand tile.
+template <int MT>
+__device__ __forceinline__ void store_split(unsigned *a_hi, unsigned *a_lo, const float (&v)[MT][2][4], int warp, int lane)
+{
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int row = 16 * mt + g + (u >= 2 ? 8 : 0), col = 16 * warp + 8 * nt + 2 * t + (u & 1);
+                const unsigned hi = tf32_hi(v[mt][nt][u]);
+                a_hi[row * LDA + col] = hi;
+                a_lo[row * LDA + col] = tf32_hi(v[mt][nt][u] - __uint_as_float(hi));
+            }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs p)
+{
+    extern __shared__ __align__(16) unsigned smem_u[];
+    constexpr int ROWS = 16 * MT;
+    unsigned *a1_hi = smem_u, *a1_lo = a1_hi + ROWS * LDA;       // operand tile 1: attn, then y, then x'
+    unsigned *a2_hi = a1_lo + ROWS * LDA, *a2_lo = a2_hi + ROWS * LDA;  // operand tile 2: a chunk of hidden units
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    const long long tiles = (p.N + ROWS - 1) / ROWS;
+    const long long my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    WeightStream ws;
+    ws.ring = reinterpret_cast<float4 *>(a2_lo + ROWS * LDA) + (size_t)warp * DEPTH * 64;
+    ws.lane = lane;
+    ws.warp = warp;
+    ws.d.Wo = p.Wo; ws.d.W1 = p.W1; ws.d.W2 = p.W2; ws.d.Wqkv = p.Wqkv; ws.d.ff = p.ff; ws.d.tail = p.tail;
+    ws.panels = (p.tail ? 1 + 2 * (p.ff / 128) : 0) + (p.head ? 3 : 0);
+    ws.produced = ws.consumed = 0;
+    ws.limit = my_tiles * ws.panels * 16;
+    ws.start();
+
+    for (long long tile = blockIdx.x; tile * ROWS < p.N; tile += gridDim.x) {
+        const long long row0 = tile * ROWS;
+        float xo[MT][2][4];  // the rows' current features at this lane's accumulator positions (x, then y, then x')
+        __syncthreads();     // the previous tile's readers are done with the operand tiles
+        if (p.tail) {
+            // ---- operand 1 <- attention output of the tile, split
+            for (int idx = tid; idx < ROWS * 32; idx += DB_THREADS) {
+                const int r = idx >> 5, c4 = idx & 31;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (row0 + r < p.N) v = reinterpret_cast<const float4 *>(p.attn + (row0 + r) * 128)[c4];
+                const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const unsigned hi = tf32_hi(vv[u]);
+                    a1_hi[r * LDA + 4 * c4 + u] = hi;
+                    a1_lo[r * LDA + 4 * c4 + u] = tf32_hi(vv[u] - __uint_as_float(hi));
+                }
+            }
+            // ---- y = x + bo + attn Wo^T
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int col = 16 * warp + 8 * nt + 2 * t;
+                    const float2 bo = *reinterpret_cast<const float2 *>(p.bo + col);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const long long row = row0 + 16 * mt + g + 8 * half;
+                        float2 xv = make_float2(0.f, 0.f);
+                        if (row < p.N) xv = *reinterpret_cast<const float2 *>(p.x + row * 128 + col);
+                        xo[mt][nt][2 * half] = xv.x + bo.x;
+                        xo[mt][nt][2 * half + 1] = xv.y + bo.y;
+                    }
+                }
+            __syncthreads();
+            product_128<MT>(xo, a1_hi, a1_lo, ws, lane);
+            __syncthreads();  // every warp has read attn
+            store_split<MT>(a1_hi, a1_lo, xo, warp, lane);
+            // ---- x' = y + b2 + sum over chunks of relu(y W1_c^T + b1_c) W2_c^T
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const float2 b2 = *reinterpret_cast<const float2 *>(p.b2 + 16 * warp + 8 * nt + 2 * t);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    xo[mt][nt][0] += b2.x; xo[mt][nt][1] += b2.y; xo[mt][nt][2] += b2.x; xo[mt][nt][3] += b2.y;
+                }
+            }
+            __syncthreads();  // y is in operand 1
+            const int chunks = p.ff / 128;
+            for (int ch = 0; ch < chunks; ++ch) {
+                float h[MT][2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const float2 b1 = *reinterpret_cast<const float2 *>(p.b1 + 128 * ch + 16 * warp + 8 * nt + 2 * t);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) { h[mt][nt][0] = b1.x; h[mt][nt][1] = b1.y; h[mt][nt][2] = b1.x; h[mt][nt][3] = b1.y; }
+                }
+                product_128<MT>(h, a1_hi, a1_lo, ws, lane);  // W1, the chunk's hidden units
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) h[mt][nt][u] = fmaxf(h[mt][nt][u], 0.f);
+                __syncthreads();  // the previous chunk's readers are done with operand 2
+                store_split<MT>(a2_hi, a2_lo, h, warp, lane);
+                __syncthreads();
+                product_128<MT>(xo, a2_hi, a2_lo, ws, lane);  // W2, the chunk's k steps
+            }
+            // ---- write x'
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const long long row = row0 + 16 * mt + g + 8 * half;
+                        if (row < p.N)
+                            *reinterpret_cast<float2 *>(p.x + row * 128 + 16 * warp + 8 * nt + 2 * t) =
+                                make_float2(xo[mt][nt][2 * half], xo[mt][nt][2 * half + 1]);
+                    }
+        } else {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const long long row = row0 + 16 * mt + g + 8 * half;
+                        float2 xv = make_float2(0.f, 0.f);
+                        if (row < p.N) xv = *reinterpret_cast<const float2 *>(p.x + row * 128 + 16 * warp + 8 * nt + 2 * t);
+                        xo[mt][nt][2 * half] = xv.x;
+                        xo[mt][nt][2 * half + 1] = xv.y;
+                    }
+        }
+        if (!p.head) continue;  // (block-uniform)
+
+        // ---- in-projection of the next layer: operand 1 <- x'
+        __syncthreads();  // every warp is done with y in operand 1
+        store_split<MT>(a1_hi, a1_lo, xo, warp, lane);
+        __syncthreads();
+        // warp w owns the 48 output columns 48 w .. 48 w + 47 of q|k|v = three 16-column groups (one head each)
+#pragma unroll
+        for (int grp = 0; grp < 3; ++grp) {
+            const int col0 = 48 * warp + 16 * grp;  // 0..127 q, 128..255 k, 256..383 v
+            float acc[MT][2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const float2 bq = *reinterpret_cast<const float2 *>(p.bqkv + col0 + 8 * nt + 2 * t);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) { acc[mt][nt][0] = bq.x; acc[mt][nt][1] = bq.y; acc[mt][nt][2] = bq.x; acc[mt][nt][3] = bq.y; }
+            }
+            product_128<MT>(acc, a1_hi, a1_lo, ws, lane);
+            const int which = col0 >> 7;           // 0 q, 1 k, 2 v (warp-uniform)
+            const int hc0 = col0 & 127;            // first column within q, k or v; the head is hc0 / 16
+            float *dst = which == 0 ? p.q : (which == 1 ? p.k : p.v);
+            if (which == 0) {
+                // the head's Gaussian width from alpha = q . w_pos (…attention_cuda.py:647-722), then q / sqrt(16)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        float alpha = 0.f;
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt) {
+                            const float2 wq = *reinterpret_cast<const float2 *>(p.w_pos + hc0 + 8 * nt + 2 * t);
+                            alpha = fmaf(acc[mt][nt][2 * half], wq.x, alpha);
+                            alpha = fmaf(acc[mt][nt][2 * half + 1], wq.y, alpha);
+                        }
+                        alpha += __shfl_xor_sync(FULL, alpha, 1);
+                        alpha += __shfl_xor_sync(FULL, alpha, 2);
+                        const long long row = row0 + 16 * mt + g + 8 * half;
+                        if (t == 0 && row < p.N) {
+                            const float xn = (alpha + p.gauss_shift) * p.gauss_scale;
+                            const float tt = xn * (p.elu_beta / (1.0f - p.lower_bound));
+                            const float elu = tt > 0.f ? tt : expm1f(tt);
+                            p.a[row * HEADS + (hc0 >> 4)] = ((1.0f - p.lower_bound) * elu + 1.0f) * p.a_factor;
+                        }
+                    }
+            }
+            const float scale = which == 0 ? 0.25f : 1.0f;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const long long row = row0 + 16 * mt + g + 8 * half;
+                        if (row < p.N)
+                            *reinterpret_cast<float2 *>(dst + row * 128 + hc0 + 8 * nt + 2 * t) =
+                                make_float2(acc[mt][nt][2 * half] * scale, acc[mt][nt][2 * half + 1] * scale);
+                    }
+        }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
+}  // namespace
+
+int launch_dense_block(const DenseArgs &p, cudaStream_t s)
+{
+    if (p.N == 0) return CF_OK;
+    if (p.tail && (p.ff <= 0 || p.ff % 128 != 0))
+        return fail(CF_ERR_UNSUPPORTED, "dense block: ff_dim=%d must be a positive multiple of 128", p.ff);
+    // 16-row tiles while they fit one wave of the SMs (more SMs busy), 32-row tiles beyond (half the weight traffic;
+    // a block is tensor-pipe bound either way, so what counts is the number of waves)
+    const long long tiles16 = (p.N + 15) / 16;
+    const int sms = sm_count();
+    const bool small = tiles16 <= sms;
+    const size_t smem = sizeof(unsigned) * (4 * (small ? 16 : 32) * LDA + DB_WARPS * RING_WORDS);
+    auto kernel = small ? dense_block_kernel<1> : dense_block_kernel<2>;
+    if (smem > 48 * 1024) {
+        static thread_local bool raised_small = false, raised_large = false;
+        bool &raised = small ? raised_small : raised_large;
+        if (!raised) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+                cudaGetLastError();
+                return fail(CF_ERR_CUDA, "dense block: %zu bytes of shared memory not available", smem);
+            }
+            raised = true;
+        }
+    }
+    const long long tiles = small ? tiles16 : (p.N + 31) / 32;
+    const long long cap = sms;  // one block per SM: the weight rings fill most of the shared memory
+    kernel<<<(unsigned)(tiles < cap ? tiles : cap), DB_THREADS, smem, s>>>(p);
+    return launch_status("dense_block_kernel");
+}
+
+}  // namespace cf

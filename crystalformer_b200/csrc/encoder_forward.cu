@@ -16,58 +16,12 @@
 //
 // cuBLAS is resolved at run time from the copy already loaded in the process (the caller passes its handle), so that
 // the handle and the functions come from the same library.  No training support: the autograd path stays in Python.
-#include <cublas_v2.h>
-#include <dlfcn.h>
-
-#include <mutex>
-
+#include "blas_dyn.cuh"
 #include "common.cuh"
+#include "dense_block.cuh"
 
 namespace cf {
 namespace {
-
-using SgemmFn = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const float *,
-                                   const float *, int, const float *, int, const float *, float *, int);
-using SetStreamFn = cublasStatus_t (*)(cublasHandle_t, cudaStream_t);
-using GetStreamFn = cublasStatus_t (*)(cublasHandle_t, cudaStream_t *);
-using SetMathFn = cublasStatus_t (*)(cublasHandle_t, cublasMath_t);
-using GetMathFn = cublasStatus_t (*)(cublasHandle_t, cublasMath_t *);
-
-struct Blas {
-    SgemmFn sgemm = nullptr;
-    SetStreamFn set_stream = nullptr;
-    GetStreamFn get_stream = nullptr;
-    SetMathFn set_math = nullptr;
-    GetMathFn get_math = nullptr;
-    bool ok = false;
-};
-
-const Blas &blas()
-{
-    static Blas b;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_NOLOAD);
-        if (!lib) lib = dlopen("libcublas.so.12", RTLD_NOW | RTLD_GLOBAL);
-        if (!lib) lib = dlopen("libcublas.so", RTLD_NOW | RTLD_GLOBAL);
-        if (!lib) return;
-        b.sgemm = (SgemmFn)dlsym(lib, "cublasSgemm_v2");
-        b.set_stream = (SetStreamFn)dlsym(lib, "cublasSetStream_v2");
-        b.get_stream = (GetStreamFn)dlsym(lib, "cublasGetStream_v2");
-        b.set_math = (SetMathFn)dlsym(lib, "cublasSetMathMode");
-        b.get_math = (GetMathFn)dlsym(lib, "cublasGetMathMode");
-        b.ok = b.sgemm && b.set_stream && b.get_stream && b.set_math && b.get_math;
-    });
-    return b;
-}
-
-// Y (rows x out) = [beta] Y + X (rows x in) W^T, W (out x in), all row-major.
-inline cublasStatus_t linear(const Blas &b, cublasHandle_t h, const float *X, const float *W, float *Y, int rows, int in,
-                             int out, float beta)
-{
-    const float one = 1.0f;
-    return b.sgemm(h, CUBLAS_OP_T, CUBLAS_OP_N, out, rows, in, &one, W, in, X, in, &beta, Y, out);
-}
 
 struct LayerScalars {
     float gauss_scale, gauss_shift;  // alpha <- (alpha + shift) * scale
@@ -166,12 +120,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
     CF_REQUIRE(bl.ok, CF_ERR_CUDA, "cf_encoder_forward: libcublas.so.12 could not be resolved in this process");
     cublasHandle_t handle = reinterpret_cast<cublasHandle_t>(cublas_handle);
     cudaStream_t s = as_stream(stream);
-    cudaStream_t old_stream = nullptr;
-    cublasMath_t old_math = CUBLAS_DEFAULT_MATH;
-    bl.get_stream(handle, &old_stream);
-    bl.get_math(handle, &old_math);
-    bl.set_stream(handle, s);
-    bl.set_math(handle, CUBLAS_DEFAULT_MATH);  // plain fp32 (no TF32), as the reference's train.py:61-62 asks
+    BlasScope scope(bl, handle, s);
 
     float *qkv = workspace;
     float *q = qkv + N * 384, *k = q + N * 128, *v = k + N * 128, *attn = v + N * 128;
@@ -179,8 +128,53 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
     const int rows = (int)N, ff = (int)ff_dim;
     int rc = CF_OK;
     cublasStatus_t st = CUBLAS_STATUS_SUCCESS;
+
+    // Fused dense path: every layer brings its weights packed for the tensor-core kernel (slot 10) and the
+    // feed-forward width is a multiple of 128.  One launch per layer boundary instead of four GEMMs and two
+    // element-wise passes; see dense_block.cu.
+    bool fused = ff % 128 == 0;
+    for (int l = 0; l < num_layers; ++l) fused = fused && weights[11 * l + 10] != nullptr;
+    if (fused) {
+        auto head_of = [&](DenseArgs &d, int l) {
+            const float *const *w = weights + 11 * l;
+            const double *sc = scalars + 6 * l;
+            d.head = 1;
+            d.Wqkv = reinterpret_cast<const float4 *>(w[10]);
+            d.bqkv = w[1];
+            d.w_pos = w[2];
+            d.gauss_scale = (float)sc[0]; d.gauss_shift = (float)sc[1]; d.a_factor = (float)sc[2];
+            d.elu_beta = (float)sc[3]; d.lower_bound = (float)sc[4];
+        };
+        DenseArgs d{};
+        d.N = N; d.ff = ff; d.x = x; d.q = q; d.k = k; d.v = v; d.a = a; d.attn = attn;
+        head_of(d, 0);
+        rc = launch_dense_block(d, s);
+        for (int l = 0; l < num_layers && rc == CF_OK; ++l) {
+            const float *const *w = weights + 11 * l;
+            const double *sc = scalars + 6 * l;
+            if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
+            rc = cf_infinite_attn_fwd(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS, HEAD_DIM,
+                                      E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range, minimum_range, attn,
+                                      logit, lse, nullptr, row_order, s);
+            if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
+            if (rc != CF_OK) break;
+            DenseArgs t{};
+            t.N = N; t.ff = ff; t.x = x; t.q = q; t.k = k; t.v = v; t.a = a; t.attn = attn;
+            t.tail = 1;
+            const float4 *packed = reinterpret_cast<const float4 *>(w[10]);
+            t.Wo = packed + 48 * 16 * 32;                     // after Wqkv (48 column tiles x 16 k steps x 32 lanes)
+            t.W1 = t.Wo + 16 * 16 * 32;
+            t.W2 = t.W1 + (size_t)(ff / 8) * 16 * 32;
+            t.bo = w[5]; t.b1 = w[7]; t.b2 = w[9];
+            if (l + 1 < num_layers) head_of(t, l + 1);
+            rc = launch_dense_block(t, s);
+        }
+        if (rc != CF_OK) return rc;
+        return launch_status("cf_encoder_forward");
+    }
+
     for (int l = 0; l < num_layers && rc == CF_OK && st == CUBLAS_STATUS_SUCCESS; ++l) {
-        const float *const *w = weights + 11 * l;  // Wqkv, bqkv, w_pos, Wpe, Wo, bo, W1, b1, W2, b2, (reserved)
+        const float *const *w = weights + 11 * l;  // Wqkv, bqkv, w_pos, Wpe, Wo, bo, W1, b1, W2, b2, packed (optional)
         const double *sc = scalars + 6 * l;        // gauss_scale, gauss_shift, a_factor, elu_beta, lower_bound, dist_max
         LayerScalars ls{(float)sc[0], (float)sc[1], (float)sc[2], (float)sc[3], (float)sc[4]};
         st = linear(bl, handle, x, w[0], qkv, rows, 128, 384, 0.0f);
@@ -201,8 +195,6 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
         ffn_post_kernel<<<(unsigned)((work + 255) / 256), 256, 0, s>>>(hidden, w[7], N, ff, x, w[9]);
         st = linear(bl, handle, hidden, w[8], x, rows, ff, 128, 1.0f);
     }
-    bl.set_math(handle, old_math);
-    bl.set_stream(handle, old_stream);
     if (st != CUBLAS_STATUS_SUCCESS) return fail(CF_ERR_CUDA, "cf_encoder_forward: cuBLAS SGEMM failed with status %d", (int)st);
     if (rc != CF_OK) return rc;
     return launch_status("cf_encoder_forward");

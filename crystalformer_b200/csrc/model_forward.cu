@@ -1,0 +1,144 @@
+// Inference forward of the whole model in ONE host call:
+//   species features -> embedding -> batch geometry -> encoder stack -> per-crystal mean -> two-layer head.
+//
+// The reference's Latticeformer.forward (models/latticeformer.py:211-302) is a chain of framework calls; at the sizes
+// of a crystal batch the host cannot issue them as fast as the GPU retires them.  Here the chain is issued back to
+// back from C++ on one stream: five geometry launches, one SGEMM for the embedding, cf_encoder_forward, and one fused
+// kernel for the pooling (models/pooling.py:19-25 with the fixed summation tree of irregular_mean_fwd.cu) and the
+// multi-layer-perceptron head (Linear - ReLU - Linear, models/latticeformer.py:176-209 with norm_type "no").
+// No allocation, no synchronisation: scratch comes from the caller's workspace.
+#include "blas_dyn.cuh"
+#include "common.cuh"
+#include "segment_mean.cuh"
+
+namespace cf {
+namespace {
+
+constexpr int MODEL_DIM = 128;
+constexpr int HEAD_THREADS = 128;
+constexpr int HEAD_MAX_HIDDEN = 1024;
+
+// One thread block per crystal: mean of the atoms' features, hidden = relu(W1 mean + b1), y = W2 hidden + b2.
+__global__ void __launch_bounds__(HEAD_THREADS) pool_head_kernel(const float *__restrict__ x,
+                                                                 const int64_t *__restrict__ atom_start,
+                                                                 const float *__restrict__ W1, const float *__restrict__ b1,
+                                                                 const float *__restrict__ W2, const float *__restrict__ b2,
+                                                                 int hidden, int targets, float *__restrict__ y)
+{
+    __shared__ __align__(16) float pooled[MODEL_DIM];
+    __shared__ float hid[HEAD_MAX_HIDDEN];
+    const long long c = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long s = atom_start[c], len = atom_start[c + 1] - s;
+    pooled[tid] = len > 0 ? segment_mean_channel(x + s * MODEL_DIM + tid, MODEL_DIM, len) : 0.f;
+    __syncthreads();
+    const float4 *p4 = reinterpret_cast<const float4 *>(pooled);
+    for (int u = tid; u < hidden; u += HEAD_THREADS) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(W1 + (size_t)u * MODEL_DIM);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 8
+        for (int d = 0; d < MODEL_DIM / 4; ++d) {
+            const float4 w = __ldg(w4 + d), v = p4[d];
+            a0 = fmaf(w.x, v.x, a0); a1 = fmaf(w.y, v.y, a1); a2 = fmaf(w.z, v.z, a2); a3 = fmaf(w.w, v.w, a3);
+        }
+        hid[u] = fmaxf((a0 + a1) + (a2 + a3) + b1[u], 0.f);
+    }
+    __syncthreads();
+    for (int t = warp; t < targets; t += HEAD_THREADS / 32) {
+        float acc = 0.f;
+        for (int u = lane; u < hidden; u += 32) acc = fmaf(W2[(size_t)t * hidden + u], hid[u], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) y[c * targets + t] = acc + b2[t];
+    }
+}
+
+inline size_t align_up(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct Carve {
+    char *base;
+    size_t used = 0;
+    template <class T>
+    T *take(size_t count)
+    {
+        T *p = base ? reinterpret_cast<T *>(base + used) : nullptr;
+        used += align_up(count * sizeof(T));
+        return p;
+    }
+};
+
+struct Scratch {
+    int64_t *atom_start, *edge_start, *batch, *row_start, *edges;
+    float *pos_ij, *rvlen, *x, *encoder;
+    int32_t *row_order;
+    size_t bytes;
+};
+
+Scratch carve(void *workspace, int64_t N, int64_t B, int64_t E, int64_t ff_dim)
+{
+    Carve c{static_cast<char *>(workspace)};
+    Scratch s{};
+    s.atom_start = c.take<int64_t>(B + 1);
+    s.edge_start = c.take<int64_t>(B + 1);
+    s.batch = c.take<int64_t>(N);
+    s.row_start = c.take<int64_t>(N + 1);
+    s.edges = c.take<int64_t>(2 * E);
+    s.pos_ij = c.take<float>(3 * E);
+    s.rvlen = c.take<float>(3 * B);
+    s.row_order = c.take<int32_t>(N);
+    s.x = c.take<float>(N * MODEL_DIM);
+    s.encoder = c.take<float>((size_t)cf_encoder_workspace_floats(N, E, ff_dim));
+    s.bytes = c.used;
+    return s;
+}
+
+}  // namespace
+}  // namespace cf
+
+extern "C" int64_t cf_model_workspace_bytes(int64_t N, int64_t B, int64_t E, int64_t ff_dim)
+{
+    return (int64_t)cf::carve(nullptr, N, B, E, ff_dim).bytes;
+}
+
+extern "C" int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
+                                const float *trans, const int64_t *sizes, int64_t N, int64_t B, int64_t E,
+                                int64_t max_atoms, const float *W_embed, int num_layers, const float *const *weights,
+                                const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                                int lattice_range, int minimum_range, const float *W1, const float *b1, int64_t hidden,
+                                const float *W2, const float *b2, int64_t targets, double order_reach, void *workspace,
+                                float *y, void *const *attn_events, void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(N >= 0 && B >= 0 && E >= 0 && feature_dim > 0, CF_ERR_INVALID, "cf_model_forward: bad size");
+    CF_REQUIRE(hidden > 0 && hidden <= HEAD_MAX_HIDDEN && targets > 0, CF_ERR_UNSUPPORTED,
+               "cf_model_forward: head of %lld hidden units, %lld targets (hidden <= %d)", (long long)hidden,
+               (long long)targets, HEAD_MAX_HIDDEN);
+    CF_REQUIRE(N < (1ll << 31) / 512, CF_ERR_RANGE, "cf_model_forward: N=%lld too large for 32-bit GEMM sizes", (long long)N);
+    if (B == 0) return CF_OK;
+    CF_REQUIRE(cublas_handle && features && pos && trans && sizes && W_embed && W1 && b1 && W2 && b2 && workspace && y,
+               CF_ERR_INVALID, "cf_model_forward: null pointer");
+    const Blas &bl = blas();
+    CF_REQUIRE(bl.ok, CF_ERR_CUDA, "cf_model_forward: libcublas.so.12 could not be resolved in this process");
+    cudaStream_t s = as_stream(stream);
+    Scratch w = carve(workspace, N, B, E, ff_dim);
+
+    int rc = cf_crystal_offsets(sizes, B, w.atom_start, w.edge_start, stream);
+    if (rc != CF_OK) return rc;
+    rc = cf_batch_prepare(pos, trans, sizes, w.atom_start, w.edge_start, B, N, E, w.batch, w.edges, w.row_start, w.pos_ij,
+                          nullptr, nullptr, w.rvlen, stream);
+    if (rc != CF_OK) return rc;
+    const int32_t *order = nullptr;  // batches beyond the one-launch sort are processed in index order
+    if (cf_row_order(w.atom_start, trans, B, N, order_reach, w.row_order, stream) == CF_OK) order = w.row_order;
+    if (N > 0) {
+        cublasHandle_t handle = reinterpret_cast<cublasHandle_t>(cublas_handle);
+        BlasScope scope(bl, handle, s);
+        const cublasStatus_t st = linear(bl, handle, features, W_embed, w.x, (int)N, (int)feature_dim, MODEL_DIM, 0.0f);
+        if (st != CUBLAS_STATUS_SUCCESS) return fail(CF_ERR_CUDA, "cf_model_forward: cuBLAS SGEMM failed with status %d", (int)st);
+    }
+    rc = cf_encoder_forward(cublas_handle, num_layers, weights, scalars, w.x, w.pos_ij, trans,
+                            cutoff_radius != 0.0 ? w.rvlen : nullptr, w.batch, w.edges, w.row_start, N, B, E, max_atoms, K,
+                            ff_dim, wscale, cutoff_radius, lattice_range, minimum_range, w.encoder, order, attn_events,
+                            stream);
+    if (rc != CF_OK) return rc;
+    pool_head_kernel<<<(unsigned)B, HEAD_THREADS, 0, s>>>(w.x, w.atom_start, W1, b1, W2, b2, (int)hidden, (int)targets, y);
+    return launch_status("cf_model_forward");
+}

@@ -30,6 +30,28 @@ def _get_activation_fn(activation):
     raise RuntimeError("activation should be relu/gelu, not {}".format(activation))
 
 
+def _tf32(x: Tensor) -> Tensor:
+    """x rounded to TF32 (10-bit mantissa, ties away from zero), as cvt.rna.tf32.f32 does."""
+    bits = x.contiguous().view(torch.int32)
+    return ((bits + 0x1000) & ~0x1FFF).view(torch.float32)
+
+
+def pack_dense_weight(W: Tensor) -> Tensor:
+    """A Linear weight (out, in) in the fragment order of the fused dense kernel: float4 entries
+    [(nt * in/8 + ks) * 32 + lane] = (hi W[n,k], hi W[n,k+4], lo W[n,k], lo W[n,k+4]) with n = 8 nt + lane // 4,
+    k = 8 ks + lane % 4, hi = TF32 rounding, lo = hi(w - hi(w)).  Returned flat."""
+    out_f, in_f = W.shape
+    assert out_f % 8 == 0 and in_f % 8 == 0
+    W = W.detach().float()
+    hi = _tf32(W)
+    lo = _tf32(W - hi)
+
+    def frag(M):  # (out, in) -> (nt, ks, g, t, half)
+        return M.view(out_f // 8, 8, in_f // 8, 2, 4).permute(0, 2, 1, 4, 3)
+
+    return torch.cat((frag(hi), frag(lo)), dim=-1).contiguous().reshape(-1)
+
+
 class BatchGeometry:
     """Everything the attention layers need besides the atom features, computed once per batch on the device."""
 
@@ -136,6 +158,7 @@ class CrystalformerEncoderCUDA(Module):
         self.d_model = d_model
         self.nhead = nhead
         self.native = True  # use the one-call inference path whenever it applies
+        self.dense_fused = True  # ... with the projections and feed-forward of a layer boundary fused into one kernel
         v_head_dim = v_dim if v_dim > 0 else d_model // nhead
         k_head_dim = k_dim if k_dim > 0 else d_model // nhead
         compile_kernels(lattice_params.lattice_range, nhead, k_head_dim, lattice_params.value_pe_dist_real, v_head_dim,
@@ -164,7 +187,7 @@ class CrystalformerEncoderCUDA(Module):
         """Device pointers and scalars of every layer in the layout cf_encoder_forward expects; rebuilt only when a
         parameter changed (in-place updates bump ``_version``)."""
         params = [p for p in self.parameters()]
-        key = (device, tuple(p._version for p in params), tuple(p.data_ptr() for p in params))
+        key = (device, self.dense_fused, tuple(p._version for p in params), tuple(p.data_ptr() for p in params))
         cache = getattr(self, "_native_cache", None)
         if cache is not None and cache[0] == key:
             return cache[1]
@@ -176,6 +199,10 @@ class CrystalformerEncoderCUDA(Module):
                        att.pe_dist_proj if att.pe_dist_proj is not None else None, att.out_proj.weight, att.out_proj.bias,
                        layer.linear1.weight, layer.linear1.bias, layer.linear2.weight, layer.linear2.bias, None]
             tensors = [None if t is None else t.detach().float().contiguous() for t in tensors]
+            if self.dense_fused and layer.linear1.weight.shape[0] % 128 == 0:
+                # slot 10: in-projection, out-projection and feed-forward weights packed for the fused dense kernel
+                tensors[10] = torch.cat([pack_dense_weight(m) for m in
+                                         (wqkv, att.out_proj.weight, layer.linear1.weight, layer.linear2.weight)])
             keep.append(tensors)
             ptrs += [0 if t is None else t.data_ptr() for t in tensors]
             beta = float(P.positive_func.split("=")[1]) if "=" in P.positive_func else 1.0
@@ -189,6 +216,16 @@ class CrystalformerEncoderCUDA(Module):
         self._native_cache = (key, packed)
         return packed
 
+    def _cutoff(self) -> float:
+        """The cut-off argument of the kernels: 0 fixed box, < 0 adaptive (sigmas), > 0 static radius in Angstrom."""
+        P = self.lattice_params
+        if P.adaptive_cutoff_sigma < 0:
+            return float(P.adaptive_cutoff_sigma)
+        if P.adaptive_cutoff_sigma > 0:
+            sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
+            return float(sr * P.gauss_lb_real ** (-0.5) * P.adaptive_cutoff_sigma)
+        return 0.0
+
     def _forward_native(self, src: Tensor, trans: Tensor, g: "BatchGeometry") -> Tensor:
         P = self.lattice_params
         dev = src.device
@@ -197,12 +234,7 @@ class CrystalformerEncoderCUDA(Module):
         x = src.detach().float().contiguous().clone()
         lib = _lib.load()
         work = torch.empty(int(lib.cf_encoder_workspace_floats(N, E, w["ff"])), dtype=torch.float32, device=dev)
-        cutoff = 0.0
-        if P.adaptive_cutoff_sigma < 0:
-            cutoff = float(P.adaptive_cutoff_sigma)
-        elif P.adaptive_cutoff_sigma > 0:
-            sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
-            cutoff = sr * P.gauss_lb_real ** (-0.5) * P.adaptive_cutoff_sigma
+        cutoff = self._cutoff()
         with torch.cuda.device(dev):
             _lib.call("cf_encoder_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()), len(self.layers),
                       w["ptrs"], w["scalars"], x.data_ptr(), g.pos_ij.data_ptr(), trans.data_ptr(),

@@ -6,12 +6,14 @@ replaced by one process per GPU (``crystalformer_b200.sharding``)."""
 from __future__ import annotations
 
 import copy
+import ctypes
 import types
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
 
+from . import _lib
 from .cuda_funcs import IrregularMeanCUDA
 from .encoder import BatchGeometry, CrystalformerEncoderCUDA
 from .params import DEFAULT_MODEL_PARAMS, LatticeformerParams
@@ -103,10 +105,63 @@ class Latticeformer(nn.Module):
         layers.append(nn.Linear(embedding_dim[-1], final_dim))
         self.mlp = nn.Sequential(*layers)
 
-    def forward(self, data, geometry: Optional[BatchGeometry] = None):
-        """``data`` carries x (N,98), pos (N,3), batch (N), trans_vec (B,3,3), sizes (B) like the reference's PyG batch."""
+    # ---------------------------------------------------------------------------------------------------------------
+    # Inference fast path: embedding, geometry, encoder, pooling and head in one call into the library
+    # (cf_model_forward); taken in eval mode without autograd when the configuration is the one it implements.
+    # ---------------------------------------------------------------------------------------------------------------
+    def _native_ok(self) -> bool:
+        if not getattr(self, "native", True) or self.pooling != "avr" or isinstance(self.proj_before_pooling, nn.Module):
+            return False
+        m = self.mlp
+        if not (len(m) == 4 and isinstance(m[0], nn.Linear) and isinstance(m[1], nn.Identity)
+                and isinstance(m[2], nn.ReLU) and isinstance(m[3], nn.Linear) and m[0].in_features == 128
+                and m[0].out_features <= 1024 and m[0].bias is not None and m[3].bias is not None):
+            return False
+        return self.input_embeddings.out_features == 128 and self.encoder.native and self.encoder._native_ok()
+
+    def _forward_native(self, data, counts: Tuple[int, int, int]) -> torch.Tensor:
+        enc = self.encoder
+        P = enc.lattice_params
+        dev = data.pos.device
+        w = enc._packed_weights(dev)
+        n_atoms, n_edges, max_atoms = (int(v) for v in counts)
+        f32 = lambda t: t.detach().float().contiguous()
+        feats, pos, trans = f32(data.x), f32(data.pos), f32(data.trans_vec)
+        sizes = data.sizes.to(device=dev, dtype=torch.int64).contiguous()
+        emb, w1, b1 = f32(self.input_embeddings.weight), f32(self.mlp[0].weight), f32(self.mlp[0].bias)
+        w2, b2 = f32(self.mlp[3].weight), f32(self.mlp[3].bias)
+        B, hidden, targets = sizes.shape[0], w1.shape[0], w2.shape[0]
+        lib = _lib.load()
+        work = torch.empty(int(lib.cf_model_workspace_bytes(n_atoms, B, n_edges, w["ff"])), dtype=torch.uint8, device=dev)
+        y = torch.empty((B, targets), dtype=torch.float32, device=dev)
+        dist_max = P.value_pe_dist_max
+        if dist_max < 0:
+            sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
+            dist_max = -dist_max * sr
+        with torch.cuda.device(dev):
+            _lib.call("cf_model_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()), feats.data_ptr(),
+                      feats.shape[1], pos.data_ptr(), trans.data_ptr(), sizes.data_ptr(), n_atoms, B, n_edges, max_atoms,
+                      emb.data_ptr(), len(enc.layers), w["ptrs"], w["scalars"], int(P.value_pe_dist_real), w["ff"],
+                      float(P.value_pe_width_scale), enc._cutoff(), int(P.lattice_range),
+                      int(P.lattice_range) if P.minimum_range else 0, w1.data_ptr(), b1.data_ptr(), hidden,
+                      w2.data_ptr(), b2.data_ptr(), targets, float(dist_max) + 1.0, work.data_ptr(), y.data_ptr(),
+                      enc._attention_events(), torch.cuda.current_stream(dev).cuda_stream)
+        return y
+
+    def forward(self, data, geometry: Optional[BatchGeometry] = None, counts: Optional[Tuple[int, int, int]] = None):
+        """``data`` carries x (N,98), pos (N,3), batch (N), trans_vec (B,3,3), sizes (B) like the reference's PyG batch.
+        ``counts`` = (atoms, edges = sum n^2, largest crystal), when the caller knows them on the host, saves the
+        device->host read of ``sizes``."""
+        if geometry is None and not self.training and not torch.is_grad_enabled() and data.pos.is_cuda \
+                and self._native_ok():
+            if counts is None:
+                host = data.sizes.tolist()  # the one device->host read per batch (the reference does the same)
+                counts = (sum(host), sum(n * n for n in host), max(host) if host else 1)
+            return self._forward_native(data, counts)
         x = self.input_embeddings(data.x)
-        g = geometry if geometry is not None else BatchGeometry(data.pos, data.trans_vec, data.sizes)
+        if geometry is None:
+            geometry = BatchGeometry(data.pos, data.trans_vec, data.sizes, *(counts if counts is not None else ()))
+        g = geometry
         x = self.encoder(x, data.pos, g.batch, data.trans_vec, g.sizes, geometry=g)
         x = self.proj_before_pooling(x)
         x = self.pooling_layer(x, g.batch, g.sizes)

@@ -22,8 +22,6 @@ from typing import Deque, Optional, Tuple
 
 import torch
 
-from .encoder import BatchGeometry
-
 
 class PipelinedPredictor:
     def __init__(self, model: torch.nn.Module, depth: int = 3, device: Optional[torch.device] = None, post=None):
@@ -60,9 +58,8 @@ class PipelinedPredictor:
         compute.wait_event(copied)
         for t in vars(dev).values():
             t.record_stream(compute)  # allocated on the copy stream, consumed on the compute stream
-        geometry = BatchGeometry(dev.pos, dev.trans_vec, dev.sizes, n_atoms, n_edges, max_atoms)
         with torch.no_grad():
-            y = self.model(dev, geometry=geometry)
+            y = self.model(dev, counts=(n_atoms, n_edges, max_atoms))
             if self.post is not None:
                 y = self.post(y)
         slot = self._next % self.depth

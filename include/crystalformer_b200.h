@@ -216,7 +216,13 @@ int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const f
  *   weights : HOST array of num_layers x 11 device pointers:
  *             Wqkv (384,128) [q,k,v rows stacked], bqkv (384), lattice_pos_weights (128), pe_dist_proj (8,16,K) or
  *             NULL, out_proj.weight (128,128), out_proj.bias (128), linear1.weight (ff,128), linear1.bias (ff),
- *             linear2.weight (128,ff), linear2.bias (128), reserved
+ *             linear2.weight (128,ff), linear2.bias (128), packed (optional)
+ *             packed: NULL, or Wqkv, out_proj.weight, linear1.weight, linear2.weight concatenated in the fragment
+ *             order of the fused dense kernel: a weight W (out,in) as float4 entries
+ *             [(nt * in/8 + ks) * 32 + lane] = (hi W[n,k], hi W[n,k+4], lo W[n,k], lo W[n,k+4]), n = 8 nt + lane/4,
+ *             k = 8 ks + lane%4, hi = rounding to TF32 (ties away), lo = hi(w - hi(w)).  When every layer has it and
+ *             ff_dim is a multiple of 128, the four products and the element-wise steps of a layer boundary run as ONE
+ *             tensor-core kernel with three-product TF32 splitting (fp32-level accuracy) instead of cuBLAS SGEMMs.
  *   scalars : HOST array of num_layers x 6 doubles: gauss_scale, gauss_shift, -0.5/scale_real^2, elu beta,
  *             gauss_lb_real, dist_max
  *   x       : (N,128) atom features, updated in place
@@ -232,6 +238,25 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
                        int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
                        int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
                        void *const *attn_events, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Inference forward of the whole model in one host call (what Latticeformer.forward does in eval mode,
+ * models/latticeformer.py:211-302, with pooling "avr", pre_pooling_op "no", norm_type "no" and a head of the form
+ * Linear - ReLU - Linear): y (B, targets) from the species features (N, feature_dim), positions, lattices and sizes.
+ * Runs cf_crystal_offsets, cf_batch_prepare, cf_row_order, one SGEMM for the embedding (W_embed (128, feature_dim),
+ * no bias), cf_encoder_forward (same weights / scalars / box arguments) and a fused mean + head kernel
+ * (W1 (hidden,128), b1, W2 (targets,hidden), b2; hidden <= 1024).  N, E = sum n, sum n^2 and max_atoms are host
+ * integers the caller knows from the sizes.  workspace: cf_model_workspace_bytes(N, B, E, ff_dim) bytes, 256-byte
+ * aligned.  order_reach: the reach handed to cf_row_order (about dist_max).
+ * ---------------------------------------------------------------------------------------------------------- */
+int64_t cf_model_workspace_bytes(int64_t N, int64_t B, int64_t E, int64_t ff_dim);
+int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
+                     const float *trans, const int64_t *sizes, int64_t N, int64_t B, int64_t E, int64_t max_atoms,
+                     const float *W_embed, int num_layers, const float *const *weights, const double *scalars,
+                     int64_t K, int64_t ff_dim, double wscale, double cutoff_radius, int lattice_range,
+                     int minimum_range, const float *W1, const float *b1, int64_t hidden, const float *W2,
+                     const float *b2, int64_t targets, double order_reach, void *workspace, float *y,
+                     void *const *attn_events, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Scheduling weight of every atom's row for the fused attention kernels (no counterpart in the reference, which

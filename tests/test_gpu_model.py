@@ -66,6 +66,7 @@ def test_one_call_encoder_forward_equals_the_operator_by_operator_path(golden_mo
     """Inference takes the single-call path (cf_encoder_forward); it must agree with the torch-operator path that
     training uses, and with the reference's output."""
     model = build(golden_model).eval()
+    model.native = False  # keep the model shell in torch so that the encoder-level call is the one exercised
     data = batch_of(golden_model)
     calls = []
     enc = model.encoder
@@ -81,6 +82,29 @@ def test_one_call_encoder_forward_equals_the_operator_by_operator_path(golden_mo
     enc.native = True
     y_grad = model(data)  # gradients enabled: must not take the inference path
     assert len(calls) == 1 and y_grad.requires_grad
+
+
+def test_one_call_model_forward_equals_the_torch_shell(golden_model):
+    """cf_model_forward (embedding, geometry, encoder, pooling and head in one library call) against the same model
+    evaluated through torch modules around the encoder, with and without host-side counts."""
+    model = build(golden_model).eval()
+    data = batch_of(golden_model)
+    calls = []
+    original = model._forward_native
+    model._forward_native = lambda *a, **k: (calls.append(1), original(*a, **k))[1]
+    sizes = golden_model["in_sizes"]
+    counts = (int(sizes.sum()), int((sizes ** 2).sum()), int(sizes.max()))
+    with torch.no_grad():
+        y_native = model(data)
+        y_counts = model(data, counts=counts)
+        model.native = False
+        y_shell = model(data)
+    assert len(calls) == 2
+    assert torch.equal(y_native, y_counts)
+    assert rel_err(y_native.cpu().numpy(), y_shell.cpu().numpy()) < 1e-5
+    assert rel_err(y_native.cpu().numpy(), golden_model["y_f64"]) < TOL
+    model.native = True
+    assert model(data).requires_grad and len(calls) == 2  # gradients enabled: the autograd path
 
 
 def test_state_dict_keys_are_the_reference_keys(golden_model):
