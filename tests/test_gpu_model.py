@@ -107,6 +107,32 @@ def test_one_call_model_forward_equals_the_torch_shell(golden_model):
     assert model(data).requires_grad and len(calls) == 2  # gradients enabled: the autograd path
 
 
+@pytest.mark.parametrize("atoms", [(1, 7), (20, 45)])
+def test_fused_dense_block_equals_the_sgemm_path(golden_model, atoms):
+    """The tensor-core dense block (three-product TF32 splitting) against the same forward with cuBLAS SGEMMs: fp32-level
+    agreement, on a batch smaller than one 16-row tile wave and on one with several tiles per block row range."""
+    from crystalformer_b200.model import Latticeformer, default_params
+    torch.manual_seed(3)
+    model = Latticeformer(default_params(num_layers=3)).cuda()
+    cb = make_crystals(60, 9, uniform_atoms(*atoms), length_range=(4.0, 10.0))
+    t = lambda x: torch.as_tensor(x).cuda()
+    data = types.SimpleNamespace(x=t(cb.x), pos=t(cb.pos), batch=t(cb.batch), trans_vec=t(cb.trans_vec), sizes=t(cb.sizes))
+    model.train()
+    with torch.no_grad():
+        model(data)  # stores gauss_scale
+    model.eval()
+    with torch.no_grad():
+        model.encoder.dense_fused = True
+        y_fused = model(data)
+        model.encoder.dense_fused = False
+        y_sgemm = model(data)
+        model.native = False
+        model.encoder.native = False
+        y_torch = model(data)
+    assert rel_err(y_fused.cpu().numpy(), y_sgemm.cpu().numpy()) < 1e-5
+    assert rel_err(y_fused.cpu().numpy(), y_torch.cpu().numpy()) < 1e-5
+
+
 def test_state_dict_keys_are_the_reference_keys(golden_model):
     model = build(golden_model)
     ref_keys = sorted(k[len("state:"):] for k in golden_model if k.startswith("state:"))
