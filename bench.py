@@ -294,7 +294,7 @@ def run_b200(args):
             "terms_per_launch": terms_per_call, "launches": op_calls, "avg_launch_us": t_call * 1e6,
             "share_of_step": op_ms / ms_total,
             "traffic": None,
-            "note": "work counted for EVERY (edge, translation) term; terms whose weights fall below 2^-40 are skipped "
+            "note": "work counted for EVERY (edge, translation) term; terms whose weights fall below 2^-30 are skipped "
                     "by the kernel, so frac may exceed the executed-instruction utilisation",
         }
         micro = lattice_microbench(ops, device, peaks)

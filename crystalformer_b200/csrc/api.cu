@@ -9,7 +9,7 @@
 namespace cf {
 
 static thread_local char g_error[512] = "";
-static std::atomic<double> g_floor_log2{-40.0};
+static std::atomic<double> g_floor_log2{-30.0};
 
 int fail(int code, const char *fmt, ...)
 {

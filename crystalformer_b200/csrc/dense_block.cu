@@ -121,15 +121,20 @@ struct WeightStream {
         cur = panel(0);
         for (int i = 0; i < DEPTH; ++i) produce();
     }
-    // the next item's two fragments; refills the slot it frees
-    __device__ __forceinline__ void consume(float4 (&b)[2])
+    // the next G items' fragments (b[i][nt]); refills the slots they free
+    template <int G>
+    __device__ __forceinline__ void consume(float4 (&b)[G][2])
     {
-        asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
-        const float4 *src = ring + (size_t)(consumed & (DEPTH - 1)) * 64 + lane;
-        b[0] = src[0];
-        b[1] = src[32];
-        ++consumed;
-        produce();
+        asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - G) : "memory");
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const float4 *src = ring + (size_t)((consumed + i) & (DEPTH - 1)) * 64 + lane;
+            b[i][0] = src[0];
+            b[i][1] = src[32];
+        }
+        consumed += G;
+#pragma unroll
+        for (int i = 0; i < G; ++i) produce();
     }
 };
 
@@ -151,28 +156,33 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int u = 0; u < 4; ++u) lo1[mt][nt][u] = lo2[mt][nt][u] = 0.f;
-#pragma unroll 2
-    for (int ks = 0; ks < 16; ++ks) {
-        float4 b[2];
-        ws.consume(b);
-        unsigned ah[MT][4], al[MT][4];
+    constexpr int G = MT == 1 ? 4 : 2;  // k steps fetched and issued together: loads of all G before the first MMA
+#pragma unroll 1
+    for (int ks0 = 0; ks0 < 16; ks0 += G) {
+        float4 b[G][2];
+        ws.template consume<G>(b);
+        unsigned ah[G][MT][4], al[G][MT][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            const int off = (16 * mt + lrow) * LDA + 8 * ks + lcol;
-            ldmatrix_x4(ah[mt], a_hi + off);
-            ldmatrix_x4(al[mt], a_lo + off);
-        }
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const unsigned bh0 = __float_as_uint(b[nt].x), bh1 = __float_as_uint(b[nt].y);
-            const unsigned bl0 = __float_as_uint(b[nt].z), bl1 = __float_as_uint(b[nt].w);
+        for (int i = 0; i < G; ++i)
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                mma_tf32(lo1[mt][nt], al[mt], bh0, bh1);
-                mma_tf32(lo2[mt][nt], ah[mt], bl0, bl1);
-                mma_tf32(acc[mt][nt], ah[mt], bh0, bh1);
+                const int off = (16 * mt + lrow) * LDA + 8 * (ks0 + i) + lcol;
+                ldmatrix_x4(ah[i][mt], a_hi + off);
+                ldmatrix_x4(al[i][mt], a_lo + off);
             }
-        }
+#pragma unroll
+        for (int i = 0; i < G; ++i)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const unsigned bh0 = __float_as_uint(b[i][nt].x), bh1 = __float_as_uint(b[i][nt].y);
+                const unsigned bl0 = __float_as_uint(b[i][nt].z), bl1 = __float_as_uint(b[i][nt].w);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_tf32(lo1[mt][nt], al[i][mt], bh0, bh1);
+                    mma_tf32(lo2[mt][nt], ah[i][mt], bl0, bl1);
+                    mma_tf32(acc[mt][nt], ah[i][mt], bh0, bh1);
+                }
+            }
     }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)

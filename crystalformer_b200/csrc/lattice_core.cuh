@@ -124,7 +124,7 @@ __device__ __forceinline__ void term_sums(const float (&a2)[8], const float (&li
                                           float floor_log2, float (&sum)[8])
 {
     // the term with d2 = m contributes 1 to every sum it belongs to, so a term whose largest weight is below the
-    // floor (2^-40 by default) changes no sum by more than that fraction: skip its eight ex2
+    // floor (2^-30 by default) changes no sum by more than that fraction: skip its eight ex2
     if (a2max * rel > floor_log2) {
 #pragma unroll
         for (int h = 0; h < 8; ++h) {
@@ -353,10 +353,7 @@ struct BasisParams {
     int windowed;      // 1: basis narrow enough for the three-window accumulation (see BinAccumulator)
 };
 
-#ifndef CF_SWEEP
-#define CF_SWEEP 0
-#endif
-constexpr int STAGE_FLOATS = 44 * 12;  // per warp: 32 entries + 3 x 3 padding rows, each (x, pad[3], w0..7); 16-byte aligned
+constexpr int STAGE_FLOATS = 32 * 12;  // per warp: 32 entries x (x, pad[3], w0..7); 16-byte aligned rows
 
 // Packed FP32 pair arithmetic of sm_100 (fma.rn.f32x2): one issue slot for two FMAs.
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
@@ -418,31 +415,6 @@ struct BinAccumulator {
             const unsigned m2 = __ballot_sync(FULL, keep && win == 2);
             if ((m0 | m1 | m2) == 0u) return;
             const int n0 = __popc(m0), n1 = __popc(m1), n2 = __popc(m2);
-#if CF_SWEEP == 2
-            // each window's entries start at a multiple of four rows and are padded with zero-weight rows to a
-            // multiple of four, so that the sweep always has four entries in flight
-            const int s1 = (n0 + 3) & ~3, s2 = s1 + ((n1 + 3) & ~3), s3 = s2 + ((n2 + 3) & ~3);
-            if (keep) {
-                const int slot = win == 0 ? __popc(m0 & lt) : (win == 1 ? s1 + __popc(m1 & lt) : s2 + __popc(m2 & lt));
-                float4 *row = reinterpret_cast<float4 *>(stage + 12 * slot);
-                row[0] = make_float4(x, 0.f, 0.f, 0.f);
-                row[1] = make_float4(w[0], w[1], w[2], w[3]);
-                row[2] = make_float4(w[4], w[5], w[6], w[7]);
-            }
-            if (lane < 9) {
-                const int pw = lane / 3, pr = lane - 3 * pw;
-                const int first = pw == 0 ? n0 : (pw == 1 ? s1 + n1 : s2 + n2), last = pw == 0 ? s1 : (pw == 1 ? s2 : s3);
-                if (first + pr < last) {
-                    float4 *row = reinterpret_cast<float4 *>(stage + 12 * (first + pr));
-                    row[0] = row[1] = row[2] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-            }
-            __syncwarp();
-            sweep_window(0, s1, c0, 0);
-            sweep_window(s1, s2, c1, 4);
-            sweep_window(s2, s3, c2, 8);
-            __syncwarp();
-#else
             if (keep) {
                 const int slot = win == 0 ? __popc(m0 & lt) : (win == 1 ? n0 + __popc(m1 & lt) : n0 + n1 + __popc(m2 & lt));
                 float4 *row = reinterpret_cast<float4 *>(stage + 12 * slot);
@@ -455,7 +427,6 @@ struct BinAccumulator {
             sweep_window(n0, n0 + n1, c1, 4);
             sweep_window(n0 + n1, n0 + n1 + n2, c2, 8);
             __syncwarp();
-#endif
         } else {
             const unsigned mask = __ballot_sync(FULL, keep);
             if (mask == 0u) return;
@@ -485,7 +456,6 @@ struct BinAccumulator {
         }
     }
 
-#if CF_SWEEP == 0
     __device__ __forceinline__ void sweep_window(int begin, int end, float centre, int base)
     {
 #pragma unroll 2
@@ -501,43 +471,6 @@ struct BinAccumulator {
             acc[base + 3] = fma2(make_float2(wb.z, wb.w), G, acc[base + 3]);
         }
     }
-#else
-    __device__ __forceinline__ void sweep_window(int begin, int end, float centre, int base)
-    {
-        int m = begin;
-        for (; m + 4 <= end; m += 4) {
-            float g[4];
-            float4 wa[4], wb[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float4 *row = reinterpret_cast<const float4 *>(stage + 12 * (m + u));
-                const float t = centre - row[0].x;
-                wa[u] = row[1];
-                wb[u] = row[2];
-                g[u] = ex2(-t * t);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float2 G = make_float2(g[u], g[u]);
-                acc[base + 0] = fma2(make_float2(wa[u].x, wa[u].y), G, acc[base + 0]);
-                acc[base + 1] = fma2(make_float2(wa[u].z, wa[u].w), G, acc[base + 1]);
-                acc[base + 2] = fma2(make_float2(wb[u].x, wb[u].y), G, acc[base + 2]);
-                acc[base + 3] = fma2(make_float2(wb[u].z, wb[u].w), G, acc[base + 3]);
-            }
-        }
-        for (; m < end; ++m) {
-            const float4 *row = reinterpret_cast<const float4 *>(stage + 12 * m);
-            const float t = centre - row[0].x;
-            const float4 wa = row[1], wb = row[2];
-            const float g = ex2(-t * t);
-            const float2 G = make_float2(g, g);
-            acc[base + 0] = fma2(make_float2(wa.x, wa.y), G, acc[base + 0]);
-            acc[base + 1] = fma2(make_float2(wa.z, wa.w), G, acc[base + 1]);
-            acc[base + 2] = fma2(make_float2(wb.x, wb.y), G, acc[base + 2]);
-            acc[base + 3] = fma2(make_float2(wb.z, wb.w), G, acc[base + 3]);
-        }
-    }
-#endif
 
     // Writes the per-bin totals of this warp into tile[h * stride + k] (shared memory, overwritten).
     __device__ __forceinline__ void flush(float *tile, int stride)

@@ -47,9 +47,11 @@ int cf_version(void);
  * failing call on the same thread. */
 const char *cf_last_error(void);
 
-/* Terms of the lattice sum whose Gaussian weight exp(a (d^2 - d^2_min)) is below 2^log2_floor for every head are
- * left out of the radial-basis accumulation (never out of the log-sum-exp itself).  Default -40 (a relative error
- * below 1e-10); pass -1000 to accumulate every term.  Process-wide tuning knob, read at launch time. */
+/* Terms of a lattice sum whose weight is below 2^log2_floor of the sum's largest term for every head are left out:
+ * in phi relative to the nearest image, in the radial-basis accumulation relative to the normalised total (in the
+ * fused attention: relative to the whole row's soft-max total).  Default -30: such a term is below 1/64 ulp of a
+ * float32 sum (measured change of the attention output 6e-8 relative, against 4e-9 at -40); pass -1000 to
+ * accumulate every term.  Process-wide tuning knob, read at launch time. */
 void cf_set_weight_floor_log2(double log2_floor);
 double cf_get_weight_floor_log2(void);
 

@@ -42,7 +42,7 @@ def test_version_and_knob(lib):
     assert lib.cf_version() >= 100
     lib.cf_set_weight_floor_log2(ctypes.c_double(-33.0))
     assert lib.cf_get_weight_floor_log2() == -33.0
-    lib.cf_set_weight_floor_log2(ctypes.c_double(-40.0))
+    lib.cf_set_weight_floor_log2(ctypes.c_double(-30.0))
 
 
 def test_validation_returns_codes_without_a_device(lib):

@@ -90,7 +90,7 @@ def test_lattice_sum_forward_against_golden(ops, golden_ops):
 
 
 @pytest.mark.parametrize("cutoff,minimum", [(-3.5, 2), (-3.5, 0), (7.5, 2), (0.0, 2)])
-@pytest.mark.parametrize("floor", [-40.0, -1000.0])
+@pytest.mark.parametrize("floor", [-30.0, -1000.0])
 def test_lattice_sum_forward_against_oracle(ops, cutoff, minimum, floor):
     """Adaptive / static cut-off rules, heads with different boxes, all W layouts, one width per edge."""
     cb, edges, pos_ij, rvlen, a, W, rng = case(32, crystals=10, nmax=7)
@@ -118,7 +118,7 @@ def test_lattice_sum_forward_against_oracle(ops, cutoff, minimum, floor):
         zk0, _ = ops.lattice_sum_fwd(*base[:5], 0, DIST_MAX, WSCALE, **dcommon)
         assert rel_err(zk0.cpu().numpy(), z64) < TOL
     finally:
-        ops.set_weight_floor_log2(-40.0)
+        ops.set_weight_floor_log2(-30.0)
 
 
 def test_lattice_sum_forward_ragged_and_degenerate(ops):
