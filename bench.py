@@ -394,10 +394,21 @@ def run_kernel_case(args):
         torch.cuda.current_stream().wait_stream(side)
         return best
 
+    # the same call reading the batch's term lists (built once per batch, shared by the layers)
+    a_widest = -0.5 * 0.5 / 1.4 ** 2
+    build = lambda: ops.term_list_build(g.pos_ij, tvecs, g.rvlen, g.batch, g.edges, g.row_start, g.max_atoms, -3.5, 2, 2,
+                                        a_widest, row_order=g.row_order)
+    lists = build()
+    run_listed = lambda: ops.infinite_attn_fwd(q, k, v, a, g.pos_ij, tvecs, g.rvlen, g.batch, g.edges, g.row_start,
+                                               g.max_atoms, K, 14.0, 1.0, W, -3.5, 2, 2, row_order=g.row_order,
+                                               term_lists=lists)
+    diff = float((run_listed()[0] - run()[0]).abs().max() / run()[0].abs().max())
     return {"case": "attention", "workload": args.workload, "crystals": cb.num_crystals, "atoms": N, "edges": cb.num_edges,
             "K": K, "ms_median": float(np.median(times)), "ms_min": float(min(times)),
             "phi_kernel_alone_ms": float(np.median(phi_times)),
-            "device_ms_per_call_graph": graph_ms(run), "device_ms_phi_graph": graph_ms(phi_only)}
+            "device_ms_per_call_graph": graph_ms(run), "device_ms_phi_graph": graph_ms(phi_only),
+            "device_ms_per_call_listed_graph": graph_ms(run_listed), "device_ms_list_build_graph": graph_ms(build),
+            "listed_vs_enumerated_rel_diff": diff}
 
 
 def lattice_microbench(ops, device, peaks, pairs=250000):

@@ -33,6 +33,9 @@ SIGNATURES = {
     "cf_pipe_probe": [I32, I32, I32, I64, P, P],
     "cf_model_forward": [P, P, I64, P, P, P, I64, I64, I64, I64, P, I32, P, P, I64, I64, F64, F64, I32, I32, P, P, I64, P,
                          P, I64, F64, P, P, P, P],
+    "cf_term_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
+    "cf_infinite_attn_fwd_listed": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
+                                    I32, P, P, P, P, P, P, F64, P],
     "cf_row_cost": [P, P, I64, I64, F64, P, P],
     "cf_row_order": [P, P, I64, I64, F64, P, P],
     "cf_reci_phase": [P, P, P, P, I64, P, P],
@@ -67,6 +70,8 @@ def load() -> ctypes.CDLL:
         lib.cf_get_weight_floor_log2.restype = c_double
         lib.cf_encoder_workspace_floats.argtypes = [I64, I64, I64]
         lib.cf_encoder_workspace_floats.restype = c_int64
+        lib.cf_term_list_workspace_bytes.argtypes = [I64, I64]
+        lib.cf_term_list_workspace_bytes.restype = c_int64
         lib.cf_model_workspace_bytes.argtypes = [I64, I64, I64, I64]
         lib.cf_model_workspace_bytes.restype = c_int64
         for name, argtypes in SIGNATURES.items():

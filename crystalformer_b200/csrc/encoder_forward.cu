@@ -19,8 +19,15 @@
 #include "blas_dyn.cuh"
 #include "common.cuh"
 #include "dense_block.cuh"
+#include "term_list.cuh"
 
 namespace cf {
+int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                           const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                           const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D,
+                           int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
+                           double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
+                           float *lse, float *psi_row, const int32_t *row_order, const TermList *list, void *stream);
 namespace {
 
 struct LayerScalars {
@@ -99,8 +106,9 @@ __global__ void ffn_post_kernel(float *__restrict__ h, const float *__restrict__
 
 extern "C" int64_t cf_encoder_workspace_floats(int64_t N, int64_t E, int64_t ff_dim)
 {
-    // qkv (384) + q,k,v (3 x 128) + attention output (128) + a (8) + lse (8) + hidden (ff) per atom, logits per edge
-    return N * (384 + 384 + 128 + 8 + 8 + ff_dim) + E * 8 + 64;
+    // qkv (384) + q,k,v (3 x 128) + attention output (128) + a (8) + lse (8) + hidden (ff) per atom, logits per edge,
+    // then the term lists: directory (2 ints per edge), allocation cursor, pool (2 floats per entry)
+    return N * (384 + 384 + 128 + 8 + 8 + ff_dim) + E * 8 + 64 + (int64_t)(cf::term_list_workspace_bytes(N, E) + 3) / 4;
 }
 
 extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars,
@@ -129,6 +137,30 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
     int rc = CF_OK;
     cublasStatus_t st = CUBLAS_STATUS_SUCCESS;
 
+    // Term lists (term_list.cuh): the geometry is the same for every layer, so the (key, translation) pairs that can
+    // matter to any layer are found once.  The widest Gaussian any layer can produce has a = lower_bound x a_factor.
+    TermList lists{};
+    const TermList *list = nullptr;
+    if (pos_ij != nullptr && weight_floor_log2() > -200.0f) {
+        float a_widest = -INFINITY;
+        for (int l = 0; l < num_layers; ++l) a_widest = fmaxf(a_widest, (float)(scalars[6 * l + 4] * scalars[6 * l + 2]));
+        if (a_widest < 0.0f) {
+            TermListBuild tb{};
+            tb.pos_ij = pos_ij; tb.tvecs = tvecs; tb.rvlen = cutoff_radius != 0.0 ? rvlen : nullptr;
+            tb.batch = batch; tb.edges = edges; tb.row_start = row_start; tb.row_order = row_order;
+            tb.N = N; tb.E = E; tb.max_atoms = (int)max_atoms;
+            tb.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
+            tb.a_widest = a_widest;
+            tb.window = term_window(weight_floor_log2(), a_widest);
+            term_list_carve(logit + E * 8 + 64, N, E, &tb.start, &tb.count, &tb.dmin, &tb.cursor, &tb.pool);
+            tb.capacity = (long long)term_pool_entries(N, E);
+            rc = launch_term_list_build(tb, s);
+            if (rc != CF_OK) return rc;
+            lists.pool = tb.pool; lists.start = tb.start; lists.count = tb.count; lists.dmin = tb.dmin; lists.window = tb.window;
+            list = &lists;
+        }
+    }
+
     // Fused dense path: every layer brings its weights packed for the tensor-core kernel (slot 10) and the
     // feed-forward width is a multiple of 128.  One launch per layer boundary instead of four GEMMs and two
     // element-wise passes; see dense_block.cu.
@@ -153,9 +185,9 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
             const float *const *w = weights + 11 * l;
             const double *sc = scalars + 6 * l;
             if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
-            rc = cf_infinite_attn_fwd(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS, HEAD_DIM,
-                                      E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range, minimum_range, attn,
-                                      logit, lse, nullptr, row_order, s);
+            rc = infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS,
+                                        HEAD_DIM, E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range,
+                                        minimum_range, attn, logit, lse, nullptr, row_order, list, s);
             if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
             if (rc != CF_OK) break;
             DenseArgs t{};
@@ -182,9 +214,9 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
         const long long nh = N * HEADS;
         qkv_post_kernel<<<(unsigned)((nh + 127) / 128), 128, 0, s>>>(qkv, w[1], w[2], w[5], ls, N, q, k, v, a, x);
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
-        rc = cf_infinite_attn_fwd(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS, HEAD_DIM,
-                                  E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range, minimum_range, attn,
-                                  logit, lse, nullptr, row_order, s);
+        rc = infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS,
+                                    HEAD_DIM, E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range,
+                                    minimum_range, attn, logit, lse, nullptr, row_order, list, s);
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
         if (rc != CF_OK) break;
         st = linear(bl, handle, attn, w[4], x, rows, 128, 128, 1.0f);

@@ -19,6 +19,7 @@
 #include <cstdlib>
 
 #include "lattice_core.cuh"
+#include "term_list.cuh"
 
 // Row tickets: each launch of the row kernel gets one zeroed counter out of a small pool, so that launches in flight
 // on different streams of a device do not share one.
@@ -38,12 +39,14 @@ unsigned *next_ticket()
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
 constexpr int KBINS = 64;
+constexpr int KV_LD = 132;  // row stride (floats) of the k / v tile: 528 bytes, 16-byte aligned and off the bank period
 
 struct RowArgs {
     const float *q, *k, *v, *a, *pos, *pos_ij, *tvecs, *rvlen, *W;
     const int64_t *batch, *edges, *row_start;
     const int32_t *row_order;  // optional: atoms in the order they are to be processed (heaviest first)
     unsigned *ticket;          // zeroed before the launch: rows beyond the first wave are handed out through it
+    TermList list;             // optional (pool == NULL: none): the rows' candidate terms, found once per batch
     long long E;
     float *out, *logit, *lse, *psi_row;
     long long N;
@@ -58,7 +61,8 @@ __host__ __device__ inline size_t row_group_floats(int max_atoms, bool with_basi
 {
     const size_t ld = ((max_atoms + 31) & ~31) + 1;
     return (size_t)max_atoms * 4 + ((16 * ld + 3) & ~(size_t)3) +
-           (with_basis ? row_warps * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + row_warps * 128;
+           (with_basis ? row_warps * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + row_warps * 128 +
+           (max_atoms <= 32 ? 32 * KV_LD : 0);  // batches of small crystals: a tile for the row's k, then v, rows
 }
 
 // ROW_WARPS = 4: one thread block per atom (large crystals: the four warps split the translations).
@@ -95,6 +99,16 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
     float *part = stage + (K > 0 ? ROW_WARPS * STAGE_FLOATS : 0);      // [ROW_WARPS][8][64]
     float *rings = part + (K > 0 ? ROW_WARPS * HEADS * KBINS : 0);     // [ROW_WARPS][RING_FLOATS]
     float *vsum = rings + (K > 0 ? ROW_WARPS * RING_FLOATS : 0);       // [ROW_WARPS][128] partial sum_j p v
+    float *kv = vsum + ROW_WARPS * 128;                                // [32][KV_LD] when max_atoms <= 32
+    const bool tiled = p.max_atoms <= 32;
+    // all threads of the group copy `rows` 512-byte rows starting at src into the tile, asynchronously
+    auto tile_fetch = [&](const float *src, int rows) {
+        for (int idx = rt; idx < rows * 32; idx += RT) {
+            const unsigned dst = (unsigned)__cvta_generic_to_shared(kv + (idx >> 5) * KV_LD + (idx & 31) * 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + (size_t)idx * 4));
+        }
+        asm volatile("cp.async.commit_group;");
+    };
 
     BinAccumulator<KBINS> bins;
     CandidateRing ring;
@@ -146,23 +160,44 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
 
         if (n <= 32) {
             // ---- up to 32 keys: the first warp of the group does the whole soft-max in registers, one key per lane
-            //      (positions, logits of all eight heads, statistics by shuffles); the other warps wait
+            //      (positions, logits of all eight heads, statistics by shuffles); the other warps wait.
+            //      In batches of small crystals all threads first bring the keys' k rows (contiguous: the crystal's
+            //      atoms) and the query into shared memory in one round trip; read by one lane per key straight from
+            //      global memory, the 32 loads of a 512-byte row go out a few at a time.
+            if (tiled) {
+                tile_fetch(kmat + a0 * HEADS * HEAD_DIM, n);
+                if (rt < 32) {
+                    const unsigned dst = (unsigned)__cvta_generic_to_shared(vsum + rt * 4);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(p.q + i * HEADS * HEAD_DIM + rt * 4));
+                }
+                asm volatile("cp.async.commit_group;");
+            }
+            float rx = 0.f, ry = 0.f, rz = 0.f;
+            float4 ph0 = make_float4(0.f, 0.f, 0.f, 0.f), ph1 = ph0;
+            if (wr == 0 && lane < n) {  // this lane's key: position and phi, requested before waiting for the tile
+                if (p.pos_ij) {
+                    const float *pp = p.pos_ij + 3 * (e0 + lane);
+                    rx = pp[0]; ry = pp[1]; rz = pp[2];
+                } else {
+                    const float *pp = p.pos + 3 * (a0 + lane), *pi = p.pos + 3 * i;
+                    rx = __fsub_rn(pp[0], pi[0]); ry = __fsub_rn(pp[1], pi[1]); rz = __fsub_rn(pp[2], pi[2]);
+                }
+                const float4 *lp = reinterpret_cast<const float4 *>(logit_io + (e0 + lane) * HEADS);
+                ph0 = lp[0]; ph1 = lp[1];
+            }
+            if (tiled) {
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                row_sync();
+            }
             if (wr == 0) {
                 const bool live = lane < n;
                 const int j = live ? lane : 0;
-                float rx, ry, rz;
-                if (p.pos_ij) {
-                    const float *pp = p.pos_ij + 3 * (e0 + j);
-                    rx = n > 0 ? pp[0] : 0.f; ry = n > 0 ? pp[1] : 0.f; rz = n > 0 ? pp[2] : 0.f;
-                } else {
-                    const float *pp = p.pos + 3 * (a0 + j), *pi = p.pos + 3 * i;
-                    rx = __fsub_rn(pp[0], pi[0]); ry = __fsub_rn(pp[1], pi[1]); rz = __fsub_rn(pp[2], pi[2]);
-                }
-                const float4 *qp = reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM);
-                const float4 *kp = reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
+                // k row and query from the tile, or (batches with larger crystals) from global memory
+                const float4 *qp = tiled ? reinterpret_cast<const float4 *>(vsum)
+                                         : reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM);
+                const float4 *kp = tiled ? reinterpret_cast<const float4 *>(kv + j * KV_LD)
+                                         : reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
                 float4 *lp = reinterpret_cast<float4 *>(logit_io + (e0 + j) * HEADS);  // phi was left here by the phi kernel
-                float4 ph0 = make_float4(0.f, 0.f, 0.f, 0.f), ph1 = ph0;
-                if (live) { ph0 = lp[0]; ph1 = lp[1]; }
                 const float phi[8] = {ph0.x, ph0.y, ph0.z, ph0.w, ph1.x, ph1.y, ph1.z, ph1.w};
                 float sc[8], lg[8];
 #pragma unroll
@@ -170,8 +205,8 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
                     for (int t = 0; t < 4; t += 2) {
-                        const float4 k0 = __ldg(kp + 4 * h + t), k1 = __ldg(kp + 4 * h + t + 1);
-                        const float4 q0 = __ldg(qp + 4 * h + t), q1 = __ldg(qp + 4 * h + t + 1);
+                        const float4 k0 = kp[4 * h + t], k1 = kp[4 * h + t + 1];
+                        const float4 q0 = qp[4 * h + t], q1 = qp[4 * h + t + 1];
                         s0 = fmaf(q0.x, k0.x, s0); s0 = fmaf(q0.y, k0.y, s0); s0 = fmaf(q0.z, k0.z, s0); s0 = fmaf(q0.w, k0.w, s0);
                         s1 = fmaf(q1.x, k1.x, s1); s1 = fmaf(q1.y, k1.y, s1); s1 = fmaf(q1.z, k1.z, s1); s1 = fmaf(q1.w, k1.w, s1);
                     }
@@ -200,6 +235,8 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                 if (live) rel[j] = make_float4(rx, ry, rz, mxo);  // .w: the key's largest offset
             }
             row_sync();
+            // the k rows are no longer needed: the tile is refilled with the keys' v rows while the histogram is built
+            if (tiled) tile_fetch(p.v + a0 * HEADS * HEAD_DIM, n);
         } else {
             // ---- relative positions of the keys
             if (p.pos_ij) {
@@ -321,70 +358,90 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                 }
                 bins.push(emax > p.basis.floor_log2, fast_sqrt(d2) * p.basis.bin_scale, w);
             };
-            // Work units are (chunk, column) pairs dealt round-robin to the warps of the group (rotated by one warp per
-            // chunk), so that the few dense columns around the origin are spread over all of them whatever the number
-            // of keys.  Lanes run over the
-            // keys of the chunk: a translation is warp-uniform and a lane's key stays in registers.
-            for (int ch = 0; ch < chunks; ++ch) {
-                const int j = 32 * ch + lane;
-                const bool live = j < n;
-                const float4 r = rel[live ? j : 0];  // r.w: the key's largest offset
-                // reach of this chunk of keys: no key farther than `far` from the origin, no candidate beyond `reach`
-                // from its key; a translation longer than reach + far cannot produce a candidate (triangle inequality)
-                const float far2 = warp_max(live ? fmaf(r.z, r.z, fmaf(r.y, r.y, r.x * r.x)) : 0.f);
-                const float cmax = warp_max(live ? r.w : -INFINITY);
-                const float reach2 = fminf(__fdividef(p.basis.floor_log2 - cmax, a2max), p.basis.d2_cut);
-                const float bound = sqrtf(fmaxf(reach2, 0.f)) + sqrtf(far2);
-                const float tau2_max = bound * bound * 1.0001f + 1e-4f;
-                // this warp's columns of the chunk: col = (wr - ch) mod ROW_WARPS, then every ROW_WARPS-th
-                int col = (wr - ch) & (ROW_WARPS - 1);
-                int n1 = -R1, n2 = col - R2;
-                while (n2 > R2) { n2 -= S2; ++n1; }
-                for (; col < columns; col += ROW_WARPS) {
-                    {
-                        const float f1 = (float)n1, f2 = (float)n2;
-                        // the n3 of this column whose translation n1 t1 + n2 t2 + n3 t3 is no longer than the bound
-                        const float bx = fmaf(cell.t2x, f2, cell.t1x * f1), by = fmaf(cell.t2y, f2, cell.t1y * f1);
-                        const float bz = fmaf(cell.t2z, f2, cell.t1z * f1);
-                        const float bb = fmaf(bz, bz, fmaf(by, by, bx * bx));
-                        const float bt = fmaf(bz, cell.t3z, fmaf(by, cell.t3y, bx * cell.t3x));
-                        const float room = fmaf(bb, 1e-5f, tau2_max) - fmaf(-bt * bt, inv_t3sq, bb);  // slack for rounding
-                        int lo = -R3, hi = R3;
-                        if (prune) {
-                            const float half = sqrtf(fmaxf(room, 0.f) * inv_t3sq) + 1e-3f, mid = -bt * inv_t3sq;
-                            lo = max(lo, __float2int_ru(mid - half));
-                            hi = min(hi, __float2int_rd(mid + half));
-                            if (room < 0.f) hi = lo - 1;
-                        }
-                        // r + n1 t1 + n2 t2, contracted like the reference's expression
-                        const float ex = fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x));
-                        const float ey = fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y));
-                        const float ez = fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z));
-                        for (int n3 = lo; n3 <= hi; n3 += 4) {
-                            const float f3 = (float)n3;
-                            bool cand[4];
-                            float d2v[4];
-                            int key[4];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                const float fu = f3 + (float)u;
-                                const float dx = fmaf(cell.t3x, fu, ex), dy = fmaf(cell.t3y, fu, ey), dz = fmaf(cell.t3z, fu, ez);
-                                d2v[u] = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
-                                cand[u] = live && n3 + u <= hi && fmaf(a2max, d2v[u], r.w) > p.basis.floor_log2 &&
-                                          d2v[u] < p.basis.d2_cut;
-                                key[u] = masked ? pack_key(j, abs(n1), abs(n2), abs(n3 + u)) : j;
-                            }
-                            ring.offer4(cand, d2v, key);
-                            while (ring.ready()) consume();
-                        }
-                    }
-                    n2 += ROW_WARPS;
+            const int list_first = (p.list.pool != nullptr && n > 0) ? p.list.start[e0] : -1;
+            if (list_first >= 0) {
+                // ---- candidates from the row's term list: its entries are contiguous, the warps of the group take
+                //      equal shares, 32 entries per step; the one-FMA bound weeds out what this layer's widths do not reach
+                const int list_end = p.list.start[e0 + n - 1] + p.list.count[e0 + n - 1];
+                const int span = list_end - list_first, share = (span + ROW_WARPS - 1) / ROW_WARPS;
+                const int w_lo = list_first + min(wr * share, span), w_hi = list_first + min((wr + 1) * share, span);
+                for (int at = w_lo; at < w_hi; at += 32) {
+                    const bool live = at + lane < w_hi;
+                    float2 en = make_float2(0.f, 0.f);
+                    if (live) en = __ldg(p.list.pool + at + lane);
+                    const int key = __float_as_int(en.y);
+                    const int j = key & 2047;
+                    const bool cand = live && fmaf(a2max, en.x, rel[live ? j : 0].w) > p.basis.floor_log2 && en.x < p.basis.d2_cut;
+                    ring.offer(cand, en.x, masked ? key : j);
+                    while (ring.ready()) consume();
+                }
+            } else {
+                // Work units are (chunk, column) pairs dealt round-robin to the warps of the group (rotated by one warp per
+                // chunk), so that the few dense columns around the origin are spread over all of them whatever the number
+                // of keys.  Lanes run over the keys of the chunk: a translation is warp-uniform and a lane's key stays
+                // in registers.
+                for (int ch = 0; ch < chunks; ++ch) {
+                    const int j = 32 * ch + lane;
+                    const bool live = j < n;
+                    const float4 r = rel[live ? j : 0];  // r.w: the key's largest offset
+                    // reach of this chunk of keys: no key farther than `far` from the origin, no candidate beyond `reach`
+                    // from its key; a translation longer than reach + far cannot produce a candidate (triangle inequality)
+                    const float far2 = warp_max(live ? fmaf(r.z, r.z, fmaf(r.y, r.y, r.x * r.x)) : 0.f);
+                    const float cmax = warp_max(live ? r.w : -INFINITY);
+                    const float reach2 = fminf(__fdividef(p.basis.floor_log2 - cmax, a2max), p.basis.d2_cut);
+                    const float bound = sqrtf(fmaxf(reach2, 0.f)) + sqrtf(far2);
+                    const float tau2_max = bound * bound * 1.0001f + 1e-4f;
+                    // this warp's columns of the chunk: col = (wr - ch) mod ROW_WARPS, then every ROW_WARPS-th
+                    int col = (wr - ch) & (ROW_WARPS - 1);
+                    int n1 = -R1, n2 = col - R2;
                     while (n2 > R2) { n2 -= S2; ++n1; }
+                    for (; col < columns; col += ROW_WARPS) {
+                        {
+                            const float f1 = (float)n1, f2 = (float)n2;
+                            // the n3 of this column whose translation n1 t1 + n2 t2 + n3 t3 is no longer than the bound
+                            const float bx = fmaf(cell.t2x, f2, cell.t1x * f1), by = fmaf(cell.t2y, f2, cell.t1y * f1);
+                            const float bz = fmaf(cell.t2z, f2, cell.t1z * f1);
+                            const float bb = fmaf(bz, bz, fmaf(by, by, bx * bx));
+                            const float bt = fmaf(bz, cell.t3z, fmaf(by, cell.t3y, bx * cell.t3x));
+                            const float room = fmaf(bb, 1e-5f, tau2_max) - fmaf(-bt * bt, inv_t3sq, bb);  // slack for rounding
+                            int lo = -R3, hi = R3;
+                            if (prune) {
+                                const float half = sqrtf(fmaxf(room, 0.f) * inv_t3sq) + 1e-3f, mid = -bt * inv_t3sq;
+                                lo = max(lo, __float2int_ru(mid - half));
+                                hi = min(hi, __float2int_rd(mid + half));
+                                if (room < 0.f) hi = lo - 1;
+                            }
+                            // r + n1 t1 + n2 t2, contracted like the reference's expression
+                            const float ex = fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x));
+                            const float ey = fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y));
+                            const float ez = fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z));
+                            for (int n3 = lo; n3 <= hi; n3 += 4) {
+                                const float f3 = (float)n3;
+                                bool cand[4];
+                                float d2v[4];
+                                int key[4];
+    #pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    const float fu = f3 + (float)u;
+                                    const float dx = fmaf(cell.t3x, fu, ex), dy = fmaf(cell.t3y, fu, ey), dz = fmaf(cell.t3z, fu, ez);
+                                    d2v[u] = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                                    cand[u] = live && n3 + u <= hi && fmaf(a2max, d2v[u], r.w) > p.basis.floor_log2 &&
+                                              d2v[u] < p.basis.d2_cut;
+                                    key[u] = masked ? pack_key(j, abs(n1), abs(n2), abs(n3 + u)) : j;
+                                }
+                                ring.offer4(cand, d2v, key);
+                                while (ring.ready()) consume();
+                            }
+                        }
+                        n2 += ROW_WARPS;
+                        while (n2 > R2) { n2 -= S2; ++n1; }
+                    }
                 }
             }
             while (ring.count > 0) consume();
             // ---- partial histograms -> shared memory, fixed-order sum over the warps of the group
             bins.flush(part + wr * HEADS * KBINS, KBINS);
+            asm volatile("cp.async.wait_all;" ::: "memory");  // this thread's part of the v tile (published by the barrier)
             row_sync();
             for (int idx = rt; idx < HEADS * KBINS; idx += RT) {
                 float s = part[idx];
@@ -403,7 +460,21 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
 
         // ---- sum_j p_ij v_j: warp wr takes keys wr, wr + ROW_WARPS, ...; a lane owns four consecutive channels (one
         //      float4 load per key); the partial rows of the group meet in shared memory
-        {
+        if (K == 0 && tiled && n <= 32) {  // no histogram phase in between: wait for the v tile here
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            row_sync();
+        }
+        if (tiled && n <= 32) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int hh = lane >> 2;
+            const float *pr = pj + hh * ld;
+            for (int j = wr; j < n; j += ROW_WARPS) {
+                const float4 v0 = reinterpret_cast<const float4 *>(kv + j * KV_LD)[lane];
+                const float p0 = pr[j];
+                acc.x = fmaf(p0, v0.x, acc.x); acc.y = fmaf(p0, v0.y, acc.y); acc.z = fmaf(p0, v0.z, acc.z); acc.w = fmaf(p0, v0.w, acc.w);
+            }
+            reinterpret_cast<float4 *>(vsum)[wr * 32 + lane] = acc;
+        } else {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             const int hh = lane >> 2;  // head of the lane's channels 4 lane .. 4 lane + 3
             const float4 *vp = reinterpret_cast<const float4 *>(p.v + a0 * HEADS * HEAD_DIM) + lane;
@@ -455,6 +526,16 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
 }  // namespace
 }  // namespace cf
 
+namespace cf {
+// cf_infinite_attn_fwd with an optional term list (see term_list.cuh) in place of the enumeration of translations.
+int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                           const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                           const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D,
+                           int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
+                           double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
+                           float *lse, float *psi_row, const int32_t *row_order, const TermList *list, void *stream);
+}
+
 extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
                                     const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
                                     const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
@@ -462,6 +543,44 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
                                     const float *W, double cutoff_radius, int lattice_range, int minimum_range,
                                     float *out, float *logit, float *lse, float *psi_row, const int32_t *row_order,
                                     void *stream)
+{
+    return cf::infinite_attn_fwd_impl(q, k, v, a, pos, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
+                                      max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, out,
+                                      logit, lse, psi_row, row_order, nullptr, stream);
+}
+
+extern "C" int cf_infinite_attn_fwd_listed(const float *q, const float *k, const float *v, const float *a,
+                                           const float *pos_ij, const float *tvecs, const float *rvlen,
+                                           const int64_t *batch, const int64_t *edges, const int64_t *row_start,
+                                           int64_t N, int64_t B, int64_t H, int64_t D, int64_t E, int64_t K,
+                                           int64_t max_atoms, double dist_max, double wscale, const float *W,
+                                           double cutoff_radius, int lattice_range, int minimum_range, float *out,
+                                           float *logit, float *lse, float *psi_row, const int32_t *row_order,
+                                           void *term_lists, double a_widest, void *stream)
+{
+    using namespace cf;
+    CF_REQUIRE(term_lists != nullptr && pos_ij != nullptr && a_widest < 0, CF_ERR_INVALID,
+               "cf_infinite_attn_fwd_listed: needs term lists, pos_ij and a negative a_widest");
+    TermList list{};
+    int *start, *count;
+    float *dmin;
+    unsigned long long *cursor;
+    float2 *pool;
+    term_list_carve(term_lists, N, E, &start, &count, &dmin, &cursor, &pool);
+    list.pool = pool; list.start = start; list.count = count; list.dmin = dmin;
+    list.window = term_window(weight_floor_log2(), (float)a_widest);
+    return infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
+                                  max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, out, logit,
+                                  lse, psi_row, row_order, &list, stream);
+}
+
+int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                               const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                               const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
+                               int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
+                               const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out,
+                               float *logit, float *lse, float *psi_row, const int32_t *row_order,
+                               const TermList *list, void *stream)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_fwd: negative size");
@@ -487,7 +606,16 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     unsigned *ticket = K > 0 ? next_ticket() : nullptr;
     CF_REQUIRE(K == 0 || ticket != nullptr, CF_ERR_CUDA, "cf_infinite_attn_fwd: the row ticket could not be set up");
     phi.zero_word = ticket;
-    int rc = launch_lattice_phi(phi, s);
+    int rc;
+    if (list != nullptr && pos_ij != nullptr) {
+        PhiListArgs pl{};
+        pl.list = *list;
+        pl.a = a; pl.pos_ij = pos_ij; pl.tvecs = tvecs; pl.rvlen = rvlen; pl.batch = batch; pl.edges = edges; pl.E = E;
+        pl.rule = phi.rule; pl.floor_log2 = phi.floor_log2; pl.z = logit; pl.zero_word = ticket;
+        rc = launch_phi_from_list(pl, s);
+    } else {
+        rc = launch_lattice_phi(phi, s);
+    }
     if (rc != CF_OK) return rc;
 
     RowArgs p{};
@@ -496,6 +624,7 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
     p.out = out; p.logit = logit; p.lse = lse; p.psi_row = psi_row; p.N = N; p.max_atoms = (int)max_atoms;
     p.keep_logit = 1;
     p.ticket = ticket;
+    if (list != nullptr && pos_ij != nullptr && K > 0) p.list = *list;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
     // warps per atom row: 1 for crystals of up to 12 atoms, else 4 (CF_ROW_WARPS = 1, 2 or 4 in the environment

@@ -329,6 +329,15 @@ struct CandidateRing {
         count = at - head;
         __syncwarp();
     }
+    // Appends the lanes' candidates of one step (lanes ascending).
+    __device__ __forceinline__ void offer(bool cand, float d2, int key)
+    {
+        const unsigned mask = __ballot_sync(FULL, cand);
+        if (mask == 0u) return;
+        if (cand) buf[(head + count + __popc(mask & ((1u << lane) - 1u))) & (RING_ENTRIES - 1)] = make_float2(d2, __int_as_float(key));
+        count += __popc(mask);
+        __syncwarp();
+    }
     __device__ __forceinline__ bool ready() const { return count >= 32; }
     // Hands one entry to each of the first min(count, 32) lanes; returns whether this lane got one.
     __device__ __forceinline__ bool take(float &d2, int &key)

@@ -208,9 +208,29 @@ def fused_attn_bwd(q, k, v, bij, edges, row_start, prob, out, gout):
     return gq, gk, gv, gaij, gbij
 
 
+def term_list_build(pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, cutoff_radius, lattice_range,
+                    minimum_range, a_widest, row_order=None):
+    """Term lists of a batch (see cf_term_list_build): (workspace tensor, a_widest), to be handed to
+    ``infinite_attn_fwd(..., term_lists=...)`` for every layer of the batch."""
+    dev = pos_ij.device
+    pos_ij, tvecs, rvlen = (_want(t, torch.float32, n, dev) for t, n in ((pos_ij, "pos_ij"), (tvecs, "tvecs"), (rvlen, "rvlen")))
+    batch, edges, row_start = (_want(t, torch.int64, n, dev) for t, n in
+                               ((batch, "batch"), (edges, "edges"), (row_start, "row_start")))
+    N, E = batch.shape[0], edges.shape[1]
+    work = torch.empty(int(_lib.load().cf_term_list_workspace_bytes(N, E)), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_term_list_build", _ptr(pos_ij), _ptr(tvecs), _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start),
+                  _ptr(_want(row_order, torch.int32, "row_order", dev)), c_int64(N), c_int64(E), c_int64(max_atoms),
+                  c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), c_double(a_widest),
+                  _ptr(work), _stream(dev))
+    return work, float(a_widest)
+
+
 def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W,
-                      cutoff_radius, lattice_range, minimum_range, want_psi_row=False, pos=None, row_order=None):
-    """Fused attention forward.  Geometry as pos_ij (E,3), or pos (N,3) when pos_ij is None.
+                      cutoff_radius, lattice_range, minimum_range, want_psi_row=False, pos=None, row_order=None,
+                      term_lists=None):
+    """Fused attention forward.  Geometry as pos_ij (E,3), or pos (N,3) when pos_ij is None.  ``term_lists`` (from
+    ``term_list_build``, needs pos_ij) replaces the enumeration of translations by the batch's precomputed lists.
     Returns (out (N,H,D), logit (E,H), lse (N,H), psi_row (N,H,K) or None)."""
     dev = q.device
     q, k, v, a, tvecs = (_want(t, torch.float32, n, dev) for t, n in
@@ -225,6 +245,16 @@ def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
     logit = torch.empty((E, H), dtype=torch.float32, device=dev)
     lse = torch.empty((N, H), dtype=torch.float32, device=dev)
     psi_row = torch.empty((N, H, K), dtype=torch.float32, device=dev) if (want_psi_row and K > 0) else None
+    if term_lists is not None:
+        work, a_widest = term_lists
+        with torch.cuda.device(dev):
+            _lib.call("cf_infinite_attn_fwd_listed", _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(pos_ij), _ptr(tvecs),
+                      _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),
+                      c_int64(D), c_int64(E), c_int64(K), c_int64(max_atoms), c_double(dist_max), c_double(wscale),
+                      _ptr(W), c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(out),
+                      _ptr(logit), _ptr(lse), _ptr(psi_row), _ptr(_want(row_order, torch.int32, "row_order", dev)),
+                      _ptr(work), c_double(a_widest), _stream(dev))
+        return out, logit, lse, psi_row
     with torch.cuda.device(dev):
         _lib.call("cf_infinite_attn_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(pos), _ptr(pos_ij), _ptr(tvecs),
                   _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),

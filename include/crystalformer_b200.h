@@ -208,6 +208,31 @@ int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const f
                          float *gk, float *gv, float *ga, float *glogit, const int32_t *row_order, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
+ * Term lists: the (key, translation) pairs of a batch that can matter to ANY layer, found once per batch (the
+ * reference enumerates every head's translation box again in every layer, real_enc_proj_fwd.cu:63-134).
+ * cf_term_list_build stores, per edge, the translations whose squared distance is within
+ * D = -floor_log2 / (|a_widest| log2 e) of the edge's nearest image, together with |n1|,|n2|,|n3| so that every
+ * (atom, head) still applies its own box; a_widest < 0 is the value closest to zero that the Gaussian parameter a can
+ * take in any layer (gauss_lb_real x -0.5/scale_real^2 for the reference's positive functions).
+ * cf_infinite_attn_fwd_listed is cf_infinite_attn_fwd reading those lists (phi as a sum over an edge's entries, the
+ * row kernel's candidates from a row's entries) instead of enumerating; rows that did not fit the workspace are
+ * enumerated as before, so the result never depends on the capacity.  workspace: cf_term_list_workspace_bytes(N, E)
+ * bytes, 16-byte aligned; built with the weight floor in force at the time (cf_set_weight_floor_log2).
+ * ---------------------------------------------------------------------------------------------------------- */
+int64_t cf_term_list_workspace_bytes(int64_t N, int64_t E);
+int cf_term_list_build(const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                       const int64_t *edges, const int64_t *row_start, const int32_t *row_order, int64_t N, int64_t E,
+                       int64_t max_atoms, double cutoff_radius, int lattice_range, int minimum_range, double a_widest,
+                       void *workspace, void *stream);
+int cf_infinite_attn_fwd_listed(const float *q, const float *k, const float *v, const float *a, const float *pos_ij,
+                                const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
+                                const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D, int64_t E,
+                                int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
+                                double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
+                                float *lse, float *psi_row, const int32_t *row_order, void *term_lists,
+                                double a_widest, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
  * Inference forward of the encoder stack (every layer of CrystalformerEncoderCUDA,
  * models/indexed_latticeformer_encoder.py:699-742 and :848-890, post-norm with LayerNorm = Identity) in one call:
  * per layer  x <- x + out_proj(attention(x)) ;  x <- x + W2 relu(W1 x + b1) + b2, with the attention of
