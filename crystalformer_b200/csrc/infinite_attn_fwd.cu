@@ -371,7 +371,9 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                     if (live) en = __ldg(p.list.pool + at + lane);
                     const int key = __float_as_int(en.y);
                     const int j = key & 2047;
-                    const bool cand = live && fmaf(a2max, en.x, rel[live ? j : 0].w) > p.basis.floor_log2 && en.x < p.basis.d2_cut;
+                    // (the lists are built for a box that contains every head's: terms outside this row's boxes drop out here)
+                    const bool cand = live && key_in_box(key, uni) && fmaf(a2max, en.x, rel[live ? j : 0].w) > p.basis.floor_log2 &&
+                                      en.x < p.basis.d2_cut;
                     ring.offer(cand, en.x, masked ? key : j);
                     while (ring.ready()) consume();
                 }

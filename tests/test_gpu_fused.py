@@ -87,6 +87,52 @@ def test_fused_forward_against_oracle_chain(ops, cutoff, minimum, nmax, Kbins):
     assert torch.equal(out, again[0]) and torch.equal(logit, again[1])  # no atomics: bitwise repeatable
 
 
+@pytest.mark.parametrize("cutoff,minimum,nmax,Kbins,floor", [(-3.5, 2, 7, 64, -30.0), (-3.5, 0, 7, 64, -30.0),
+                                                             (7.5, 2, 5, 64, -30.0), (0.0, 2, 40, 64, -30.0),
+                                                             (-3.5, 2, 7, 0, -30.0), (-3.5, 2, 150, 64, -30.0),
+                                                             (-3.5, 2, 7, 64, -1000.0)])
+def test_term_lists_give_the_enumerated_result(ops, cutoff, minimum, nmax, Kbins, floor):
+    """The same attention fed from the batch's term lists (found once, for the widest admissible Gaussian) instead of
+    enumerating every head's box: against the float64 oracle chain and against the enumerating kernels.  The widths
+    here span a factor of 2.5, so heads have different boxes and the listed terms are masked per head.  With the
+    weight floor switched off the lists would hold whole boxes; they then do not fit their pool and every row falls
+    back to enumeration, which the last case exercises."""
+    crystals = 3 if nmax > 100 else 10
+    cb = make_crystals(61, crystals, uniform_atoms(max(1, nmax // 3), nmax), length_range=(2.5, 9.0) if nmax < 100 else (8.0, 16.0))
+    prep = prepare(ops, cb)
+    N = cb.num_atoms
+    rng = np.random.default_rng(61)
+    sig = 1.4 * (0.6 + 0.9 * rng.random((N, H)))
+    a = (-0.5 / sig ** 2).astype(np.float32)
+    a_widest = float(-0.5 / (1.4 * 1.5) ** 2)  # no sigma above 1.4 x 1.5
+    W = (rng.standard_normal((H, D, K)) * 0.1).astype(np.float32)
+    q = (rng.standard_normal((N, H, D)) * 0.5).astype(np.float32)
+    k, v = (rng.standard_normal((N, H, D)).astype(np.float32) for _ in range(2))
+    tv, max_atoms = dev(cb.trans_vec), int(cb.sizes.max())
+    args = (dev(q), dev(k), dev(v), dev(a), prep["pos_ij"], tv, prep["rvlen"], prep["batch"], prep["edges"],
+            prep["row_start"], max_atoms, Kbins, DIST_MAX, WSCALE, dev(W) if Kbins else None, cutoff, 2, minimum)
+    ops.set_weight_floor_log2(floor)
+    try:
+        lists = ops.term_list_build(prep["pos_ij"], tv, prep["rvlen"], prep["batch"], prep["edges"], prep["row_start"],
+                                    max_atoms, cutoff, 2, minimum, a_widest)
+        listed = ops.infinite_attn_fwd(*args, term_lists=lists)
+        plain = ops.infinite_attn_fwd(*args)
+        again = ops.infinite_attn_fwd(*args, term_lists=lists)
+    finally:
+        ops.set_weight_floor_log2(-30.0)
+    assert torch.equal(listed[0], again[0]) and torch.equal(listed[1], again[1])  # bitwise repeatable
+    assert rel_err(listed[0].cpu().numpy(), plain[0].cpu().numpy()) < 2e-6
+    assert rel_err(listed[1].cpu().numpy(), plain[1].cpu().numpy()) < 2e-6
+    edges = oracle.edge_index(cb.sizes)
+    pos_ij, _, _, rvlen = oracle.geometry(cb.pos, cb.trans_vec, edges)
+    precision = "f64" if nmax < 100 else "f32"
+    z, psiW = oracle.lattice_sum_fwd(a, pos_ij, cb.trans_vec, cb.batch, edges, Kbins, DIST_MAX, WSCALE,
+                                     W=W[None] if Kbins else None, rvlen=rvlen, cutoff_radius=cutoff, minimum_range=minimum,
+                                     precision=precision)
+    _, ref = oracle.fused_attn_fwd(q, k, v, z, psiW, edges, precision=precision)
+    assert rel_err(listed[0].cpu().numpy(), ref) < TOL
+
+
 def test_fused_forward_flags_understated_max_atoms(ops):
     cb = make_crystals(62, 4, uniform_atoms(5, 9))
     prep = prepare(ops, cb)
