@@ -9,11 +9,13 @@ has the configuration's crystal count; with N GPUs a batch of N times that many 
 by the reference's greedy rule on n^2 (crystalformer_b200.sharding.lpt_assign) and only the per-crystal outputs are
 all-gathered (weak scaling).  Rank 0 prints ONE JSON line:
 
-  value            crystals / s over all ranks, inputs already resident in HBM, device-timed (CUDA events), max over ranks
-  e2e              the same through the public model call with HOST inputs: pinned host -> device copies of the step's
-                   inputs and the device -> host read of the outputs are inside the timed region
-  roofline         the dominant operator (lattice_phi_kernel + infinite_attn_rows_kernel of every layer), timed live
-                   with CUDA events on the launch stream during the timed steps; work = (edge, translation) terms of the
+  value            crystals / s over all ranks, inputs already resident in HBM, device-timed (CUDA events), max over ranks;
+                   the steps are issued back to back (no host synchronisation in between), each inside its own event
+                   pair, the L2 flush between the pairs
+  e2e              the same through crystalformer_b200.serving.PipelinedPredictor with HOST inputs: pinned host -> device
+                   copies of the step's inputs and the device -> host copy of the outputs are inside the timed region
+  roofline         the dominant operator (the phi and row kernels of every layer's fused attention), timed live with
+                   CUDA events on the launch stream during the timed steps; work = (edge, translation) terms of the
                    batch x FP32-pipe instructions per term; peak = FP32 FMA issue rate measured by cf_pipe_probe
   lattice_sum_microbench   the 2,000,000 (i,j,head) lattice-sum kernel benchmark (phi + 64-bin psi, forward), same units
   cpu_baseline     (N = 1) the CPU oracle's model forward on a bounded sample of the same batch, on the host cores

@@ -30,6 +30,31 @@ int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const
                            float *lse, float *psi_row, const int32_t *row_order, const TermList *list, void *stream);
 namespace {
 
+// A second stream and two events per (host thread, device), created on first use and kept for the life of the
+// process: the term-list build of a forward depends on the geometry only and runs beside the first dense block.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    bool ok = false;
+};
+SideStream &side_stream()
+{
+    static thread_local SideStream per_device[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    SideStream &s = per_device[dev & 63];
+    if (!s.ok && s.stream == nullptr) {
+        s.ok = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
+               cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess &&
+               cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
+        if (!s.ok) {
+            cudaGetLastError();
+            s.stream = reinterpret_cast<cudaStream_t>(1);  // do not try again
+        }
+    }
+    return s;
+}
+
 struct LayerScalars {
     float gauss_scale, gauss_shift;  // alpha <- (alpha + shift) * scale
     float a_factor;                  // -0.5 / scale_real^2
@@ -141,6 +166,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
     // matter to any layer are found once.  The widest Gaussian any layer can produce has a = lower_bound x a_factor.
     TermList lists{};
     const TermList *list = nullptr;
+    bool forked = false;  // the build runs on the side stream; the first attention waits for it
     if (pos_ij != nullptr && weight_floor_log2() > -200.0f) {
         float a_widest = -INFINITY;
         for (int l = 0; l < num_layers; ++l) a_widest = fmaxf(a_widest, (float)(scalars[6 * l + 4] * scalars[6 * l + 2]));
@@ -154,7 +180,11 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
             tb.window = term_window(weight_floor_log2(), a_widest);
             term_list_carve(logit + E * 8 + 64, N, E, &tb.start, &tb.count, &tb.dmin, &tb.cursor, &tb.pool);
             tb.capacity = (long long)term_pool_entries(N, E);
-            rc = launch_term_list_build(tb, s);
+            SideStream &side = side_stream();
+            forked = side.ok && cudaEventRecord(side.fork, s) == cudaSuccess &&
+                     cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
+            rc = launch_term_list_build(tb, forked ? side.stream : s);
+            if (forked && cudaEventRecord(side.join, side.stream) != cudaSuccess) rc = launch_status("term list join");
             if (rc != CF_OK) return rc;
             lists.pool = tb.pool; lists.start = tb.start; lists.count = tb.count; lists.dmin = tb.dmin; lists.window = tb.window;
             list = &lists;
@@ -181,6 +211,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
         d.N = N; d.ff = ff; d.x = x; d.q = q; d.k = k; d.v = v; d.a = a; d.attn = attn;
         head_of(d, 0);
         rc = launch_dense_block(d, s);
+        if (forked) cudaStreamWaitEvent(s, side_stream().join, 0);
         for (int l = 0; l < num_layers && rc == CF_OK; ++l) {
             const float *const *w = weights + 11 * l;
             const double *sc = scalars + 6 * l;
@@ -205,6 +236,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
         return launch_status("cf_encoder_forward");
     }
 
+    if (forked) cudaStreamWaitEvent(s, side_stream().join, 0);
     for (int l = 0; l < num_layers && rc == CF_OK && st == CUBLAS_STATUS_SUCCESS; ++l) {
         const float *const *w = weights + 11 * l;  // Wqkv, bqkv, w_pos, Wpe, Wo, bo, W1, b1, W2, b2, packed (optional)
         const double *sc = scalars + 6 * l;        // gauss_scale, gauss_shift, a_factor, elu_beta, lower_bound, dist_max

@@ -62,7 +62,8 @@ __host__ __device__ inline size_t row_group_floats(int max_atoms, bool with_basi
     const size_t ld = ((max_atoms + 31) & ~31) + 1;
     return (size_t)max_atoms * 4 + ((16 * ld + 3) & ~(size_t)3) +
            (with_basis ? row_warps * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + row_warps * 128 +
-           (max_atoms <= 32 ? 32 * KV_LD : 0);  // batches of small crystals: a tile for the row's k, then v, rows
+           (max_atoms <= 32 ? 32 * KV_LD + 128 : 0);  // batches of small crystals: a tile for the row's k, then v, rows
+                                                      // and the row's query
 }
 
 // ROW_WARPS = 4: one thread block per atom (large crystals: the four warps split the translations).
@@ -100,12 +101,18 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
     float *rings = part + (K > 0 ? ROW_WARPS * HEADS * KBINS : 0);     // [ROW_WARPS][RING_FLOATS]
     float *vsum = rings + (K > 0 ? ROW_WARPS * RING_FLOATS : 0);       // [ROW_WARPS][128] partial sum_j p v
     float *kv = vsum + ROW_WARPS * 128;                                // [32][KV_LD] when max_atoms <= 32
+    float *qrow = kv + 32 * KV_LD;                                     // [128] the row's query (same condition)
     const bool tiled = p.max_atoms <= 32;
+    bool prefetched = false;  // the k tile and query of the current row were requested during the previous row
     // all threads of the group copy `rows` 512-byte rows starting at src into the tile, asynchronously
-    auto tile_fetch = [&](const float *src, int rows) {
+    auto tile_fetch = [&](const float *src, int rows, const float *query) {
         for (int idx = rt; idx < rows * 32; idx += RT) {
             const unsigned dst = (unsigned)__cvta_generic_to_shared(kv + (idx >> 5) * KV_LD + (idx & 31) * 4);
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + (size_t)idx * 4));
+        }
+        if (query != nullptr && rt < 32) {
+            const unsigned dst = (unsigned)__cvta_generic_to_shared(qrow + rt * 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(query + rt * 4));
         }
         asm volatile("cp.async.commit_group;");
     };
@@ -164,14 +171,7 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             //      In batches of small crystals all threads first bring the keys' k rows (contiguous: the crystal's
             //      atoms) and the query into shared memory in one round trip; read by one lane per key straight from
             //      global memory, the 32 loads of a 512-byte row go out a few at a time.
-            if (tiled) {
-                tile_fetch(kmat + a0 * HEADS * HEAD_DIM, n);
-                if (rt < 32) {
-                    const unsigned dst = (unsigned)__cvta_generic_to_shared(vsum + rt * 4);
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(p.q + i * HEADS * HEAD_DIM + rt * 4));
-                }
-                asm volatile("cp.async.commit_group;");
-            }
+            if (tiled && !prefetched) tile_fetch(kmat + a0 * HEADS * HEAD_DIM, n, p.q + i * HEADS * HEAD_DIM);
             float rx = 0.f, ry = 0.f, rz = 0.f;
             float4 ph0 = make_float4(0.f, 0.f, 0.f, 0.f), ph1 = ph0;
             if (wr == 0 && lane < n) {  // this lane's key: position and phi, requested before waiting for the tile
@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                 const bool live = lane < n;
                 const int j = live ? lane : 0;
                 // k row and query from the tile, or (batches with larger crystals) from global memory
-                const float4 *qp = tiled ? reinterpret_cast<const float4 *>(vsum)
+                const float4 *qp = tiled ? reinterpret_cast<const float4 *>(qrow)
                                          : reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM);
                 const float4 *kp = tiled ? reinterpret_cast<const float4 *>(kv + j * KV_LD)
                                          : reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             }
             row_sync();
             // the k rows are no longer needed: the tile is refilled with the keys' v rows while the histogram is built
-            if (tiled) tile_fetch(p.v + a0 * HEADS * HEAD_DIM, n);
+            if (tiled) tile_fetch(p.v + a0 * HEADS * HEAD_DIM, n, nullptr);
         } else {
             // ---- relative positions of the keys
             if (p.pos_ij) {
@@ -499,6 +499,10 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             reinterpret_cast<float4 *>(vsum)[wr * 32 + lane] = acc;
         }
         row_sync();
+        // the v tile has been consumed: the next row's k rows and query are requested now and arrive while this row is
+        // projected and written
+        prefetched = tiled && has_next && n_n <= 32;
+        if (prefetched) tile_fetch(kmat + a0_n * HEADS * HEAD_DIM, n_n, p.q + i_n * HEADS * HEAD_DIM);
         // ---- out[h][m] = (sum over the partial rows) + sum_k W[h][m][k] Psi[h][k]; one output (h, m) per thread and turn
         for (int idx = rt; idx < HEADS * HEAD_DIM; idx += RT) {
             const int h = idx >> 4;
