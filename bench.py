@@ -289,7 +289,7 @@ def run_b200(args):
         achieved = terms_per_call * fp32_instr_per_term(K) / t_call
         achieved_sfu = terms_per_call * sfu_per_term(K) / t_call
         roofline = {
-            "kernel": "lattice_phi_kernel + infinite_attn_rows_kernel (one fused-attention call)",
+            "kernel": "phi_from_list_kernel + infinite_attn_rows_kernel (one fused-attention call)",
             "bound": "fp32_simt", "achieved": achieved / 1e9, "peak": peaks["fp32"] / 1e9, "unit": "G lane-instr/s",
             "frac": achieved / peaks["fp32"], "peak_source": "cf_pipe_probe FFMA, measured in this run",
             "sfu": {"achieved": achieved_sfu / 1e9, "peak": peaks["sfu"] / 1e9, "frac": achieved_sfu / peaks["sfu"]},
@@ -303,8 +303,9 @@ def run_b200(args):
         }
         micro = lattice_microbench(ops, device, peaks)
         cpu = cpu_baseline(model, params, mine) if (world == 1 and not args.no_cpu_baseline) else None
-        # own kernels per forward: offsets, cell, atom, edge, row cost; per layer qkv_post, phi, rows, ffn_post; mean
-        per_step_launches = 5 + 4 * wl["layers"] + 1
+        # own kernels per forward: offsets, cell, atom, edge, row order, term lists; L + 1 dense blocks; per layer phi and
+        # rows; pooling + head
+        per_step_launches = 6 + (wl["layers"] + 1) + 2 * wl["layers"] + 1
         result = {
             "metric": "crystals/sec (4-layer, fwd)" if wl["layers"] == 4 else f"crystals/sec ({wl['layers']}-layer, fwd)",
             "value": value, "unit": "crystals/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
