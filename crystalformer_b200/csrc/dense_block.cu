@@ -22,7 +22,14 @@
 namespace cf {
 namespace {
 
-constexpr int DB_THREADS = 256;           // 8 warps; warp w owns output columns 16 w .. 16 w + 15 of every 128-wide product
+// Warp w = 8 kh + cp: column pair cp owns output columns 16 cp .. 16 cp + 15 of every 128-wide product, k half kh the
+// k steps 8 kh .. 8 kh + 7 of it.  The two halves of a product are added through shared memory by the kh = 0 warp,
+// which also holds biases and residuals and does the epilogues.  Sixteen warps instead of eight halve the dependent
+// chain of a product and double the warps a scheduler can choose from; the tile has too few rows to give them more
+// columns.
+constexpr int KSPLIT = 2;
+constexpr int KSTEPS = 16 / KSPLIT;       // k steps of a 128-deep product per warp
+constexpr int DB_THREADS = 256 * KSPLIT;
 constexpr int DB_WARPS = DB_THREADS / 32;
 constexpr int LDA = 132;                  // row stride of the operand tiles (words): 528 bytes, so the eight 16-byte rows
                                           // of an ldmatrix fall into distinct bank groups
@@ -55,7 +62,7 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const unsigned (&a)[4], 
 // makes a fragment lane-private (a lane reads back exactly the 16 bytes it fetched), so each warp runs its own
 // cp.async ring, DEPTH items (k steps) ahead, across product, barrier and tile boundaries alike, with no block-level
 // synchronisation: weights stream from L2 continuously while the tensor cores work.
-constexpr int DEPTH = 8;                  // k steps in flight per warp: 8 x 1 KB
+constexpr int DEPTH = 8;                  // k steps in flight per warp, 1 KB each
 constexpr int RING_WORDS = DEPTH * 2 * 32 * 4;
 
 struct Panel {
@@ -67,9 +74,10 @@ struct WeightStream {
     float4 *ring;         // this warp's [DEPTH][2][32] float4
     int lane;
     int panels;           // panels per row tile
-    long long produced, consumed, limit;  // items; limit = tiles of this block x panels x 16
+    long long produced, consumed, limit;  // items; limit = tiles of this block x panels x KSTEPS
     struct { const float4 *Wo, *W1, *W2, *Wqkv; int ff, tail; } d;
-    int warp;
+    int warp;             // column pair (0..7)
+    int kh;               // k half
     int p_panel, p_ks;    // producer position within the row tile's sequence
     Panel cur;            // the producer's current panel
 
@@ -100,13 +108,13 @@ struct WeightStream {
     {
         if (produced < limit) {
             float4 *dst = ring + (size_t)(produced & (DEPTH - 1)) * 64 + lane;
-            const float4 *src = cur.base + (size_t)p_ks * 32 + lane;
+            const float4 *src = cur.base + (size_t)(kh * KSTEPS + p_ks) * 32 + lane;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const unsigned saddr = (unsigned)__cvta_generic_to_shared(dst + 32 * nt);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + nt * cur.tile_stride));
             }
-            if (++p_ks == 16) {  // next panel of the sequence (wrapping to the next row tile's first)
+            if (++p_ks == KSTEPS) {  // next panel of the sequence (wrapping to the next row tile's first)
                 p_ks = 0;
                 if (++p_panel == panels) p_panel = 0;
                 cur = panel(p_panel);
@@ -157,8 +165,9 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
 #pragma unroll
             for (int u = 0; u < 4; ++u) lo1[mt][nt][u] = lo2[mt][nt][u] = 0.f;
     constexpr int G = MT == 1 ? 4 : 2;  // k steps fetched and issued together: loads of all G before the first MMA
+    const int k_first = ws.kh * KSTEPS;
 #pragma unroll 1
-    for (int ks0 = 0; ks0 < 16; ks0 += G) {
+    for (int ks0 = 0; ks0 < KSTEPS; ks0 += G) {
         float4 b[G][2];
         ws.template consume<G>(b);
         unsigned ah[G][MT][4], al[G][MT][4];
@@ -166,7 +175,7 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
         for (int i = 0; i < G; ++i)
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                const int off = (16 * mt + lrow) * LDA + 8 * (ks0 + i) + lcol;
+                const int off = (16 * mt + lrow) * LDA + 8 * (k_first + ks0 + i) + lcol;
                 ldmatrix_x4(ah[i][mt], a_hi + off);
                 ldmatrix_x4(al[i][mt], a_lo + off);
             }
@@ -217,19 +226,57 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
     constexpr int ROWS = 16 * MT;
     unsigned *a1_hi = smem_u, *a1_lo = a1_hi + ROWS * LDA;       // operand tile 1: attn, then y, then x'
     unsigned *a2_hi = a1_lo + ROWS * LDA, *a2_lo = a2_hi + ROWS * LDA;  // operand tile 2: a chunk of hidden units
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = (tid >> 5) & 7;      // column pair of this warp
+    const int kh = tid >> 8;              // k half of this warp
+    const bool owner = kh == 0;           // holds biases and residuals, does the epilogues
     const int g = lane >> 2, t = lane & 3;
 
     const long long tiles = (p.N + ROWS - 1) / ROWS;
     const long long my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     WeightStream ws;
-    ws.ring = reinterpret_cast<float4 *>(a2_lo + ROWS * LDA) + (size_t)warp * DEPTH * 64;
+    ws.ring = reinterpret_cast<float4 *>(a2_lo + ROWS * LDA) + (size_t)(tid >> 5) * DEPTH * 64;
     ws.lane = lane;
     ws.warp = warp;
+    ws.kh = kh;
+    // exchange buffers for the halves of a product: [2][8 column pairs][32 lanes][8 MT floats]
+    float *xch = reinterpret_cast<float *>(ws.ring - (size_t)(tid >> 5) * DEPTH * 64 + (size_t)DB_WARPS * DEPTH * 64);
+    int xsel = 0;
+    // acc <- acc(kh = 0) + acc(kh = 1), valid in the owner warps afterwards; contains one block barrier
+    auto combine = [&](float (&acc)[MT][2][4]) {
+        if (KSPLIT == 1) return;
+        float4 *mine = reinterpret_cast<float4 *>(xch + ((size_t)(xsel * 8 + warp) * 32 + lane) * 8 * MT);
+        if (!owner) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+                    mine[2 * mt + nt] = make_float4(acc[mt][nt][0], acc[mt][nt][1], acc[mt][nt][2], acc[mt][nt][3]);
+        }
+        __syncthreads();
+        if (owner) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const float4 o = mine[2 * mt + nt];
+                    acc[mt][nt][0] += o.x; acc[mt][nt][1] += o.y; acc[mt][nt][2] += o.z; acc[mt][nt][3] += o.w;
+                }
+        }
+        xsel ^= 1;  // the next exchange uses the other buffer, so no barrier is needed before it
+    };
+    auto zero = [&](float (&acc)[MT][2][4]) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[mt][nt][u] = 0.f;
+    };
     ws.d.Wo = p.Wo; ws.d.W1 = p.W1; ws.d.W2 = p.W2; ws.d.Wqkv = p.Wqkv; ws.d.ff = p.ff; ws.d.tail = p.tail;
     ws.panels = (p.tail ? 1 + 2 * (p.ff / 128) : 0) + (p.head ? 3 : 0);
     ws.produced = ws.consumed = 0;
-    ws.limit = my_tiles * ws.panels * 16;
+    ws.limit = my_tiles * ws.panels * KSTEPS;
     ws.start();
 
     for (long long tile = blockIdx.x; tile * ROWS < p.N; tile += gridDim.x) {
@@ -266,10 +313,12 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                         xo[mt][nt][2 * half + 1] = xv.y + bo.y;
                     }
                 }
+            if (!owner) zero(xo);
             __syncthreads();
             product_128<MT>(xo, a1_hi, a1_lo, ws, lane);
-            __syncthreads();  // every warp has read attn
-            store_split<MT>(a1_hi, a1_lo, xo, warp, lane);
+            combine(xo);      // (its barrier: every warp has read attn)
+            if (KSPLIT == 1) __syncthreads();
+            if (owner) store_split<MT>(a1_hi, a1_lo, xo, warp, lane);
             // ---- x' = y + b2 + sum over chunks of relu(y W1_c^T + b1_c) W2_c^T
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
@@ -279,6 +328,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                     xo[mt][nt][0] += b2.x; xo[mt][nt][1] += b2.y; xo[mt][nt][2] += b2.x; xo[mt][nt][3] += b2.y;
                 }
             }
+            if (!owner) zero(xo);  // from here on the second half collects its own part of the feed-forward output
             __syncthreads();  // y is in operand 1
             const int chunks = p.ff / 128;
             for (int ch = 0; ch < chunks; ++ch) {
@@ -289,18 +339,21 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) { h[mt][nt][0] = b1.x; h[mt][nt][1] = b1.y; h[mt][nt][2] = b1.x; h[mt][nt][3] = b1.y; }
                 }
+                if (!owner) zero(h);
                 product_128<MT>(h, a1_hi, a1_lo, ws, lane);  // W1, the chunk's hidden units
+                combine(h);       // (its barrier: the previous chunk's readers are done with operand 2)
+                if (KSPLIT == 1) __syncthreads();
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                         for (int u = 0; u < 4; ++u) h[mt][nt][u] = fmaxf(h[mt][nt][u], 0.f);
-                __syncthreads();  // the previous chunk's readers are done with operand 2
-                store_split<MT>(a2_hi, a2_lo, h, warp, lane);
+                if (owner) store_split<MT>(a2_hi, a2_lo, h, warp, lane);
                 __syncthreads();
                 product_128<MT>(xo, a2_hi, a2_lo, ws, lane);  // W2, the chunk's k steps
             }
+            combine(xo);
             // ---- write x'
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
@@ -309,7 +362,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         const long long row = row0 + 16 * mt + g + 8 * half;
-                        if (row < p.N)
+                        if (owner && row < p.N)
                             *reinterpret_cast<float2 *>(p.x + row * 128 + 16 * warp + 8 * nt + 2 * t) =
                                 make_float2(xo[mt][nt][2 * half], xo[mt][nt][2 * half + 1]);
                     }
@@ -331,7 +384,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
 
         // ---- in-projection of the next layer: operand 1 <- x'
         __syncthreads();  // every warp is done with y in operand 1
-        store_split<MT>(a1_hi, a1_lo, xo, warp, lane);
+        if (owner) store_split<MT>(a1_hi, a1_lo, xo, warp, lane);
         __syncthreads();
         // warp w owns the 48 output columns 48 w .. 48 w + 47 of q|k|v = three 16-column groups (one head each)
 #pragma unroll
@@ -344,7 +397,10 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) { acc[mt][nt][0] = bq.x; acc[mt][nt][1] = bq.y; acc[mt][nt][2] = bq.x; acc[mt][nt][3] = bq.y; }
             }
+            if (!owner) zero(acc);
             product_128<MT>(acc, a1_hi, a1_lo, ws, lane);
+            combine(acc);
+            if (!owner) continue;  // (warp-uniform; the epilogue below has no block barrier)
             const int which = col0 >> 7;           // 0 q, 1 k, 2 v (warp-uniform)
             const int hc0 = col0 & 127;            // first column within q, k or v; the head is hc0 / 16
             float *dst = which == 0 ? p.q : (which == 1 ? p.k : p.v);
@@ -401,7 +457,8 @@ int launch_dense_block(const DenseArgs &p, cudaStream_t s)
     const long long tiles16 = (p.N + 15) / 16;
     const int sms = sm_count();
     const bool small = tiles16 <= sms;
-    const size_t smem = sizeof(unsigned) * (4 * (small ? 16 : 32) * LDA + DB_WARPS * RING_WORDS);
+    const size_t smem = sizeof(unsigned) * (4 * (small ? 16 : 32) * LDA + DB_WARPS * RING_WORDS +
+                                            (KSPLIT > 1 ? 2 * 8 * 32 * 8 * (small ? 1 : 2) : 0));
     auto kernel = small ? dense_block_kernel<1> : dense_block_kernel<2>;
     if (smem > 48 * 1024) {
         static thread_local bool raised_small = false, raised_large = false;
