@@ -303,9 +303,9 @@ def run_b200(args):
         }
         micro = lattice_microbench(ops, device, peaks)
         cpu = cpu_baseline(model, params, mine) if (world == 1 and not args.no_cpu_baseline) else None
-        # own kernels per forward: offsets, cell, atom, edge, row order, term lists; L + 1 dense blocks; per layer phi and
-        # rows; pooling + head
-        per_step_launches = 6 + (wl["layers"] + 1) + 2 * wl["layers"] + 1
+        # own kernels per forward: offsets, geometry + row order, term lists; L + 1 dense blocks; per layer phi and rows;
+        # pooling + head
+        per_step_launches = 3 + (wl["layers"] + 1) + 2 * wl["layers"] + 1
         result = {
             "metric": "crystals/sec (4-layer, fwd)" if wl["layers"] == 4 else f"crystals/sec ({wl['layers']}-layer, fwd)",
             "value": value, "unit": "crystals/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

@@ -63,10 +63,9 @@ __device__ __forceinline__ long long find_segment(const int64_t *__restrict__ st
     return lo;
 }
 
-__global__ void cell_kernel(const float *__restrict__ trans, long long B, float *__restrict__ rvecs,
-                            float *__restrict__ vcell, float *__restrict__ rvlen)
+__device__ __forceinline__ void cell_body(long long b, const float *__restrict__ trans, long long B,
+                                          float *__restrict__ rvecs, float *__restrict__ vcell, float *__restrict__ rvlen)
 {
-    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const float *m = trans + 9 * b;
     // determinant by the rule of Sarrus, term order as models/indexed_latticeformer_encoder.py:34-44
@@ -92,11 +91,16 @@ __global__ void cell_kernel(const float *__restrict__ trans, long long B, float 
     }
 }
 
-__global__ void atom_kernel(const int64_t *__restrict__ atom_start, const int64_t *__restrict__ edge_start,
-                            long long B, long long N, int64_t *__restrict__ batch, int64_t *__restrict__ row_start,
-                            long long E)
+__global__ void cell_kernel(const float *__restrict__ trans, long long B, float *__restrict__ rvecs,
+                            float *__restrict__ vcell, float *__restrict__ rvlen)
 {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    cell_body((long long)blockIdx.x * blockDim.x + threadIdx.x, trans, B, rvecs, vcell, rvlen);
+}
+
+__device__ __forceinline__ void atom_body(long long i, const int64_t *__restrict__ atom_start,
+                                          const int64_t *__restrict__ edge_start, long long B, long long N,
+                                          int64_t *__restrict__ batch, int64_t *__restrict__ row_start, long long E)
+{
     if (i > N) return;
     if (i == N) {
         if (row_start) row_start[N] = E;
@@ -107,11 +111,17 @@ __global__ void atom_kernel(const int64_t *__restrict__ atom_start, const int64_
     if (row_start) row_start[i] = edge_start[c] + (i - atom_start[c]) * (atom_start[c + 1] - atom_start[c]);
 }
 
-__global__ void edge_kernel(const float *__restrict__ pos, const int64_t *__restrict__ atom_start,
-                            const int64_t *__restrict__ edge_start, long long B, long long E,
-                            int64_t *__restrict__ edges, float *__restrict__ pos_ij)
+__global__ void atom_kernel(const int64_t *__restrict__ atom_start, const int64_t *__restrict__ edge_start,
+                            long long B, long long N, int64_t *__restrict__ batch, int64_t *__restrict__ row_start,
+                            long long E)
 {
-    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    atom_body((long long)blockIdx.x * blockDim.x + threadIdx.x, atom_start, edge_start, B, N, batch, row_start, E);
+}
+
+__device__ __forceinline__ void edge_body(long long e, const float *__restrict__ pos, const int64_t *__restrict__ atom_start,
+                                          const int64_t *__restrict__ edge_start, long long B, long long E,
+                                          int64_t *__restrict__ edges, float *__restrict__ pos_ij)
+{
     if (e >= E) return;
     const long long c = find_segment(edge_start, B, e);
     const long long n = atom_start[c + 1] - atom_start[c];
@@ -126,6 +136,13 @@ __global__ void edge_kernel(const float *__restrict__ pos, const int64_t *__rest
         pos_ij[3 * e + 1] = __fsub_rn(pos[3 * j + 1], pos[3 * i + 1]);
         pos_ij[3 * e + 2] = __fsub_rn(pos[3 * j + 2], pos[3 * i + 2]);
     }
+}
+
+__global__ void edge_kernel(const float *__restrict__ pos, const int64_t *__restrict__ atom_start,
+                            const int64_t *__restrict__ edge_start, long long B, long long E,
+                            int64_t *__restrict__ edges, float *__restrict__ pos_ij)
+{
+    edge_body((long long)blockIdx.x * blockDim.x + threadIdx.x, pos, atom_start, edge_start, B, E, edges, pos_ij);
 }
 
 // Scheduling weight of an atom's row in the fused attention kernels: a fixed part plus the expected number of
@@ -149,9 +166,8 @@ __global__ void row_cost_kernel(const int64_t *__restrict__ atom_start, const fl
 constexpr int ORDER_THREADS = 1024;
 constexpr int ORDER_MAX_CRYSTALS = 2048;
 
-__global__ void __launch_bounds__(ORDER_THREADS) row_order_kernel(const int64_t *__restrict__ atom_start,
-                                                                  const float *__restrict__ trans, int B, int padded,
-                                                                  float sphere, int32_t *__restrict__ order)
+__device__ __forceinline__ void row_order_body(const int64_t *__restrict__ atom_start, const float *__restrict__ trans,
+                                               int B, int padded, float sphere, int32_t *__restrict__ order)
 {
     __shared__ unsigned long long key[ORDER_MAX_CRYSTALS];
     __shared__ int offset[ORDER_MAX_CRYSTALS];
@@ -216,7 +232,63 @@ __global__ void __launch_bounds__(ORDER_THREADS) row_order_kernel(const int64_t 
     }
 }
 
+__global__ void __launch_bounds__(ORDER_THREADS) row_order_kernel(const int64_t *__restrict__ atom_start,
+                                                                  const float *__restrict__ trans, int B, int padded,
+                                                                  float sphere, int32_t *__restrict__ order)
+{
+    row_order_body(atom_start, trans, B, padded, sphere, order);
+}
+
+// Everything that follows the offsets in ONE launch of 1024-thread blocks: block 0 sorts the rows (when asked to), the
+// other blocks cover the cells, then the atoms, then the edges.
+struct PrepareAll {
+    const float *pos, *trans;
+    const int64_t *atom_start, *edge_start;
+    long long B, N, E;
+    int64_t *batch, *edges, *row_start;
+    float *pos_ij, *rvecs, *vcell, *rvlen;
+    int32_t *order;   // NULL: no ordering
+    int padded;
+    float sphere;
+};
+
+__global__ void __launch_bounds__(ORDER_THREADS) prepare_all_kernel(const PrepareAll p)
+{
+    if (blockIdx.x == 0) {
+        if (p.order != nullptr) row_order_body(p.atom_start, p.trans, (int)p.B, p.padded, p.sphere, p.order);
+        return;
+    }
+    const long long idx = (long long)(blockIdx.x - 1) * ORDER_THREADS + threadIdx.x;
+    if (idx < p.B) {
+        cell_body(idx, p.trans, p.B, p.rvecs, p.vcell, p.rvlen);
+    } else if (idx < p.B + p.N + 1) {
+        atom_body(idx - p.B, p.atom_start, p.edge_start, p.B, p.N, p.batch, p.row_start, p.E);
+    } else {
+        edge_body(idx - p.B - p.N - 1, p.pos, p.atom_start, p.edge_start, p.B, p.E, p.edges, p.pos_ij);
+    }
+}
+
 }  // namespace
+
+// cf_batch_prepare and cf_row_order in one launch (the one-call model forward); *ordered says whether row_order was
+// written (batches of more than ORDER_MAX_CRYSTALS crystals are not ordered).
+int launch_prepare_all(const float *pos, const float *trans, const int64_t *atom_start, const int64_t *edge_start,
+                       long long B, long long N, long long E, int64_t *batch, int64_t *edges, int64_t *row_start,
+                       float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered, cudaStream_t s)
+{
+    PrepareAll p{};
+    p.pos = pos; p.trans = trans; p.atom_start = atom_start; p.edge_start = edge_start; p.B = B; p.N = N; p.E = E;
+    p.batch = batch; p.edges = edges; p.row_start = row_start; p.pos_ij = pos_ij; p.rvlen = rvlen;
+    *ordered = row_order != nullptr && B <= ORDER_MAX_CRYSTALS && N < (1ll << 31);
+    p.order = *ordered ? row_order : nullptr;
+    p.padded = 2;
+    while (p.padded < B) p.padded <<= 1;
+    p.sphere = (float)(4.18879020478639 * reach * reach * reach);
+    const long long items = B + N + 1 + E;
+    prepare_all_kernel<<<(unsigned)(1 + (items + ORDER_THREADS - 1) / ORDER_THREADS), ORDER_THREADS, 0, s>>>(p);
+    return launch_status("prepare_all_kernel");
+}
+
 }  // namespace cf
 
 extern "C" int cf_row_order(const int64_t *atom_start, const float *trans, int64_t B, int64_t N, double reach,

@@ -3,7 +3,7 @@
 //
 // The reference's Latticeformer.forward (models/latticeformer.py:211-302) is a chain of framework calls; at the sizes
 // of a crystal batch the host cannot issue them as fast as the GPU retires them.  Here the chain is issued back to
-// back from C++ on one stream: five geometry launches, one SGEMM for the embedding, cf_encoder_forward, and one fused
+// back from C++ on one stream: two geometry launches, one SGEMM for the embedding, cf_encoder_forward, and one fused
 // kernel for the pooling (models/pooling.py:19-25 with the fixed summation tree of irregular_mean_fwd.cu) and the
 // multi-layer-perceptron head (Linear - ReLU - Linear, models/latticeformer.py:176-209 with norm_type "no").
 // No allocation, no synchronisation: scratch comes from the caller's workspace.
@@ -12,6 +12,9 @@
 #include "segment_mean.cuh"
 
 namespace cf {
+int launch_prepare_all(const float *pos, const float *trans, const int64_t *atom_start, const int64_t *edge_start,
+                       long long B, long long N, long long E, int64_t *batch, int64_t *edges, int64_t *row_start,
+                       float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered, cudaStream_t s);
 namespace {
 
 constexpr int MODEL_DIM = 128;
@@ -123,11 +126,11 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
 
     int rc = cf_crystal_offsets(sizes, B, w.atom_start, w.edge_start, stream);
     if (rc != CF_OK) return rc;
-    rc = cf_batch_prepare(pos, trans, sizes, w.atom_start, w.edge_start, B, N, E, w.batch, w.edges, w.row_start, w.pos_ij,
-                          nullptr, nullptr, w.rvlen, stream);
+    bool ordered = false;  // batches beyond the one-launch sort are processed in index order
+    rc = launch_prepare_all(pos, trans, w.atom_start, w.edge_start, B, N, E, w.batch, w.edges, w.row_start, w.pos_ij, w.rvlen,
+                            order_reach, w.row_order, &ordered, s);
     if (rc != CF_OK) return rc;
-    const int32_t *order = nullptr;  // batches beyond the one-launch sort are processed in index order
-    if (cf_row_order(w.atom_start, trans, B, N, order_reach, w.row_order, stream) == CF_OK) order = w.row_order;
+    const int32_t *order = ordered ? w.row_order : nullptr;
     if (N > 0) {
         cublasHandle_t handle = reinterpret_cast<cublasHandle_t>(cublas_handle);
         BlasScope scope(bl, handle, s);
