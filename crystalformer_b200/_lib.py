@@ -31,7 +31,7 @@ SIGNATURES = {
     "cf_infinite_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                              I32, P, P, P, P, P, P, P, P, P, P, P],
     "cf_pipe_probe": [I32, I32, I32, I64, P, P],
-    "cf_model_forward": [P, P, I64, P, P, P, I64, I64, I64, I64, P, I32, P, P, I64, I64, F64, F64, I32, I32, P, P, I64, P,
+    "cf_model_forward": [P, P, I64, P, P, P, I64, I64, I64, I64, P, P, I32, P, P, I64, I64, F64, F64, I32, I32, P, P, I64, P,
                          P, I64, F64, P, P, P, P],
     "cf_term_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
     "cf_infinite_attn_fwd_listed": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,

@@ -75,7 +75,7 @@ struct WeightStream {
     int lane;
     int panels;           // panels per row tile
     long long produced, consumed, limit;  // items; limit = tiles of this block x panels x KSTEPS
-    struct { const float4 *Wo, *W1, *W2, *Wqkv; int ff, tail; } d;
+    struct { const float4 *Wo, *W1, *W2, *Wqkv, *Wembed; int ff, tail; } d;
     int warp;             // column pair (0..7)
     int kh;               // k half
     int p_panel, p_ks;    // producer position within the row tile's sequence
@@ -85,7 +85,10 @@ struct WeightStream {
     {
         const int chunks = d.ff / 128;
         Panel r;
-        if (d.tail && idx == 0) {
+        if (d.Wembed != nullptr && idx == 0) {  // the embedding comes first (never together with a tail)
+            r.base = d.Wembed + (size_t)(2 * warp) * 16 * 32;
+            r.tile_stride = 16 * 32;
+        } else if (d.tail && idx == 0) {
             r.base = d.Wo + (size_t)(2 * warp) * 16 * 32;
             r.tile_stride = 16 * 32;
         } else if (d.tail && idx <= 2 * chunks) {
@@ -98,7 +101,7 @@ struct WeightStream {
                 r.tile_stride = 16 * 32;
             }
         } else {                  // Wqkv, group 0..2 of the warp's 48 output columns
-            const int grp = idx - (d.tail ? 1 + 2 * chunks : 0);
+            const int grp = idx - (d.tail ? 1 + 2 * chunks : 0) - (d.Wembed != nullptr ? 1 : 0);
             r.base = d.Wqkv + (size_t)((48 * warp + 16 * grp) / 8) * 16 * 32;
             r.tile_stride = 16 * 32;
         }
@@ -274,7 +277,8 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                 for (int u = 0; u < 4; ++u) acc[mt][nt][u] = 0.f;
     };
     ws.d.Wo = p.Wo; ws.d.W1 = p.W1; ws.d.W2 = p.W2; ws.d.Wqkv = p.Wqkv; ws.d.ff = p.ff; ws.d.tail = p.tail;
-    ws.panels = (p.tail ? 1 + 2 * (p.ff / 128) : 0) + (p.head ? 3 : 0);
+    ws.d.Wembed = p.tail ? nullptr : p.Wembed;
+    ws.panels = (p.tail ? 1 + 2 * (p.ff / 128) : 0) + (p.head ? 3 : 0) + (ws.d.Wembed != nullptr ? 1 : 0);
     ws.produced = ws.consumed = 0;
     ws.limit = my_tiles * ws.panels * KSTEPS;
     ws.start();
@@ -355,6 +359,32 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
             }
             combine(xo);
             // ---- write x'
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const long long row = row0 + 16 * mt + g + 8 * half;
+                        if (owner && row < p.N)
+                            *reinterpret_cast<float2 *>(p.x + row * 128 + 16 * warp + 8 * nt + 2 * t) =
+                                make_float2(xo[mt][nt][2 * half], xo[mt][nt][2 * half + 1]);
+                    }
+        } else if (ws.d.Wembed != nullptr) {
+            // ---- x = features W_embed^T: operand 1 <- the tile's feature rows, zero beyond feature_dim
+            for (int idx = tid; idx < ROWS * 128; idx += DB_THREADS) {
+                const int r = idx >> 7, col = idx & 127;
+                float v = 0.f;
+                if (row0 + r < p.N && col < p.feature_dim) v = p.features[(row0 + r) * p.feature_dim + col];
+                const unsigned hi = tf32_hi(v);
+                a1_hi[r * LDA + col] = hi;
+                a1_lo[r * LDA + col] = tf32_hi(v - __uint_as_float(hi));
+            }
+            zero(xo);
+            __syncthreads();
+            product_128<MT>(xo, a1_hi, a1_lo, ws, lane);
+            combine(xo);
+            if (KSPLIT == 1) __syncthreads();
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -452,6 +482,8 @@ int launch_dense_block(const DenseArgs &p, cudaStream_t s)
     if (p.N == 0) return CF_OK;
     if (p.tail && (p.ff <= 0 || p.ff % 128 != 0))
         return fail(CF_ERR_UNSUPPORTED, "dense block: ff_dim=%d must be a positive multiple of 128", p.ff);
+    if (!p.tail && p.Wembed != nullptr && (p.features == nullptr || p.feature_dim < 1 || p.feature_dim > 128))
+        return fail(CF_ERR_UNSUPPORTED, "dense block: embedding of %d features (1..128)", p.feature_dim);
     // 16-row tiles while they fit one wave of the SMs (more SMs busy), 32-row tiles beyond (half the weight traffic;
     // a block is tensor-pipe bound either way, so what counts is the number of waves)
     const long long tiles16 = (p.N + 15) / 16;

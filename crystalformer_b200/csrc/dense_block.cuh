@@ -19,11 +19,31 @@ struct DenseArgs {
     const float4 *Wqkv;             // packed (384 x 128)
     const float *bqkv, *w_pos;
     float gauss_scale, gauss_shift, a_factor, elu_beta, lower_bound;
+    // embedding (optional, only without a tail): x = features W_embed^T, written and carried into the head
+    const float *features;          // (N, feature_dim), feature_dim <= 128
+    int feature_dim;
+    const float4 *Wembed;           // packed (128 x 128, input columns beyond feature_dim zero)
     // activations
     float *x;                       // (N,128), updated in place by the tail
     float *q, *k, *v, *a;           // outputs of the head: (N,128) x 3 and (N,8)
 };
 
 int launch_dense_block(const DenseArgs &p, cudaStream_t s);
+
+// True if an encoder of these layers runs through the dense block: every layer brings packed weights (slot 10 of its
+// 11 weight pointers) and the feed-forward width is a multiple of 128.
+inline bool dense_path_available(int num_layers, const float *const *weights, long long ff_dim)
+{
+    bool ok = ff_dim > 0 && ff_dim % 128 == 0;
+    for (int l = 0; l < num_layers; ++l) ok = ok && weights[11 * l + 10] != nullptr;
+    return ok;
+}
+
+// Embedding to run inside the first dense block of an encoder (x is then an output of the encoder call).
+struct EmbedStage {
+    const float *features;   // (N, feature_dim)
+    int feature_dim;         // <= 128
+    const float4 *packed;    // W_embed packed as a 128 x 128 weight (input columns beyond feature_dim zero)
+};
 
 }  // namespace cf

@@ -22,6 +22,12 @@
 #include "term_list.cuh"
 
 namespace cf {
+int encoder_forward_impl(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars,
+                         float *x, const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                         const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
+                         int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                         int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
+                         void *const *attn_events, void *stream, const EmbedStage *embed);
 int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
                            const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
                            const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D,
@@ -143,24 +149,34 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
                                   double cutoff_radius, int lattice_range, int minimum_range, float *workspace,
                                   const int32_t *row_order, void *const *attn_events, void *stream)
 {
-    using namespace cf;
+    return cf::encoder_forward_impl(cublas_handle, num_layers, weights, scalars, x, pos_ij, tvecs, rvlen, batch, edges,
+                                    row_start, N, B, E, max_atoms, K, ff_dim, wscale, cutoff_radius, lattice_range,
+                                    minimum_range, workspace, row_order, attn_events, stream, nullptr);
+}
+
+// cf_encoder_forward with an optional embedding stage (dense path only): x is then written by the first dense block.
+int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars,
+                             float *x, const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                             const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
+                             int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                             int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
+                             void *const *attn_events, void *stream, const EmbedStage *embed)
+{
     CF_REQUIRE(N >= 0 && E >= 0 && num_layers >= 0, CF_ERR_INVALID, "cf_encoder_forward: negative size");
     CF_REQUIRE(ff_dim > 0 && ff_dim % 4 == 0, CF_ERR_UNSUPPORTED, "cf_encoder_forward: ff_dim must be a positive multiple of 4");
     CF_REQUIRE(N < (1ll << 31) / 512, CF_ERR_RANGE, "cf_encoder_forward: N=%lld too large for 32-bit GEMM sizes", (long long)N);
     if (N == 0 || num_layers == 0) return CF_OK;
-    CF_REQUIRE(cublas_handle && weights && scalars && x && workspace, CF_ERR_INVALID, "cf_encoder_forward: null pointer");
-    const Blas &bl = blas();
-    CF_REQUIRE(bl.ok, CF_ERR_CUDA, "cf_encoder_forward: libcublas.so.12 could not be resolved in this process");
-    cublasHandle_t handle = reinterpret_cast<cublasHandle_t>(cublas_handle);
+    CF_REQUIRE(weights && scalars && x && workspace, CF_ERR_INVALID, "cf_encoder_forward: null pointer");
+    const int ff = (int)ff_dim;
+    const bool fused = dense_path_available(num_layers, weights, ff_dim);  // one launch per layer boundary, no cuBLAS
+    CF_REQUIRE(fused || embed == nullptr, CF_ERR_INVALID, "cf_encoder_forward: embedding stage without the dense path");
+    CF_REQUIRE(fused || cublas_handle, CF_ERR_INVALID, "cf_encoder_forward: null cuBLAS handle");
     cudaStream_t s = as_stream(stream);
-    BlasScope scope(bl, handle, s);
 
     float *qkv = workspace;
     float *q = qkv + N * 384, *k = q + N * 128, *v = k + N * 128, *attn = v + N * 128;
     float *a = attn + N * 128, *lse = a + N * 8, *hidden = lse + N * 8, *logit = hidden + N * ff_dim;
-    const int rows = (int)N, ff = (int)ff_dim;
     int rc = CF_OK;
-    cublasStatus_t st = CUBLAS_STATUS_SUCCESS;
 
     // Term lists (term_list.cuh): the geometry is the same for every layer, so the (key, translation) pairs that can
     // matter to any layer are found once.  The widest Gaussian any layer can produce has a = lower_bound x a_factor.
@@ -194,8 +210,6 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
     // Fused dense path: every layer brings its weights packed for the tensor-core kernel (slot 10) and the
     // feed-forward width is a multiple of 128.  One launch per layer boundary instead of four GEMMs and two
     // element-wise passes; see dense_block.cu.
-    bool fused = ff % 128 == 0;
-    for (int l = 0; l < num_layers; ++l) fused = fused && weights[11 * l + 10] != nullptr;
     if (fused) {
         auto head_of = [&](DenseArgs &d, int l) {
             const float *const *w = weights + 11 * l;
@@ -210,6 +224,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
         DenseArgs d{};
         d.N = N; d.ff = ff; d.x = x; d.q = q; d.k = k; d.v = v; d.a = a; d.attn = attn;
         head_of(d, 0);
+        if (embed != nullptr) { d.features = embed->features; d.feature_dim = embed->feature_dim; d.Wembed = embed->packed; }
         rc = launch_dense_block(d, s);
         if (forked) cudaStreamWaitEvent(s, side_stream().join, 0);
         for (int l = 0; l < num_layers && rc == CF_OK; ++l) {
@@ -236,6 +251,12 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
         return launch_status("cf_encoder_forward");
     }
 
+    const Blas &bl = blas();
+    CF_REQUIRE(bl.ok, CF_ERR_CUDA, "cf_encoder_forward: libcublas.so.12 could not be resolved in this process");
+    cublasHandle_t handle = reinterpret_cast<cublasHandle_t>(cublas_handle);
+    BlasScope scope(bl, handle, s);
+    const int rows = (int)N;
+    cublasStatus_t st = CUBLAS_STATUS_SUCCESS;
     if (forked) cudaStreamWaitEvent(s, side_stream().join, 0);
     for (int l = 0; l < num_layers && rc == CF_OK && st == CUBLAS_STATUS_SUCCESS; ++l) {
         const float *const *w = weights + 11 * l;  // Wqkv, bqkv, w_pos, Wpe, Wo, bo, W1, b1, W2, b2, packed (optional)

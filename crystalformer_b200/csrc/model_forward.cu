@@ -3,18 +3,25 @@
 //
 // The reference's Latticeformer.forward (models/latticeformer.py:211-302) is a chain of framework calls; at the sizes
 // of a crystal batch the host cannot issue them as fast as the GPU retires them.  Here the chain is issued back to
-// back from C++ on one stream: two geometry launches, one SGEMM for the embedding, cf_encoder_forward, and one fused
-// kernel for the pooling (models/pooling.py:19-25 with the fixed summation tree of irregular_mean_fwd.cu) and the
+// back from C++ on one stream: two geometry launches, the embedding (inside the first dense block of the encoder when
+// its packed weight is given, else one SGEMM), the encoder stack, and one fused kernel for the pooling (models/pooling.py:19-25 with the fixed summation tree of irregular_mean_fwd.cu) and the
 // multi-layer-perceptron head (Linear - ReLU - Linear, models/latticeformer.py:176-209 with norm_type "no").
 // No allocation, no synchronisation: scratch comes from the caller's workspace.
 #include "blas_dyn.cuh"
 #include "common.cuh"
+#include "dense_block.cuh"
 #include "segment_mean.cuh"
 
 namespace cf {
 int launch_prepare_all(const float *pos, const float *trans, const int64_t *atom_start, const int64_t *edge_start,
                        long long B, long long N, long long E, int64_t *batch, int64_t *edges, int64_t *row_start,
                        float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered, cudaStream_t s);
+int encoder_forward_impl(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars,
+                         float *x, const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                         const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
+                         int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                         int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
+                         void *const *attn_events, void *stream, const EmbedStage *embed);
 namespace {
 
 constexpr int MODEL_DIM = 128;
@@ -104,8 +111,8 @@ extern "C" int64_t cf_model_workspace_bytes(int64_t N, int64_t B, int64_t E, int
 
 extern "C" int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
                                 const float *trans, const int64_t *sizes, int64_t N, int64_t B, int64_t E,
-                                int64_t max_atoms, const float *W_embed, int num_layers, const float *const *weights,
-                                const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                                int64_t max_atoms, const float *W_embed, const float *W_embed_packed, int num_layers,
+                                const float *const *weights, const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
                                 int lattice_range, int minimum_range, const float *W1, const float *b1, int64_t hidden,
                                 const float *W2, const float *b2, int64_t targets, double order_reach, void *workspace,
                                 float *y, void *const *attn_events, void *stream)
@@ -117,10 +124,12 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
                (long long)targets, HEAD_MAX_HIDDEN);
     CF_REQUIRE(N < (1ll << 31) / 512, CF_ERR_RANGE, "cf_model_forward: N=%lld too large for 32-bit GEMM sizes", (long long)N);
     if (B == 0) return CF_OK;
-    CF_REQUIRE(cublas_handle && features && pos && trans && sizes && W_embed && W1 && b1 && W2 && b2 && workspace && y,
-               CF_ERR_INVALID, "cf_model_forward: null pointer");
-    const Blas &bl = blas();
-    CF_REQUIRE(bl.ok, CF_ERR_CUDA, "cf_model_forward: libcublas.so.12 could not be resolved in this process");
+    CF_REQUIRE(features && pos && trans && sizes && W_embed && W1 && b1 && W2 && b2 && workspace && y, CF_ERR_INVALID,
+               "cf_model_forward: null pointer");
+    // With packed weights everywhere the whole forward runs in this library's kernels and cuBLAS is not touched.
+    const bool embed_fused = W_embed_packed != nullptr && feature_dim <= MODEL_DIM && num_layers > 0 && N > 0 &&
+                             dense_path_available(num_layers, weights, ff_dim);
+    CF_REQUIRE(embed_fused || cublas_handle, CF_ERR_INVALID, "cf_model_forward: null cuBLAS handle");
     cudaStream_t s = as_stream(stream);
     Scratch w = carve(workspace, N, B, E, ff_dim);
 
@@ -131,16 +140,19 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
                             order_reach, w.row_order, &ordered, s);
     if (rc != CF_OK) return rc;
     const int32_t *order = ordered ? w.row_order : nullptr;
-    if (N > 0) {
+    if (N > 0 && !embed_fused) {
+        const Blas &bl = blas();
+        CF_REQUIRE(bl.ok, CF_ERR_CUDA, "cf_model_forward: libcublas.so.12 could not be resolved in this process");
         cublasHandle_t handle = reinterpret_cast<cublasHandle_t>(cublas_handle);
         BlasScope scope(bl, handle, s);
         const cublasStatus_t st = linear(bl, handle, features, W_embed, w.x, (int)N, (int)feature_dim, MODEL_DIM, 0.0f);
         if (st != CUBLAS_STATUS_SUCCESS) return fail(CF_ERR_CUDA, "cf_model_forward: cuBLAS SGEMM failed with status %d", (int)st);
     }
-    rc = cf_encoder_forward(cublas_handle, num_layers, weights, scalars, w.x, w.pos_ij, trans,
-                            cutoff_radius != 0.0 ? w.rvlen : nullptr, w.batch, w.edges, w.row_start, N, B, E, max_atoms, K,
-                            ff_dim, wscale, cutoff_radius, lattice_range, minimum_range, w.encoder, order, attn_events,
-                            stream);
+    const EmbedStage embed{features, (int)feature_dim, reinterpret_cast<const float4 *>(W_embed_packed)};
+    rc = encoder_forward_impl(cublas_handle, num_layers, weights, scalars, w.x, w.pos_ij, trans,
+                              cutoff_radius != 0.0 ? w.rvlen : nullptr, w.batch, w.edges, w.row_start, N, B, E, max_atoms, K,
+                              ff_dim, wscale, cutoff_radius, lattice_range, minimum_range, w.encoder, order, attn_events,
+                              stream, embed_fused ? &embed : nullptr);
     if (rc != CF_OK) return rc;
     pool_head_kernel<<<(unsigned)B, HEAD_THREADS, 0, s>>>(w.x, w.atom_start, W1, b1, W2, b2, (int)hidden, (int)targets, y);
     return launch_status("cf_model_forward");

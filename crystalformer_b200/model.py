@@ -15,7 +15,7 @@ import torch.nn as nn
 
 from . import _lib
 from .cuda_funcs import IrregularMeanCUDA
-from .encoder import BatchGeometry, CrystalformerEncoderCUDA
+from .encoder import BatchGeometry, CrystalformerEncoderCUDA, pack_dense_weight
 from .params import DEFAULT_MODEL_PARAMS, LatticeformerParams
 
 
@@ -119,6 +119,21 @@ class Latticeformer(nn.Module):
             return False
         return self.input_embeddings.out_features == 128 and self.encoder.native and self.encoder._native_ok()
 
+    def _embedding_packed(self, device) -> Optional[torch.Tensor]:
+        """The embedding weight, input columns zero-padded to 128, in the fragment order of the fused dense kernel
+        (which then computes the embedding inside the encoder's first launch); None when that kernel is not in use.
+        Rebuilt only when the weight changed."""
+        W = self.input_embeddings.weight
+        if not self.encoder.dense_fused or W.shape[1] > 128:
+            return None
+        key = (device, W._version, W.data_ptr())
+        cache = getattr(self, "_embed_cache", None)
+        if cache is None or cache[0] != key:
+            padded = torch.zeros((128, 128), dtype=torch.float32, device=device)
+            padded[:, :W.shape[1]] = W.detach().float()
+            self._embed_cache = cache = (key, pack_dense_weight(padded))
+        return cache[1]
+
     def _forward_native(self, data, counts: Tuple[int, int, int]) -> torch.Tensor:
         enc = self.encoder
         P = enc.lattice_params
@@ -134,6 +149,7 @@ class Latticeformer(nn.Module):
         lib = _lib.load()
         work = torch.empty(int(lib.cf_model_workspace_bytes(n_atoms, B, n_edges, w["ff"])), dtype=torch.uint8, device=dev)
         y = torch.empty((B, targets), dtype=torch.float32, device=dev)
+        emb_packed = self._embedding_packed(dev)
         dist_max = P.value_pe_dist_max
         if dist_max < 0:
             sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
@@ -141,7 +157,7 @@ class Latticeformer(nn.Module):
         with torch.cuda.device(dev):
             _lib.call("cf_model_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()), feats.data_ptr(),
                       feats.shape[1], pos.data_ptr(), trans.data_ptr(), sizes.data_ptr(), n_atoms, B, n_edges, max_atoms,
-                      emb.data_ptr(), len(enc.layers), w["ptrs"], w["scalars"], int(P.value_pe_dist_real), w["ff"],
+                      emb.data_ptr(), None if emb_packed is None else emb_packed.data_ptr(), len(enc.layers), w["ptrs"], w["scalars"], int(P.value_pe_dist_real), w["ff"],
                       float(P.value_pe_width_scale), enc._cutoff(), int(P.lattice_range),
                       int(P.lattice_range) if P.minimum_range else 0, w1.data_ptr(), b1.data_ptr(), hidden,
                       w2.data_ptr(), b2.data_ptr(), targets, float(dist_max) + 1.0, work.data_ptr(), y.data_ptr(),

@@ -275,12 +275,15 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
  * (W1 (hidden,128), b1, W2 (targets,hidden), b2; hidden <= 1024).  N, E = sum n, sum n^2 and max_atoms are host
  * integers the caller knows from the sizes.  workspace: cf_model_workspace_bytes(N, B, E, ff_dim) bytes, 256-byte
  * aligned.  order_reach: the reach handed to cf_row_order (about dist_max).
+ * W_embed_packed (optional, NULL to skip): W_embed with its input columns zero-padded to 128, packed like slot 10 of
+ * the layer weights (feature_dim <= 128).  When it is given and every layer brings packed weights, the embedding runs
+ * inside the first dense block, the whole forward runs in this library's kernels and cublas_handle may be NULL.
  * ---------------------------------------------------------------------------------------------------------- */
 int64_t cf_model_workspace_bytes(int64_t N, int64_t B, int64_t E, int64_t ff_dim);
 int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
                      const float *trans, const int64_t *sizes, int64_t N, int64_t B, int64_t E, int64_t max_atoms,
-                     const float *W_embed, int num_layers, const float *const *weights, const double *scalars,
-                     int64_t K, int64_t ff_dim, double wscale, double cutoff_radius, int lattice_range,
+                     const float *W_embed, const float *W_embed_packed, int num_layers, const float *const *weights,
+                     const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius, int lattice_range,
                      int minimum_range, const float *W1, const float *b1, int64_t hidden, const float *W2,
                      const float *b2, int64_t targets, double order_reach, void *workspace, float *y,
                      void *const *attn_events, void *stream);
