@@ -271,8 +271,8 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
  * models/latticeformer.py:211-302, with pooling "avr", pre_pooling_op "no", norm_type "no" and a head of the form
  * Linear - ReLU - Linear): y (B, targets) from the species features (N, feature_dim), positions, lattices and sizes.
  * Runs cf_crystal_offsets, the work of cf_batch_prepare and cf_row_order (one launch), the embedding (W_embed
- * (128, feature_dim), no bias; one SGEMM unless W_embed_packed is given), cf_encoder_forward (same weights / scalars / box arguments) and a fused mean + head kernel
- * (W1 (hidden,128), b1, W2 (targets,hidden), b2; hidden <= 1024).  N, E = sum n, sum n^2 and max_atoms are host
+ * (128, feature_dim), no bias; one SGEMM unless W_embed_packed is given), cf_encoder_forward (same weights /
+ * scalars / box arguments) and a fused mean + head kernel (W1 (hidden,128), b1, W2 (targets,hidden), b2; hidden <= 1024).  N, E = sum n, sum n^2 and max_atoms are host
  * integers the caller knows from the sizes.  workspace: cf_model_workspace_bytes(N, B, E, ff_dim) bytes, 256-byte
  * aligned.  order_reach: the reach handed to cf_row_order (about dist_max).
  * W_embed_packed (optional, NULL to skip): W_embed with its input columns zero-padded to 128, packed like slot 10 of
