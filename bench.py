@@ -7,7 +7,8 @@ One "step" is one forward pass of the Crystalformer model (4 layers, model_dim 1
 cfg0/cfg4; 7 layers without the value encoding for cfg2) over one batch of seeded synthetic crystals.  Per GPU the batch
 has the configuration's crystal count; with N GPUs a batch of N times that many crystals is drawn, split over the ranks
 by the reference's greedy rule on n^2 (crystalformer_b200.sharding.lpt_assign) and only the per-crystal outputs are
-all-gathered (weak scaling).  Rank 0 prints ONE JSON line:
+gathered on every rank, by stores into the peers' memory (crystalformer_b200.sharding.PeerGather; weak scaling).
+Rank 0 prints ONE JSON line:
 
   value            crystals / s over all ranks, inputs already resident in HBM, device-timed (CUDA events), max over ranks;
                    the steps are issued back to back (no host synchronisation in between), each inside its own event
@@ -145,7 +146,7 @@ def run_b200(args):
     import types
     from crystalformer_b200 import ops
     from crystalformer_b200.encoder import BatchGeometry
-    from crystalformer_b200.sharding import gather_outputs, lpt_assign, shard_balance
+    from crystalformer_b200.sharding import PeerGather, lpt_assign, shard_balance
     from crystalformer_b200.synthetic import make_config
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -195,18 +196,21 @@ def run_b200(args):
     native_log = []                            # one-call path: the library records the events itself
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)  # > 126 MB L2
 
+    # N > 1: the pooling + head kernel of every rank stores its outputs into every rank's gather buffer over NVLink
+    # and a small kernel waits for all ranks (sharding.PeerGather); no collective library on the data path.
+    peers = PeerGather(shards, model.mlp[-1].out_features, device) if world > 1 else None
+    extra = {} if peers is None else {"gather": peers}
+
     def step_resident():
         with torch.no_grad():
-            y = model(resident, counts=(n_atoms, n_edges, max_atoms))
-        return gather_outputs(y, shards) if world > 1 else y
+            return model(resident, counts=(n_atoms, n_edges, max_atoms), **extra)
 
     pinned = to_device_batch(mine, device, pinned=True)
     h2d_bytes = sum(t.numel() * t.element_size() for t in vars(pinned).values())
     d2h_bytes = (global_batch.num_crystals if world > 1 else mine.num_crystals) * 4
 
     from crystalformer_b200.serving import PipelinedPredictor
-    runner = PipelinedPredictor(model, depth=3, device=device,
-                                post=(lambda y: gather_outputs(y, shards)) if world > 1 else None)
+    runner = PipelinedPredictor(model, depth=3, device=device, gather=peers)
     pending = []
 
     def step_e2e():
@@ -235,6 +239,7 @@ def run_b200(args):
         drain()
         barrier()
         spans = []
+        host_t0 = time.perf_counter()
         record["on"] = instrument
         model.encoder.attention_event_log = native_log if instrument else None
         for _ in range(steps):
@@ -244,16 +249,30 @@ def run_b200(args):
             step()
             e.record()
             spans.append((s, e))
+        host_issue = time.perf_counter() - host_t0  # the host is done issuing; the device may still be busy
         drain()
         record["on"] = False
         model.encoder.attention_event_log = None
         barrier()
         total = sum(s.elapsed_time(e) for s, e in spans)
+        if peers is not None:
+            peers.check()  # raises if a collect gave up waiting for a rank
         t = torch.tensor([total], device=device, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        # where the time went on this rank: its own spans, the device wall clock from the first step's start to the
+        # last step's end (flushes and any idle gaps included) and the host time spent issuing the steps
+        mine_diag = {"rank": rank, "span_ms_per_step": total / steps,
+                     "device_wall_ms_per_step": spans[0][0].elapsed_time(spans[-1][1]) / steps,
+                     "host_issue_ms_per_step": host_issue * 1e3 / steps}
+        every = [mine_diag]
+        if world > 1:
+            every = [None] * world
+            dist.all_gather_object(every, mine_diag)
+        diag.append(every)
         return float(t.item())  # ms for all steps, max over ranks
 
+    diag = []
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         time.sleep(0.3)  # let nvidia-smi start sampling
@@ -316,8 +335,9 @@ def run_b200(args):
                        "atoms_this_rank": n_atoms, "edges_this_rank": n_edges, "cutoff": "adaptive -3.5 sigma, minimum box R=2",
                        "l2": "flushed between timed steps (256 MB write between the per-step event pairs)",
                        "timing": "steps issued back to back without host synchronisation; sum of per-step event spans",
-                       "parallelism": f"dp{world} (LPT on n^2, all-gather of outputs)",
+                       "parallelism": f"dp{world} (LPT on n^2, outputs gathered by peer stores)",
                        "shard_balance": shard_balance(global_batch.sizes, shards)},
+            "per_rank": {"resident": diag[0], "e2e": diag[1]},
             "e2e": {"value": e2e_value, "unit": "crystals/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                     "api": "crystalformer_b200.serving.PipelinedPredictor, 3 batches in flight"},

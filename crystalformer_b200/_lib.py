@@ -32,7 +32,13 @@ SIGNATURES = {
                              I32, P, P, P, P, P, P, P, P, P, P, P],
     "cf_pipe_probe": [I32, I32, I32, I64, P, P],
     "cf_model_forward": [P, P, I64, P, P, P, I64, I64, I64, I64, P, P, I32, P, P, I64, I64, F64, F64, I32, I32, P, P, I64, P,
-                         P, I64, F64, P, P, P, P],
+                         P, I64, F64, P, P, P, P, P],
+    "cf_peer_alloc": [I64, P, P],
+    "cf_peer_open": [P, P],
+    "cf_peer_close": [P],
+    "cf_peer_free": [P],
+    "cf_peer_gather_store": [P, I64, I64, P, P],
+    "cf_peer_gather_collect": [P, ctypes.c_uint32, P, I64, I64, I64, P, P, F64, P],
     "cf_term_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
     "cf_infinite_attn_fwd_listed": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                                     I32, P, P, P, P, P, P, F64, P],
@@ -44,6 +50,16 @@ SIGNATURES = {
     "cf_encoder_forward": [P, I32, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, F64, F64, I32, I32, P, P, P,
                            P],
 }
+
+
+MAX_PEERS = 16
+PEER_HANDLE_BYTES = 64
+
+
+class PeerGatherDescriptor(ctypes.Structure):
+    """``cf_peer_gather`` of include/crystalformer_b200.h: one step of a peer gather as seen by one rank."""
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("rows_per_rank", c_int64),
+                ("step", ctypes.c_uint32), ("reserved", ctypes.c_uint32), ("cells", c_void_p * MAX_PEERS)]
 
 
 class CrystalformerB200Error(RuntimeError):

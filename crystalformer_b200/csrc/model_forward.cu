@@ -10,9 +10,11 @@
 #include "blas_dyn.cuh"
 #include "common.cuh"
 #include "dense_block.cuh"
+#include "peer_gather.cuh"
 #include "segment_mean.cuh"
 
 namespace cf {
+int validate_peer_gather(const cf_peer_gather *g, long long rows, const char *who);
 int launch_prepare_all(const float *pos, const float *trans, const int64_t *atom_start, const int64_t *edge_start,
                        long long B, long long N, long long E, int64_t *batch, int64_t *edges, int64_t *row_start,
                        float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered, cudaStream_t s);
@@ -29,11 +31,14 @@ constexpr int HEAD_THREADS = 128;
 constexpr int HEAD_MAX_HIDDEN = 1024;
 
 // One thread block per crystal: mean of the atoms' features, hidden = relu(W1 mean + b1), y = W2 hidden + b2.
+// GATHER: y also goes into every rank's gather buffer (peer_gather.cuh).
+template <bool GATHER>
 __global__ void __launch_bounds__(HEAD_THREADS) pool_head_kernel(const float *__restrict__ x,
                                                                  const int64_t *__restrict__ atom_start,
                                                                  const float *__restrict__ W1, const float *__restrict__ b1,
                                                                  const float *__restrict__ W2, const float *__restrict__ b2,
-                                                                 int hidden, int targets, float *__restrict__ y)
+                                                                 int hidden, int targets, float *__restrict__ y,
+                                                                 const cf_peer_gather gather)
 {
     __shared__ __align__(16) float pooled[MODEL_DIM];
     __shared__ float hid[HEAD_MAX_HIDDEN];
@@ -58,7 +63,10 @@ __global__ void __launch_bounds__(HEAD_THREADS) pool_head_kernel(const float *__
         float acc = 0.f;
         for (int u = lane; u < hidden; u += 32) acc = fmaf(W2[(size_t)t * hidden + u], hid[u], acc);
         acc = warp_sum(acc);
-        if (lane == 0) y[c * targets + t] = acc + b2[t];
+        if (lane == 0) {
+            y[c * targets + t] = acc + b2[t];
+            if (GATHER) peer_store(gather, c, targets, t, acc + b2[t]);
+        }
     }
 }
 
@@ -115,10 +123,14 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
                                 const float *const *weights, const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
                                 int lattice_range, int minimum_range, const float *W1, const float *b1, int64_t hidden,
                                 const float *W2, const float *b2, int64_t targets, double order_reach, void *workspace,
-                                float *y, void *const *attn_events, void *stream)
+                                float *y, void *const *attn_events, const cf_peer_gather *gather, void *stream)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && B >= 0 && E >= 0 && feature_dim > 0, CF_ERR_INVALID, "cf_model_forward: bad size");
+    if (gather != nullptr) {
+        const int grc = validate_peer_gather(gather, B, "cf_model_forward");
+        if (grc != CF_OK) return grc;
+    }
     CF_REQUIRE(hidden > 0 && hidden <= HEAD_MAX_HIDDEN && targets > 0, CF_ERR_UNSUPPORTED,
                "cf_model_forward: head of %lld hidden units, %lld targets (hidden <= %d)", (long long)hidden,
                (long long)targets, HEAD_MAX_HIDDEN);
@@ -154,6 +166,11 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
                               ff_dim, wscale, cutoff_radius, lattice_range, minimum_range, w.encoder, order, attn_events,
                               stream, embed_fused ? &embed : nullptr);
     if (rc != CF_OK) return rc;
-    pool_head_kernel<<<(unsigned)B, HEAD_THREADS, 0, s>>>(w.x, w.atom_start, W1, b1, W2, b2, (int)hidden, (int)targets, y);
+    if (gather != nullptr)
+        pool_head_kernel<true><<<(unsigned)B, HEAD_THREADS, 0, s>>>(w.x, w.atom_start, W1, b1, W2, b2, (int)hidden,
+                                                                    (int)targets, y, *gather);
+    else
+        pool_head_kernel<false><<<(unsigned)B, HEAD_THREADS, 0, s>>>(w.x, w.atom_start, W1, b1, W2, b2, (int)hidden,
+                                                                     (int)targets, y, cf_peer_gather{});
     return launch_status("cf_model_forward");
 }

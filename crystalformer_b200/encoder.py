@@ -185,8 +185,8 @@ class CrystalformerEncoderCUDA(Module):
 
     def _packed_weights(self, device):
         """Device pointers and scalars of every layer in the layout cf_encoder_forward expects; rebuilt only when a
-        parameter changed (in-place updates bump ``_version``)."""
-        params = [p for p in self.parameters()]
+        parameter or buffer changed (in-place updates bump ``_version``)."""
+        params = [p for p in self.parameters()] + [b for b in self.buffers()]  # (gauss_scale is a buffer)
         key = (device, self.dense_fused, tuple(p._version for p in params), tuple(p.data_ptr() for p in params))
         cache = getattr(self, "_native_cache", None)
         if cache is not None and cache[0] == key:

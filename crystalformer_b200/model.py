@@ -134,7 +134,7 @@ class Latticeformer(nn.Module):
             self._embed_cache = cache = (key, pack_dense_weight(padded))
         return cache[1]
 
-    def _forward_native(self, data, counts: Tuple[int, int, int]) -> torch.Tensor:
+    def _forward_native(self, data, counts: Tuple[int, int, int], gather=None) -> torch.Tensor:
         enc = self.encoder
         P = enc.lattice_params
         dev = data.pos.device
@@ -154,6 +154,7 @@ class Latticeformer(nn.Module):
         if dist_max < 0:
             sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
             dist_max = -dist_max * sr
+        desc = None if gather is None else gather.next_descriptor()
         with torch.cuda.device(dev):
             _lib.call("cf_model_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()), feats.data_ptr(),
                       feats.shape[1], pos.data_ptr(), trans.data_ptr(), sizes.data_ptr(), n_atoms, B, n_edges, max_atoms,
@@ -161,19 +162,22 @@ class Latticeformer(nn.Module):
                       float(P.value_pe_width_scale), enc._cutoff(), int(P.lattice_range),
                       int(P.lattice_range) if P.minimum_range else 0, w1.data_ptr(), b1.data_ptr(), hidden,
                       w2.data_ptr(), b2.data_ptr(), targets, float(dist_max) + 1.0, work.data_ptr(), y.data_ptr(),
-                      enc._attention_events(), torch.cuda.current_stream(dev).cuda_stream)
-        return y
+                      enc._attention_events(), None if desc is None else ctypes.byref(desc),
+                      torch.cuda.current_stream(dev).cuda_stream)
+        return y if gather is None else gather.collect()
 
-    def forward(self, data, geometry: Optional[BatchGeometry] = None, counts: Optional[Tuple[int, int, int]] = None):
+    def forward(self, data, geometry: Optional[BatchGeometry] = None, counts: Optional[Tuple[int, int, int]] = None,
+                gather=None):
         """``data`` carries x (N,98), pos (N,3), batch (N), trans_vec (B,3,3), sizes (B) like the reference's PyG batch.
         ``counts`` = (atoms, edges = sum n^2, largest crystal), when the caller knows them on the host, saves the
-        device->host read of ``sizes``."""
+        device->host read of ``sizes``.  ``gather`` (a ``sharding.PeerGather``, inference only): the outputs of every
+        rank's crystals are returned, in the order of the unsharded batch."""
         if geometry is None and not self.training and not torch.is_grad_enabled() and data.pos.is_cuda \
                 and self._native_ok():
             if counts is None:
                 host = data.sizes.tolist()  # the one device->host read per batch (the reference does the same)
                 counts = (sum(host), sum(n * n for n in host), max(host) if host else 1)
-            return self._forward_native(data, counts)
+            return self._forward_native(data, counts, gather)
         x = self.input_embeddings(data.x)
         if geometry is None:
             geometry = BatchGeometry(data.pos, data.trans_vec, data.sizes, *(counts if counts is not None else ()))
@@ -181,4 +185,8 @@ class Latticeformer(nn.Module):
         x = self.encoder(x, data.pos, g.batch, data.trans_vec, g.sizes, geometry=g)
         x = self.proj_before_pooling(x)
         x = self.pooling_layer(x, g.batch, g.sizes)
-        return self.mlp(x)
+        y = self.mlp(x)
+        if gather is not None:
+            gather.store(y)
+            return gather.collect()
+        return y

@@ -24,9 +24,11 @@ import torch
 
 
 class PipelinedPredictor:
-    def __init__(self, model: torch.nn.Module, depth: int = 3, device: Optional[torch.device] = None, post=None):
+    def __init__(self, model: torch.nn.Module, depth: int = 3, device: Optional[torch.device] = None, post=None,
+                 gather=None):
         """``post``: optional callable applied to the model output on the device before it is copied to the host
-        (e.g. an all-gather of the ranks' outputs)."""
+        (e.g. an all-gather of the ranks' outputs).  ``gather``: a ``sharding.PeerGather`` handed to the model, which
+        then returns the outputs of every rank's crystals."""
         if depth < 1:
             raise ValueError("depth must be at least 1")
         self.model = model
@@ -35,6 +37,7 @@ class PipelinedPredictor:
             raise RuntimeError("PipelinedPredictor needs a CUDA model: crystalformer_b200 has no CPU path")
         self.depth = depth
         self.post = post
+        self.gather = gather
         self.copy_stream = torch.cuda.Stream(self.device)
         self._inflight: Deque[Tuple[int, torch.cuda.Event, torch.Tensor, int]] = deque()
         self._out_ring = [None] * depth
@@ -59,7 +62,8 @@ class PipelinedPredictor:
         for t in vars(dev).values():
             t.record_stream(compute)  # allocated on the copy stream, consumed on the compute stream
         with torch.no_grad():
-            y = self.model(dev, counts=(n_atoms, n_edges, max_atoms))
+            extra = {} if self.gather is None else {"gather": self.gather}
+            y = self.model(dev, counts=(n_atoms, n_edges, max_atoms), **extra)
             if self.post is not None:
                 y = self.post(y)
         slot = self._next % self.depth

@@ -9,11 +9,14 @@ a few KB per forward.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+import ctypes
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 import torch.distributed as dist
+
+from . import _lib
 
 
 def lpt_assign(sizes: Sequence[int], num_shards: int) -> List[List[int]]:
@@ -80,3 +83,112 @@ def gather_outputs(local: torch.Tensor, shards: List[List[int]], group=None) -> 
     gathered = local.new_empty((world * longest, T))
     dist.all_gather_into_tensor(gathered, padded, group=group)
     return gathered.index_select(0, index)
+
+
+def peer_descriptor(world: int, rank: int, rows_per_rank: int, step: int,
+                    cell_ptrs: Sequence[int]) -> _lib.PeerGatherDescriptor:
+    """A ``cf_peer_gather`` for one step: ``cell_ptrs[r]`` is the address, in this process, of the step's slot inside
+    rank r's gather buffer."""
+    d = _lib.PeerGatherDescriptor()
+    d.world, d.rank, d.rows_per_rank, d.step, d.reserved = world, rank, rows_per_rank, step & 0xFFFFFFFF, 0
+    for r in range(world):
+        d.cells[r] = cell_ptrs[r]
+    return d
+
+
+class PeerGather:
+    """The gather of every rank's per-crystal outputs by stores into the peers' memory (one process per GPU of one
+    machine), instead of a library all-gather: see ``cf_peer_gather`` in include/crystalformer_b200.h.
+
+        gather = PeerGather(shards, n_targets, device)            # collective: every rank of the group calls it
+        y_all = model(batch_of_this_rank, counts=..., gather=gather)   # (all crystals, n_targets), unsharded order
+
+    ``model`` stores its outputs straight from the pooling + head kernel into every rank's buffer; ``store`` does the
+    same for outputs that exist already.  Every rank must run the same sequence of gathers.  ``check()`` (a device
+    synchronisation) raises if a collect gave up waiting for a rank.
+    """
+
+    def __init__(self, shards: List[List[int]], targets: int, device, group=None, slots: int = 4,
+                 timeout_s: float = 20.0):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if len(shards) != self.world or self.world > _lib.MAX_PEERS:
+            raise ValueError(f"{len(shards)} shards for {self.world} ranks (at most {_lib.MAX_PEERS})")
+        if slots < 2:
+            raise ValueError("a peer gather needs at least two slots")
+        self.device = torch.device(device)
+        self.targets, self.slots, self.timeout_s = int(targets), int(slots), float(timeout_s)
+        self.rows_per_rank = max(len(s) for s in shards)
+        self.local_rows = len(shards[self.rank])
+        self.total_rows = sum(len(s) for s in shards)
+        self.index = _gather_index(shards, self.rows_per_rank, self.device)
+        self._slot_bytes = (self.world * self.rows_per_rank * self.targets * 8 + 255) // 256 * 256
+        own, handle = ctypes.c_void_p(), (ctypes.c_ubyte * _lib.PEER_HANDLE_BYTES)()
+        with torch.cuda.device(self.device):
+            _lib.call("cf_peer_alloc", self._slot_bytes * self.slots, ctypes.byref(own), handle)
+            self._own = own.value
+            handles: List[Optional[bytes]] = [bytes(handle)] * self.world
+            if self.world > 1:
+                dist.all_gather_object(handles, bytes(handle), group=group)
+            self._bases: List[int] = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self._bases.append(self._own)
+                else:
+                    mapped = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * _lib.PEER_HANDLE_BYTES).from_buffer_copy(handles[r])
+                    _lib.call("cf_peer_open", buf, ctypes.byref(mapped))
+                    self._bases.append(mapped.value)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.step = 0
+        if self.world > 1:
+            dist.barrier(group=group)  # every buffer is mapped everywhere before the first store
+
+    def next_descriptor(self) -> _lib.PeerGatherDescriptor:
+        """Advances to the next step and returns its descriptor (for ``cf_model_forward`` / ``store``)."""
+        self.step += 1
+        at = (self.step % self.slots) * self._slot_bytes
+        return peer_descriptor(self.world, self.rank, self.rows_per_rank, self.step, [b + at for b in self._bases])
+
+    def store(self, y: torch.Tensor) -> None:
+        """Opens the next step with outputs that exist already: (local crystals, targets) on this rank's device."""
+        y = y.detach().float().contiguous()
+        if y.shape != (self.local_rows, self.targets):
+            raise ValueError(f"expected {(self.local_rows, self.targets)} outputs, got {tuple(y.shape)}")
+        d = self.next_descriptor()
+        with torch.cuda.device(self.device):
+            _lib.call("cf_peer_gather_store", y.data_ptr(), y.shape[0], self.targets, ctypes.byref(d),
+                      torch.cuda.current_stream(self.device).cuda_stream)
+
+    def collect(self) -> torch.Tensor:
+        """Waits, on the device, for every rank's rows of the current step; returns (all crystals, targets) in the
+        order of the unsharded batch."""
+        if self.step == 0:
+            raise RuntimeError("collect() before the first store")
+        out = torch.empty((self.total_rows, self.targets), dtype=torch.float32, device=self.device)
+        at = self._own + (self.step % self.slots) * self._slot_bytes
+        with torch.cuda.device(self.device):
+            _lib.call("cf_peer_gather_collect", at, self.step & 0xFFFFFFFF, self.index.data_ptr(), self.total_rows,
+                      self.targets, self.rows_per_rank, out.data_ptr(), self.status.data_ptr(), self.timeout_s,
+                      torch.cuda.current_stream(self.device).cuda_stream)
+        return out
+
+    def check(self) -> None:
+        code = int(self.status.item())
+        if code != 0:
+            raise RuntimeError(f"peer gather: rank {self.rank} gave up waiting for the outputs of rank {code - 1}")
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' buffers, then frees the own one."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for r, base in enumerate(self._bases):
+                if r != self.rank:
+                    _lib.call("cf_peer_close", base)
+            if self.world > 1:
+                dist.barrier(group=self.group)  # nobody has the buffer mapped any more
+            _lib.call("cf_peer_free", self._own)
+        self._own, self._bases = None, []

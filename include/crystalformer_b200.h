@@ -267,6 +267,37 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
                        void *const *attn_events, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
+ * Peer gather of the per-crystal outputs of data-parallel ranks (one process per GPU of one machine), without a
+ * collective library on the data path.  The reference gathers inside one process (models/latticeformer.py:278-289).
+ * Every rank allocates a gather buffer (cf_peer_alloc), hands its 64-byte handle to the other processes (any channel,
+ * e.g. an all-gather of bytes at set-up) and maps theirs (cf_peer_open).  A buffer holds `slots` (>= 2) slots of
+ * world * rows_per_rank * targets 8-byte cells; cell ((r * rows_per_rank + c) * targets + t) carries output t of
+ * crystal c of rank r as { float bits (low word), step (high word) }, written by ONE 8-byte store, so that a reader
+ * who sees the step has the value.  Step s (1, 2, 3, ...; the same sequence on every rank) uses slot s % slots.
+ * A cf_peer_gather describes one step: cells[r] = the slot inside rank r's buffer as mapped in THIS process
+ * (r = rank: the own buffer).  The producer - cf_model_forward given the descriptor, or cf_peer_gather_store for
+ * outputs that exist already - stores this rank's rows into every rank's buffer; cf_peer_gather_collect, on the same
+ * stream afterwards, waits until the cells of the own slot carry `step` and writes out[g] = value of row index[g] for
+ * the `rows` crystals of the unsharded batch (index: int64 row numbers within the slot).  The wait is bounded: after
+ * timeout_s the kernel writes status[0] = 1 + (a rank whose rows are missing), NaN for the missing values, and returns.
+ * ---------------------------------------------------------------------------------------------------------- */
+#define CF_MAX_PEERS 16
+#define CF_PEER_HANDLE_BYTES 64
+typedef struct cf_peer_gather {
+    int32_t world, rank;
+    int64_t rows_per_rank;
+    uint32_t step, reserved;
+    uint64_t *cells[CF_MAX_PEERS];
+} cf_peer_gather;
+int cf_peer_alloc(int64_t bytes, void **ptr, unsigned char *handle);  /* zero-filled; handle: 64 bytes out */
+int cf_peer_open(const unsigned char *handle, void **ptr);            /* maps another process's buffer */
+int cf_peer_close(void *ptr);                                         /* unmaps (cf_peer_open) */
+int cf_peer_free(void *ptr);                                          /* frees (cf_peer_alloc) */
+int cf_peer_gather_store(const float *y, int64_t rows, int64_t targets, const cf_peer_gather *gather, void *stream);
+int cf_peer_gather_collect(const uint64_t *cells, uint32_t step, const int64_t *index, int64_t rows, int64_t targets,
+                           int64_t rows_per_rank, float *out, int32_t *status, double timeout_s, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
  * Inference forward of the whole model in one host call (what Latticeformer.forward does in eval mode,
  * models/latticeformer.py:211-302, with pooling "avr", pre_pooling_op "no", norm_type "no" and a head of the form
  * Linear - ReLU - Linear): y (B, targets) from the species features (N, feature_dim), positions, lattices and sizes.
@@ -278,6 +309,8 @@ int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *
  * W_embed_packed (optional, NULL to skip): W_embed with its input columns zero-padded to 128, packed like slot 10 of
  * the layer weights (feature_dim <= 128).  When it is given and every layer brings packed weights, the embedding runs
  * inside the first dense block, the whole forward runs in this library's kernels and cublas_handle may be NULL.
+ * gather (optional, NULL to skip): the pooling + head kernel also stores y into every rank's gather buffer (see
+ * cf_peer_gather above; B <= gather->rows_per_rank).
  * ---------------------------------------------------------------------------------------------------------- */
 int64_t cf_model_workspace_bytes(int64_t N, int64_t B, int64_t E, int64_t ff_dim);
 int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
@@ -286,7 +319,7 @@ int cf_model_forward(void *cublas_handle, const float *features, int64_t feature
                      const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius, int lattice_range,
                      int minimum_range, const float *W1, const float *b1, int64_t hidden, const float *W2,
                      const float *b2, int64_t targets, double order_reach, void *workspace, float *y,
-                     void *const *attn_events, void *stream);
+                     void *const *attn_events, const cf_peer_gather *gather, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Scheduling weight of every atom's row for the fused attention kernels (no counterpart in the reference, which
