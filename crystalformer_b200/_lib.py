@@ -42,6 +42,8 @@ SIGNATURES = {
     "cf_term_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
     "cf_infinite_attn_fwd_listed": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                                     I32, P, P, P, P, P, P, F64, P],
+    "cf_infinite_attn_bwd_listed": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
+                                    I32, P, P, P, P, P, P, P, P, P, P, P, F64, P],
     "cf_row_cost": [P, P, I64, I64, F64, P, P],
     "cf_row_order": [P, P, I64, I64, F64, P, P],
     "cf_reci_phase": [P, P, P, P, I64, P, P],

@@ -69,6 +69,32 @@ def edge_info(edges: Tensor, N: int) -> Tuple[Tensor, int, Tensor]:
     return _EDGE_CACHE[key]
 
 
+# Term lists (ops.term_list_build) of the batches in flight: the geometry is the same for every layer of a forward and
+# for its backward, so the (key, translation) pairs that can matter are found once per batch and cut-off configuration.
+_TERM_LIST_CACHE: "OrderedDict[tuple, tuple]" = OrderedDict()
+
+
+def term_lists_for(edges: Tensor, pos_ij: Tensor, tvecs: Tensor, rvlen: Optional[Tensor], batch: Tensor,
+                   row_start: Tensor, max_atoms: int, row_order: Optional[Tensor], cutoff: float, lattice_range: int,
+                   minimum_range: int, a_widest: float):
+    """The batch's term lists for Gaussian parameters a <= a_widest < 0, built on first use and shared by the layers
+    of the batch; None when the kernels would not use them (weight floor switched off)."""
+    floor = ops.get_weight_floor_log2()
+    if not (a_widest < 0.0) or floor <= -200.0 or max_atoms > 1024:
+        return None
+    key = (edges.data_ptr(), tuple(edges.shape), edges.device, edges._version, pos_ij.data_ptr(), pos_ij._version,
+           tvecs.data_ptr(), tvecs._version, float(cutoff), int(lattice_range), int(minimum_range), float(a_widest), floor)
+    hit = _TERM_LIST_CACHE.get(key)
+    if hit is None:
+        hit = ops.term_list_build(pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, cutoff, lattice_range,
+                                  minimum_range, a_widest, row_order=row_order)
+        # (the cache keeps the geometry tensors alive, so that their addresses cannot be reused while the entry lives)
+        _TERM_LIST_CACHE[key] = hit + (edges, pos_ij, tvecs)
+        while len(_TERM_LIST_CACHE) > 2:
+            _TERM_LIST_CACHE.popitem(last=False)
+    return hit[0], hit[1]
+
+
 class InfiniteAttentionFunction(torch.autograd.Function):
     """out_i = sum_j softmax_j(q_i.k_j + phi_ij) (v_j + W psi_ij), phi/psi recomputed in forward and backward.
 
@@ -77,7 +103,7 @@ class InfiniteAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, a, W, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale,
-                cutoff, lattice_range, minimum_range, row_order=None):
+                cutoff, lattice_range, minimum_range, row_order=None, term_lists=None):
         q, k, v, a = (t.contiguous().detach() for t in (q, k, v, a))
         W3 = None
         if K > 0:
@@ -85,9 +111,10 @@ class InfiniteAttentionFunction(torch.autograd.Function):
         need_grad = any(ctx.needs_input_grad[:5])
         out, logit, lse, psi_row = ops.infinite_attn_fwd(
             q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W3, cutoff,
-            lattice_range, minimum_range, want_psi_row=need_grad and K > 0, row_order=row_order)
+            lattice_range, minimum_range, want_psi_row=need_grad and K > 0, row_order=row_order, term_lists=term_lists)
         if need_grad:
             ctx.row_order = row_order
+            ctx.term_lists = term_lists
             ctx.save_for_backward(q, k, v, a, W3, pos_ij, tvecs, rvlen, batch, edges, row_start, logit, lse, out, psi_row)
             ctx.cfg = (max_atoms, K, dist_max, wscale, cutoff, lattice_range, minimum_range)
             ctx.w_shape = None if W is None else tuple(W.shape)
@@ -100,11 +127,11 @@ class InfiniteAttentionFunction(torch.autograd.Function):
         gout = gout.contiguous()
         gq, gk, gv, ga = ops.infinite_attn_bwd(
             q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W3, cutoff,
-            lattice_range, minimum_range, logit, lse, out, gout, row_order=ctx.row_order)
+            lattice_range, minimum_range, logit, lse, out, gout, row_order=ctx.row_order, term_lists=ctx.term_lists)
         gW = None
         if K > 0 and ctx.needs_input_grad[4]:
             gW = torch.einsum("nhd,nhk->hdk", gout, psi_row).reshape(ctx.w_shape)
-        return (gq, gk, gv, ga, gW) + (None,) * 14
+        return (gq, gk, gv, ga, gW) + (None,) * 15
 
 
 def positive_function(name: str):
@@ -143,6 +170,7 @@ class CrystalformerMultiheadAttentionCUDA(Module):
             raise NotImplementedError("value_pe_wave_real / value_pe_wave_reci > 0 is not supported")
         self.params = params
         self.fused = fused
+        self.term_lists = True  # fused operator: find the translations that matter once per batch (ops.term_list_build)
         self.gauss_scale = Parameter(torch.zeros(2, **factory_kwargs), requires_grad=False)
         self.atten_scale = Parameter(torch.zeros(1, **factory_kwargs), requires_grad=False)
         self.num_heads = num_heads
@@ -310,9 +338,15 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         values = None
         if self.fused and not need_weights and P.domain == "real":
             row_start, max_atoms, row_order = edge_info(edges, N)
+            # every positive function is bounded below by gauss_lb_real, so a <= gauss_lb_real x (-0.5 / scale_real^2)
+            lists = None
+            if getattr(self, "term_lists", True) and points is not None and P.gauss_lb_real > 0 \
+                    and not isinstance(P.scale_real, (list, tuple)):
+                lists = term_lists_for(edges, points, tvecs, rvlen, batch_q, row_start, max_atoms, row_order, cutoff,
+                                       lattice_range, minimum_range, -0.5 * P.gauss_lb_real / float(P.scale_real) ** 2)
             attn = InfiniteAttentionFunction.apply(
                 q_scaled, k, v, a, self.pe_dist_proj, points, tvecs, rvlen, batch_q, edges, row_start, max_atoms, K,
-                float(dist_max), float(P.value_pe_width_scale), cutoff, lattice_range, minimum_range, row_order)
+                float(dist_max), float(P.value_pe_width_scale), cutoff, lattice_range, minimum_range, row_order, lists)
             weights = None
         else:
             # the reference's operator split, through the drop-in autograd functions

@@ -16,6 +16,7 @@
 //   infinite_attn_bwd_cols_kernel  warp per (key j, head): gk_j, gv_j from glogit and p_ij = exp(logit - lse_i), reading
 //                                  the crystal's n x n block in column order by index arithmetic.
 #include "lattice_bwd_core.cuh"
+#include "term_list.cuh"
 
 namespace cf {
 namespace {
@@ -33,6 +34,7 @@ struct BwdRowArgs {
     int max_atoms;
     BoxRule rule;
     BasisParams basis;
+    TermList list;  // optional (pool == NULL: none): the rows' terms, found once per batch (term_list.cuh)
 };
 
 __host__ __device__ inline size_t bwd_row_smem_floats(int max_atoms, bool with_basis)
@@ -143,47 +145,26 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_bwd_rows_kernel(const B
             a2[h] = __shfl_sync(FULL, a_own, h) * LOG2E;
             pk[h] = __shfl_sync(FULL, pk_own, h);
         }
-        const int R1 = box_r1(uni), R2 = box_r2(uni), R3 = box_r3(uni);
-        const unsigned per_key = (unsigned)((2 * R1 + 1) * (2 * R2 + 1) * (2 * R3 + 1));
-        const int keys_per_warp = (n + WARPS - 1) / WARPS;
-        const int j_begin = min(warp * keys_per_warp, n), j_end = min(j_begin + keys_per_warp, n);
-        const unsigned begin = (unsigned)j_begin * per_key, end = (unsigned)j_end * per_key;
-        Cell cell;
-        cell.load(p.tvecs + 9 * c);
-        const float F1 = (float)R1, F2 = (float)R2, F3 = (float)R3;
-        TermWalker walk;
-        walk.init(R1, R2, R3, begin + lane);
         float G[8];
 #pragma unroll
         for (int h = 0; h < 8; ++h) G[h] = 0.f;
         // lanes 0..7 carry the running per-key sum of head (lane) while walking the staged entries in order
         float run = 0.f;
         int run_key = -1;
-        for (unsigned base = begin; base < end; base += 32) {
-            const bool valid = base + lane < end;
-            const int j = valid ? walk.row : j_begin;
-            const float4 r = rel[j];
+        // one term per lane: the eight joint weights, their part of ga, and (K > 0) the contraction of the basis with u
+        auto term = [&](bool valid, int j, float d2, int key) {
             const float4 ca = *reinterpret_cast<const float4 *>(cj + j * 8);
             const float4 cb = *reinterpret_cast<const float4 *>(cj + j * 8 + 4);
             const float4 ga4 = *reinterpret_cast<const float4 *>(gov + j * 8);
             const float4 gb4 = *reinterpret_cast<const float4 *>(gov + j * 8 + 4);
             const float off[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
             const float gj[8] = {ga4.x, ga4.y, ga4.z, ga4.w, gb4.x, gb4.y, gb4.z, gb4.w};
-            const float f1 = walk.u1 - F1, f2 = walk.u2 - F2, f3 = walk.u3 - F3;
-            const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
-            const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
-            const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
-            const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
-            int i1 = 0, i2 = 0, i3 = 0;
-            if (masked) {
-                i1 = abs(__float2int_rn(f1)); i2 = abs(__float2int_rn(f2)); i3 = abs(__float2int_rn(f3));
-            }
             float w[8];
             float emax = -INFINITY;
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
                 float eh = fmaf(a2[h], d2, off[h]);
-                if (!valid || (masked && !(i1 <= box_r1(pk[h]) && i2 <= box_r2(pk[h]) && i3 <= box_r3(pk[h])))) eh = -INFINITY;
+                if (!valid || (masked && !key_in_box(key, pk[h]))) eh = -INFINITY;
                 w[h] = ex2(eh);
                 emax = fmaxf(emax, eh);
                 G[h] = fmaf(w[h] * d2, gj[h], G[h]);
@@ -198,7 +179,8 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_bwd_rows_kernel(const B
                         const float4 hd = row[0], pa = row[1], pb = row[2];
                         const float pw[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
                         float cd[8];
-                        basis_dot<(K > 0 ? K : 4)>(u, hd.x, p.basis.bin_step, cd);
+                        if (K == 64 && p.basis.windowed) basis_dot_window(u, hd.x, p.basis.bin_step, cd);
+                        else basis_dot<(K > 0 ? K : 4)>(u, hd.x, p.basis.bin_step, cd);
                         float pc[8];
 #pragma unroll
                         for (int h = 0; h < 8; ++h) {
@@ -211,11 +193,11 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_bwd_rows_kernel(const B
                     __syncwarp();
                     if (lane < 8) {  // ordered walk: entries are sorted by key
                         for (int m = 0; m < cnt; ++m) {
-                            const int key = __float_as_int(stage[BWD_ENTRY_FLOATS * m + 2]);
-                            if (key != run_key) {
+                            const int key_m = __float_as_int(stage[BWD_ENTRY_FLOATS * m + 2]);
+                            if (key_m != run_key) {
                                 if (run_key >= 0) s0[run_key * 8 + lane] = run;
                                 run = 0.f;
-                                run_key = key;
+                                run_key = key_m;
                             }
                             run += res[8 * m + lane];
                         }
@@ -223,7 +205,59 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_bwd_rows_kernel(const B
                 }
                 __syncwarp();
             }
-            walk.step();
+        };
+        const int list_first = (p.list.pool != nullptr && n > 0) ? p.list.start[e0] : -1;
+        if (list_first >= 0) {
+            // ---- terms from the row's list (entries contiguous, keys ascending).  A warp takes whole keys, so that
+            //      every per-key sum has one owner: warp w gets the keys whose first entry lies in its equal share
+            const int list_end = p.list.start[e0 + n - 1] + p.list.count[e0 + n - 1];
+            const int span = list_end - list_first, share = (span + WARPS - 1) / WARPS;
+            auto keys_before = [&](int target) {  // number of keys whose entries start before `target` (warp-uniform)
+                int cnt = 0;
+                for (int j0 = 0; j0 < n; j0 += 32) {
+                    const int j = j0 + lane;
+                    const bool before = j < n && p.list.start[e0 + j] - list_first < target;
+                    cnt += __popc(__ballot_sync(FULL, before));
+                }
+                return cnt;
+            };
+            const int k_lo = warp == 0 ? 0 : keys_before(warp * share);
+            const int k_hi = warp == WARPS - 1 ? n : keys_before((warp + 1) * share);
+            const int w_lo = k_lo < n ? p.list.start[e0 + k_lo] : list_end;
+            const int w_hi = k_hi < n ? p.list.start[e0 + k_hi] : list_end;
+            for (int at = w_lo; at < w_hi; at += 32) {
+                const bool live = at + lane < w_hi;
+                float2 en = make_float2(0.f, 0.f);
+                if (live) en = __ldg(p.list.pool + at + lane);
+                const int key = __float_as_int(en.y);
+                // (the lists are built for a box that contains every head's: terms outside this row's boxes drop out here)
+                term(live && key_in_box(key, uni), live ? (key & 2047) : k_lo, en.x, key);
+            }
+        } else {
+            const int R1 = box_r1(uni), R2 = box_r2(uni), R3 = box_r3(uni);
+            const unsigned per_key = (unsigned)((2 * R1 + 1) * (2 * R2 + 1) * (2 * R3 + 1));
+            const int keys_per_warp = (n + WARPS - 1) / WARPS;
+            const int j_begin = min(warp * keys_per_warp, n), j_end = min(j_begin + keys_per_warp, n);
+            const unsigned begin = (unsigned)j_begin * per_key, end = (unsigned)j_end * per_key;
+            Cell cell;
+            cell.load(p.tvecs + 9 * c);
+            const float F1 = (float)R1, F2 = (float)R2, F3 = (float)R3;
+            TermWalker walk;
+            walk.init(R1, R2, R3, begin + lane);
+            for (unsigned base = begin; base < end; base += 32) {
+                const bool valid = base + lane < end;
+                const int j = valid ? walk.row : j_begin;
+                const float4 r = rel[j];
+                const float f1 = walk.u1 - F1, f2 = walk.u2 - F2, f3 = walk.u3 - F3;
+                const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
+                const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
+                const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
+                const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                int key = 0;
+                if (masked) key = pack_key(0, abs(__float2int_rn(f1)), abs(__float2int_rn(f2)), abs(__float2int_rn(f3)));
+                term(valid, j, d2, key);
+                walk.step();
+            }
         }
         if (K > 0 && lane < 8 && run_key >= 0) s0[run_key * 8 + lane] = run;
 #pragma unroll
@@ -279,6 +313,15 @@ __global__ void __launch_bounds__(256) infinite_attn_bwd_cols_kernel(const BwdRo
 }
 
 }  // namespace
+
+int infinite_attn_bwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                           const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                           const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D,
+                           int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
+                           double cutoff_radius, int lattice_range, int minimum_range, const float *logit,
+                           const float *lse, const float *out, const float *gout, float *gq, float *gk, float *gv,
+                           float *ga, float *glogit, const int32_t *row_order, const TermList *list, void *stream);
+
 }  // namespace cf
 
 extern "C" int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
@@ -290,7 +333,47 @@ extern "C" int cf_infinite_attn_bwd(const float *q, const float *k, const float 
                                     float *gk, float *gv, float *ga, float *glogit, const int32_t *row_order,
                                     void *stream)
 {
+    return cf::infinite_attn_bwd_impl(q, k, v, a, pos, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
+                                      max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, logit,
+                                      lse, out, gout, gq, gk, gv, ga, glogit, row_order, nullptr, stream);
+}
+
+extern "C" int cf_infinite_attn_bwd_listed(const float *q, const float *k, const float *v, const float *a,
+                                           const float *pos_ij, const float *tvecs, const float *rvlen,
+                                           const int64_t *batch, const int64_t *edges, const int64_t *row_start,
+                                           int64_t N, int64_t B, int64_t H, int64_t D, int64_t E, int64_t K,
+                                           int64_t max_atoms, double dist_max, double wscale, const float *W,
+                                           double cutoff_radius, int lattice_range, int minimum_range,
+                                           const float *logit, const float *lse, const float *out, const float *gout,
+                                           float *gq, float *gk, float *gv, float *ga, float *glogit,
+                                           const int32_t *row_order, void *term_lists, double a_widest, void *stream)
+{
     using namespace cf;
+    CF_REQUIRE(term_lists != nullptr && pos_ij != nullptr && a_widest < 0, CF_ERR_INVALID,
+               "cf_infinite_attn_bwd_listed: needs term lists, pos_ij and a negative a_widest");
+    CF_REQUIRE(N >= 0 && E >= 0, CF_ERR_INVALID, "cf_infinite_attn_bwd_listed: negative size");
+    TermList list{};
+    int *start, *count;
+    float *dmin;
+    unsigned long long *cursor;
+    float2 *pool;
+    term_list_carve(term_lists, N, E, &start, &count, &dmin, &cursor, &pool);
+    list.pool = pool; list.start = start; list.count = count; list.dmin = dmin;
+    list.window = term_window(weight_floor_log2(), (float)a_widest);
+    return infinite_attn_bwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
+                                  max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, logit, lse,
+                                  out, gout, gq, gk, gv, ga, glogit, row_order, &list, stream);
+}
+
+int cf::infinite_attn_bwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
+                               const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                               const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H,
+                               int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
+                               const float *W, double cutoff_radius, int lattice_range, int minimum_range,
+                               const float *logit, const float *lse, const float *out, const float *gout, float *gq,
+                               float *gk, float *gv, float *ga, float *glogit, const int32_t *row_order,
+                               const TermList *list, void *stream)
+{
     CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_bwd: negative size");
     CF_REQUIRE(H == HEADS && D == HEAD_DIM, CF_ERR_UNSUPPORTED, "cf_infinite_attn_bwd: H=%lld D=%lld, only H=8 D=16 is compiled",
                (long long)H, (long long)D);
@@ -311,6 +394,7 @@ extern "C" int cf_infinite_attn_bwd(const float *q, const float *k, const float 
     p.gq = gq; p.gk = gk; p.gv = gv; p.ga = ga; p.glogit = glogit; p.row_order = row_order; p.N = N; p.E = E; p.max_atoms = (int)max_atoms;
     p.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
+    if (list != nullptr) p.list = *list;
     const size_t smem = sizeof(float) * bwd_row_smem_floats((int)max_atoms, K > 0);
     auto kernel = K > 0 ? infinite_attn_bwd_rows_kernel<64> : infinite_attn_bwd_rows_kernel<0>;
     if (smem > 48 * 1024) {

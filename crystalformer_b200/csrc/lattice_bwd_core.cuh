@@ -38,6 +38,33 @@ __device__ __forceinline__ void basis_dot(const float *__restrict__ u, float x, 
     }
 }
 
+// The same for a basis of one bin width (BasisParams::windowed): a value more than 8 bins from the term's centre
+// xi = x / step - 1 is below 2^-40, so only the 20 bins k0 .. k0 + 19 are evaluated, k0 the multiple of 4 with
+// k0 <= floor(xi) - 8 < k0 + 4 (clamped to the table).  The rows of u are then read at lane-dependent offsets.
+__device__ __forceinline__ void basis_dot_window(const float *__restrict__ u, float x, float bin_step, float (&c)[8])
+{
+#pragma unroll
+    for (int h = 0; h < 8; ++h) c[h] = 0.f;
+    int k0 = (__float2int_rd(__fdividef(x, bin_step)) - 9) & ~3;
+    k0 = max(0, min(k0, 44));
+    float t = (float)(k0 + 1) * bin_step - x;
+    const float *uw = u + k0;
+#pragma unroll
+    for (int k = 0; k < 20; k += 4) {
+        const float t1 = t + bin_step, t2 = t1 + bin_step, t3 = t2 + bin_step;
+        const float g0 = ex2(-t * t), g1 = ex2(-t1 * t1), g2 = ex2(-t2 * t2), g3 = ex2(-t3 * t3);
+        t = t3 + bin_step;
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+            const float4 uv = *reinterpret_cast<const float4 *>(uw + h * U_STRIDE + k);
+            c[h] = fmaf(uv.x, g0, c[h]);
+            c[h] = fmaf(uv.y, g1, c[h]);
+            c[h] = fmaf(uv.z, g2, c[h]);
+            c[h] = fmaf(uv.w, g3, c[h]);
+        }
+    }
+}
+
 // Compacts the lanes' surviving terms into the warp's staging area; returns how many were staged.
 __device__ __forceinline__ int stage_terms(float *stage, int lane, bool keep, float x, float d2, int key,
                                            const float (&p)[8])

@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(THREADS) lattice_bwd_edges_kernel(const BwdArg
                             const float4 hd = row[0], pa = row[1], pb = row[2];
                             const float pw[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
                             float cd[8];
-                            basis_dot<(K > 0 ? K : 4)>(u, hd.x, p.basis.bin_step, cd);
+                            if (K == 64 && p.basis.windowed) basis_dot_window(u, hd.x, p.basis.bin_step, cd);
+                            else basis_dot<(K > 0 ? K : 4)>(u, hd.x, p.basis.bin_step, cd);
 #pragma unroll
                             for (int h = 0; h < 8; ++h) {
                                 const float pc = pw[h] * cd[h];

@@ -265,8 +265,10 @@ def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
 
 
 def infinite_attn_bwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W,
-                      cutoff_radius, lattice_range, minimum_range, logit, lse, out, gout, pos=None, row_order=None):
-    """Backward of infinite_attn_fwd: (gq, gk, gv, ga).  gq is with respect to the pre-scaled q."""
+                      cutoff_radius, lattice_range, minimum_range, logit, lse, out, gout, pos=None, row_order=None,
+                      term_lists=None):
+    """Backward of infinite_attn_fwd: (gq, gk, gv, ga).  gq is with respect to the pre-scaled q.  ``term_lists``: the
+    lists the forward was given (needs pos_ij)."""
     dev = q.device
     q, k, v, a, tvecs, logit, lse, out, gout = (_want(t, torch.float32, n, dev) for t, n in (
         (q, "q"), (k, "k"), (v, "v"), (a, "a"), (tvecs, "tvecs"), (logit, "logit"), (lse, "lse"), (out, "out"),
@@ -280,6 +282,16 @@ def infinite_attn_bwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
     gq, gk, gv = (torch.empty_like(q) for _ in range(3))
     ga = torch.empty((N, H), dtype=torch.float32, device=dev)
     glogit = torch.empty((E, H), dtype=torch.float32, device=dev)
+    if term_lists is not None:
+        work, a_widest = term_lists
+        with torch.cuda.device(dev):
+            _lib.call("cf_infinite_attn_bwd_listed", _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(pos_ij), _ptr(tvecs),
+                      _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),
+                      c_int64(D), c_int64(E), c_int64(K), c_int64(max_atoms), c_double(dist_max), c_double(wscale),
+                      _ptr(W), c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(logit),
+                      _ptr(lse), _ptr(out), _ptr(gout), _ptr(gq), _ptr(gk), _ptr(gv), _ptr(ga), _ptr(glogit),
+                      _ptr(_want(row_order, torch.int32, "row_order", dev)), _ptr(work), c_double(a_widest), _stream(dev))
+        return gq, gk, gv, ga
     with torch.cuda.device(dev):
         _lib.call("cf_infinite_attn_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(pos), _ptr(pos_ij), _ptr(tvecs),
                   _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H),

@@ -218,6 +218,9 @@ int cf_infinite_attn_bwd(const float *q, const float *k, const float *v, const f
  * row kernel's candidates from a row's entries) instead of enumerating; rows that did not fit the workspace are
  * enumerated as before, so the result never depends on the capacity.  workspace: cf_term_list_workspace_bytes(N, E)
  * bytes, 16-byte aligned; built with the weight floor in force at the time (cf_set_weight_floor_log2).
+ * cf_infinite_attn_bwd_listed is cf_infinite_attn_bwd with its sums over translations running over the same lists
+ * (the terms the listed forward summed), for a training step that builds the lists once and uses them in the forward
+ * and backward of every layer.
  * ---------------------------------------------------------------------------------------------------------- */
 int64_t cf_term_list_workspace_bytes(int64_t N, int64_t E);
 int cf_term_list_build(const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
@@ -231,6 +234,14 @@ int cf_infinite_attn_fwd_listed(const float *q, const float *k, const float *v, 
                                 double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
                                 float *lse, float *psi_row, const int32_t *row_order, void *term_lists,
                                 double a_widest, void *stream);
+int cf_infinite_attn_bwd_listed(const float *q, const float *k, const float *v, const float *a, const float *pos_ij,
+                                const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
+                                const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D, int64_t E,
+                                int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
+                                double cutoff_radius, int lattice_range, int minimum_range, const float *logit,
+                                const float *lse, const float *out, const float *gout, float *gq, float *gk, float *gv,
+                                float *ga, float *glogit, const int32_t *row_order, void *term_lists, double a_widest,
+                                void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Inference forward of the encoder stack (every layer of CrystalformerEncoderCUDA,

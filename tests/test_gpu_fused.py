@@ -131,6 +131,19 @@ def test_term_lists_give_the_enumerated_result(ops, cutoff, minimum, nmax, Kbins
                                      precision=precision)
     _, ref = oracle.fused_attn_fwd(q, k, v, z, psiW, edges, precision=precision)
     assert rel_err(listed[0].cpu().numpy(), ref) < TOL
+    # backward over the same lists: against the enumerating backward (both from the enumerated forward's logits, so
+    # that only the backward differs) and bitwise repeatable; a warp owns whole keys, whatever the list sizes
+    go = dev(rng.standard_normal((N, H, D)).astype(np.float32))
+    ops.set_weight_floor_log2(floor)
+    try:
+        g_plain = ops.infinite_attn_bwd(*args, plain[1], plain[2], plain[0], go)
+        g_listed = ops.infinite_attn_bwd(*args, plain[1], plain[2], plain[0], go, term_lists=lists)
+        g_again = ops.infinite_attn_bwd(*args, plain[1], plain[2], plain[0], go, term_lists=lists)
+    finally:
+        ops.set_weight_floor_log2(-30.0)
+    for got, want, twice in zip(g_listed, g_plain, g_again):
+        assert torch.equal(got, twice)
+        assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 5e-6
 
 
 def test_fused_forward_flags_understated_max_atoms(ops):
