@@ -258,7 +258,9 @@ __global__ void __launch_bounds__(128) phi_from_list_kernel(const PhiListArgs p)
 
 }  // namespace
 
-size_t term_pool_entries(long long N, long long E) { return (size_t)(8 * E + 64 * N + (1ll << 20)); }
+// About 25 entries per edge are needed for cells of 3-15 Angstrom edges at the default widths (sphere of the window
+// over the cell volume), 3 for cells of 10-25 Angstrom; rows that do not fit are enumerated instead.
+size_t term_pool_entries(long long N, long long E) { return (size_t)(32 * E + 64 * N + (1ll << 20)); }
 
 size_t term_list_workspace_bytes(long long N, long long E)
 {
