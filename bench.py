@@ -357,7 +357,9 @@ def ops_sm_count(device):
 
 def run_kernel_case(args):
     """--only microbench : the lattice-sum kernels on --pairs pairs (3 warm-up + 10 timed launches).
-    --only attention  : the fused attention forward on the workload's crystals (3 warm-up + 10 timed calls)."""
+    --only attention  : the fused attention forward on the workload's crystals (3 warm-up + 10 timed calls).
+    --only train      : one training step (forward + backward, L1 loss against N(0,1) targets, autograd path) of the
+                        4-layer K=64 model on the 256-crystal training batch (1-40 atoms), 5 warm-up + 20 timed steps."""
     import torch
     from crystalformer_b200 import ops
     device = torch.device("cuda", 0)
@@ -366,6 +368,8 @@ def run_kernel_case(args):
         return lattice_microbench(ops, device, None, pairs=args.pairs)
     from crystalformer_b200.encoder import BatchGeometry
     from crystalformer_b200.synthetic import make_config
+    if args.only == "train":
+        return train_step_case(ops, device, args)
     wl = WORKLOADS[args.workload]
     cb = make_config(wl["config"], num_crystals=args.crystals or wl["crystals"])
     d = lambda x: torch.as_tensor(np.ascontiguousarray(x)).to(device)
@@ -432,6 +436,65 @@ def run_kernel_case(args):
             "device_ms_per_call_graph": graph_ms(run), "device_ms_phi_graph": graph_ms(phi_only),
             "device_ms_per_call_listed_graph": graph_ms(run_listed), "device_ms_list_build_graph": graph_ms(build),
             "listed_vs_enumerated_rel_diff": diff}
+
+
+def train_step_case(ops, device, args):
+    """Device time of a training step and of the fused attention operators inside it (forward and backward)."""
+    import torch
+    from crystalformer_b200.synthetic import make_config
+    cb = make_config("cfg3", num_crystals=args.crystals)
+    model, _ = make_model(4, 64)
+    model = model.to(device)
+    batch = to_device_batch(cb, device)
+    fix_gauss_scale(model, batch)
+    model.train()
+    counts = (cb.num_atoms, cb.num_edges, int(cb.sizes.max()))
+    target = torch.randn((cb.num_crystals, 1), device=device, generator=torch.Generator(device=device).manual_seed(3))
+    events = {"fwd": [], "bwd": []}
+    on = {"v": False}
+
+    def wrap(fn, key):
+        def inner(*a, **k):
+            if not on["v"]:
+                return fn(*a, **k)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); r = fn(*a, **k); e.record()
+            events[key].append((s, e))
+            return r
+        return inner
+
+    raw = ops.infinite_attn_fwd, ops.infinite_attn_bwd
+    ops.infinite_attn_fwd, ops.infinite_attn_bwd = wrap(raw[0], "fwd"), wrap(raw[1], "bwd")
+
+    def step():
+        model.zero_grad(set_to_none=True)
+        loss = (model(batch, counts=counts) - target).abs().mean()
+        loss.backward()
+        return loss
+
+    try:
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+        on["v"] = True
+        reps = 20
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        s.record()
+        for _ in range(reps):
+            loss = step()
+        e.record()
+        host = time.perf_counter() - t0
+        torch.cuda.synchronize()
+    finally:
+        ops.infinite_attn_fwd, ops.infinite_attn_bwd = raw
+    ms = s.elapsed_time(e) / reps
+    per = {k: sum(a.elapsed_time(b) for a, b in v) / max(len(v), 1) for k, v in events.items()}
+    return {"case": "train", "workload": "cfg3", "crystals": cb.num_crystals, "atoms": cb.num_atoms, "edges": cb.num_edges,
+            "ms_per_step": ms, "crystals_per_s": cb.num_crystals / (ms * 1e-3), "host_issue_ms_per_step": host * 1e3 / reps,
+            "attention_fwd_ms_per_call": per["fwd"], "attention_bwd_ms_per_call": per["bwd"],
+            "attention_calls_per_step": len(events["fwd"]) // reps, "loss": float(loss.item()),
+            "note": "term lists built once per step inside the first forward call; the rest of the step is torch autograd"}
 
 
 def lattice_microbench(ops, device, peaks, pairs=250000):
@@ -564,7 +627,7 @@ def main():
     ap.add_argument("--workload", default="cfg0", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--reference-sample", type=int, default=24, help="crystals per step of the reference arm")
-    ap.add_argument("--only", default=None, choices=["microbench", "attention"],
+    ap.add_argument("--only", default=None, choices=["microbench", "attention", "train"],
                     help="run one kernel case a few times and exit (small, fixed work: meant for profiler captures)")
     ap.add_argument("--pairs", type=int, default=250000, help="(i,j) pairs of the lattice-sum microbenchmark")
     ap.add_argument("--crystals", type=int, default=None, help="crystals of the --only attention case")
