@@ -225,10 +225,12 @@ __global__ void __launch_bounds__(THREADS) infinite_attn_bwd_rows_kernel(const B
             const int k_hi = warp == WARPS - 1 ? n : keys_before((warp + 1) * share);
             const int w_lo = k_lo < n ? p.list.start[e0 + k_lo] : list_end;
             const int w_hi = k_hi < n ? p.list.start[e0 + k_hi] : list_end;
+            float2 ahead = make_float2(0.f, 0.f);  // the entries of the next step, requested one step early
+            if (w_lo + lane < w_hi) ahead = __ldg(p.list.pool + w_lo + lane);
             for (int at = w_lo; at < w_hi; at += 32) {
                 const bool live = at + lane < w_hi;
-                float2 en = make_float2(0.f, 0.f);
-                if (live) en = __ldg(p.list.pool + at + lane);
+                const float2 en = ahead;
+                if (at + 32 + lane < w_hi) ahead = __ldg(p.list.pool + at + 32 + lane);
                 const int key = __float_as_int(en.y);
                 // (the lists are built for a box that contains every head's: terms outside this row's boxes drop out here)
                 term(live && key_in_box(key, uni), live ? (key & 2047) : k_lo, en.x, key);

@@ -365,10 +365,13 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                 const int list_end = p.list.start[e0 + n - 1] + p.list.count[e0 + n - 1];
                 const int span = list_end - list_first, share = (span + ROW_WARPS - 1) / ROW_WARPS;
                 const int w_lo = list_first + min(wr * share, span), w_hi = list_first + min((wr + 1) * share, span);
+                // (the entries of the next step are requested before this step's are processed)
+                float2 ahead = make_float2(0.f, 0.f);
+                if (w_lo + lane < w_hi) ahead = __ldg(p.list.pool + w_lo + lane);
                 for (int at = w_lo; at < w_hi; at += 32) {
                     const bool live = at + lane < w_hi;
-                    float2 en = make_float2(0.f, 0.f);
-                    if (live) en = __ldg(p.list.pool + at + lane);
+                    const float2 en = ahead;
+                    if (at + 32 + lane < w_hi) ahead = __ldg(p.list.pool + at + 32 + lane);
                     const int key = __float_as_int(en.y);
                     const int j = key & 2047;
                     // (the lists are built for a box that contains every head's: terms outside this row's boxes drop out here)

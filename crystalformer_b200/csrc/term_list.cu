@@ -225,8 +225,14 @@ __global__ void __launch_bounds__(128) phi_from_list_kernel(const PhiListArgs p)
     const float m = first >= 0 ? p.list.dmin[e] : 0.f;
     const float2 *ent = p.list.pool + (first >= 0 ? first : 0);
     float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    // entries are requested two steps ahead of their use: the lists stream from memory, and a step is short
+    float2 n0 = make_float2(0.f, 0.f), n1 = n0;
+    if (sub < cnt) n0 = __ldg(ent + sub);
+    if (sub + TPE < cnt) n1 = __ldg(ent + sub + TPE);
     for (int t = sub; t < cnt; t += TPE) {
-        const float2 en = __ldg(ent + t);
+        const float2 en = n0;
+        n0 = n1;
+        if (t + 2 * TPE < cnt) n1 = __ldg(ent + t + 2 * TPE);
         const float rel = en.x - m;
         if (a2max * rel < p.floor_log2) continue;  // below the floor for every head
         const int key = __float_as_int(en.y);
