@@ -315,8 +315,9 @@ def run_b200(args):
             "terms_per_launch": terms_per_call, "launches": op_calls, "avg_launch_us": t_call * 1e6,
             "share_of_step": op_ms / ms_total,
             # dram__bytes_read.sum + dram__bytes_write.sum per fused-attention call from the ncu capture of this workload
-            # (phi 0.95 MB + rows 5.40 MB at cfg0); not re-measured per run, and only known for cfg0
-            "traffic": 6.35e6 if args.workload == "cfg0" else None, "traffic_unit": "bytes per call (ncu, cfg0)",
+            # (phi from lists 8.33 MB + rows 13.09 MB at cfg0, caches cold under ncu: the 8 MB of term lists are streamed
+            # from DRAM by each kernel); not re-measured per run, and only known for cfg0
+            "traffic": 21.4e6 if args.workload == "cfg0" else None, "traffic_unit": "bytes per call (ncu, cfg0, cold caches)",
             "note": "work counted for EVERY (edge, translation) term; terms whose weights fall below 2^-30 are skipped "
                     "by the kernel, so frac may exceed the executed-instruction utilisation",
         }
