@@ -33,7 +33,9 @@ int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const
                            const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D,
                            int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
                            double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
-                           float *lse, float *psi_row, const int32_t *row_order, const TermList *list, void *stream);
+                           float *lse, float *psi_row, const int32_t *row_order, const TermList *list,
+                           unsigned *ticket_ready, void *stream);
+unsigned *row_ticket_block(int count);
 namespace {
 
 // A second stream and two events per (host thread, device), created on first use and kept for the life of the
@@ -183,6 +185,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
     TermList lists{};
     const TermList *list = nullptr;
     bool forked = false;  // the build runs on the side stream; the first attention waits for it
+    unsigned *tickets = nullptr;
     if (pos_ij != nullptr && weight_floor_log2() > -200.0f) {
         float a_widest = -INFINITY;
         for (int l = 0; l < num_layers; ++l) a_widest = fmaxf(a_widest, (float)(scalars[6 * l + 4] * scalars[6 * l + 2]));
@@ -199,6 +202,10 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
             SideStream &side = side_stream();
             forked = side.ok && cudaEventRecord(side.fork, s) == cudaSuccess &&
                      cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
+            // the row tickets of all layers, zeroed once here instead of by a phi launch per layer
+            if (K > 0 && num_layers <= 16 && (tickets = row_ticket_block(num_layers)) != nullptr &&
+                cudaMemsetAsync(tickets, 0, sizeof(unsigned) * num_layers, forked ? side.stream : s) != cudaSuccess)
+                tickets = nullptr;
             rc = launch_term_list_build(tb, forked ? side.stream : s);
             if (forked && cudaEventRecord(side.join, side.stream) != cudaSuccess) rc = launch_status("term list join");
             if (rc != CF_OK) return rc;
@@ -233,7 +240,8 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
             if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
             rc = infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS,
                                         HEAD_DIM, E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range,
-                                        minimum_range, attn, logit, lse, nullptr, row_order, list, s);
+                                        minimum_range, attn, logit, lse, nullptr, row_order, list,
+                                        tickets ? tickets + l : nullptr, s);
             if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
             if (rc != CF_OK) break;
             DenseArgs t{};
@@ -269,7 +277,8 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
         rc = infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS,
                                     HEAD_DIM, E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range,
-                                    minimum_range, attn, logit, lse, nullptr, row_order, list, s);
+                                    minimum_range, attn, logit, lse, nullptr, row_order, list,
+                                        tickets ? tickets + l : nullptr, s);
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
         if (rc != CF_OK) break;
         st = linear(bl, handle, attn, w[4], x, rows, 128, 128, 1.0f);

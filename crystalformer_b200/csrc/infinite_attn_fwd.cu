@@ -23,7 +23,7 @@
 
 // Row tickets: each launch of the row kernel gets one zeroed counter out of a small pool, so that launches in flight
 // on different streams of a device do not share one.
-__device__ unsigned g_row_tickets[64];
+__device__ unsigned g_row_tickets[64 + 8 * 16];
 
 namespace cf {
 namespace {
@@ -34,6 +34,15 @@ unsigned *next_ticket()
     void *base = nullptr;
     if (cudaGetSymbolAddress(&base, g_row_tickets) != cudaSuccess) return nullptr;
     return static_cast<unsigned *>(base) + (turn.fetch_add(1) & 63u);
+}
+
+// `count` (<= 16) consecutive tickets out of the same pool, in its second half so that a block never wraps.
+unsigned *next_ticket_block(int count)
+{
+    static std::atomic<unsigned> turn{0};
+    void *base = nullptr;
+    if (count < 1 || count > 16 || cudaGetSymbolAddress(&base, g_row_tickets) != cudaSuccess) return nullptr;
+    return static_cast<unsigned *>(base) + 64 + 16 * (turn.fetch_add(1) & 7u);
 }
 
 constexpr int THREADS = 128;
@@ -52,6 +61,7 @@ struct RowArgs {
     long long N;
     int max_atoms;
     int keep_logit;  // 0: inference, the logits are not written back
+    int phi_in_row;  // 1: no phi kernel ran; rows (all of at most 32 keys) sum phi from their term lists themselves
     BoxRule rule;
     BasisParams basis;
 };
@@ -64,6 +74,21 @@ __host__ __device__ inline size_t row_group_floats(int max_atoms, bool with_basi
            (with_basis ? row_warps * (STAGE_FLOATS + HEADS * KBINS + RING_FLOATS) : 0) + row_warps * 128 +
            (max_atoms <= 32 ? 32 * KV_LD + 128 : 0);  // batches of small crystals: a tile for the row's k, then v, rows
                                                       // and the row's query
+}
+
+// phi of one edge by enumeration, for the rare edge whose row has no term list or whose listed terms miss a head's
+// box when the row kernel computes phi itself; kept out of line so that the row kernel's registers do not pay for it.
+__device__ __noinline__ void edge_phi_enumerated(const BoxRule rule, const float *a_row, const float *rvlen3,
+                                                 const float *tvecs9, const float *pos3, float floor_log2, float *z_out)
+{
+    float a[8], z[8];
+#pragma unroll
+    for (int h = 0; h < 8; ++h) a[h] = a_row[h];
+    Cell cell;
+    cell.load(tvecs9);
+    edge_phi<1>(rule, a, rvlen3, cell, pos3[0], pos3[1], pos3[2], floor_log2, 0, z);
+#pragma unroll
+    for (int h = 0; h < 8; ++h) z_out[h] = z[h];
 }
 
 // ROW_WARPS = 4: one thread block per atom (large crystals: the four warps split the translations).
@@ -172,6 +197,65 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             //      atoms) and the query into shared memory in one round trip; read by one lane per key straight from
             //      global memory, the 32 loads of a 512-byte row go out a few at a time.
             if (tiled && !prefetched) tile_fetch(kmat + a0 * HEADS * HEAD_DIM, n, p.q + i * HEADS * HEAD_DIM);
+            const bool phi_here = K > 0 && p.phi_in_row != 0;
+            if (K > 0 && phi_here) {
+                // ---- phi of the row's edges from their term lists, ROW_WARPS lanes per key (key = rt / ROW_WARPS): the
+                //      lanes of a key read its entries sub, sub + ROW_WARPS, ... and combine by a fixed butterfly
+                float a8[8], a2p[8];
+                int pkp[8];
+                float a2mx = -INFINITY;
+                const int pk_mine = packed_box(p.rule, a_own, p.rvlen ? rvl : nullptr);
+#pragma unroll
+                for (int h = 0; h < 8; ++h) {
+                    a8[h] = __shfl_sync(FULL, a_own, h);
+                    pkp[h] = __shfl_sync(FULL, pk_mine, h);
+                    a2p[h] = a8[h] * LOG2E;
+                    a2mx = fmaxf(a2mx, a2p[h]);
+                }
+                const int jk = rt / ROW_WARPS, sub = rt % ROW_WARPS;
+                const bool mine = jk < n;
+                const long long e = e0 + (mine ? jk : 0);
+                const int first = mine ? p.list.start[e] : -1;
+                const int cnt = first >= 0 ? p.list.count[e] : 0;
+                const float m = first >= 0 ? p.list.dmin[e] : 0.f;
+                const float2 *ent = p.list.pool + (first >= 0 ? first : 0);
+                float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                float2 n0 = make_float2(0.f, 0.f), n1 = n0;
+                if (sub < cnt) n0 = __ldg(ent + sub);
+                if (sub + ROW_WARPS < cnt) n1 = __ldg(ent + sub + ROW_WARPS);
+                for (int t = sub; t < cnt; t += ROW_WARPS) {
+                    const float2 en = n0;
+                    n0 = n1;
+                    if (t + 2 * ROW_WARPS < cnt) n1 = __ldg(ent + t + 2 * ROW_WARPS);
+                    const float d = en.x - m;
+                    if (a2mx * d < p.basis.floor_log2) continue;  // below the floor for every head
+                    const int key = __float_as_int(en.y);
+#pragma unroll
+                    for (int h = 0; h < 8; ++h)
+                        if (key_in_box(key, pkp[h])) s8[h] += ex2(a2p[h] * d);
+                }
+                bool done = cnt > 0;
+                float z8[8];
+#pragma unroll
+                for (int h = 0; h < 8; ++h) {  // (all lanes take part in the shuffles, listed or not)
+                    float t = s8[h];
+#pragma unroll
+                    for (int o = 1; o < ROW_WARPS; o <<= 1) t += __shfl_xor_sync(FULL, t, o);
+                    z8[h] = fmaf(m, a8[h], logf(t));
+                    done = done && t > 1e-30f;  // a head whose box misses the listed terms: enumerate instead
+                }
+                if (mine && sub == 0) {
+                    float *zs = part + 8 * jk;
+                    if (!done) {
+                        edge_phi_enumerated(p.rule, p.a + i * HEADS, p.rvlen ? p.rvlen + 3 * c : nullptr, p.tvecs + 9 * c,
+                                            p.pos_ij + 3 * e, p.basis.floor_log2, zs);
+                    } else {
+                        reinterpret_cast<float4 *>(zs)[0] = make_float4(z8[0], z8[1], z8[2], z8[3]);
+                        reinterpret_cast<float4 *>(zs)[1] = make_float4(z8[4], z8[5], z8[6], z8[7]);
+                    }
+                }
+                row_sync();
+            }
             float rx = 0.f, ry = 0.f, rz = 0.f;
             float4 ph0 = make_float4(0.f, 0.f, 0.f, 0.f), ph1 = ph0;
             if (wr == 0 && lane < n) {  // this lane's key: position and phi, requested before waiting for the tile
@@ -182,7 +266,8 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                     const float *pp = p.pos + 3 * (a0 + lane), *pi = p.pos + 3 * i;
                     rx = __fsub_rn(pp[0], pi[0]); ry = __fsub_rn(pp[1], pi[1]); rz = __fsub_rn(pp[2], pi[2]);
                 }
-                const float4 *lp = reinterpret_cast<const float4 *>(logit_io + (e0 + lane) * HEADS);
+                const float4 *lp = phi_here ? reinterpret_cast<const float4 *>(part + 8 * lane)
+                                            : reinterpret_cast<const float4 *>(logit_io + (e0 + lane) * HEADS);
                 ph0 = lp[0]; ph1 = lp[1];
             }
             if (tiled) {
@@ -542,7 +627,9 @@ int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const
                            const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D,
                            int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
                            double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
-                           float *lse, float *psi_row, const int32_t *row_order, const TermList *list, void *stream);
+                           float *lse, float *psi_row, const int32_t *row_order, const TermList *list, unsigned *ticket_ready,
+                           void *stream);
+unsigned *row_ticket_block(int count);
 }
 
 extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
@@ -555,7 +642,7 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
 {
     return cf::infinite_attn_fwd_impl(q, k, v, a, pos, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
                                       max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, out,
-                                      logit, lse, psi_row, row_order, nullptr, stream);
+                                      logit, lse, psi_row, row_order, nullptr, nullptr, stream);
 }
 
 extern "C" int cf_infinite_attn_fwd_listed(const float *q, const float *k, const float *v, const float *a,
@@ -580,7 +667,7 @@ extern "C" int cf_infinite_attn_fwd_listed(const float *q, const float *k, const
     list.window = term_window(weight_floor_log2(), (float)a_widest);
     return infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
                                   max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, out, logit,
-                                  lse, psi_row, row_order, &list, stream);
+                                  lse, psi_row, row_order, &list, nullptr, stream);
 }
 
 int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
@@ -589,7 +676,7 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
                                int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
                                const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out,
                                float *logit, float *lse, float *psi_row, const int32_t *row_order,
-                               const TermList *list, void *stream)
+                               const TermList *list, unsigned *ticket_ready, void *stream)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_fwd: negative size");
@@ -612,11 +699,19 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
     phi.floor_log2 = weight_floor_log2();
     // rows with a basis expansion differ widely in cost and are drawn through a ticket, which the phi launch zeroes;
     // without one (K = 0) rows are cheap and uniform and are dealt round-robin
-    unsigned *ticket = K > 0 ? next_ticket() : nullptr;
+    // (ticket_ready: a ticket that an earlier operation on this stream has zeroed already)
+    unsigned *ticket = K > 0 ? (ticket_ready != nullptr ? ticket_ready : next_ticket()) : nullptr;
     CF_REQUIRE(K == 0 || ticket != nullptr, CF_ERR_CUDA, "cf_infinite_attn_fwd: the row ticket could not be set up");
     phi.zero_word = ticket;
-    int rc;
-    if (list != nullptr && pos_ij != nullptr) {
+    // With term lists and rows of at most 32 keys the row kernel sums phi from the lists itself (one launch less per
+    // layer, and the lists are read while they are needed); CF_PHI_IN_ROW=0 in the environment keeps the phi kernel.
+    static const bool phi_fusable = [] { const char *e = getenv("CF_PHI_IN_ROW"); return !(e && atoi(e) == 0); }();
+    const bool phi_in_row = phi_fusable && list != nullptr && pos_ij != nullptr && K > 0 && max_atoms <= 32;
+    int rc = CF_OK;
+    if (phi_in_row) {
+        if (ticket_ready == nullptr && cudaMemsetAsync(ticket, 0, sizeof(unsigned), s) != cudaSuccess)
+            rc = launch_status("row ticket");
+    } else if (list != nullptr && pos_ij != nullptr) {
         PhiListArgs pl{};
         pl.list = *list;
         pl.a = a; pl.pos_ij = pos_ij; pl.tvecs = tvecs; pl.rvlen = rvlen; pl.batch = batch; pl.edges = edges; pl.E = E;
@@ -632,6 +727,7 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
     p.batch = batch; p.edges = edges; p.row_start = row_start; p.row_order = row_order; p.E = E;
     p.out = out; p.logit = logit; p.lse = lse; p.psi_row = psi_row; p.N = N; p.max_atoms = (int)max_atoms;
     p.keep_logit = 1;
+    p.phi_in_row = phi_in_row ? 1 : 0;
     p.ticket = ticket;
     if (list != nullptr && pos_ij != nullptr && K > 0) p.list = *list;
     p.rule = phi.rule;
@@ -670,3 +766,5 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
     kernel<<<blocks, THREADS, smem, s>>>(p);
     return launch_status("cf_infinite_attn_fwd");
 }
+
+unsigned *cf::row_ticket_block(int count) { return next_ticket_block(count); }
