@@ -307,25 +307,29 @@ def run_b200(args):
         t_call = op_ms * 1e-3 / max(op_calls, 1)
         achieved = terms_per_call * fp32_instr_per_term(K) / t_call
         achieved_sfu = terms_per_call * sfu_per_term(K) / t_call
+        # crystals of up to 32 atoms with a value encoding: the row kernel sums phi from the term lists itself
+        phi_in_row = K > 0 and max_atoms <= 32 and os.environ.get("CF_PHI_IN_ROW", "1") != "0"
         roofline = {
-            "kernel": "phi_from_list_kernel + infinite_attn_rows_kernel (one fused-attention call)",
+            "kernel": ("infinite_attn_rows_kernel, phi summed from the term lists inside (one fused-attention call)"
+                       if phi_in_row else "phi_from_list_kernel + infinite_attn_rows_kernel (one fused-attention call)"),
             "bound": "fp32_simt", "achieved": achieved / 1e9, "peak": peaks["fp32"] / 1e9, "unit": "G lane-instr/s",
             "frac": achieved / peaks["fp32"], "peak_source": "cf_pipe_probe FFMA, measured in this run",
             "sfu": {"achieved": achieved_sfu / 1e9, "peak": peaks["sfu"] / 1e9, "frac": achieved_sfu / peaks["sfu"]},
             "terms_per_launch": terms_per_call, "launches": op_calls, "avg_launch_us": t_call * 1e6,
             "share_of_step": op_ms / ms_total,
             # dram__bytes_read.sum + dram__bytes_write.sum per fused-attention call from the ncu capture of this workload
-            # (phi from lists 8.33 MB + rows 13.09 MB at cfg0, caches cold under ncu: the 8 MB of term lists are streamed
-            # from DRAM by each kernel); not re-measured per run, and only known for cfg0
-            "traffic": 21.4e6 if args.workload == "cfg0" else None, "traffic_unit": "bytes per call (ncu, cfg0, cold caches)",
+            # (row kernel with phi inside: 11.95 MB at cfg0, caches cold under ncu, of which 8 MB are the term lists; the
+            # two-kernel form read 8.33 + 13.09 MB); not re-measured per run, and only known for cfg0
+            "traffic": (11.95e6 if phi_in_row else 21.4e6) if args.workload == "cfg0" else None,
+            "traffic_unit": "bytes per call (ncu, cfg0, cold caches)",
             "note": "work counted for EVERY (edge, translation) term; terms whose weights fall below 2^-30 are skipped "
                     "by the kernel, so frac may exceed the executed-instruction utilisation",
         }
         micro = lattice_microbench(ops, device, peaks)
         cpu = cpu_baseline(model, params, mine) if (world == 1 and not args.no_cpu_baseline) else None
-        # own kernels per forward: offsets, geometry + row order, term lists; L + 1 dense blocks; per layer phi and rows;
-        # pooling + head
-        per_step_launches = 3 + (wl["layers"] + 1) + 2 * wl["layers"] + 1
+        # own kernels per forward: offsets, geometry + row order, term lists; L + 1 dense blocks; per layer rows (and phi,
+        # unless the row kernel computes it); pooling + head (N > 1: + the collect of the peer gather)
+        per_step_launches = 3 + (wl["layers"] + 1) + (1 if phi_in_row else 2) * wl["layers"] + 1 + (1 if world > 1 else 0)
         result = {
             "metric": "crystals/sec (4-layer, fwd)" if wl["layers"] == 4 else f"crystals/sec ({wl['layers']}-layer, fwd)",
             "value": value, "unit": "crystals/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
