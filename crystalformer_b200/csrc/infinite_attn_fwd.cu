@@ -190,6 +190,66 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             if (p.rvlen) { rvl[0] = p.rvlen[3 * c]; rvl[1] = p.rvlen[3 * c + 1]; rvl[2] = p.rvlen[3 * c + 2]; }
         }
 
+        // phi of key jk of this row from the edge's term list, by the ROW_WARPS lanes rt % ROW_WARPS of the key: they
+        // read its entries sub, sub + ROW_WARPS, ... and combine by a fixed butterfly; lane 0 of the key stores the eight
+        // values at dst.  Every thread of the group calls it (keys beyond the row just take part in the shuffles).  The
+        // rare edge without a list, or whose listed terms miss a head's box, is enumerated out of line.
+        const bool phi_here = K > 0 && p.phi_in_row != 0;
+        auto phi_from_lists = [&](int jk, float *dst) {
+            float a8[8], a2p[8];
+            int pkp[8];
+            float a2mx = -INFINITY;
+            const int pk_mine = packed_box(p.rule, a_own, p.rvlen ? rvl : nullptr);
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                a8[h] = __shfl_sync(FULL, a_own, h);
+                pkp[h] = __shfl_sync(FULL, pk_mine, h);
+                a2p[h] = a8[h] * LOG2E;
+                a2mx = fmaxf(a2mx, a2p[h]);
+            }
+            const int sub = rt % ROW_WARPS;
+            const bool mine = jk < n;
+            const long long e = e0 + (mine ? jk : 0);
+            const int first = mine ? p.list.start[e] : -1;
+            const int cnt = first >= 0 ? p.list.count[e] : 0;
+            const float m = first >= 0 ? p.list.dmin[e] : 0.f;
+            const float2 *ent = p.list.pool + (first >= 0 ? first : 0);
+            float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            float2 n0 = make_float2(0.f, 0.f), n1 = n0;  // entries are requested two steps ahead of their use
+            if (sub < cnt) n0 = __ldg(ent + sub);
+            if (sub + ROW_WARPS < cnt) n1 = __ldg(ent + sub + ROW_WARPS);
+            for (int t = sub; t < cnt; t += ROW_WARPS) {
+                const float2 en = n0;
+                n0 = n1;
+                if (t + 2 * ROW_WARPS < cnt) n1 = __ldg(ent + t + 2 * ROW_WARPS);
+                const float d = en.x - m;
+                if (a2mx * d < p.basis.floor_log2) continue;  // below the floor for every head
+                const int key = __float_as_int(en.y);
+#pragma unroll
+                for (int h = 0; h < 8; ++h)
+                    if (key_in_box(key, pkp[h])) s8[h] += ex2(a2p[h] * d);
+            }
+            bool done = cnt > 0;
+            float z8[8];
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {  // (all lanes take part in the shuffles, listed or not)
+                float t = s8[h];
+#pragma unroll
+                for (int o = 1; o < ROW_WARPS; o <<= 1) t += __shfl_xor_sync(FULL, t, o);
+                z8[h] = fmaf(m, a8[h], logf(t));
+                done = done && t > 1e-30f;  // a head whose box misses the listed terms: enumerate instead
+            }
+            if (mine && sub == 0) {
+                if (!done) {
+                    edge_phi_enumerated(p.rule, p.a + i * HEADS, p.rvlen ? p.rvlen + 3 * c : nullptr, p.tvecs + 9 * c,
+                                        p.pos_ij + 3 * e, p.basis.floor_log2, dst);
+                } else {
+                    reinterpret_cast<float4 *>(dst)[0] = make_float4(z8[0], z8[1], z8[2], z8[3]);
+                    reinterpret_cast<float4 *>(dst)[1] = make_float4(z8[4], z8[5], z8[6], z8[7]);
+                }
+            }
+        };
+
         if (n <= 32) {
             // ---- up to 32 keys: the first warp of the group does the whole soft-max in registers, one key per lane
             //      (positions, logits of all eight heads, statistics by shuffles); the other warps wait.
@@ -197,63 +257,9 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             //      atoms) and the query into shared memory in one round trip; read by one lane per key straight from
             //      global memory, the 32 loads of a 512-byte row go out a few at a time.
             if (tiled && !prefetched) tile_fetch(kmat + a0 * HEADS * HEAD_DIM, n, p.q + i * HEADS * HEAD_DIM);
-            const bool phi_here = K > 0 && p.phi_in_row != 0;
             if (K > 0 && phi_here) {
-                // ---- phi of the row's edges from their term lists, ROW_WARPS lanes per key (key = rt / ROW_WARPS): the
-                //      lanes of a key read its entries sub, sub + ROW_WARPS, ... and combine by a fixed butterfly
-                float a8[8], a2p[8];
-                int pkp[8];
-                float a2mx = -INFINITY;
-                const int pk_mine = packed_box(p.rule, a_own, p.rvlen ? rvl : nullptr);
-#pragma unroll
-                for (int h = 0; h < 8; ++h) {
-                    a8[h] = __shfl_sync(FULL, a_own, h);
-                    pkp[h] = __shfl_sync(FULL, pk_mine, h);
-                    a2p[h] = a8[h] * LOG2E;
-                    a2mx = fmaxf(a2mx, a2p[h]);
-                }
-                const int jk = rt / ROW_WARPS, sub = rt % ROW_WARPS;
-                const bool mine = jk < n;
-                const long long e = e0 + (mine ? jk : 0);
-                const int first = mine ? p.list.start[e] : -1;
-                const int cnt = first >= 0 ? p.list.count[e] : 0;
-                const float m = first >= 0 ? p.list.dmin[e] : 0.f;
-                const float2 *ent = p.list.pool + (first >= 0 ? first : 0);
-                float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                float2 n0 = make_float2(0.f, 0.f), n1 = n0;
-                if (sub < cnt) n0 = __ldg(ent + sub);
-                if (sub + ROW_WARPS < cnt) n1 = __ldg(ent + sub + ROW_WARPS);
-                for (int t = sub; t < cnt; t += ROW_WARPS) {
-                    const float2 en = n0;
-                    n0 = n1;
-                    if (t + 2 * ROW_WARPS < cnt) n1 = __ldg(ent + t + 2 * ROW_WARPS);
-                    const float d = en.x - m;
-                    if (a2mx * d < p.basis.floor_log2) continue;  // below the floor for every head
-                    const int key = __float_as_int(en.y);
-#pragma unroll
-                    for (int h = 0; h < 8; ++h)
-                        if (key_in_box(key, pkp[h])) s8[h] += ex2(a2p[h] * d);
-                }
-                bool done = cnt > 0;
-                float z8[8];
-#pragma unroll
-                for (int h = 0; h < 8; ++h) {  // (all lanes take part in the shuffles, listed or not)
-                    float t = s8[h];
-#pragma unroll
-                    for (int o = 1; o < ROW_WARPS; o <<= 1) t += __shfl_xor_sync(FULL, t, o);
-                    z8[h] = fmaf(m, a8[h], logf(t));
-                    done = done && t > 1e-30f;  // a head whose box misses the listed terms: enumerate instead
-                }
-                if (mine && sub == 0) {
-                    float *zs = part + 8 * jk;
-                    if (!done) {
-                        edge_phi_enumerated(p.rule, p.a + i * HEADS, p.rvlen ? p.rvlen + 3 * c : nullptr, p.tvecs + 9 * c,
-                                            p.pos_ij + 3 * e, p.basis.floor_log2, zs);
-                    } else {
-                        reinterpret_cast<float4 *>(zs)[0] = make_float4(z8[0], z8[1], z8[2], z8[3]);
-                        reinterpret_cast<float4 *>(zs)[1] = make_float4(z8[4], z8[5], z8[6], z8[7]);
-                    }
-                }
+                // ---- phi of the row's edges from their term lists, ROW_WARPS lanes per key (key = rt / ROW_WARPS)
+                phi_from_lists(rt / ROW_WARPS, part + 8 * (rt / ROW_WARPS));
                 row_sync();
             }
             float rx = 0.f, ry = 0.f, rz = 0.f;
@@ -340,6 +346,14 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             float4 *qs = reinterpret_cast<float4 *>(vsum);
             for (int idx = rt; idx < HEADS * HEAD_DIM / 4; idx += RT)
                 qs[idx] = __ldg(reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM) + idx);
+            if (K > 0 && phi_here) {
+                // ---- phi of the row's edges from their term lists, 32 keys per pass, left where the phi kernel leaves it
+                //      (only with CF_PHI_IN_ROW=2: for rows of many keys the separate phi kernel is faster)
+                for (int base = 0; base < n; base += 32) {
+                    const int jk = base + rt / ROW_WARPS;
+                    phi_from_lists(jk, logit_io + (e0 + (jk < n ? jk : 0)) * HEADS);
+                }
+            }
             row_sync();
             // ---- logits: one key per thread, all eight heads; the key's 512-byte row is 32 independent 16-byte loads
             for (int j = rt; j < n; j += RT) {
@@ -704,9 +718,12 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
     CF_REQUIRE(K == 0 || ticket != nullptr, CF_ERR_CUDA, "cf_infinite_attn_fwd: the row ticket could not be set up");
     phi.zero_word = ticket;
     // With term lists and rows of at most 32 keys the row kernel sums phi from the lists itself (one launch less per
-    // layer, and the lists are read while they are needed); CF_PHI_IN_ROW=0 in the environment keeps the phi kernel.
-    static const bool phi_fusable = [] { const char *e = getenv("CF_PHI_IN_ROW"); return !(e && atoi(e) == 0); }();
-    const bool phi_in_row = phi_fusable && list != nullptr && pos_ij != nullptr && K > 0 && max_atoms <= 32;
+    // layer, and the lists are read while they are needed); CF_PHI_IN_ROW=0 in the environment keeps the phi kernel, 2
+    // lets rows of any size sum phi themselves.
+    // Rows of more keys keep the phi kernel: with four lanes per key and one block per row the same sums took longer
+    // inside the row kernel (64 crystals of 100-200 atoms: 663 against 621 us per call).
+    static const int phi_mode = [] { const char *e = getenv("CF_PHI_IN_ROW"); return e ? atoi(e) : 1; }();
+    const bool phi_in_row = phi_mode != 0 && list != nullptr && pos_ij != nullptr && K > 0 && (max_atoms <= 32 || phi_mode == 2);
     int rc = CF_OK;
     if (phi_in_row) {
         if (ticket_ready == nullptr && cudaMemsetAsync(ticket, 0, sizeof(unsigned), s) != cudaSuccess)
