@@ -90,13 +90,15 @@ def test_fused_forward_against_oracle_chain(ops, cutoff, minimum, nmax, Kbins):
 @pytest.mark.parametrize("cutoff,minimum,nmax,Kbins,floor", [(-3.5, 2, 7, 64, -30.0), (-3.5, 0, 7, 64, -30.0),
                                                              (7.5, 2, 5, 64, -30.0), (0.0, 2, 40, 64, -30.0),
                                                              (-3.5, 2, 7, 0, -30.0), (-3.5, 2, 150, 64, -30.0),
+                                                             (-3.5, 2, 24, 64, -30.0), (-3.5, 0, 30, 64, -30.0),
                                                              (-3.5, 2, 7, 64, -1000.0)])
 def test_term_lists_give_the_enumerated_result(ops, cutoff, minimum, nmax, Kbins, floor):
     """The same attention fed from the batch's term lists (found once, for the widest admissible Gaussian) instead of
     enumerating every head's box: against the float64 oracle chain and against the enumerating kernels.  The widths
     here span a factor of 2.5, so heads have different boxes and the listed terms are masked per head.  With the
     weight floor switched off the lists would hold whole boxes; they then do not fit their pool and every row falls
-    back to enumeration, which the last case exercises."""
+    back to enumeration, which the last case exercises.  Crystals of up to 12 atoms take one warp per row, up to 32
+    atoms four warps per row with phi summed inside the row kernel, larger ones the separate phi kernel."""
     crystals = 3 if nmax > 100 else 10
     cb = make_crystals(61, crystals, uniform_atoms(max(1, nmax // 3), nmax), length_range=(2.5, 9.0) if nmax < 100 else (8.0, 16.0))
     prep = prepare(ops, cb)
