@@ -251,8 +251,8 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
         };
 
         if (n <= 32) {
-            // ---- up to 32 keys: the first warp of the group does the whole soft-max in registers, one key per lane
-            //      (positions, logits of all eight heads, statistics by shuffles); the other warps wait.
+            // ---- up to 32 keys: the soft-max in registers, one key per lane, the heads split over the warps of the group
+            //      (logits, statistics by shuffles).
             //      In batches of small crystals all threads first bring the keys' k rows (contiguous: the crystal's
             //      atoms) and the query into shared memory in one round trip; read by one lane per key straight from
             //      global memory, the 32 loads of a 512-byte row go out a few at a time.
@@ -262,25 +262,43 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                 phi_from_lists(rt / ROW_WARPS, part + 8 * (rt / ROW_WARPS));
                 row_sync();
             }
+            // The warps of the row split the heads (HPW each), one key per lane: a warp's chain of shuffle reductions
+            // is then HPW heads long instead of eight.
+            constexpr int HPW = HEADS / ROW_WARPS;
+            const int h0 = wr * HPW;
             float rx = 0.f, ry = 0.f, rz = 0.f;
-            float4 ph0 = make_float4(0.f, 0.f, 0.f, 0.f), ph1 = ph0;
-            if (wr == 0 && lane < n) {  // this lane's key: position and phi, requested before waiting for the tile
-                if (p.pos_ij) {
-                    const float *pp = p.pos_ij + 3 * (e0 + lane);
-                    rx = pp[0]; ry = pp[1]; rz = pp[2];
-                } else {
-                    const float *pp = p.pos + 3 * (a0 + lane), *pi = p.pos + 3 * i;
-                    rx = __fsub_rn(pp[0], pi[0]); ry = __fsub_rn(pp[1], pi[1]); rz = __fsub_rn(pp[2], pi[2]);
+            float phi[HPW];
+#pragma unroll
+            for (int u = 0; u < HPW; ++u) phi[u] = 0.f;
+            if (lane < n) {  // this lane's key: position and phi, requested before waiting for the tile
+                if (wr == 0) {
+                    if (p.pos_ij) {
+                        const float *pp = p.pos_ij + 3 * (e0 + lane);
+                        rx = pp[0]; ry = pp[1]; rz = pp[2];
+                    } else {
+                        const float *pp = p.pos + 3 * (a0 + lane), *pi = p.pos + 3 * i;
+                        rx = __fsub_rn(pp[0], pi[0]); ry = __fsub_rn(pp[1], pi[1]); rz = __fsub_rn(pp[2], pi[2]);
+                    }
                 }
-                const float4 *lp = phi_here ? reinterpret_cast<const float4 *>(part + 8 * lane)
-                                            : reinterpret_cast<const float4 *>(logit_io + (e0 + lane) * HEADS);
-                ph0 = lp[0]; ph1 = lp[1];
+                // phi: left in shared memory by the phase above, or in the logit array by the phi kernel
+                const float *src = (phi_here ? part + 8 * lane : logit_io + (e0 + lane) * HEADS) + h0;
+                if (HPW == 8) {
+                    const float4 v0 = reinterpret_cast<const float4 *>(src)[0], v1 = reinterpret_cast<const float4 *>(src)[1];
+                    phi[0] = v0.x; phi[1] = v0.y; phi[2] = v0.z; phi[3] = v0.w;
+                    phi[4 % HPW] = v1.x; phi[5 % HPW] = v1.y; phi[6 % HPW] = v1.z; phi[7 % HPW] = v1.w;
+                } else if (HPW == 4) {
+                    const float4 v0 = reinterpret_cast<const float4 *>(src)[0];
+                    phi[0] = v0.x; phi[1] = v0.y; phi[2 % HPW] = v0.z; phi[3 % HPW] = v0.w;
+                } else {
+                    const float2 v0 = reinterpret_cast<const float2 *>(src)[0];
+                    phi[0] = v0.x; phi[1] = v0.y;
+                }
             }
             if (tiled) {
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 row_sync();
             }
-            if (wr == 0) {
+            {
                 const bool live = lane < n;
                 const int j = live ? lane : 0;
                 // k row and query from the tile, or (batches with larger crystals) from global memory
@@ -288,11 +306,10 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                                          : reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM);
                 const float4 *kp = tiled ? reinterpret_cast<const float4 *>(kv + j * KV_LD)
                                          : reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
-                float4 *lp = reinterpret_cast<float4 *>(logit_io + (e0 + j) * HEADS);  // phi was left here by the phi kernel
-                const float phi[8] = {ph0.x, ph0.y, ph0.z, ph0.w, ph1.x, ph1.y, ph1.z, ph1.w};
-                float sc[8], lg[8];
+                float sc[HPW], lg[HPW];
 #pragma unroll
-                for (int h = 0; h < HEADS; ++h) {
+                for (int u = 0; u < HPW; ++u) {
+                    const int h = h0 + u;
                     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
                     for (int t = 0; t < 4; t += 2) {
@@ -301,33 +318,48 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                         s0 = fmaf(q0.x, k0.x, s0); s0 = fmaf(q0.y, k0.y, s0); s0 = fmaf(q0.z, k0.z, s0); s0 = fmaf(q0.w, k0.w, s0);
                         s1 = fmaf(q1.x, k1.x, s1); s1 = fmaf(q1.y, k1.y, s1); s1 = fmaf(q1.z, k1.z, s1); s1 = fmaf(q1.w, k1.w, s1);
                     }
-                    sc[h] = s0 + s1;
-                    lg[h] = live ? sc[h] + phi[h] : -INFINITY;
+                    sc[u] = s0 + s1;
+                    lg[u] = live ? sc[u] + phi[u] : -INFINITY;
                 }
                 if (p.keep_logit && live) {
-                    lp[0] = make_float4(lg[0], lg[1], lg[2], lg[3]);
-                    lp[1] = make_float4(lg[4], lg[5], lg[6], lg[7]);
+                    float *lp = logit_io + (e0 + j) * HEADS + h0;
+#pragma unroll
+                    for (int u = 0; u < HPW; ++u) lp[u] = lg[u];
                 }
                 float mxo = -INFINITY, lse_mine = 0.f;
 #pragma unroll
-                for (int h = 0; h < HEADS; ++h) {
-                    const float mx = warp_max(lg[h]);
-                    const float den = warp_sum(ex2((lg[h] - mx) * LOG2E));
+                for (int u = 0; u < HPW; ++u) {
+                    const int h = h0 + u;
+                    const float mx = warp_max(lg[u]);
+                    const float den = warp_sum(ex2((lg[u] - mx) * LOG2E));
                     const float lse = mx + logf(den);
-                    if (lane == h) lse_mine = lse;
-                    const float off = (sc[h] - lse) * LOG2E;
+                    if (lane == u) lse_mine = lse;
+                    const float off = (sc[u] - lse) * LOG2E;
                     if (live) {
                         cj[h * ld + j] = off;
-                        pj[h * ld + j] = ex2((lg[h] - lse) * LOG2E);
+                        pj[h * ld + j] = ex2((lg[u] - lse) * LOG2E);
                     }
                     mxo = fmaxf(mxo, off);
                 }
-                if (lane < HEADS) p.lse[i * HEADS + lane] = lse_mine;
-                if (live) rel[j] = make_float4(rx, ry, rz, mxo);  // .w: the key's largest offset
+                if (lane < HPW) p.lse[i * HEADS + h0 + lane] = lse_mine;
+                if (ROW_WARPS == 1) {
+                    if (live) rel[j] = make_float4(rx, ry, rz, mxo);  // .w: the key's largest offset
+                } else if (live) {
+                    vsum[wr * 32 + lane] = mxo;  // this warp's heads only; combined below
+                }
             }
             row_sync();
             // the k rows are no longer needed: the tile is refilled with the keys' v rows while the histogram is built
             if (tiled) tile_fetch(p.v + a0 * HEADS * HEAD_DIM, n, nullptr);
+            if (ROW_WARPS > 1) {
+                if (wr == 0 && lane < n) {
+                    float mxo = vsum[lane];
+#pragma unroll
+                    for (int w = 1; w < ROW_WARPS; ++w) mxo = fmaxf(mxo, vsum[w * 32 + lane]);
+                    rel[lane] = make_float4(rx, ry, rz, mxo);  // .w: the key's largest offset
+                }
+                row_sync();
+            }
         } else {
             // ---- relative positions of the keys
             if (p.pos_ij) {
