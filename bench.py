@@ -327,9 +327,12 @@ def run_b200(args):
         }
         micro = lattice_microbench(ops, device, peaks)
         cpu = cpu_baseline(model, params, mine) if (world == 1 and not args.no_cpu_baseline) else None
-        # own kernels per forward: offsets, geometry + row order, term lists; L + 1 dense blocks; per layer rows (and phi,
-        # unless the row kernel computes it); pooling + head (N > 1: + the collect of the peer gather)
-        per_step_launches = 3 + (wl["layers"] + 1) + (1 if phi_in_row else 2) * wl["layers"] + 1 + (1 if world > 1 else 0)
+        # own kernels per forward: geometry (offsets, cells, atoms, edges, row order; the offsets are a launch of their own
+        # above 1024 crystals), term lists; L + 1 dense blocks; per layer rows (and phi, unless the row kernel computes
+        # it); pooling + head (N > 1: + the collect of the peer gather)
+        geometry = 1 if mine.num_crystals <= 1024 else 2
+        per_step_launches = (geometry + 1 + (wl["layers"] + 1) + (1 if phi_in_row else 2) * wl["layers"] + 1
+                             + (1 if world > 1 else 0))
         result = {
             "metric": "crystals/sec (4-layer, fwd)" if wl["layers"] == 4 else f"crystals/sec ({wl['layers']}-layer, fwd)",
             "value": value, "unit": "crystals/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

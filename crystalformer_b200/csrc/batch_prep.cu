@@ -239,11 +239,15 @@ __global__ void __launch_bounds__(ORDER_THREADS) row_order_kernel(const int64_t 
     row_order_body(atom_start, trans, B, padded, sphere, order);
 }
 
-// Everything that follows the offsets in ONE launch of 1024-thread blocks: block 0 sorts the rows (when asked to), the
-// other blocks cover the cells, then the atoms, then the edges.
+// The batch geometry in ONE launch of 1024-thread blocks: block 0 sorts the rows (when asked to), the other blocks
+// cover the cells, then the atoms, then the edges.  For batches of up to 1024 crystals the offsets are part of it:
+// every block scans the crystals' sizes itself (sizes != NULL; one crystal per thread), works from its copy in shared
+// memory, and block 1 stores them; larger batches bring offsets computed by crystal_offsets_kernel.
+constexpr int INLINE_OFFSETS_MAX = 1024;
 struct PrepareAll {
     const float *pos, *trans;
-    const int64_t *atom_start, *edge_start;
+    const int64_t *sizes;            // NULL: atom_start / edge_start are inputs
+    int64_t *atom_start, *edge_start;
     long long B, N, E;
     int64_t *batch, *edges, *row_start;
     float *pos_ij, *rvecs, *vcell, *rvlen;
@@ -254,30 +258,62 @@ struct PrepareAll {
 
 __global__ void __launch_bounds__(ORDER_THREADS) prepare_all_kernel(const PrepareAll p)
 {
+    __shared__ int64_t atom_sh[INLINE_OFFSETS_MAX + 1], edge_sh[INLINE_OFFSETS_MAX + 1];
+    __shared__ long long warp_n[ORDER_THREADS / 32], warp_e[ORDER_THREADS / 32];
+    const int64_t *atom_start = p.atom_start, *edge_start = p.edge_start;
+    if (p.sizes != nullptr) {
+        // exclusive prefix sums of sizes and sizes^2 (B <= 1024 = ORDER_THREADS): warp scans, then the warps' totals
+        const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+        const long long n = t < p.B ? p.sizes[t] : 0;
+        long long in = n, ie = n * n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long un = __shfl_up_sync(FULL, in, o), ue = __shfl_up_sync(FULL, ie, o);
+            if (lane >= o) { in += un; ie += ue; }
+        }
+        if (lane == 31) { warp_n[w] = in; warp_e[w] = ie; }
+        __syncthreads();
+        long long bn = 0, be = 0;
+        for (int k = 0; k < w; ++k) { bn += warp_n[k]; be += warp_e[k]; }
+        if (t < p.B) { atom_sh[t + 1] = bn + in; edge_sh[t + 1] = be + ie; }
+        if (t == 0) { atom_sh[0] = 0; edge_sh[0] = 0; }
+        __syncthreads();
+        if (blockIdx.x == 1)
+            for (long long b = t; b <= p.B; b += ORDER_THREADS) { p.atom_start[b] = atom_sh[b]; p.edge_start[b] = edge_sh[b]; }
+        atom_start = atom_sh;
+        edge_start = edge_sh;
+    }
     if (blockIdx.x == 0) {
-        if (p.order != nullptr) row_order_body(p.atom_start, p.trans, (int)p.B, p.padded, p.sphere, p.order);
+        if (p.order != nullptr) row_order_body(atom_start, p.trans, (int)p.B, p.padded, p.sphere, p.order);
         return;
     }
     const long long idx = (long long)(blockIdx.x - 1) * ORDER_THREADS + threadIdx.x;
     if (idx < p.B) {
         cell_body(idx, p.trans, p.B, p.rvecs, p.vcell, p.rvlen);
     } else if (idx < p.B + p.N + 1) {
-        atom_body(idx - p.B, p.atom_start, p.edge_start, p.B, p.N, p.batch, p.row_start, p.E);
+        atom_body(idx - p.B, atom_start, edge_start, p.B, p.N, p.batch, p.row_start, p.E);
     } else {
-        edge_body(idx - p.B - p.N - 1, p.pos, p.atom_start, p.edge_start, p.B, p.E, p.edges, p.pos_ij);
+        edge_body(idx - p.B - p.N - 1, p.pos, atom_start, edge_start, p.B, p.E, p.edges, p.pos_ij);
     }
 }
 
 }  // namespace
 
-// cf_batch_prepare and cf_row_order in one launch (the one-call model forward); *ordered says whether row_order was
-// written (batches of more than ORDER_MAX_CRYSTALS crystals are not ordered).
-int launch_prepare_all(const float *pos, const float *trans, const int64_t *atom_start, const int64_t *edge_start,
-                       long long B, long long N, long long E, int64_t *batch, int64_t *edges, int64_t *row_start,
-                       float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered, cudaStream_t s)
+// cf_crystal_offsets, cf_batch_prepare and cf_row_order in one launch (the one-call model forward; two launches for
+// batches of more than 1024 crystals); *ordered says whether row_order was written (batches of more than
+// ORDER_MAX_CRYSTALS crystals are not ordered).
+int launch_prepare_all(const float *pos, const float *trans, const int64_t *sizes, int64_t *atom_start,
+                       int64_t *edge_start, long long B, long long N, long long E, int64_t *batch, int64_t *edges,
+                       int64_t *row_start, float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered,
+                       cudaStream_t s)
 {
     PrepareAll p{};
     p.pos = pos; p.trans = trans; p.atom_start = atom_start; p.edge_start = edge_start; p.B = B; p.N = N; p.E = E;
+    if (B <= INLINE_OFFSETS_MAX) {
+        p.sizes = sizes;
+    } else {
+        crystal_offsets_kernel<<<1, SCAN_THREADS, 0, s>>>(sizes, B, atom_start, edge_start);
+    }
     p.batch = batch; p.edges = edges; p.row_start = row_start; p.pos_ij = pos_ij; p.rvlen = rvlen;
     *ordered = row_order != nullptr && B <= ORDER_MAX_CRYSTALS && N < (1ll << 31);
     p.order = *ordered ? row_order : nullptr;

@@ -15,9 +15,10 @@
 
 namespace cf {
 int validate_peer_gather(const cf_peer_gather *g, long long rows, const char *who);
-int launch_prepare_all(const float *pos, const float *trans, const int64_t *atom_start, const int64_t *edge_start,
-                       long long B, long long N, long long E, int64_t *batch, int64_t *edges, int64_t *row_start,
-                       float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered, cudaStream_t s);
+int launch_prepare_all(const float *pos, const float *trans, const int64_t *sizes, int64_t *atom_start,
+                       int64_t *edge_start, long long B, long long N, long long E, int64_t *batch, int64_t *edges,
+                       int64_t *row_start, float *pos_ij, float *rvlen, double reach, int32_t *row_order, bool *ordered,
+                       cudaStream_t s);
 int encoder_forward_impl(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars,
                          float *x, const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
                          const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
@@ -145,10 +146,9 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
     cudaStream_t s = as_stream(stream);
     Scratch w = carve(workspace, N, B, E, ff_dim);
 
-    int rc = cf_crystal_offsets(sizes, B, w.atom_start, w.edge_start, stream);
-    if (rc != CF_OK) return rc;
+    CF_REQUIRE(B <= (1 << 20), CF_ERR_RANGE, "cf_model_forward: B=%lld above 2^20 crystals", (long long)B);
     bool ordered = false;  // batches beyond the one-launch sort are processed in index order
-    rc = launch_prepare_all(pos, trans, w.atom_start, w.edge_start, B, N, E, w.batch, w.edges, w.row_start, w.pos_ij, w.rvlen,
+    int rc = launch_prepare_all(pos, trans, sizes, w.atom_start, w.edge_start, B, N, E, w.batch, w.edges, w.row_start, w.pos_ij, w.rvlen,
                             order_reach, w.row_order, &ordered, s);
     if (rc != CF_OK) return rc;
     const int32_t *order = ordered ? w.row_order : nullptr;

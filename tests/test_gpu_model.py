@@ -107,6 +107,29 @@ def test_one_call_model_forward_equals_the_torch_shell(golden_model):
     assert model(data).requires_grad and len(calls) == 2  # gradients enabled: the autograd path
 
 
+def test_one_call_model_forward_on_more_than_1024_crystals(golden_model):
+    """Above 1024 crystals the offsets come from their own launch instead of the geometry launch: same outputs as the
+    torch shell, and the first crystals' outputs equal those of a batch that holds only them (below the limit)."""
+    from crystalformer_b200.model import Latticeformer, default_params
+    torch.manual_seed(5)
+    model = Latticeformer(default_params(num_layers=2)).cuda()
+    cb = make_crystals(77, 1100, uniform_atoms(1, 3), length_range=(4.0, 9.0))
+    t = lambda x: torch.as_tensor(x).cuda()
+    of = lambda c: types.SimpleNamespace(x=t(c.x), pos=t(c.pos), batch=t(c.batch), trans_vec=t(c.trans_vec), sizes=t(c.sizes))
+    data, head = of(cb), of(cb.select(range(300)))
+    model.train()
+    with torch.no_grad():
+        model(head)  # fixes gauss_scale
+    model.eval()
+    with torch.no_grad():
+        y = model(data)
+        y_head = model(head)
+        model.native = False
+        y_shell = model(data)
+    assert rel_err(y.cpu().numpy(), y_shell.cpu().numpy()) < 1e-5
+    assert rel_err(y[:300].cpu().numpy(), y_head.cpu().numpy()) < 1e-5
+
+
 @pytest.mark.parametrize("atoms", [(1, 7), (20, 45)])
 def test_fused_dense_block_equals_the_sgemm_path(golden_model, atoms):
     """The tensor-core dense block (three-product TF32 splitting) against the same forward with cuBLAS SGEMMs: fp32-level
