@@ -3,7 +3,7 @@
 //
 // The reference's Latticeformer.forward (models/latticeformer.py:211-302) is a chain of framework calls; at the sizes
 // of a crystal batch the host cannot issue them as fast as the GPU retires them.  Here the chain is issued back to
-// back from C++ on one stream: two geometry launches, the embedding (inside the first dense block of the encoder when
+// back from C++ on one stream: one geometry launch, the embedding (inside the first dense block of the encoder when
 // its packed weight is given, else one SGEMM), the encoder stack, and one fused kernel for the pooling (models/pooling.py:19-25 with the fixed summation tree of irregular_mean_fwd.cu) and the
 // multi-layer-perceptron head (Linear - ReLU - Linear, models/latticeformer.py:176-209 with norm_type "no").
 // No allocation, no synchronisation: scratch comes from the caller's workspace.

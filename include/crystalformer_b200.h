@@ -312,7 +312,7 @@ int cf_peer_gather_collect(const uint64_t *cells, uint32_t step, const int64_t *
  * Inference forward of the whole model in one host call (what Latticeformer.forward does in eval mode,
  * models/latticeformer.py:211-302, with pooling "avr", pre_pooling_op "no", norm_type "no" and a head of the form
  * Linear - ReLU - Linear): y (B, targets) from the species features (N, feature_dim), positions, lattices and sizes.
- * Runs cf_crystal_offsets, the work of cf_batch_prepare and cf_row_order (one launch), the embedding (W_embed
+ * Runs the work of cf_crystal_offsets, cf_batch_prepare and cf_row_order (one launch), the embedding (W_embed
  * (128, feature_dim), no bias; one SGEMM unless W_embed_packed is given), cf_encoder_forward (same weights /
  * scalars / box arguments) and a fused mean + head kernel (W1 (hidden,128), b1, W2 (targets,hidden), b2; hidden <= 1024).  N, E = sum n, sum n^2 and max_atoms are host
  * integers the caller knows from the sizes.  workspace: cf_model_workspace_bytes(N, B, E, ff_dim) bytes, 256-byte
