@@ -202,11 +202,12 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
             SideStream &side = side_stream();
             forked = side.ok && cudaEventRecord(side.fork, s) == cudaSuccess &&
                      cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
-            // the row tickets of all layers, zeroed once here instead of by a phi launch per layer
-            if (K > 0 && num_layers <= 16 && (tickets = row_ticket_block(num_layers)) != nullptr &&
-                cudaMemsetAsync(tickets, 0, sizeof(unsigned) * num_layers, forked ? side.stream : s) != cudaSuccess)
-                tickets = nullptr;
             rc = launch_term_list_build(tb, forked ? side.stream : s);
+            // the row tickets of all layers, zeroed once here instead of by a phi launch per layer (on the main stream,
+            // ahead of the first dense block: the list build is the longer of the two branches)
+            if (K > 0 && num_layers <= 16 && (tickets = row_ticket_block(num_layers)) != nullptr &&
+                cudaMemsetAsync(tickets, 0, sizeof(unsigned) * num_layers, s) != cudaSuccess)
+                tickets = nullptr;
             if (forked && cudaEventRecord(side.join, side.stream) != cudaSuccess) rc = launch_status("term list join");
             if (rc != CF_OK) return rc;
             lists.pool = tb.pool; lists.start = tb.start; lists.count = tb.count; lists.dmin = tb.dmin; lists.window = tb.window;

@@ -5,12 +5,12 @@
 namespace cf {
 namespace {
 
-constexpr int TL_THREADS = 128;
-constexpr int TL_WARPS = TL_THREADS / 32;
+// Threads per row of the build: 128 for batches of small crystals (many rows, short walks), 256 when crystals have
+// more than 32 atoms (the warps split a row's columns, so a long row finishes sooner).
 
 // Enumerates the terms of one 32-key chunk of a row that belong to warp `wr` (columns dealt round-robin, rotated by
 // the chunk as in the row kernel) and calls visit(d2, n1, n2, n3) for every term of this lane's key with d2 <= thr.
-template <class Visit>
+template <int TL_WARPS, class Visit>
 __device__ __forceinline__ void walk_chunk(const Cell &cell, int R1, int R2, int R3, float4 r, float thr, bool live,
                                            int ch, int wr, Visit &&visit)
 {
@@ -55,8 +55,10 @@ __device__ __forceinline__ void walk_chunk(const Cell &cell, int R1, int R2, int
     }
 }
 
+template <int TL_THREADS>
 __global__ void __launch_bounds__(TL_THREADS) term_list_build_kernel(const TermListBuild p)
 {
+    constexpr int TL_WARPS = TL_THREADS / 32;
     extern __shared__ int smem_i[];
     int *cntw = smem_i;                                      // [4][max_atoms] entries per (warp, key)
     float *thr = reinterpret_cast<float *>(cntw + TL_WARPS * p.max_atoms);  // [max_atoms] d2 threshold per key
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(TL_THREADS) term_list_build_kernel(const TermL
             const float4 r = make_float4(pp[0], pp[1], pp[2], 0.f);
             int cnt = 0;
             float dm = INFINITY;
-            walk_chunk(cell, R1, R2, R3, r, live ? thr[j] : 0.f, live, ch, wr, [&](float d2, int, int, int) {
+            walk_chunk<TL_WARPS>(cell, R1, R2, R3, r, live ? thr[j] : 0.f, live, ch, wr, [&](float d2, int, int, int) {
                 ++cnt;
                 dm = fminf(dm, d2);
             });
@@ -175,7 +177,7 @@ __global__ void __launch_bounds__(TL_THREADS) term_list_build_kernel(const TermL
             const float *pp = p.pos_ij + 3 * (e0 + (live ? j : 0));
             const float4 r = make_float4(pp[0], pp[1], pp[2], 0.f);
             float2 *out = p.pool + base + (live ? cntw[wr * p.max_atoms + j] : 0);
-            walk_chunk(cell, R1, R2, R3, r, live ? thr[j] : 0.f, live, ch, wr, [&](float d2, int n1, int n2, int n3) {
+            walk_chunk<TL_WARPS>(cell, R1, R2, R3, r, live ? thr[j] : 0.f, live, ch, wr, [&](float d2, int n1, int n2, int n3) {
                 *out++ = make_float2(d2, __int_as_float(pack_key(j, abs(n1), abs(n2), abs(n3))));
             });
         }
@@ -290,15 +292,17 @@ int launch_term_list_build(const TermListBuild &b, cudaStream_t s)
 {
     if (b.N == 0) return CF_OK;
     if (cudaMemsetAsync(b.cursor, 0, sizeof(unsigned long long), s) != cudaSuccess) return launch_status("term list cursor");
-    const size_t smem = sizeof(int) * (2 * TL_WARPS + 1) * (size_t)b.max_atoms;
+    const int threads = b.max_atoms <= 32 ? 128 : 256;
+    const size_t smem = sizeof(int) * (2 * (threads / 32) + 1) * (size_t)b.max_atoms;
+    auto kernel = threads == 128 ? term_list_build_kernel<128> : term_list_build_kernel<256>;
     if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(term_list_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
             return fail(CF_ERR_RANGE, "term list: %zu bytes of shared memory for max_atoms=%d not available", smem, b.max_atoms);
         }
     }
     const long long cap = (long long)sm_count() * 8;
-    term_list_build_kernel<<<(unsigned)(b.N < cap ? b.N : cap), TL_THREADS, smem, s>>>(b);
+    kernel<<<(unsigned)(b.N < cap ? b.N : cap), threads, smem, s>>>(b);
     return launch_status("term_list_build_kernel");
 }
 
