@@ -77,3 +77,15 @@ def test_package_refuses_cpu_tensors():
     from crystalformer_b200 import ops
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.segment_mean(torch.zeros((4, 8)), torch.tensor([0, 4]))
+
+
+def test_peer_gather_descriptor_matches_the_header_layout():
+    """cf_peer_gather of the header: two int32, one int64, two uint32, CF_MAX_PEERS pointers, naturally aligned."""
+    from crystalformer_b200 import _lib
+    header = open(os.path.join(REPO, "include", "crystalformer_b200.h")).read()
+    peers = int(re.search(r"#define CF_MAX_PEERS (\d+)", header).group(1))
+    handle = int(re.search(r"#define CF_PEER_HANDLE_BYTES (\d+)", header).group(1))
+    assert peers == _lib.MAX_PEERS and handle == _lib.PEER_HANDLE_BYTES
+    D = _lib.PeerGatherDescriptor
+    assert ctypes.sizeof(D) == 24 + 8 * peers
+    assert (D.world.offset, D.rank.offset, D.rows_per_rank.offset, D.step.offset, D.cells.offset) == (0, 4, 8, 16, 24)
