@@ -44,6 +44,9 @@ SIGNATURES = {
                                     I32, P, P, P, P, P, P, F64, P],
     "cf_infinite_attn_bwd_listed": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                                     I32, P, P, P, P, P, P, P, P, P, P, P, F64, P],
+    "cf_row_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
+    "cf_infinite_attn_fwd_sorted": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
+                                    I32, P, P, P, P],
     "cf_row_cost": [P, P, I64, I64, F64, P, P],
     "cf_row_order": [P, P, I64, I64, F64, P, P],
     "cf_reci_phase": [P, P, P, P, I64, P, P],
@@ -90,6 +93,11 @@ def load() -> ctypes.CDLL:
         lib.cf_encoder_workspace_floats.restype = c_int64
         lib.cf_term_list_workspace_bytes.argtypes = [I64, I64]
         lib.cf_term_list_workspace_bytes.restype = c_int64
+        lib.cf_row_list_workspace_bytes.argtypes = [I64, I64]
+        lib.cf_row_list_workspace_bytes.restype = c_int64
+        lib.cf_set_sorted_rows.argtypes = [c_int]
+        lib.cf_set_sorted_rows.restype = None
+        lib.cf_get_sorted_rows.restype = c_int
         lib.cf_model_workspace_bytes.argtypes = [I64, I64, I64, I64]
         lib.cf_model_workspace_bytes.restype = c_int64
         for name, argtypes in SIGNATURES.items():

@@ -51,7 +51,9 @@ def register_edge_info(edges: Tensor, row_start: Tensor, max_atoms: int, row_ord
     key = (edges.data_ptr(), tuple(edges.shape), edges.device, edges._version)
     if row_order is None:
         row_order = heaviest_first(row_start)
-    _EDGE_CACHE[key] = (row_start, int(max_atoms), row_order)
+    # the entry holds `edges` itself: while it lives the allocator cannot hand the same address to another batch's
+    # edge list (same E = sum n^2, other crystal sizes), which would otherwise hit this key with stale offsets
+    _EDGE_CACHE[key] = (row_start, int(max_atoms), row_order, edges)
     while len(_EDGE_CACHE) > 16:
         _EDGE_CACHE.popitem(last=False)
 
@@ -59,14 +61,14 @@ def register_edge_info(edges: Tensor, row_start: Tensor, max_atoms: int, row_ord
 def edge_info(edges: Tensor, N: int) -> Tuple[Tensor, int, Tensor]:
     key = (edges.data_ptr(), tuple(edges.shape), edges.device, edges._version)
     hit = _EDGE_CACHE.get(key)
-    if hit is not None:
-        return hit
+    if hit is not None and hit[3] is edges:
+        return hit[:3]
     row_start = torch.zeros(N + 1, dtype=torch.int64, device=edges.device)
     row_start.scatter_add_(0, edges[0] + 1, torch.ones_like(edges[0]))
     row_start = row_start.cumsum(0)
     max_atoms = int((row_start[1:] - row_start[:-1]).max().item()) if N > 0 else 1
     register_edge_info(edges, row_start, max_atoms)
-    return _EDGE_CACHE[key]
+    return _EDGE_CACHE[key][:3]
 
 
 # Term lists (ops.term_list_build) of the batches in flight: the geometry is the same for every layer of a forward and
@@ -207,6 +209,15 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         self._scale_known = False
         return super()._load_from_state_dict(*args, **kwargs)
 
+    def headed_pe_proj(self) -> Optional[Tensor]:
+        """pe_dist_proj with one projection per head, (1, H, Dv, K): with value_pe_headed = False the parameter holds a
+        single (Dv, K) matrix shared by the heads (...attention_cuda.py:869-878), which the kernels, compiled for one
+        matrix per head, get as H views of it (autograd sums the heads' gradients back into the shared matrix)."""
+        W = self.pe_dist_proj
+        if W is not None and W.shape[1] == 1 and self.num_heads > 1:
+            W = W.expand(W.shape[0], self.num_heads, W.shape[2], W.shape[3])
+        return W
+
     def _reset_parameters(self):
         # …attention_cuda.py:882-948
         xavier_uniform_(self.q_proj_weight)
@@ -345,7 +356,7 @@ class CrystalformerMultiheadAttentionCUDA(Module):
                 lists = term_lists_for(edges, points, tvecs, rvlen, batch_q, row_start, max_atoms, row_order, cutoff,
                                        lattice_range, minimum_range, -0.5 * P.gauss_lb_real / float(P.scale_real) ** 2)
             attn = InfiniteAttentionFunction.apply(
-                q_scaled, k, v, a, self.pe_dist_proj, points, tvecs, rvlen, batch_q, edges, row_start, max_atoms, K,
+                q_scaled, k, v, a, self.headed_pe_proj(), points, tvecs, rvlen, batch_q, edges, row_start, max_atoms, K,
                 float(dist_max), float(P.value_pe_width_scale), cutoff, lattice_range, minimum_range, row_order, lists)
             weights = None
         else:
@@ -356,7 +367,7 @@ class CrystalformerMultiheadAttentionCUDA(Module):
                 phi = None
                 if P.domain in ("real", "multihead"):
                     extra = (rvlen, cutoff) if cutoff != 0.0 else ()
-                    a_real, W = a, self.pe_dist_proj
+                    a_real, W = a, self.headed_pe_proj()
                     if P.domain == "multihead":
                         # the kernels are compiled for eight heads: the four real-space heads are computed twice and
                         # the copy is dropped (…attention_cuda.py:731-746 passes half the heads to each operator)

@@ -10,6 +10,7 @@ namespace cf {
 
 static thread_local char g_error[512] = "";
 static std::atomic<double> g_floor_log2{-30.0};
+static std::atomic<int> g_sorted_rows{1};
 
 int fail(int code, const char *fmt, ...)
 {
@@ -36,6 +37,8 @@ float weight_floor_log2()
     return f < -1e30 ? -1e30f : (float)f;
 }
 
+bool sorted_rows_enabled() { return g_sorted_rows.load() != 0; }
+
 int sm_count()
 {
     static thread_local int cached_dev = -1, cached = 0;
@@ -61,5 +64,9 @@ const char *cf_last_error(void) { return cf::g_error; }
 void cf_set_weight_floor_log2(double log2_floor) { cf::g_floor_log2.store(log2_floor); }
 
 double cf_get_weight_floor_log2(void) { return cf::g_floor_log2.load(); }
+
+void cf_set_sorted_rows(int enabled) { cf::g_sorted_rows.store(enabled != 0); }
+
+int cf_get_sorted_rows(void) { return cf::g_sorted_rows.load(); }
 
 }  // extern "C"

@@ -19,6 +19,7 @@
 #include "blas_dyn.cuh"
 #include "common.cuh"
 #include "dense_block.cuh"
+#include "row_list.cuh"
 #include "term_list.cuh"
 
 namespace cf {
@@ -36,6 +37,11 @@ int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const
                            float *lse, float *psi_row, const int32_t *row_order, const TermList *list,
                            unsigned *ticket_ready, void *stream);
 unsigned *row_ticket_block(int count);
+int sorted_attn_impl(const float *q, const float *k, const float *v, const float *a, const float *pos_ij,
+                     const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
+                     const int64_t *row_start, int64_t N, int64_t E, int64_t max_atoms, double dist_max, double wscale,
+                     const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out, float *lse,
+                     const RowListView &view, int sched_slot, bool zeroed, cudaStream_t s);
 namespace {
 
 // A second stream and two events per (host thread, device), created on first use and kept for the life of the
@@ -141,7 +147,9 @@ extern "C" int64_t cf_encoder_workspace_floats(int64_t N, int64_t E, int64_t ff_
 {
     // qkv (384) + q,k,v (3 x 128) + attention output (128) + a (8) + lse (8) + hidden (ff) per atom, logits per edge,
     // then the term lists: directory (2 ints per edge), allocation cursor, pool (2 floats per entry)
-    return N * (384 + 384 + 128 + 8 + 8 + ff_dim) + E * 8 + 64 + (int64_t)(cf::term_list_workspace_bytes(N, E) + 3) / 4;
+    // (or, for batches of small crystals, the row lists: whichever is larger)
+    const size_t lists = cf::term_list_workspace_bytes(N, E), rows = cf::row_list_workspace_bytes(N, E);
+    return N * (384 + 384 + 128 + 8 + 8 + ff_dim) + E * 8 + 64 + (int64_t)((lists > rows ? lists : rows) + 3) / 4;
 }
 
 extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const float *const *weights, const double *scalars,
@@ -184,36 +192,60 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
     // matter to any layer are found once.  The widest Gaussian any layer can produce has a = lower_bound x a_factor.
     TermList lists{};
     const TermList *list = nullptr;
+    RowListView row_lists{};
+    bool sorted_rows = false;  // batches of crystals of at most 32 atoms with a value encoding: row lists + sorted row kernel
     bool forked = false;  // the build runs on the side stream; the first attention waits for it
     unsigned *tickets = nullptr;
     if (pos_ij != nullptr && weight_floor_log2() > -200.0f) {
         float a_widest = -INFINITY;
         for (int l = 0; l < num_layers; ++l) a_widest = fmaxf(a_widest, (float)(scalars[6 * l + 4] * scalars[6 * l + 2]));
         if (a_widest < 0.0f) {
-            TermListBuild tb{};
-            tb.pos_ij = pos_ij; tb.tvecs = tvecs; tb.rvlen = cutoff_radius != 0.0 ? rvlen : nullptr;
-            tb.batch = batch; tb.edges = edges; tb.row_start = row_start; tb.row_order = row_order;
-            tb.N = N; tb.E = E; tb.max_atoms = (int)max_atoms;
-            tb.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
-            tb.a_widest = a_widest;
-            tb.window = term_window(weight_floor_log2(), a_widest);
-            term_list_carve(logit + E * 8 + 64, N, E, &tb.start, &tb.count, &tb.dmin, &tb.cursor, &tb.pool);
-            tb.capacity = (long long)term_pool_entries(N, E);
+            const BoxRule rule{(float)cutoff_radius, lattice_range, minimum_range};
+            const float window = term_window(weight_floor_log2(), a_widest);
             SideStream &side = side_stream();
             forked = side.ok && cudaEventRecord(side.fork, s) == cudaSuccess &&
                      cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
-            rc = launch_term_list_build(tb, forked ? side.stream : s);
-            // the row tickets of all layers, zeroed once here instead of by a phi launch per layer (on the main stream,
-            // ahead of the first dense block: the list build is the longer of the two branches)
-            if (K > 0 && num_layers <= 16 && (tickets = row_ticket_block(num_layers)) != nullptr &&
-                cudaMemsetAsync(tickets, 0, sizeof(unsigned) * num_layers, s) != cudaSuccess)
-                tickets = nullptr;
+            sorted_rows = sorted_rows_enabled() && K == 64 && max_atoms <= ROW_LIST_MAX_KEYS && N < (1ll << 31) && E < (1ll << 31);
+            if (sorted_rows) {
+                RowListBuild rb{};
+                rb.pos_ij = pos_ij; rb.tvecs = tvecs; rb.rvlen = cutoff_radius != 0.0 ? rvlen : nullptr;
+                rb.batch = batch; rb.edges = edges; rb.row_start = row_start; rb.row_order = row_order;
+                rb.N = N; rb.E = E; rb.rule = rule; rb.a_widest = a_widest; rb.window = window; rb.coop_chunks = ROW_COOP_CHUNKS;
+                rb.out = row_lists = row_list_carve(logit + E * 8 + 64, N, E);
+                rc = launch_row_list_build(rb, forked ? side.stream : s);
+            } else {
+                TermListBuild tb{};
+                tb.pos_ij = pos_ij; tb.tvecs = tvecs; tb.rvlen = cutoff_radius != 0.0 ? rvlen : nullptr;
+                tb.batch = batch; tb.edges = edges; tb.row_start = row_start; tb.row_order = row_order;
+                tb.N = N; tb.E = E; tb.max_atoms = (int)max_atoms;
+                tb.rule = rule;
+                tb.a_widest = a_widest;
+                tb.window = window;
+                term_list_carve(logit + E * 8 + 64, N, E, &tb.start, &tb.count, &tb.dmin, &tb.cursor, &tb.pool);
+                tb.capacity = (long long)term_pool_entries(N, E);
+                rc = launch_term_list_build(tb, forked ? side.stream : s);
+                // the row tickets of all layers, zeroed once here instead of by a phi launch per layer (on the main
+                // stream, ahead of the first dense block: the list build is the longer of the two branches)
+                if (K > 0 && num_layers <= 16 && (tickets = row_ticket_block(num_layers)) != nullptr &&
+                    cudaMemsetAsync(tickets, 0, sizeof(unsigned) * num_layers, s) != cudaSuccess)
+                    tickets = nullptr;
+                lists.pool = tb.pool; lists.start = tb.start; lists.count = tb.count; lists.dmin = tb.dmin; lists.window = tb.window;
+                list = &lists;
+            }
             if (forked && cudaEventRecord(side.join, side.stream) != cudaSuccess) rc = launch_status("term list join");
             if (rc != CF_OK) return rc;
-            lists.pool = tb.pool; lists.start = tb.start; lists.count = tb.count; lists.dmin = tb.dmin; lists.window = tb.window;
-            list = &lists;
         }
     }
+    // one attention call of layer l (dist_max, W of that layer)
+    auto attention = [&](int l, double dist_max, const float *W, float *attn_out, float *lse_out) {
+        if (sorted_rows)
+            return sorted_attn_impl(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, N, E, max_atoms, dist_max, wscale,
+                                    W, cutoff_radius, lattice_range, minimum_range, attn_out, lse_out, row_lists,
+                                    l < ROW_SCHED_SLOTS - 1 ? l : ROW_SCHED_SLOTS - 1, l < ROW_SCHED_SLOTS - 1, s);
+        return infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS, HEAD_DIM,
+                                      E, K, max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range,
+                                      attn_out, logit, lse_out, nullptr, row_order, list, tickets ? tickets + l : nullptr, s);
+    };
 
     // Fused dense path: every layer brings its weights packed for the tensor-core kernel (slot 10) and the
     // feed-forward width is a multiple of 128.  One launch per layer boundary instead of four GEMMs and two
@@ -239,10 +271,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
             const float *const *w = weights + 11 * l;
             const double *sc = scalars + 6 * l;
             if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
-            rc = infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS,
-                                        HEAD_DIM, E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range,
-                                        minimum_range, attn, logit, lse, nullptr, row_order, list,
-                                        tickets ? tickets + l : nullptr, s);
+            rc = attention(l, sc[5], w[3], attn, lse);
             if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
             if (rc != CF_OK) break;
             DenseArgs t{};
@@ -276,10 +305,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
         const long long nh = N * HEADS;
         qkv_post_kernel<<<(unsigned)((nh + 127) / 128), 128, 0, s>>>(qkv, w[1], w[2], w[5], ls, N, q, k, v, a, x);
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l]), s);
-        rc = infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS,
-                                    HEAD_DIM, E, K, max_atoms, sc[5], wscale, w[3], cutoff_radius, lattice_range,
-                                    minimum_range, attn, logit, lse, nullptr, row_order, list,
-                                        tickets ? tickets + l : nullptr, s);
+        rc = attention(l, sc[5], w[3], attn, lse);
         if (attn_events) cudaEventRecord(reinterpret_cast<cudaEvent_t>(attn_events[2 * l + 1]), s);
         if (rc != CF_OK) break;
         st = linear(bl, handle, attn, w[4], x, rows, 128, 128, 1.0f);

@@ -16,7 +16,6 @@
 //                             turn-around of BinAccumulator; the four partial histograms are added in a fixed order
 //                             (deterministic), projected with W and added to sum_j p_ij v_j.
 #include <atomic>
-#include <cstdlib>
 
 #include "lattice_core.cuh"
 #include "term_list.cuh"
@@ -54,6 +53,7 @@ struct RowArgs {
     const float *q, *k, *v, *a, *pos, *pos_ij, *tvecs, *rvlen, *W;
     const int64_t *batch, *edges, *row_start;
     const int32_t *row_order;  // optional: atoms in the order they are to be processed (heaviest first)
+    const unsigned *rows_on_device;  // optional: the number of rows to process (entries of row_order), read on the device
     unsigned *ticket;          // zeroed before the launch: rows beyond the first wave are handed out through it
     TermList list;             // optional (pool == NULL: none): the rows' candidate terms, found once per batch
     long long E;
@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
     __shared__ long long next_slot_sh[GROUPS];
     const long long first_wave = (long long)gridDim.x * GROUPS;
     long long slot = (long long)blockIdx.x * GROUPS + group;
-    if (slot >= p.N) return;
+    const long long rows = p.rows_on_device ? (long long)*p.rows_on_device : p.N;
+    if (slot >= rows) return;
     long long i = p.row_order ? p.row_order[slot] : slot;
     long long c = p.batch[i];
     long long e0 = p.row_start[i];
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
 
     while (true) {
         // stage 0 of the look-ahead: the next row's atom; thread 0 draws the ticket of the row after it
-        const bool has_next = nslot < p.N;
+        const bool has_next = nslot < rows;
         const long long i_n = has_next ? (p.row_order ? (long long)p.row_order[nslot] : nslot) : 0;
         unsigned drawn = 0;
         if (p.ticket && rt == 0) drawn = atomicAdd(p.ticket, 1u);
@@ -210,7 +211,7 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             const int sub = rt % ROW_WARPS;
             const bool mine = jk < n;
             const long long e = e0 + (mine ? jk : 0);
-            const int first = mine ? p.list.start[e] : -1;
+            const int first = (mine && p.list.start != nullptr) ? p.list.start[e] : -1;
             const int cnt = first >= 0 ? p.list.count[e] : 0;
             const float m = first >= 0 ? p.list.dmin[e] : 0.f;
             const float2 *ent = p.list.pool + (first >= 0 ? first : 0);
@@ -676,6 +677,7 @@ int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const
                            float *lse, float *psi_row, const int32_t *row_order, const TermList *list, unsigned *ticket_ready,
                            void *stream);
 unsigned *row_ticket_block(int count);
+int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s);
 }
 
 extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
@@ -750,12 +752,10 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
     CF_REQUIRE(K == 0 || ticket != nullptr, CF_ERR_CUDA, "cf_infinite_attn_fwd: the row ticket could not be set up");
     phi.zero_word = ticket;
     // With term lists and rows of at most 32 keys the row kernel sums phi from the lists itself (one launch less per
-    // layer, and the lists are read while they are needed); CF_PHI_IN_ROW=0 in the environment keeps the phi kernel, 2
-    // lets rows of any size sum phi themselves.
-    // Rows of more keys keep the phi kernel: with four lanes per key and one block per row the same sums took longer
-    // inside the row kernel (64 crystals of 100-200 atoms: 663 against 621 us per call).
-    static const int phi_mode = [] { const char *e = getenv("CF_PHI_IN_ROW"); return e ? atoi(e) : 1; }();
-    const bool phi_in_row = phi_mode != 0 && list != nullptr && pos_ij != nullptr && K > 0 && (max_atoms <= 32 || phi_mode == 2);
+    // layer, and the lists are read while they are needed).  Rows of more keys keep the phi kernel: with four lanes per
+    // key and one block per row the same sums took longer inside the row kernel (64 crystals of 100-200 atoms: 663
+    // against 621 us per call).
+    const bool phi_in_row = list != nullptr && pos_ij != nullptr && K > 0 && max_atoms <= 32;
     int rc = CF_OK;
     if (phi_in_row) {
         if (ticket_ready == nullptr && cudaMemsetAsync(ticket, 0, sizeof(unsigned), s) != cudaSuccess)
@@ -781,39 +781,67 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
     if (list != nullptr && pos_ij != nullptr && K > 0) p.list = *list;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
-    // warps per atom row: 1 for crystals of up to 12 atoms, else 4 (CF_ROW_WARPS = 1, 2 or 4 in the environment
-    // overrides; fewer warps per row keep more rows in flight but stretch the heaviest rows, which bound the kernel)
-    static const int forced = [] { const char *e = getenv("CF_ROW_WARPS"); return e ? atoi(e) : 0; }();
-    int row_warps = max_atoms <= 12 ? 1 : WARPS;
-    if (forced == 1 || forced == 2 || forced == 4) row_warps = forced;
+    return launch_rows(p, K, N, s);
+}
+
+namespace cf {
+// Launches the row kernel for `grid_rows` rows (the grid is sized for them; the kernel itself processes p.N rows, or
+// *p.rows_on_device).  Warps per atom row: 1 for crystals of up to 12 atoms, else 4 (fewer warps per row keep more
+// rows in flight but stretch the heaviest rows, which bound the kernel).
+int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s)
+{
+    const int max_atoms = p.max_atoms;
+    const int row_warps = max_atoms <= 12 ? 1 : WARPS;
     const int groups = WARPS / row_warps;
-    const size_t smem = sizeof(float) * groups * row_group_floats((int)max_atoms, K > 0, row_warps);
+    const size_t smem = sizeof(float) * groups * row_group_floats(max_atoms, K > 0, row_warps);
     void (*kernel)(const RowArgs);
     if (K > 0)
-        kernel = row_warps == 1 ? infinite_attn_rows_kernel<64, 1> : (row_warps == 2 ? infinite_attn_rows_kernel<64, 2> : infinite_attn_rows_kernel<64, 4>);
+        kernel = row_warps == 1 ? infinite_attn_rows_kernel<64, 1> : infinite_attn_rows_kernel<64, 4>;
     else
-        kernel = row_warps == 1 ? infinite_attn_rows_kernel<0, 1> : (row_warps == 2 ? infinite_attn_rows_kernel<0, 2> : infinite_attn_rows_kernel<0, 4>);
+        kernel = row_warps == 1 ? infinite_attn_rows_kernel<0, 1> : infinite_attn_rows_kernel<0, 4>;
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
-            return fail(CF_ERR_RANGE, "cf_infinite_attn_fwd: %zu bytes of shared memory for max_atoms=%lld not available",
-                        smem, (long long)max_atoms);
+            return fail(CF_ERR_RANGE, "cf_infinite_attn_fwd: %zu bytes of shared memory for max_atoms=%d not available",
+                        smem, max_atoms);
         }
     }
-    static thread_local size_t cached_smem[6] = {0, 0, 0, 0, 0, 0};
-    static thread_local int cached_occ[6] = {0, 0, 0, 0, 0, 0};
-    const int slot = (K > 0 ? 3 : 0) + (row_warps == 1 ? 0 : (row_warps == 2 ? 1 : 2));
+    static thread_local size_t cached_smem[4] = {0, 0, 0, 0};
+    static thread_local int cached_occ[4] = {0, 0, 0, 0};
+    const int slot = (K > 0 ? 2 : 0) + (row_warps == 1 ? 0 : 1);
     if (cached_occ[slot] == 0 || cached_smem[slot] != smem) {
         int occ = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, THREADS, smem) != cudaSuccess || occ <= 0) occ = 1;
         cached_occ[slot] = occ;
         cached_smem[slot] = smem;
     }
-    const long long want = (N + groups - 1) / groups;
+    const long long want = (grid_rows + groups - 1) / groups;
     const long long cap = (long long)sm_count() * cached_occ[slot];
     const int blocks = (int)(want < cap ? want : cap);
     kernel<<<blocks, THREADS, smem, s>>>(p);
     return launch_status("cf_infinite_attn_fwd");
 }
+
+// The rows that the sorted row kernel (infinite_attn_sorted.cu) left over: atoms rows[0 .. *count), processed by the
+// row kernel above without lists (phi and the candidates by enumeration).  `ticket` must be zero on entry.
+int launch_leftover_rows(const float *q, const float *k, const float *v, const float *a, const float *pos_ij,
+                         const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
+                         const int64_t *row_start, int64_t N, int64_t E, int64_t max_atoms, double dist_max,
+                         double wscale, const float *W, double cutoff_radius, int lattice_range, int minimum_range,
+                         float *out, float *lse, const int *rows, const unsigned *count, unsigned *ticket, cudaStream_t s)
+{
+    RowArgs p{};
+    p.q = q; p.k = k; p.v = v; p.a = a; p.pos_ij = pos_ij; p.tvecs = tvecs; p.rvlen = rvlen; p.W = W;
+    p.batch = batch; p.edges = edges; p.row_start = row_start; p.row_order = rows; p.rows_on_device = count; p.E = E;
+    p.out = out; p.logit = nullptr; p.lse = lse; p.psi_row = nullptr; p.N = N; p.max_atoms = (int)max_atoms;
+    p.keep_logit = 0;
+    p.phi_in_row = 1;  // no list: every edge's phi is enumerated inside the row kernel
+    p.ticket = ticket;
+    p.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
+    p.basis = make_basis_params(64, dist_max, wscale, weight_floor_log2());
+    // left-over rows are rare: a grid of one block per SM draws them through the ticket
+    return launch_rows(p, 64, (long long)sm_count() * (max_atoms <= 12 ? WARPS : 1), s);
+}
+}  // namespace cf
 
 unsigned *cf::row_ticket_block(int count) { return next_ticket_block(count); }

@@ -196,7 +196,7 @@ class CrystalformerEncoderCUDA(Module):
             att, P = layer.self_attn, layer.self_attn.params
             wqkv = torch.cat((att.q_proj_weight, att.k_proj_weight, att.v_proj_weight), 0).detach().float().contiguous()
             tensors = [wqkv, att.in_proj_bias, att.lattice_pos_weights,
-                       att.pe_dist_proj if att.pe_dist_proj is not None else None, att.out_proj.weight, att.out_proj.bias,
+                       att.headed_pe_proj(), att.out_proj.weight, att.out_proj.bias,
                        layer.linear1.weight, layer.linear1.bias, layer.linear2.weight, layer.linear2.bias, None]
             tensors = [None if t is None else t.detach().float().contiguous() for t in tensors]
             if self.dense_fused and layer.linear1.weight.shape[0] % 128 == 0:

@@ -37,6 +37,18 @@ def _want(t: Optional[torch.Tensor], dtype, name: str, device=None) -> Optional[
     return t if t.is_contiguous() else t.contiguous()
 
 
+def _check_projection(W: Optional[torch.Tensor], H: int, K: int, name: str) -> None:
+    """The kernels index W as one (Dv, K) matrix per head: a projection shared by the heads (shape (..., 1, Dv, K)) must
+    be expanded to H heads by the caller, or the kernels would read past its end."""
+    if W is not None and K > 0 and (W.dim() < 3 or W.shape[-3] != H or W.shape[-1] != K):
+        raise ValueError(f"{name}: W must end in (H={H}, Dv, K={K}), got {tuple(W.shape)}")
+
+
+def set_sorted_rows(enabled: bool) -> None:
+    """Whether the one-call forwards may use row lists and the sorted row kernel (cf_set_sorted_rows)."""
+    _lib.load().cf_set_sorted_rows(c_int(1 if enabled else 0))
+
+
 def set_weight_floor_log2(value: float) -> None:
     _lib.load().cf_set_weight_floor_log2(c_double(value))
 
@@ -105,6 +117,7 @@ def lattice_sum_fwd(a, pos_ij, tvecs, batch, edges, K, dist_max, wscale, W=None,
     batch, edges = _want(batch, torch.int64, "batch", dev), _want(edges, torch.int64, "edges", dev)
     W, rvlen = _want(W, torch.float32, "W", dev), _want(rvlen, torch.float32, "rvlen", dev)
     E, H, N = edges.shape[1], a.shape[1], batch.shape[0]
+    _check_projection(W, H, K, "lattice_sum_fwd")
     if W is not None:
         W_num = 1 if W.dim() == 3 else W.shape[0]
         Dv = W.shape[-2]
@@ -226,6 +239,48 @@ def term_list_build(pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, cu
     return work, float(a_widest)
 
 
+def row_list_build(pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, cutoff_radius, lattice_range,
+                   minimum_range, a_widest, row_order=None):
+    """Row lists of a batch of crystals of at most 32 atoms (see cf_row_list_build): the workspace tensor to hand to
+    ``infinite_attn_fwd_sorted`` for every layer of the batch."""
+    dev = pos_ij.device
+    pos_ij, tvecs, rvlen = (_want(t, torch.float32, n, dev) for t, n in ((pos_ij, "pos_ij"), (tvecs, "tvecs"), (rvlen, "rvlen")))
+    batch, edges, row_start = (_want(t, torch.int64, n, dev) for t, n in
+                               ((batch, "batch"), (edges, "edges"), (row_start, "row_start")))
+    N, E = batch.shape[0], edges.shape[1]
+    work = torch.empty(int(_lib.load().cf_row_list_workspace_bytes(N, E)), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_row_list_build", _ptr(pos_ij), _ptr(tvecs), _ptr(rvlen), _ptr(batch), _ptr(edges), _ptr(row_start),
+                  _ptr(_want(row_order, torch.int32, "row_order", dev)), c_int64(N), c_int64(E), c_int64(max_atoms),
+                  c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), c_double(a_widest),
+                  _ptr(work), _stream(dev))
+    return work
+
+
+def infinite_attn_fwd_sorted(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale,
+                             W, cutoff_radius, lattice_range, minimum_range, row_lists):
+    """Fused attention forward over a batch's row lists (inference; crystals of at most 32 atoms, K = 64).
+    Returns (out (N,H,D), lse (N,H))."""
+    dev = q.device
+    q, k, v, a, tvecs = (_want(t, torch.float32, n, dev) for t, n in
+                         ((q, "q"), (k, "k"), (v, "v"), (a, "a"), (tvecs, "tvecs")))
+    pos_ij, rvlen, W = (_want(t, torch.float32, n, dev) for t, n in ((pos_ij, "pos_ij"), (rvlen, "rvlen"), (W, "W")))
+    batch, edges, row_start = (_want(t, torch.int64, n, dev) for t, n in
+                               ((batch, "batch"), (edges, "edges"), (row_start, "row_start")))
+    N, H, D = q.shape
+    _check_projection(W, H, K, "infinite_attn_fwd_sorted")
+    E, B = edges.shape[1], tvecs.shape[0]
+    out = torch.empty((N, H, D), dtype=torch.float32, device=dev)
+    lse = torch.empty((N, H), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.call("cf_infinite_attn_fwd_sorted", _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(pos_ij), _ptr(tvecs), _ptr(rvlen),
+                  _ptr(batch), _ptr(edges), _ptr(row_start), c_int64(N), c_int64(B), c_int64(H), c_int64(D), c_int64(E),
+                  c_int64(K), c_int64(max_atoms), c_double(dist_max), c_double(wscale), _ptr(W),
+                  c_double(cutoff_radius or 0.0), c_int(lattice_range), c_int(minimum_range), _ptr(out), _ptr(lse),
+                  _ptr(row_lists), _stream(dev))
+    return out, lse
+
+
 def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale, W,
                       cutoff_radius, lattice_range, minimum_range, want_psi_row=False, pos=None, row_order=None,
                       term_lists=None):
@@ -240,6 +295,7 @@ def infinite_attn_fwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
     batch, edges, row_start = (_want(t, torch.int64, n, dev) for t, n in
                                ((batch, "batch"), (edges, "edges"), (row_start, "row_start")))
     N, H, D = q.shape
+    _check_projection(W, H, K, "infinite_attn_fwd")
     E, B = edges.shape[1], tvecs.shape[0]
     out = torch.empty((N, H, D), dtype=torch.float32, device=dev)
     logit = torch.empty((E, H), dtype=torch.float32, device=dev)
@@ -278,6 +334,7 @@ def infinite_attn_bwd(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start,
     batch, edges, row_start = (_want(t, torch.int64, n, dev) for t, n in
                                ((batch, "batch"), (edges, "edges"), (row_start, "row_start")))
     N, H, D = q.shape
+    _check_projection(W, H, K, "infinite_attn_bwd")
     E, B = edges.shape[1], tvecs.shape[0]
     gq, gk, gv = (torch.empty_like(q) for _ in range(3))
     ga = torch.empty((N, H), dtype=torch.float32, device=dev)

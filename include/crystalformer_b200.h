@@ -6,12 +6,21 @@
  * Every entry point
  *   - takes raw DEVICE pointers to contiguous arrays (float32 data, int64 indices, as the reference kernels do),
  *     plain sizes and scalars, and the CUDA stream to launch on (a cudaStream_t passed as void*; NULL = default),
- *   - launches asynchronously on that stream of the CURRENT device; it never synchronises, never allocates and
- *     never frees device memory (outputs and scratch are the caller's, as with the reference wrappers, which
- *     allocate with torch.empty and hand pointers to the kernels),
+ *   - launches asynchronously on that stream of the CURRENT device and does not synchronise; outputs and scratch
+ *     are the caller's (as with the reference wrappers, which allocate with torch.empty and hand pointers to the
+ *     kernels).  The exceptions are named where they are declared: cf_peer_alloc / cf_peer_free allocate and free
+ *     device memory and synchronise the device (set-up calls, never on the data path),
  *   - returns CF_OK or a negative CF_ERR_* code and never throws; cf_last_error() gives the message of the last
  *     failure on the calling thread.
- * The library keeps no per-call state, so it may be called concurrently from one host thread per GPU (the
+ * State kept by the library: the two process-wide tuning values (cf_set_weight_floor_log2, cf_set_sorted_rows), a
+ * side stream and two events per (host thread, device) created by the first cf_encoder_forward / cf_model_forward,
+ * the 8 MiB scratch array of cf_lattice_sum_bwd_static, and a pool of row tickets per device: 64 single counters
+ * handed round-robin to the cf_infinite_attn_fwd[_listed] calls with K > 0 and 8 blocks of 16 handed round-robin to the
+ * one-call forwards that use term lists.  A ticket is reused after 64 calls (8 forwards): at most that many such calls
+ * may be PENDING on one device at a time, whatever streams they were issued on; beyond that two row kernels can share
+ * a counter and rows would be skipped.  (The row-list path, cf_row_list_build / cf_infinite_attn_fwd_sorted and the
+ * one-call forwards of batches of small crystals, keeps its counters in the caller's workspace and has no such limit.)
+ * Otherwise no per-call state, so the library may be called concurrently from one host thread per GPU (the
  * reference's multi-GPU path does that: models/latticeformer.py:274).
  *
  * Compile-time constants of the reference (HEAD_NUM, K_HEAD_DIM, V_HEAD_DIM, VPE_DIM, LATTICE_RANGE, MINIMUM_RANGE;
@@ -54,6 +63,12 @@ const char *cf_last_error(void);
  * accumulate every term.  Process-wide tuning knob, read at launch time. */
 void cf_set_weight_floor_log2(double log2_floor);
 double cf_get_weight_floor_log2(void);
+
+/* Whether cf_encoder_forward / cf_model_forward may take the row-list path (cf_row_list_build +
+ * cf_infinite_attn_fwd_sorted, below) for batches whose crystals have at most 32 atoms; 1 by default, 0 keeps the
+ * term-list kernels for every batch.  Process-wide, read at launch time. */
+void cf_set_sorted_rows(int enabled);
+int cf_get_sorted_rows(void);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Batch preparation.  Replaces get_edge_index and compute_lattice_distances_for_cuda
@@ -242,6 +257,35 @@ int cf_infinite_attn_bwd_listed(const float *q, const float *k, const float *v, 
                                 const float *lse, const float *out, const float *gout, float *gq, float *gk, float *gv,
                                 float *ga, float *glogit, const int32_t *row_order, void *term_lists, double a_widest,
                                 void *stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Row lists and the tensor-core row kernel for batches of small crystals (max_atoms <= 32, K = 64, inference).
+ * Same function as cf_infinite_attn_fwd (real_enc_proj_fwd + fused_dpa_fwd of the reference,
+ * models/kernels/real_enc_proj_fwd.cu:63-169, models/kernels/fused_dpa_fwd_v3.cu), other organisation:
+ * cf_row_list_build stores, per ATOM ROW, all (key, translation) terms within the term-list window of their edge's
+ * nearest image (same rule and a_widest as cf_term_list_build), sorted by distance.  cf_infinite_attn_fwd_sorted then
+ * computes a row with one warp in a single sweep over its entries: weights exp2(a d2 + q.k - M) against an upper
+ * bound M, so that phi, the soft-max statistics and the radial-basis histogram are plain sums over the entries, done
+ * as mma.m16n8k8 products (TF32 operands split into high and low parts: fp32-level accuracy).  The sweep stops at the
+ * first eight entries that are below the weight floor for every head of this layer.  Rows that do not fit the
+ * workspace (more than 4096 entries, or the pool is full) and rows where a head's box misses every listed term are
+ * processed by the enumerating kernel of cf_infinite_attn_fwd inside the same call: results do not depend on the
+ * capacities.  No logits are written (inference); lse (N,H) is.
+ *   workspace: cf_row_list_workspace_bytes(N, E) bytes, 16-byte aligned, built with the weight floor in force at the
+ *   time; it also holds the row counters of the calls that use it, so calls sharing a workspace must be ordered
+ *   (one stream), and every build allows any number of calls.
+ * ---------------------------------------------------------------------------------------------------------- */
+int64_t cf_row_list_workspace_bytes(int64_t N, int64_t E);
+int cf_row_list_build(const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
+                      const int64_t *edges, const int64_t *row_start, const int32_t *row_order, int64_t N, int64_t E,
+                      int64_t max_atoms, double cutoff_radius, int lattice_range, int minimum_range, double a_widest,
+                      void *workspace, void *stream);
+int cf_infinite_attn_fwd_sorted(const float *q, const float *k, const float *v, const float *a, const float *pos_ij,
+                                const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
+                                const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D, int64_t E,
+                                int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
+                                double cutoff_radius, int lattice_range, int minimum_range, float *out, float *lse,
+                                void *row_lists, void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Inference forward of the encoder stack (every layer of CrystalformerEncoderCUDA,
