@@ -17,6 +17,7 @@ constexpr float LN2 = 0.6931471805599453f;
 int fail(int code, const char *fmt, ...);
 int launch_status(const char *what);
 float weight_floor_log2();  // log2 of the weight below which a term is left out of the basis accumulation
+unsigned long long *row_stats_words();  // device words that the sorted row kernel adds its work counts to, or NULL
 bool sorted_rows_enabled();  // the one-call forwards may use row lists and the sorted row kernel (cf_set_sorted_rows)
 
 #define CF_REQUIRE(cond, code, ...) \

@@ -52,6 +52,7 @@ struct SortedRowArgs {
     float inv_bin_step;
     float tile_reach;    // bins beyond which a basis value is below the floor
     float floor_log2;
+    unsigned long long *stats;  // optional: { chunks swept, (chunk, bin tile) pairs computed, rows } are added here
 };
 
 __device__ __forceinline__ void mma_tf32(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1)
@@ -203,6 +204,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
     const float step16 = 16.0f * p.bin_step, step8 = 8.0f * p.bin_step;
     bool more = true;
     int ring_slot = 0;
+    int swept = 0, tiles_done = 0;  // diagnostics (p.stats)
     for (int grp = 0; grp < groups && more; ++grp) {
         int ahead = ring_slot + RING_SLOTS - 1;
         if (ahead >= RING_SLOTS) ahead -= RING_SLOTS;
@@ -254,6 +256,8 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
             const int m_lo = max(0, __float2int_rd(b_lo * 0.0625f));
             const int m_hi = b_hi < 0.0f ? -1 : min(3, __float2int_rd(b_hi * 0.0625f));  // (beyond the last bin: only phi needs the terms)
             const float uu[4] = {x[0] - ucg, x[1] - ucg, x[2] - ucg, x[3] - ucg};
+            swept += two ? 2 : 1;
+            tiles_done += max(m_hi - m_lo + 1, 0) * (two ? 2 : 1);
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
                 if (m < m_lo || m > m_hi) continue;  // (the same for every lane)
@@ -277,6 +281,11 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
         if (++ring_slot == RING_SLOTS) ring_slot = 0;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");  // fetches still in flight after an early end
+    if (p.stats != nullptr && lane == 0) {
+        atomicAdd(p.stats, (unsigned long long)swept);
+        atomicAdd(p.stats + 1, (unsigned long long)tiles_done);
+        if (!COOP || warp == 0) atomicAdd(p.stats + 2, 1ull);
+    }
 
     // ---- accumulators -> shared memory (C fragment: rows g, g + 8; columns = heads 2 t, 2 t + 1)
     __syncwarp();
@@ -446,6 +455,7 @@ int launch_sorted_rows(const SortedRowLaunch &l, cudaStream_t s)
     const float fl = fminf(fmaxf(-weight_floor_log2(), 24.0f), 126.0f);
     p.tile_reach = sqrtf(fl) / bp.bin_step;
     p.floor_log2 = weight_floor_log2();
+    p.stats = row_stats_words();
     auto kernel = l.max_atoms <= 16 ? infinite_attn_sorted_rows_kernel<1> : infinite_attn_sorted_rows_kernel<2>;
     static thread_local bool configured[64][2] = {};
     int dev = 0;

@@ -82,10 +82,14 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
             // ---- the walk: unit u = (pass of 32 translations, quarter of the keys); r + n1 t1 + n2 t2 + n3 t3 is
             //      contracted like the reference's expression
             const int units = 4 * ((T + 31) >> 5);
+            const float inv_s3 = __frcp_rn((float)S3), inv_s2 = __frcp_rn((float)S2);
             for (int u = wr; u < units; u += RL_WARPS) {
                 const int tr = 32 * (u >> 2) + lane;
                 const bool in_box = tr < T;
-                const int i3 = tr % S3, i12 = tr / S3, i2 = i12 % S2, i1 = i12 / S2;
+                // digits of tr in the mixed radix (S1, S2, S3): quotients by a rounded-down product with the reciprocal
+                // (exact for these small integers: tr < 2^12, S <= 65)
+                const int i12 = __float2int_rd(((float)tr + 0.5f) * inv_s3), i3 = tr - i12 * S3;
+                const int i1 = __float2int_rd(((float)i12 + 0.5f) * inv_s2), i2 = i12 - i1 * S2;
                 const int n1 = i1 - R1, n2 = i2 - R2, n3 = i3 - R3;
                 const float f1 = (float)n1, f2 = (float)n2, f3 = (float)n3;
                 const int key123 = (abs(n1) << 8) | (abs(n2) << 16) | (abs(n3) << 24);
@@ -101,13 +105,10 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
                     int base = 0;
                     if (lane == 0) base = atomicAdd(&cnt_s, __popc(mask));
                     base = __shfl_sync(FULL, base, 0);
-                    float dm = keep ? d2 : INFINITY;
                     if (keep) {
                         const int at = base + __popc(mask & lt);
                         if (at < ROW_LIST_CAP) ent[at] = ((unsigned long long)__float_as_uint(d2) << 32) | (unsigned)(key123 | j);
                     }
-                    dm = warp_min(dm);
-                    if (lane == 0) atomicMin(&dmin_s[j], __float_as_int(dm));  // (d2 >= 0: bit patterns order like the values)
                 }
             }
         }
@@ -158,6 +159,8 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
                     rank += (other < item || (other == item && u < t)) ? 1 : 0;
                 }
                 ent[lo + rank] = item;
+                // smallest listed d2 of the item's key (d2 >= 0: the bit patterns order like the values)
+                atomicMin(&dmin_s[(int)(item & 255u)], (int)(item >> 32));
             }
             if (tid == 0) {
                 const unsigned long long at = atomicAdd(p.out.cursor, (unsigned long long)out_total);

@@ -49,6 +49,12 @@ def set_sorted_rows(enabled: bool) -> None:
     _lib.load().cf_set_sorted_rows(c_int(1 if enabled else 0))
 
 
+def set_row_stats(words: Optional[torch.Tensor]) -> None:
+    """Work counters of the sorted row kernel (cf_set_row_stats): a zeroed CUDA int64 tensor of four words, or None to
+    switch the counting off.  The tensor must stay alive while set."""
+    _lib.load().cf_set_row_stats(_ptr(words))
+
+
 def set_weight_floor_log2(value: float) -> None:
     _lib.load().cf_set_weight_floor_log2(c_double(value))
 

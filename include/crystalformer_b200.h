@@ -70,6 +70,13 @@ double cf_get_weight_floor_log2(void);
 void cf_set_sorted_rows(int enabled);
 int cf_get_sorted_rows(void);
 
+/* Work counters of the sorted row kernel (diagnostic, for roofline accounting): while `device_words` (DEVICE memory,
+ * four uint64, zeroed by the caller) is set, every cf_infinite_attn_fwd_sorted launch - also inside the one-call
+ * forwards - adds { chunks of eight entries swept, (chunk, 16-bin tile) pairs whose basis values were evaluated,
+ * rows processed, 0 }.  NULL (the default) switches the counting off.  Process-wide; the memory must stay valid
+ * while set. */
+void cf_set_row_stats(void *device_words);
+
 /* ------------------------------------------------------------------------------------------------------------
  * Batch preparation.  Replaces get_edge_index and compute_lattice_distances_for_cuda
  * (models/indexed_latticeformer_encoder.py:15-32, 183-253) and the CSR construction repeated in every wrapper

@@ -35,7 +35,8 @@ def test_binding_table_covers_the_header():
     bound = set(_lib.SIGNATURES) | {"cf_version", "cf_last_error", "cf_set_weight_floor_log2",
                                     "cf_get_weight_floor_log2", "cf_encoder_workspace_floats",
                                     "cf_model_workspace_bytes", "cf_term_list_workspace_bytes",
-                                    "cf_row_list_workspace_bytes", "cf_set_sorted_rows", "cf_get_sorted_rows"}
+                                    "cf_row_list_workspace_bytes", "cf_set_sorted_rows", "cf_get_sorted_rows",
+                                    "cf_set_row_stats"}
     assert set(declared_symbols()) <= bound
 
 
