@@ -2,7 +2,8 @@
 
 The names, call signatures, return conventions and error behaviour are the reference's, so its own host code
 (``models/indexed_lattice_multi_head_attention_cuda.py``, ``models/pooling.py``, ``models/indexed_latticeformer_encoder.py``)
-runs unchanged when this package is installed as ``models.cuda_funcs``.  Behind the names the
+runs unchanged when this package is installed as ``models.cuda_funcs`` (``sys.modules['models.cuda_funcs'] = crystalformer_b200.cuda_funcs``
+before the reference's modules are imported, with ``models.global_config.REPRODUCIBLITY_STATE = 3``).  Behind the names the
 reference's CuPy ``RawKernel`` launches are replaced by calls into ``libcrystalformer_b200.so``.
 
 ``CUPY_AVAILABLE`` keeps its name because the reference reads it (models/latticeformer.py:139-143) to choose its CUDA

@@ -134,36 +134,51 @@ class Latticeformer(nn.Module):
             self._embed_cache = cache = (key, pack_dense_weight(padded))
         return cache[1]
 
-    def _forward_native(self, data, counts: Tuple[int, int, int], gather=None) -> torch.Tensor:
+    def native_plan(self, device) -> dict:
+        """Everything of a native forward that does not depend on the batch: packed encoder weights, the head's weights
+        as contiguous float32 tensors, the packed embedding and the scalar arguments of cf_model_forward.  Building it
+        checks every parameter's version; a caller that runs many batches through unchanged weights (the serving
+        pipeline) builds it once and hands it to ``_forward_native``."""
         enc = self.encoder
         P = enc.lattice_params
-        dev = data.pos.device
-        w = enc._packed_weights(dev)
-        n_atoms, n_edges, max_atoms = (int(v) for v in counts)
         f32 = lambda t: t.detach().float().contiguous()
-        feats, pos, trans = f32(data.x), f32(data.pos), f32(data.trans_vec)
-        sizes = data.sizes.to(device=dev, dtype=torch.int64).contiguous()
-        emb, w1, b1 = f32(self.input_embeddings.weight), f32(self.mlp[0].weight), f32(self.mlp[0].bias)
-        w2, b2 = f32(self.mlp[3].weight), f32(self.mlp[3].bias)
-        B, hidden, targets = sizes.shape[0], w1.shape[0], w2.shape[0]
-        lib = _lib.load()
-        work = torch.empty(int(lib.cf_model_workspace_bytes(n_atoms, B, n_edges, w["ff"])), dtype=torch.uint8, device=dev)
-        y = torch.empty((B, targets), dtype=torch.float32, device=dev)
-        emb_packed = self._embedding_packed(dev)
+        w = enc._packed_weights(device)
+        plan = dict(w=w, emb=f32(self.input_embeddings.weight), w1=f32(self.mlp[0].weight), b1=f32(self.mlp[0].bias),
+                    w2=f32(self.mlp[3].weight), b2=f32(self.mlp[3].bias), emb_packed=self._embedding_packed(device))
         dist_max = P.value_pe_dist_max
         if dist_max < 0:
             sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
             dist_max = -dist_max * sr
+        plan["hidden"], plan["targets"] = plan["w1"].shape[0], plan["w2"].shape[0]
+        plan["tail"] = (len(enc.layers), w["ptrs"], w["scalars"], int(P.value_pe_dist_real), w["ff"],
+                        float(P.value_pe_width_scale), enc._cutoff(), int(P.lattice_range),
+                        int(P.lattice_range) if P.minimum_range else 0, plan["w1"].data_ptr(), plan["b1"].data_ptr(),
+                        plan["hidden"], plan["w2"].data_ptr(), plan["b2"].data_ptr(), plan["targets"], float(dist_max) + 1.0)
+        return plan
+
+    def _forward_native(self, data, counts: Tuple[int, int, int], gather=None, plan: Optional[dict] = None) -> torch.Tensor:
+        dev = data.pos.device
+        if plan is None:
+            plan = self.native_plan(dev)
+        n_atoms, n_edges, max_atoms = (int(v) for v in counts)
+        f32 = lambda t: t if (t.dtype == torch.float32 and t.is_contiguous()) else t.detach().float().contiguous()
+        feats, pos, trans = f32(data.x), f32(data.pos), f32(data.trans_vec)
+        sizes = data.sizes
+        if sizes.device != dev or sizes.dtype != torch.int64 or not sizes.is_contiguous():
+            sizes = sizes.to(device=dev, dtype=torch.int64).contiguous()
+        B = sizes.shape[0]
+        lib = _lib.load()
+        ff = plan["w"]["ff"]
+        work = torch.empty(int(lib.cf_model_workspace_bytes(n_atoms, B, n_edges, ff)), dtype=torch.uint8, device=dev)
+        y = torch.empty((B, plan["targets"]), dtype=torch.float32, device=dev)
+        emb_packed = plan["emb_packed"]
         desc = None if gather is None else gather.next_descriptor()
         with torch.cuda.device(dev):
-            _lib.call("cf_model_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()), feats.data_ptr(),
-                      feats.shape[1], pos.data_ptr(), trans.data_ptr(), sizes.data_ptr(), n_atoms, B, n_edges, max_atoms,
-                      emb.data_ptr(), None if emb_packed is None else emb_packed.data_ptr(), len(enc.layers), w["ptrs"], w["scalars"], int(P.value_pe_dist_real), w["ff"],
-                      float(P.value_pe_width_scale), enc._cutoff(), int(P.lattice_range),
-                      int(P.lattice_range) if P.minimum_range else 0, w1.data_ptr(), b1.data_ptr(), hidden,
-                      w2.data_ptr(), b2.data_ptr(), targets, float(dist_max) + 1.0, work.data_ptr(), y.data_ptr(),
-                      enc._attention_events(), None if desc is None else ctypes.byref(desc),
-                      torch.cuda.current_stream(dev).cuda_stream)
+            _lib.call("cf_model_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()),
+                      feats.data_ptr(), feats.shape[1], pos.data_ptr(), trans.data_ptr(), sizes.data_ptr(), n_atoms, B,
+                      n_edges, max_atoms, plan["emb"].data_ptr(), None if emb_packed is None else emb_packed.data_ptr(),
+                      *plan["tail"], work.data_ptr(), y.data_ptr(), self.encoder._attention_events(),
+                      None if desc is None else ctypes.byref(desc), torch.cuda.current_stream(dev).cuda_stream)
         return y if gather is None else gather.collect()
 
     def forward(self, data, geometry: Optional[BatchGeometry] = None, counts: Optional[Tuple[int, int, int]] = None,

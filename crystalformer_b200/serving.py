@@ -1,6 +1,6 @@
 """Pipelined inference over a stream of host batches.
 
-``Latticeformer.forward`` on one batch is a chain host -> device copy, ~40 kernel launches, device -> host copy; run
+``Latticeformer.forward`` on one batch is a chain host -> device copy, a dozen kernel launches, device -> host copy; run
 batch after batch with a synchronisation in between, the GPU idles while the host issues the next batch's launches
 and the host idles while the GPU computes.  ``PipelinedPredictor`` keeps ``depth`` batches in flight instead: the
 inputs of batch t+1 are copied on a second stream while batch t computes, results land in a ring of pinned host
@@ -12,7 +12,8 @@ buffers, and the caller only waits when it asks for a result (or when the ring i
 
 Host batches should be pinned (``tensor.pin_memory()``) for the copies to be asynchronous.  Results must be collected
 in submission order.  The model must be in eval mode with its ``gauss_scale`` buffers set (a trained model, or one
-calibrating training-mode forward); outputs are identical to ``model(batch)``.
+calibrating training-mode forward); outputs are identical to ``model(batch)``.  The model's weights are read when the
+predictor is built (and again after ``refresh()``): change them, then call ``refresh()``.
 """
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ import types
 from collections import deque
 from typing import Deque, Optional, Tuple
 
+import numpy as np
 import torch
 
 
@@ -39,53 +41,103 @@ class PipelinedPredictor:
         self.post = post
         self.gather = gather
         self.copy_stream = torch.cuda.Stream(self.device)
-        self._inflight: Deque[Tuple[int, torch.cuda.Event, torch.Tensor, int]] = deque()
+        self._inflight: Deque[Tuple[int, torch.cuda.Event, torch.Tensor, Optional[torch.Tensor]]] = deque()
+        # per slot of the ring: device input buffers, an event "the forward that read them has run", the pinned output
+        # buffer and (with a peer gather) a pinned copy of the gather's status word
+        self._in_ring = [None] * depth
+        self._in_free = [None] * depth
+        self._copied = [torch.cuda.Event() for _ in range(depth)]
+        self._done = [torch.cuda.Event() for _ in range(depth)]
         self._out_ring = [None] * depth
+        self._status_ring = [None] * depth
         self._next = 0
+        self._plan = None
+        self.refresh()
+
+    def refresh(self) -> None:
+        """Re-reads the model's weights (call after changing them)."""
+        native = getattr(self.model, "_native_ok", None)
+        self._plan = self.model.native_plan(self.device) if (native is not None and not self.model.training
+                                                             and native_ok_without_grad(self.model)) else None
+
+    def _device_inputs(self, slot: int, batch):
+        """Device tensors of the slot with the batch's shapes (allocated once per shape, not per batch)."""
+        bufs = self._in_ring[slot]
+        shapes = (tuple(batch.x.shape), tuple(batch.pos.shape), tuple(batch.trans_vec.shape), tuple(batch.sizes.shape))
+        if bufs is None or bufs[0] != shapes:
+            dev = self.device
+            ns = types.SimpleNamespace(
+                x=torch.empty(shapes[0], dtype=batch.x.dtype, device=dev), pos=torch.empty(shapes[1], dtype=batch.pos.dtype, device=dev),
+                trans_vec=torch.empty(shapes[2], dtype=batch.trans_vec.dtype, device=dev),
+                sizes=torch.empty(shapes[3], dtype=torch.int64, device=dev))
+            bufs = self._in_ring[slot] = (shapes, ns)
+        return bufs[1]
 
     def submit(self, batch) -> int:
         """Queues one host batch (attributes x (N,98), pos (N,3), trans_vec (B,3,3), sizes (B) int64); returns a ticket."""
         if len(self._inflight) >= self.depth:
             raise RuntimeError("the pipeline is full: collect a result before submitting more")
-        sizes_host = batch.sizes
-        counts = sizes_host.tolist()  # host memory: no device synchronisation
-        n_atoms, n_edges, max_atoms = sum(counts), sum(n * n for n in counts), max(counts) if counts else 1
+        sizes_np = batch.sizes.numpy()  # host memory: no device synchronisation
+        n_atoms, n_edges = int(sizes_np.sum()), int(np.dot(sizes_np, sizes_np))
+        max_atoms = int(sizes_np.max()) if sizes_np.size else 1
+        slot = self._next % self.depth
         compute = torch.cuda.current_stream(self.device)
+        dev = self._device_inputs(slot, batch)
         with torch.cuda.stream(self.copy_stream):
-            dev = types.SimpleNamespace(
-                x=batch.x.to(self.device, non_blocking=True), pos=batch.pos.to(self.device, non_blocking=True),
-                trans_vec=batch.trans_vec.to(self.device, non_blocking=True),
-                sizes=sizes_host.to(self.device, non_blocking=True))
-            copied = torch.cuda.Event()
-            copied.record(self.copy_stream)
-        compute.wait_event(copied)
-        for t in vars(dev).values():
-            t.record_stream(compute)  # allocated on the copy stream, consumed on the compute stream
+            if self._in_free[slot] is not None:
+                self.copy_stream.wait_event(self._in_free[slot])  # the forward that last read these buffers has run
+            dev.x.copy_(batch.x, non_blocking=True)
+            dev.pos.copy_(batch.pos, non_blocking=True)
+            dev.trans_vec.copy_(batch.trans_vec, non_blocking=True)
+            dev.sizes.copy_(batch.sizes, non_blocking=True)
+            self._copied[slot].record(self.copy_stream)
+        compute.wait_event(self._copied[slot])
         with torch.no_grad():
-            extra = {} if self.gather is None else {"gather": self.gather}
-            y = self.model(dev, counts=(n_atoms, n_edges, max_atoms), **extra)
+            counts = (n_atoms, n_edges, max_atoms)
+            if self._plan is not None:
+                y = self.model._forward_native(dev, counts, self.gather, self._plan)
+            else:
+                extra = {} if self.gather is None else {"gather": self.gather}
+                y = self.model(dev, counts=counts, **extra)
             if self.post is not None:
                 y = self.post(y)
-        slot = self._next % self.depth
+        if self._in_free[slot] is None:
+            self._in_free[slot] = torch.cuda.Event()
+        self._in_free[slot].record(compute)
         out = self._out_ring[slot]
         if out is None or out.shape != y.shape:
             out = self._out_ring[slot] = torch.empty(y.shape, dtype=y.dtype).pin_memory()
         out.copy_(y, non_blocking=True)
-        done = torch.cuda.Event()
+        status = None
+        if self.gather is not None:
+            status = self._status_ring[slot]
+            if status is None:
+                status = self._status_ring[slot] = torch.zeros(1, dtype=torch.int32).pin_memory()
+            status.copy_(self.gather.status, non_blocking=True)
+        done = self._done[slot]
         done.record(compute)
         ticket = self._next
-        self._inflight.append((ticket, done, out, len(counts)))
+        self._inflight.append((ticket, done, out, status))
         self._next += 1
         return ticket
 
     def result(self, ticket: int) -> torch.Tensor:
         """Waits for the oldest batch in flight (``ticket`` must be its ticket) and returns its output on the host.
-        The returned tensor is a view of a ring buffer that is reused ``depth`` submissions later: copy it to keep it."""
+        The returned tensor is a view of a ring buffer that is reused ``depth`` submissions later: copy it to keep it.
+        Raises if the batch's peer gather gave up waiting for a rank (its rows would be NaN)."""
         if not self._inflight or self._inflight[0][0] != ticket:
             raise RuntimeError("results must be collected in submission order")
-        _, done, out, _ = self._inflight.popleft()
+        _, done, out, status = self._inflight.popleft()
         done.synchronize()
+        if status is not None and int(status[0]) != 0:
+            raise RuntimeError(f"peer gather: gave up waiting for the outputs of rank {int(status[0]) - 1}")
         return out
 
     def pending(self) -> int:
         return len(self._inflight)
+
+
+def native_ok_without_grad(model) -> bool:
+    """Whether the model's one-call inference path applies (its check reads the autograd mode)."""
+    with torch.no_grad():
+        return bool(model._native_ok())

@@ -109,7 +109,7 @@ class PeerGather:
     """
 
     def __init__(self, shards: List[List[int]], targets: int, device, group=None, slots: int = 4,
-                 timeout_s: float = 20.0):
+                 timeout_s: float = 5.0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0

@@ -1,5 +1,5 @@
-"""The reference project's own host code accepts this package as its ``models.cuda_funcs`` (the swap described in
-INTEGRATION.md).  Runs only where the reference tree is mounted; no GPU and no kernel launch are involved: the test
+"""The reference project's own host code accepts this package as its ``models.cuda_funcs`` (the swap: the package is
+put into ``sys.modules`` under that name before the reference's modules are imported).  Runs only where the reference tree is mounted; no GPU and no kernel launch are involved: the test
 checks that the reference's modules import against the shim, pick their CUDA encoder, build with our kernels
 "compiled", and that the state_dict keys of the reference model and of the mirror in this package coincide."""
 import contextlib
