@@ -98,6 +98,8 @@ def load() -> ctypes.CDLL:
         lib.cf_set_sorted_rows.argtypes = [c_int]
         lib.cf_set_sorted_rows.restype = None
         lib.cf_get_sorted_rows.restype = c_int
+        lib.cf_set_chained_launches.argtypes = [c_int]
+        lib.cf_set_chained_launches.restype = None
         lib.cf_set_row_stats.argtypes = [c_void_p]
         lib.cf_set_row_stats.restype = None
         lib.cf_model_workspace_bytes.argtypes = [I64, I64, I64, I64]

@@ -11,6 +11,7 @@ namespace cf {
 static thread_local char g_error[512] = "";
 static std::atomic<double> g_floor_log2{-30.0};
 static std::atomic<int> g_sorted_rows{1};
+static std::atomic<int> g_chained{1};
 static std::atomic<unsigned long long *> g_row_stats{nullptr};
 
 int fail(int code, const char *fmt, ...)
@@ -39,6 +40,8 @@ float weight_floor_log2()
 }
 
 bool sorted_rows_enabled() { return g_sorted_rows.load() != 0; }
+
+bool chained_launches_enabled() { return g_chained.load() != 0; }
 
 unsigned long long *row_stats_words() { return g_row_stats.load(); }
 
@@ -71,6 +74,8 @@ double cf_get_weight_floor_log2(void) { return cf::g_floor_log2.load(); }
 void cf_set_sorted_rows(int enabled) { cf::g_sorted_rows.store(enabled != 0); }
 
 int cf_get_sorted_rows(void) { return cf::g_sorted_rows.load(); }
+
+void cf_set_chained_launches(int enabled) { cf::g_chained.store(enabled != 0); }
 
 void cf_set_row_stats(void *device_words) { cf::g_row_stats.store(static_cast<unsigned long long *>(device_words)); }
 

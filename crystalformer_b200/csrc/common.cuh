@@ -97,6 +97,33 @@ __device__ __forceinline__ float pick8(const float (&x)[8], int idx)
     return r;
 }
 
+// ---- chained launches (programmatic dependent launch) ------------------------------------------------------
+// The one-call forwards issue a dozen short kernels back to back on one stream.  A kernel launched with
+// launch_chained(..., chained = true) may be scheduled while its predecessor in the stream is still draining: its
+// blocks run their prologue (staging of weights into shared memory, index setup), then grid_dependency_wait() blocks
+// until the predecessor grid has completed and its writes are visible.  Every kernel launched this way calls
+// grid_launch_dependents() first (which lets ITS successor be scheduled once all of this grid's blocks have started)
+// and grid_dependency_wait() before it reads or overwrites anything an earlier kernel of the stream touches - and it
+// calls the wait unconditionally, so that completion of a kernel always implies completion of all before it.  In a
+// kernel launched the ordinary way both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool chained_launches_enabled();  // cf_set_chained_launches
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  bool chained, Args &&...args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (chained && chained_launches_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 int sm_count();
 

@@ -281,7 +281,9 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
     ws.panels = (p.tail ? 1 + 2 * (p.ff / 128) : 0) + (p.head ? 3 : 0) + (ws.d.Wembed != nullptr ? 1 : 0);
     ws.produced = ws.consumed = 0;
     ws.limit = my_tiles * ws.panels * KSTEPS;
-    ws.start();
+    grid_launch_dependents();
+    ws.start();               // weights are constants: their stream starts while the previous kernel drains
+    grid_dependency_wait();   // activations of the previous kernel (attention output, x) from here on
 
     for (long long tile = blockIdx.x; tile * ROWS < p.N; tile += gridDim.x) {
         const long long row0 = tile * ROWS;
@@ -505,7 +507,8 @@ int launch_dense_block(const DenseArgs &p, cudaStream_t s)
     }
     const long long tiles = small ? tiles16 : (p.N + 31) / 32;
     const long long cap = sms;  // one block per SM: the weight rings fill most of the shared memory
-    kernel<<<(unsigned)(tiles < cap ? tiles : cap), DB_THREADS, smem, s>>>(p);
+    if (launch_chained(kernel, dim3((unsigned)(tiles < cap ? tiles : cap)), dim3(DB_THREADS), smem, s, p.chained != 0, p) != cudaSuccess)
+        return launch_status("dense_block_kernel");
     return launch_status("dense_block_kernel");
 }
 

@@ -11,6 +11,7 @@ namespace cf {
 struct DenseArgs {
     long long N;
     int tail, head, ff;
+    int chained;                    // launch as a chained kernel (common.cuh): set by the one-call forwards
     // tail: weights of the layer that just ran its attention
     const float *attn;              // (N,128) attention output
     const float4 *Wo, *W1, *W2;     // packed

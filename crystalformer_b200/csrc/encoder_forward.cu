@@ -35,7 +35,7 @@ int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const
                            int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
                            double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
                            float *lse, float *psi_row, const int32_t *row_order, const TermList *list,
-                           unsigned *ticket_ready, void *stream);
+                           unsigned *ticket_ready, void *stream, bool chained);
 unsigned *row_ticket_block(int count);
 int sorted_attn_impl(const float *q, const float *k, const float *v, const float *a, const float *pos_ij,
                      const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
@@ -244,7 +244,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
                                     l < ROW_SCHED_SLOTS - 1 ? l : ROW_SCHED_SLOTS - 1, l < ROW_SCHED_SLOTS - 1, s);
         return infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, HEADS, HEAD_DIM,
                                       E, K, max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range,
-                                      attn_out, logit, lse_out, nullptr, row_order, list, tickets ? tickets + l : nullptr, s);
+                                      attn_out, logit, lse_out, nullptr, row_order, list, tickets ? tickets + l : nullptr, s, true);
     };
 
     // Fused dense path: every layer brings its weights packed for the tensor-core kernel (slot 10) and the
@@ -264,6 +264,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
         DenseArgs d{};
         d.N = N; d.ff = ff; d.x = x; d.q = q; d.k = k; d.v = v; d.a = a; d.attn = attn;
         head_of(d, 0);
+        d.chained = 0;  // (first kernel of the forward on this stream: nothing to chain to)
         if (embed != nullptr) { d.features = embed->features; d.feature_dim = embed->feature_dim; d.Wembed = embed->packed; }
         rc = launch_dense_block(d, s);
         if (forked) cudaStreamWaitEvent(s, side_stream().join, 0);
@@ -277,6 +278,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
             DenseArgs t{};
             t.N = N; t.ff = ff; t.x = x; t.q = q; t.k = k; t.v = v; t.a = a; t.attn = attn;
             t.tail = 1;
+            t.chained = 1;
             const float4 *packed = reinterpret_cast<const float4 *>(w[10]);
             t.Wo = packed + 48 * 16 * 32;                     // after Wqkv (48 column tiles x 16 k steps x 32 lanes)
             t.W1 = t.Wo + 16 * 16 * 32;

@@ -156,6 +156,8 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
     // block computes a row has no influence on the row's result.  The ticket and the row's indices (atom, crystal,
     // edge range, first key) are fetched one row ahead, in stages placed where their latency is hidden.
     __shared__ long long next_slot_sh[GROUPS];
+    grid_launch_dependents();
+    grid_dependency_wait();  // (chained launches: the kernel before this one wrote q, k, v, a, phi or the row count)
     const long long first_wave = (long long)gridDim.x * GROUPS;
     long long slot = (long long)blockIdx.x * GROUPS + group;
     const long long rows = p.rows_on_device ? (long long)*p.rows_on_device : p.N;
@@ -675,9 +677,9 @@ int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const
                            int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale, const float *W,
                            double cutoff_radius, int lattice_range, int minimum_range, float *out, float *logit,
                            float *lse, float *psi_row, const int32_t *row_order, const TermList *list, unsigned *ticket_ready,
-                           void *stream);
+                           void *stream, bool chained);
 unsigned *row_ticket_block(int count);
-int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s);
+int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s, bool chained);
 }
 
 extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float *v, const float *a, const float *pos,
@@ -690,7 +692,7 @@ extern "C" int cf_infinite_attn_fwd(const float *q, const float *k, const float 
 {
     return cf::infinite_attn_fwd_impl(q, k, v, a, pos, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
                                       max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, out,
-                                      logit, lse, psi_row, row_order, nullptr, nullptr, stream);
+                                      logit, lse, psi_row, row_order, nullptr, nullptr, stream, false);
 }
 
 extern "C" int cf_infinite_attn_fwd_listed(const float *q, const float *k, const float *v, const float *a,
@@ -715,7 +717,7 @@ extern "C" int cf_infinite_attn_fwd_listed(const float *q, const float *k, const
     list.window = term_window(weight_floor_log2(), (float)a_widest);
     return infinite_attn_fwd_impl(q, k, v, a, nullptr, pos_ij, tvecs, rvlen, batch, edges, row_start, N, B, H, D, E, K,
                                   max_atoms, dist_max, wscale, W, cutoff_radius, lattice_range, minimum_range, out, logit,
-                                  lse, psi_row, row_order, &list, nullptr, stream);
+                                  lse, psi_row, row_order, &list, nullptr, stream, false);
 }
 
 int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
@@ -724,7 +726,7 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
                                int64_t D, int64_t E, int64_t K, int64_t max_atoms, double dist_max, double wscale,
                                const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out,
                                float *logit, float *lse, float *psi_row, const int32_t *row_order,
-                               const TermList *list, unsigned *ticket_ready, void *stream)
+                               const TermList *list, unsigned *ticket_ready, void *stream, bool chained)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_fwd: negative size");
@@ -781,14 +783,14 @@ int cf::infinite_attn_fwd_impl(const float *q, const float *k, const float *v, c
     if (list != nullptr && pos_ij != nullptr && K > 0) p.list = *list;
     p.rule = phi.rule;
     p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
-    return launch_rows(p, K, N, s);
+    return launch_rows(p, K, N, s, chained);
 }
 
 namespace cf {
 // Launches the row kernel for `grid_rows` rows (the grid is sized for them; the kernel itself processes p.N rows, or
 // *p.rows_on_device).  Warps per atom row: 1 for crystals of up to 12 atoms, else 4 (fewer warps per row keep more
 // rows in flight but stretch the heaviest rows, which bound the kernel).
-int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s)
+int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s, bool chained)
 {
     const int max_atoms = p.max_atoms;
     const int row_warps = max_atoms <= 12 ? 1 : WARPS;
@@ -818,7 +820,7 @@ int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s
     const long long want = (grid_rows + groups - 1) / groups;
     const long long cap = (long long)sm_count() * cached_occ[slot];
     const int blocks = (int)(want < cap ? want : cap);
-    kernel<<<blocks, THREADS, smem, s>>>(p);
+    launch_chained(kernel, dim3(blocks), dim3(THREADS), smem, s, chained, p);
     return launch_status("cf_infinite_attn_fwd");
 }
 
@@ -840,7 +842,7 @@ int launch_leftover_rows(const float *q, const float *k, const float *v, const f
     p.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
     p.basis = make_basis_params(64, dist_max, wscale, weight_floor_log2());
     // left-over rows are rare: a grid of one block per SM draws them through the ticket
-    return launch_rows(p, 64, (long long)sm_count() * (max_atoms <= 12 ? WARPS : 1), s);
+    return launch_rows(p, 64, (long long)sm_count() * (max_atoms <= 12 ? WARPS : 1), s, true);
 }
 }  // namespace cf
 

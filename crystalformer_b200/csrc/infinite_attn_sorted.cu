@@ -397,7 +397,9 @@ __global__ void __launch_bounds__(SR_THREADS, 4) infinite_attn_sorted_rows_kerne
     extern __shared__ __align__(16) unsigned char sorted_smem_raw[];
     SortedSmem &sm = *reinterpret_cast<SortedSmem *>(sorted_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // W (8,16,64) -> wt[k][channel]: thread = channel, 256 contiguous bytes read, 64 conflict-free stores
+    grid_launch_dependents();
+    // W (8,16,64) -> wt[k][channel]: thread = channel, 256 contiguous bytes read, 64 conflict-free stores (W is a
+    // constant: in a chained launch this runs while the kernel before this one drains)
     {
         const float4 *src = reinterpret_cast<const float4 *>(p.W + (size_t)tid * 64);
 #pragma unroll 4
@@ -409,6 +411,7 @@ __global__ void __launch_bounds__(SR_THREADS, 4) infinite_attn_sorted_rows_kerne
             sm.wt[(4 * k4 + 3) * CHANNELS + tid] = w.w;
         }
     }
+    grid_dependency_wait();  // q, k, v, a of the dense block before this kernel; its reads of `out` are over
     const long long n_shared = __ldg(p.task_count), n_single = __ldg(p.task_count + 1);
     // ---- rows shared by the block
     long long task = blockIdx.x;
@@ -470,7 +473,7 @@ int launch_sorted_rows(const SortedRowLaunch &l, cudaStream_t s)
     }
     const long long cap = (long long)sm_count() * 4;
     const unsigned blocks = (unsigned)(l.N < cap ? l.N : cap);
-    kernel<<<blocks, SR_THREADS, sizeof(SortedSmem), s>>>(p);
+    launch_chained(kernel, dim3(blocks), dim3(SR_THREADS), sizeof(SortedSmem), s, l.chained, p);
     return launch_status("infinite_attn_sorted_rows_kernel");
 }
 
@@ -493,6 +496,7 @@ int sorted_attn_impl(const float *q, const float *k, const float *v, const float
                      const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out, float *lse,
                      const RowListView &view, int sched_slot, bool zeroed, cudaStream_t s)
 {
+    // (chained launches only when no memset sits between this call's kernels and the one before them)
     unsigned *sched = view.sched + 4 * sched_slot;
     if (!zeroed && cudaMemsetAsync(sched, 0, 4 * sizeof(unsigned), s) != cudaSuccess) return launch_status("row scheduling block");
     SortedRowLaunch l{};
@@ -500,6 +504,7 @@ int sorted_attn_impl(const float *q, const float *k, const float *v, const float
     l.view = view; l.sched = sched; l.out = out; l.lse = lse; l.N = N; l.max_atoms = (int)max_atoms;
     l.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
     l.dist_max = dist_max; l.wscale = wscale;
+    l.chained = zeroed;
     int rc = launch_sorted_rows(l, s);
     if (rc != CF_OK) return rc;
     return launch_leftover_rows(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, N, E, max_atoms, dist_max, wscale,

@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(HEAD_THREADS) pool_head_kernel(const float *__
     __shared__ float hid[HEAD_MAX_HIDDEN];
     const long long c = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    grid_dependency_wait();  // (chained launch behind the last dense block)
     const long long s = atom_start[c], len = atom_start[c + 1] - s;
     pooled[tid] = len > 0 ? segment_mean_channel(x + s * MODEL_DIM + tid, MODEL_DIM, len) : 0.f;
     __syncthreads();
@@ -166,11 +167,12 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
                               ff_dim, wscale, cutoff_radius, lattice_range, minimum_range, w.encoder, order, attn_events,
                               stream, embed_fused ? &embed : nullptr);
     if (rc != CF_OK) return rc;
+    const bool chained = num_layers > 0 && N > 0;  // behind the encoder's last dense block
     if (gather != nullptr)
-        pool_head_kernel<true><<<(unsigned)B, HEAD_THREADS, 0, s>>>(w.x, w.atom_start, W1, b1, W2, b2, (int)hidden,
-                                                                    (int)targets, y, *gather);
+        launch_chained(pool_head_kernel<true>, dim3((unsigned)B), dim3(HEAD_THREADS), 0, s, chained, (const float *)w.x,
+                       (const int64_t *)w.atom_start, W1, b1, W2, b2, (int)hidden, (int)targets, y, *gather);
     else
-        pool_head_kernel<false><<<(unsigned)B, HEAD_THREADS, 0, s>>>(w.x, w.atom_start, W1, b1, W2, b2, (int)hidden,
-                                                                     (int)targets, y, cf_peer_gather{});
+        launch_chained(pool_head_kernel<false>, dim3((unsigned)B), dim3(HEAD_THREADS), 0, s, chained, (const float *)w.x,
+                       (const int64_t *)w.atom_start, W1, b1, W2, b2, (int)hidden, (int)targets, y, cf_peer_gather{});
     return launch_status("cf_model_forward");
 }

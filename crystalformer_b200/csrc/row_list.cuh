@@ -87,6 +87,7 @@ struct SortedRowLaunch {
     int max_atoms;
     BoxRule rule;
     double dist_max, wscale;
+    bool chained;  // launch as a chained kernel (common.cuh)
 };
 int launch_sorted_rows(const SortedRowLaunch &p, cudaStream_t s);
 

@@ -49,6 +49,11 @@ def set_sorted_rows(enabled: bool) -> None:
     _lib.load().cf_set_sorted_rows(c_int(1 if enabled else 0))
 
 
+def set_chained_launches(enabled: bool) -> None:
+    """Whether the one-call forwards chain their kernels by programmatic dependent launches (cf_set_chained_launches)."""
+    _lib.load().cf_set_chained_launches(c_int(1 if enabled else 0))
+
+
 def set_row_stats(words: Optional[torch.Tensor]) -> None:
     """Work counters of the sorted row kernel (cf_set_row_stats): a zeroed CUDA int64 tensor of four words, or None to
     switch the counting off.  The tensor must stay alive while set."""

@@ -70,6 +70,11 @@ double cf_get_weight_floor_log2(void);
 void cf_set_sorted_rows(int enabled);
 int cf_get_sorted_rows(void);
 
+/* Whether the kernels of cf_encoder_forward / cf_model_forward are launched as a chain of programmatic dependent
+ * launches (a kernel's blocks are scheduled and run their prologue - staging of weights - while its predecessor
+ * drains, then wait for it to complete); 1 by default, 0 launches them the ordinary way.  Results are identical. */
+void cf_set_chained_launches(int enabled);
+
 /* Work counters of the sorted row kernel (diagnostic, for roofline accounting): while `device_words` (DEVICE memory,
  * four uint64, zeroed by the caller) is set, every cf_infinite_attn_fwd_sorted launch - also inside the one-call
  * forwards - adds { chunks of eight entries swept, (chunk, 16-bin tile) pairs whose basis values were evaluated,

@@ -145,3 +145,105 @@ def test_training_step_at_cfg3_size_is_finite_and_repeatable(ops):
     assert rel_err(g1[1].cpu().numpy(), gk.cpu().numpy()) < TOL
     assert rel_err(g1[2].cpu().numpy(), gv.cpu().numpy()) < TOL
     assert rel_err(torch.einsum("nhd,nhk->hdk", go, psi_row).cpu().numpy(), gW.cpu().numpy()) < TOL
+
+
+def oracle_rows(cb, pick, q, k, v, a, W, Kbins):
+    """float64 oracle output for every row of the crystals `pick`: (row indices into the batch, reference rows)."""
+    sub = cb.select(pick)
+    starts = np.concatenate([[0], np.cumsum(cb.sizes)])
+    rows = np.concatenate([np.arange(starts[c], starts[c + 1]) for c in pick])
+    e_sub = oracle.edge_index(sub.sizes)
+    pij, _, _, rvl = oracle.geometry(sub.pos, sub.trans_vec, e_sub)
+    qn, kn, vn, an = (t[rows].cpu().numpy() for t in (q, k, v, a))
+    zr, pw = oracle.lattice_sum_fwd(an, pij, sub.trans_vec, sub.batch, e_sub, Kbins, DIST_MAX, WSCALE,
+                                    W=None if W is None else W.cpu().numpy()[None], rvlen=rvl, cutoff_radius=-3.5,
+                                    precision="f64")
+    prob, ref = oracle.fused_attn_fwd(qn, kn, vn, zr, pw, e_sub, precision="f64")
+    return rows, ref, (sub, e_sub, pij, rvl, zr, pw, prob)
+
+
+@pytest.mark.parametrize("cfg,Kbins", [("cfg0", 64), ("cfg2", 0), ("cfg4", 64)])
+def test_listed_attention_at_full_size(ops, cfg, Kbins):
+    """The kernels that the one-call forwards run - term lists built once per batch - at the sizes of the benchmark
+    configurations (cfg2: 7-layer model without the value encoding, K = 0, crystals of up to 60 atoms): invariants,
+    agreement with the enumerating kernels and with the operator split, and every row of a few crystals against the
+    float64 oracle."""
+    cb = make_config(cfg, num_crystals=16 if cfg == "cfg4" else None)
+    prep = prepared(ops, cb)
+    N = cb.num_atoms
+    q, k, v, a, W = random_inputs(N, 11)
+    if Kbins == 0:
+        W = None
+    tv, max_atoms = dev(cb.trans_vec), int(cb.sizes.max())
+    geo = (prep["pos_ij"], tv, prep["rvlen"], prep["batch"], prep["edges"], prep["row_start"], max_atoms)
+    a_widest = float(a.max())
+    lists = ops.term_list_build(*geo, -3.5, 2, 2, a_widest)
+    out, logit, lse, _ = ops.infinite_attn_fwd(q, k, v, a, *geo, Kbins, DIST_MAX, WSCALE, W, -3.5, 2, 2, term_lists=lists)
+    plain = ops.infinite_attn_fwd(q, k, v, a, *geo, Kbins, DIST_MAX, WSCALE, W, -3.5, 2, 2)
+    assert torch.isfinite(out).all() and torch.isfinite(logit).all()
+    p = torch.exp(logit - lse[prep["edges"][0]])
+    row_sum = torch.zeros((N, H), device="cuda").index_add_(0, prep["edges"][0], p)
+    assert float((row_sum - 1).abs().max()) < 1e-5
+    assert rel_err(out.cpu().numpy(), plain[0].cpu().numpy()) < 5e-6
+    assert rel_err(logit.cpu().numpy(), plain[1].cpu().numpy()) < 5e-6
+    z, psiW = ops.lattice_sum_fwd(a, prep["pos_ij"], tv, prep["batch"], prep["edges"], Kbins, DIST_MAX, WSCALE, W=W,
+                                  rvlen=prep["rvlen"], cutoff_radius=-3.5)
+    _, out_split = ops.fused_attn_fwd(q, k, v, z, psiW, prep["edges"], prep["row_start"])
+    assert rel_err(out.cpu().numpy(), out_split.cpu().numpy()) < TOL
+    small = [int(c) for c in np.argsort(cb.sizes)[:2]] if cfg == "cfg4" else [3, 17, 40]
+    rows, ref, _ = oracle_rows(cb, small, q, k, v, a, W, Kbins)
+    assert rel_err(out[rows].cpu().numpy(), ref) < TOL
+    if Kbins == 64 and max_atoms <= 32:  # the row-list organisation of the same batch
+        rl = ops.row_list_build(*geo, -3.5, 2, 2, a_widest)
+        out_sorted, lse_sorted = ops.infinite_attn_fwd_sorted(q, k, v, a, *geo, Kbins, DIST_MAX, WSCALE, W, -3.5, 2, 2, rl)
+        assert rel_err(out_sorted[rows].cpu().numpy(), ref) < TOL
+        assert rel_err(out_sorted.cpu().numpy(), out.cpu().numpy()) < 2e-5
+
+
+def test_listed_backward_against_the_float64_oracle_at_cfg3_size(ops):
+    """cf_infinite_attn_bwd_listed on the 256-crystal training batch (term lists as in a training step): the gradients
+    of every row of three crystals against the float64 oracle chain (attention backward -> lattice-sum backward)."""
+    cb = make_config("cfg3")
+    prep = prepared(ops, cb)
+    N = cb.num_atoms
+    q, k, v, a, W = random_inputs(N, 13)
+    go = torch.randn((N, H, D), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    tv, max_atoms = dev(cb.trans_vec), int(cb.sizes.max())
+    geo = (prep["pos_ij"], tv, prep["rvlen"], prep["batch"], prep["edges"], prep["row_start"], max_atoms)
+    lists = ops.term_list_build(*geo, -3.5, 2, 2, float(a.max()))
+    args = (q, k, v, a, *geo, K, DIST_MAX, WSCALE, W, -3.5, 2, 2)
+    out, logit, lse, _ = ops.infinite_attn_fwd(*args, term_lists=lists)
+    gq, gk, gv, ga = ops.infinite_attn_bwd(*args, logit, lse, out, go, term_lists=lists)
+    pick = [5, 77, 201]
+    rows, ref, (sub, e_sub, pij, rvl, zr, pw, prob) = oracle_rows(cb, pick, q, k, v, a, W, K)
+    qn, kn, vn, an, gon = (t[rows].cpu().numpy() for t in (q, k, v, a, go))
+    rq, rk, rv, rphi, rpsiW = oracle.fused_attn_bwd(qn, kn, vn, pw, e_sub, prob, ref, gon, precision="f64")
+    ra, _ = oracle.lattice_sum_bwd(an, pij, sub.trans_vec, sub.batch, e_sub, zr, rphi, rpsiW, K, DIST_MAX, WSCALE,
+                                   W=W.cpu().numpy()[None], rvlen=rvl, cutoff_radius=-3.5, lattice_range=2, minimum_range=2,
+                                   precision="f64")
+    assert rel_err(out[rows].cpu().numpy(), ref) < TOL
+    for got, want, name in ((gq, rq, "gq"), (gk, rk, "gk"), (gv, rv, "gv"), (ga, ra, "ga")):
+        assert rel_err(got[rows].cpu().numpy(), want) < TOL, name
+
+
+def test_one_call_model_forward_of_the_bench_configuration_against_the_cpu_model():
+    """The path the benchmark times - cf_model_forward: embedding inside the first dense block, row lists, the sorted
+    row kernel, the fused dense blocks, pooling + head - on the 4-layer, ff 512, K = 64 model over 24 crystals of the
+    headline configuration, against the CPU restatement of the reference model with the same state_dict."""
+    import types
+    import bench
+    from oracle.model_cpu import forward_cpu
+    cb = make_config("cfg0", num_crystals=24)
+    model, params = bench.make_model(4, 64)
+    model = model.cuda()
+    batch = bench.to_device_batch(cb, torch.device("cuda"))
+    bench.fix_gauss_scale(model, batch)
+    with torch.no_grad():
+        y = model(batch)
+        model.native = False  # the same model operator by operator (torch modules + the fused attention operator)
+        y_ops = model(batch)
+        model.native = True
+    state = {k: v.detach().cpu() for k, v in model.state_dict().items()}
+    y_cpu = forward_cpu(state, params, cb, use_ref=False)
+    assert rel_err(y.cpu().numpy(), y_cpu) < TOL
+    assert rel_err(y_ops.cpu().numpy(), y_cpu) < TOL

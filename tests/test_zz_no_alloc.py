@@ -56,17 +56,23 @@ def run_both(ops, _lib, N, E, t):
               c_double(DIST_MAX), c_double(WSCALE), ptr(t["rvlen"]), c_double(-3.5), c_int(2), c_int(2), ptr(ga), ptr(None),
               stream)
     torch.cuda.synchronize()
-    return ga, ga_ref
+    return ga, ga_ref, z
 
 
 def test_static_scratch_variant_matches_the_ordinary_entry_point_twice_in_a_row():
     from crystalformer_b200 import _lib, ops
     for seed, crystals, nmax in ((91, 12, 9), (92, 5, 6)):  # the second call is smaller: stale contents stay behind it
         N, E, t = make_case(seed, crystals, nmax)
-        ga, ga_ref = run_both(ops, _lib, N, E, t)
+        ga, ga_ref, z = run_both(ops, _lib, N, E, t)
         assert torch.isfinite(ga).all()
         err = float((ga - ga_ref).abs().max() / ga_ref.abs().max())
         assert err < 1e-4, err  # the tolerance of the other fp32 parity tests; in practice the bits are equal
+        # ... and against the float64 CPU oracle of the reference's backward kernel (real_enc_bwd.cu)
+        c = lambda x: x.cpu().numpy()
+        ga_cpu, _ = oracle.lattice_sum_bwd(c(t["a"]), c(t["pos_ij"]), c(t["tvecs"]), c(t["batch"]), c(t["edges"]), c(z),
+                                           c(t["gz"]), c(t["gpsi"]), K, DIST_MAX, WSCALE, rvlen=c(t["rvlen"]),
+                                           cutoff_radius=-3.5, lattice_range=2, minimum_range=2, precision="f64")
+        assert float(np.abs(c(ga) - ga_cpu).max() / np.abs(ga_cpu).max()) < 1e-4
 
 
 def test_static_scratch_variant_refuses_too_many_edges():
