@@ -32,7 +32,7 @@ SIGNATURES = {
                              I32, P, P, P, P, P, P, P, P, P, P, P],
     "cf_pipe_probe": [I32, I32, I32, I64, P, P],
     "cf_model_forward": [P, P, I64, P, P, P, I64, I64, I64, I64, P, P, I32, P, P, I64, I64, F64, F64, I32, I32, P, P, I64, P,
-                         P, I64, F64, P, P, P, P, P],
+                         P, I64, F64, P, P, P, P, P, P, P],
     "cf_peer_alloc": [I64, P, P],
     "cf_peer_open": [P, P],
     "cf_peer_close": [P],

@@ -28,7 +28,7 @@ int encoder_forward_impl(void *cublas_handle, int num_layers, const float *const
                          const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
                          int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
                          int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
-                         void *const *attn_events, void *stream, const EmbedStage *embed);
+                         void *const *attn_events, void *stream, const EmbedStage *embed, bool early_prep);
 int infinite_attn_fwd_impl(const float *q, const float *k, const float *v, const float *a, const float *pos,
                            const float *pos_ij, const float *tvecs, const float *rvlen, const int64_t *batch,
                            const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t H, int64_t D,
@@ -68,6 +68,21 @@ SideStream &side_stream()
     }
     return s;
 }
+
+}  // namespace
+
+// The side stream made to wait for the caller's events (either may be NULL), for cf_model_forward's early preparation;
+// NULL if the side stream could not be created.
+cudaStream_t early_prep_stream(void *inputs_ready, void *slot_free)
+{
+    SideStream &side = side_stream();
+    if (!side.ok) return nullptr;
+    if (inputs_ready != nullptr && cudaStreamWaitEvent(side.stream, reinterpret_cast<cudaEvent_t>(inputs_ready), 0) != cudaSuccess) return nullptr;
+    if (slot_free != nullptr && cudaStreamWaitEvent(side.stream, reinterpret_cast<cudaEvent_t>(slot_free), 0) != cudaSuccess) return nullptr;
+    return side.stream;
+}
+
+namespace {
 
 struct LayerScalars {
     float gauss_scale, gauss_shift;  // alpha <- (alpha + shift) * scale
@@ -161,7 +176,7 @@ extern "C" int cf_encoder_forward(void *cublas_handle, int num_layers, const flo
 {
     return cf::encoder_forward_impl(cublas_handle, num_layers, weights, scalars, x, pos_ij, tvecs, rvlen, batch, edges,
                                     row_start, N, B, E, max_atoms, K, ff_dim, wscale, cutoff_radius, lattice_range,
-                                    minimum_range, workspace, row_order, attn_events, stream, nullptr);
+                                    minimum_range, workspace, row_order, attn_events, stream, nullptr, false);
 }
 
 // cf_encoder_forward with an optional embedding stage (dense path only): x is then written by the first dense block.
@@ -170,7 +185,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
                              const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
                              int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
                              int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
-                             void *const *attn_events, void *stream, const EmbedStage *embed)
+                             void *const *attn_events, void *stream, const EmbedStage *embed, bool early_prep)
 {
     CF_REQUIRE(N >= 0 && E >= 0 && num_layers >= 0, CF_ERR_INVALID, "cf_encoder_forward: negative size");
     CF_REQUIRE(ff_dim > 0 && ff_dim % 4 == 0, CF_ERR_UNSUPPORTED, "cf_encoder_forward: ff_dim must be a positive multiple of 4");
@@ -194,7 +209,10 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
     const TermList *list = nullptr;
     RowListView row_lists{};
     bool sorted_rows = false;  // batches of crystals of at most 32 atoms with a value encoding: row lists + sorted row kernel
-    bool forked = false;  // the build runs on the side stream; the first attention waits for it
+    // The build runs on the side stream and the first attention waits for it.  early_prep: the caller has already put the
+    // geometry launch on the side stream (cf_model_forward with an inputs-ready event), so the side stream is not made
+    // to wait for this stream here.
+    bool forked = early_prep;
     unsigned *tickets = nullptr;
     if (pos_ij != nullptr && weight_floor_log2() > -200.0f) {
         float a_widest = -INFINITY;
@@ -203,8 +221,9 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
             const BoxRule rule{(float)cutoff_radius, lattice_range, minimum_range};
             const float window = term_window(weight_floor_log2(), a_widest);
             SideStream &side = side_stream();
-            forked = side.ok && cudaEventRecord(side.fork, s) == cudaSuccess &&
-                     cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
+            if (!early_prep)
+                forked = side.ok && cudaEventRecord(side.fork, s) == cudaSuccess &&
+                         cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
             sorted_rows = sorted_rows_enabled() && K == 64 && max_atoms <= ROW_LIST_MAX_KEYS && N < (1ll << 31) && E < (1ll << 31);
             if (sorted_rows) {
                 RowListBuild rb{};
@@ -232,10 +251,10 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
                 lists.pool = tb.pool; lists.start = tb.start; lists.count = tb.count; lists.dmin = tb.dmin; lists.window = tb.window;
                 list = &lists;
             }
-            if (forked && cudaEventRecord(side.join, side.stream) != cudaSuccess) rc = launch_status("term list join");
             if (rc != CF_OK) return rc;
         }
     }
+    if (forked && cudaEventRecord(side_stream().join, side_stream().stream) != cudaSuccess) return launch_status("side stream join");
     // one attention call of layer l (dist_max, W of that layer)
     auto attention = [&](int l, double dist_max, const float *W, float *attn_out, float *lse_out) {
         if (sorted_rows)

@@ -24,7 +24,8 @@ int encoder_forward_impl(void *cublas_handle, int num_layers, const float *const
                          const int64_t *edges, const int64_t *row_start, int64_t N, int64_t B, int64_t E,
                          int64_t max_atoms, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
                          int lattice_range, int minimum_range, float *workspace, const int32_t *row_order,
-                         void *const *attn_events, void *stream, const EmbedStage *embed);
+                         void *const *attn_events, void *stream, const EmbedStage *embed, bool early_prep);
+cudaStream_t early_prep_stream(void *inputs_ready, void *slot_free);
 namespace {
 
 constexpr int MODEL_DIM = 128;
@@ -125,7 +126,8 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
                                 const float *const *weights, const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
                                 int lattice_range, int minimum_range, const float *W1, const float *b1, int64_t hidden,
                                 const float *W2, const float *b2, int64_t targets, double order_reach, void *workspace,
-                                float *y, void *const *attn_events, const cf_peer_gather *gather, void *stream)
+                                float *y, void *const *attn_events, const cf_peer_gather *gather, void *inputs_ready,
+                                void *slot_free, void *stream)
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && B >= 0 && E >= 0 && feature_dim > 0, CF_ERR_INVALID, "cf_model_forward: bad size");
@@ -148,9 +150,15 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
     Scratch w = carve(workspace, N, B, E, ff_dim);
 
     CF_REQUIRE(B <= (1 << 20), CF_ERR_RANGE, "cf_model_forward: B=%lld above 2^20 crystals", (long long)B);
+    // Early preparation: given an event after which the inputs are valid, the geometry launch and the list build go to
+    // the library's side stream, ordered after that event (and after slot_free: the previous use of this workspace) but
+    // NOT after the work already queued on `stream`, so they run beside the previous batch's forward.
+    cudaStream_t prep = nullptr;
+    if (inputs_ready != nullptr && embed_fused && N > 0) prep = early_prep_stream(inputs_ready, slot_free);
+    const bool early = prep != nullptr;
     bool ordered = false;  // batches beyond the one-launch sort are processed in index order
     int rc = launch_prepare_all(pos, trans, sizes, w.atom_start, w.edge_start, B, N, E, w.batch, w.edges, w.row_start, w.pos_ij, w.rvlen,
-                            order_reach, w.row_order, &ordered, s);
+                            order_reach, w.row_order, &ordered, early ? prep : s);
     if (rc != CF_OK) return rc;
     const int32_t *order = ordered ? w.row_order : nullptr;
     if (N > 0 && !embed_fused) {
@@ -165,7 +173,7 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
     rc = encoder_forward_impl(cublas_handle, num_layers, weights, scalars, w.x, w.pos_ij, trans,
                               cutoff_radius != 0.0 ? w.rvlen : nullptr, w.batch, w.edges, w.row_start, N, B, E, max_atoms, K,
                               ff_dim, wscale, cutoff_radius, lattice_range, minimum_range, w.encoder, order, attn_events,
-                              stream, embed_fused ? &embed : nullptr);
+                              stream, embed_fused ? &embed : nullptr, early);
     if (rc != CF_OK) return rc;
     const bool chained = num_layers > 0 && N > 0;  // behind the encoder's last dense block
     if (gather != nullptr)

@@ -156,7 +156,24 @@ class Latticeformer(nn.Module):
                         plan["hidden"], plan["w2"].data_ptr(), plan["b2"].data_ptr(), plan["targets"], float(dist_max) + 1.0)
         return plan
 
-    def _forward_native(self, data, counts: Tuple[int, int, int], gather=None, plan: Optional[dict] = None) -> torch.Tensor:
+    WORKSPACE_RING = 4  # forwards whose preparation may be in flight at a time (see _forward_native, inputs_ready)
+
+    def _ring_workspace(self, dev, nbytes: int):
+        """Next workspace of a small ring of persistent buffers, with the event that marks the end of its previous use:
+        a forward whose preparation starts early (``inputs_ready``) runs beside the forwards before it, so it cannot
+        share their scratch memory."""
+        ring = getattr(self, "_ws_ring", None)
+        if ring is None or ring["dev"] != dev:
+            ring = self._ws_ring = dict(dev=dev, slots=[None] * self.WORKSPACE_RING, next=0)
+        at = ring["next"] % self.WORKSPACE_RING
+        ring["next"] += 1
+        slot = ring["slots"][at]
+        if slot is None or slot[0].numel() < nbytes:
+            slot = ring["slots"][at] = [torch.empty(nbytes, dtype=torch.uint8, device=dev), torch.cuda.Event(), False]
+        return slot
+
+    def _forward_native(self, data, counts: Tuple[int, int, int], gather=None, plan: Optional[dict] = None,
+                        inputs_ready: Optional[torch.cuda.Event] = None) -> torch.Tensor:
         dev = data.pos.device
         if plan is None:
             plan = self.native_plan(dev)
@@ -169,30 +186,45 @@ class Latticeformer(nn.Module):
         B = sizes.shape[0]
         lib = _lib.load()
         ff = plan["w"]["ff"]
-        work = torch.empty(int(lib.cf_model_workspace_bytes(n_atoms, B, n_edges, ff)), dtype=torch.uint8, device=dev)
-        y = torch.empty((B, plan["targets"]), dtype=torch.float32, device=dev)
+        nbytes = int(lib.cf_model_workspace_bytes(n_atoms, B, n_edges, ff))
         emb_packed = plan["emb_packed"]
+        slot = None
+        if inputs_ready is not None and emb_packed is not None:
+            slot = self._ring_workspace(dev, nbytes)
+            work = slot[0]
+        else:
+            work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        y = torch.empty((B, plan["targets"]), dtype=torch.float32, device=dev)
         desc = None if gather is None else gather.next_descriptor()
         with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev)
             _lib.call("cf_model_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()),
                       feats.data_ptr(), feats.shape[1], pos.data_ptr(), trans.data_ptr(), sizes.data_ptr(), n_atoms, B,
                       n_edges, max_atoms, plan["emb"].data_ptr(), None if emb_packed is None else emb_packed.data_ptr(),
                       *plan["tail"], work.data_ptr(), y.data_ptr(), self.encoder._attention_events(),
-                      None if desc is None else ctypes.byref(desc), torch.cuda.current_stream(dev).cuda_stream)
+                      None if desc is None else ctypes.byref(desc),
+                      None if slot is None else ctypes.c_void_p(inputs_ready.cuda_event),
+                      None if (slot is None or not slot[2]) else ctypes.c_void_p(slot[1].cuda_event), stream.cuda_stream)
+            if slot is not None:
+                slot[1].record(stream)  # the next forward that takes this workspace waits for this one
+                slot[2] = True
         return y if gather is None else gather.collect()
 
     def forward(self, data, geometry: Optional[BatchGeometry] = None, counts: Optional[Tuple[int, int, int]] = None,
-                gather=None):
+                gather=None, inputs_ready: Optional[torch.cuda.Event] = None):
         """``data`` carries x (N,98), pos (N,3), batch (N), trans_vec (B,3,3), sizes (B) like the reference's PyG batch.
         ``counts`` = (atoms, edges = sum n^2, largest crystal), when the caller knows them on the host, saves the
         device->host read of ``sizes``.  ``gather`` (a ``sharding.PeerGather``, inference only): the outputs of every
-        rank's crystals are returned, in the order of the unsharded batch."""
+        rank's crystals are returned, in the order of the unsharded batch.  ``inputs_ready`` (inference through the
+        one-call path only): a CUDA event after which the tensors of ``data`` are valid.  The batch preparation, which
+        depends on the inputs alone, is then not ordered behind the work already queued on the current stream and
+        overlaps the previous batch's forward; the tensors must stay unchanged until this forward has run."""
         if geometry is None and not self.training and not torch.is_grad_enabled() and data.pos.is_cuda \
                 and self._native_ok():
             if counts is None:
                 host = data.sizes.tolist()  # the one device->host read per batch (the reference does the same)
                 counts = (sum(host), sum(n * n for n in host), max(host) if host else 1)
-            return self._forward_native(data, counts, gather)
+            return self._forward_native(data, counts, gather, inputs_ready=inputs_ready)
         x = self.input_embeddings(data.x)
         if geometry is None:
             geometry = BatchGeometry(data.pos, data.trans_vec, data.sizes, *(counts if counts is not None else ()))

@@ -3,8 +3,9 @@
 ``Latticeformer.forward`` on one batch is a chain host -> device copy, a dozen kernel launches, device -> host copy; run
 batch after batch with a synchronisation in between, the GPU idles while the host issues the next batch's launches
 and the host idles while the GPU computes.  ``PipelinedPredictor`` keeps ``depth`` batches in flight instead: the
-inputs of batch t+1 are copied on a second stream while batch t computes, results land in a ring of pinned host
-buffers, and the caller only waits when it asks for a result (or when the ring is full).
+inputs of batch t+1 are copied on a second stream while batch t computes, its preparation (geometry, term lists)
+starts as soon as the copy is done, results land in a ring of pinned host buffers, and the caller only waits when it
+asks for a result (or when the ring is full).
 
     runner = PipelinedPredictor(model, depth=3)
     tickets = [runner.submit(batch) for batch in host_batches]      # batch: x, pos, trans_vec, sizes on the host
@@ -95,7 +96,7 @@ class PipelinedPredictor:
         with torch.no_grad():
             counts = (n_atoms, n_edges, max_atoms)
             if self._plan is not None:
-                y = self.model._forward_native(dev, counts, self.gather, self._plan)
+                y = self.model._forward_native(dev, counts, self.gather, self._plan, inputs_ready=self._copied[slot])
             else:
                 extra = {} if self.gather is None else {"gather": self.gather}
                 y = self.model(dev, counts=counts, **extra)

@@ -378,6 +378,13 @@ int cf_peer_gather_collect(const uint64_t *cells, uint32_t step, const int64_t *
  * inside the first dense block, the whole forward runs in this library's kernels and cublas_handle may be NULL.
  * gather (optional, NULL to skip): the pooling + head kernel also stores y into every rank's gather buffer (see
  * cf_peer_gather above; B <= gather->rows_per_rank).
+ *   inputs_ready, slot_free: NULL, or cudaEvent_t (passed as void*) for pipelined use.  With inputs_ready given (an event
+ *             after which features, pos, trans and sizes are valid) the batch preparation - the geometry launch and the
+ *             list build, which depend on the inputs only - is issued on a stream of the library's own, ordered after
+ *             inputs_ready and slot_free but NOT after the work already queued on `stream`: it then runs beside the
+ *             previous batch's forward.  The caller must hand every forward that can be in flight its own workspace;
+ *             slot_free is an event recorded on `stream` after the previous forward that used THIS workspace (NULL if
+ *             there was none).  Only with packed weights (the cuBLAS-free path); otherwise ignored.
  * ---------------------------------------------------------------------------------------------------------- */
 int64_t cf_model_workspace_bytes(int64_t N, int64_t B, int64_t E, int64_t ff_dim);
 int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
@@ -386,7 +393,8 @@ int cf_model_forward(void *cublas_handle, const float *features, int64_t feature
                      const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius, int lattice_range,
                      int minimum_range, const float *W1, const float *b1, int64_t hidden, const float *W2,
                      const float *b2, int64_t targets, double order_reach, void *workspace, float *y,
-                     void *const *attn_events, const cf_peer_gather *gather, void *stream);
+                     void *const *attn_events, const cf_peer_gather *gather, void *inputs_ready, void *slot_free,
+                     void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Scheduling weight of every atom's row for the fused attention kernels (no counterpart in the reference, which
