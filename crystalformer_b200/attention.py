@@ -132,7 +132,11 @@ class InfiniteAttentionFunction(torch.autograd.Function):
             lattice_range, minimum_range, logit, lse, out, gout, row_order=ctx.row_order, term_lists=ctx.term_lists)
         gW = None
         if K > 0 and ctx.needs_input_grad[4]:
-            gW = torch.einsum("nhd,nhk->hdk", gout, psi_row).reshape(ctx.w_shape)
+            # gW[h] = sum_n gout[n,h,:] (x) psi_row[n,h,:]: the diagonal blocks of ONE (H D) x (H K) product over the
+            # atoms (eight times the flops of the per-head products, and a fraction of their time at these sizes)
+            N, H, D = gout.shape
+            full = gout.reshape(N, H * D).t() @ psi_row.reshape(N, H * K)
+            gW = torch.stack([full[h * D:(h + 1) * D, h * K:(h + 1) * K] for h in range(H)]).reshape(ctx.w_shape)
         return (gq, gk, gv, ga, gW) + (None,) * 15
 
 
@@ -254,9 +258,11 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         N, H, Dq = q.shape
         w = self.lattice_pos_weights
         if P.gauss_state.startswith("q"):
-            alpha = q.reshape(N, H, 1, Dq) @ w.reshape(H, Dq, 1)
+            # q_h . w_h per (atom, head): an element-wise product and a 16-term sum (the reference writes it as a batched
+            # matrix product, ...attention_cuda.py:647, which launches a GEMM per head for a dot product)
+            alpha = (q * w.reshape(1, H, Dq)).sum(dim=-1)
         elif P.gauss_state == "1":
-            alpha = torch.ones_like(q).reshape(N, H, 1, Dq) @ w.reshape(H, Dq, 1)
+            alpha = w.reshape(1, H, Dq).sum(dim=-1).expand(N, H)
         else:
             alpha = F.linear(query, w)
         alpha = alpha.view(N, H)
