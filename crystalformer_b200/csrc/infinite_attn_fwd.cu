@@ -381,14 +381,6 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             float4 *qs = reinterpret_cast<float4 *>(vsum);
             for (int idx = rt; idx < HEADS * HEAD_DIM / 4; idx += RT)
                 qs[idx] = __ldg(reinterpret_cast<const float4 *>(p.q + i * HEADS * HEAD_DIM) + idx);
-            if (K > 0 && phi_here) {
-                // ---- phi of the row's edges from their term lists, 32 keys per pass, left where the phi kernel leaves it
-                //      (only with CF_PHI_IN_ROW=2: for rows of many keys the separate phi kernel is faster)
-                for (int base = 0; base < n; base += 32) {
-                    const int jk = base + rt / ROW_WARPS;
-                    phi_from_lists(jk, logit_io + (e0 + (jk < n ? jk : 0)) * HEADS);
-                }
-            }
             row_sync();
             // ---- logits: one key per thread, all eight heads; the key's 512-byte row is 32 independent 16-byte loads
             for (int j = rt; j < n; j += RT) {
