@@ -316,7 +316,10 @@ def run_b200(args):
     d2h_bytes = (global_batch.num_crystals if world > 1 else mine.num_crystals) * 4
 
     from crystalformer_b200.serving import PipelinedPredictor
-    runner = PipelinedPredictor(model, depth=3, device=device, gather=peers)
+    # one GPU: four batches in flight alternating between three compute streams (the kernels of independent batches fill
+    # each other's idle issue slots); with a peer gather the steps must run in one order on every rank: one stream
+    e2e_depth, e2e_streams = (4, 3) if peers is None else (3, 1)
+    runner = PipelinedPredictor(model, depth=e2e_depth, device=device, gather=peers, streams=e2e_streams)
     pending = []
 
     def step_e2e():
@@ -435,7 +438,7 @@ def run_b200(args):
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "timed_steps": e2e_steps,
                     "host_issue_ms_per_step": e2e_issue * 1e3 / e2e_steps,
                     "clock": "host wall clock (perf_counter) from the first submit to the last result, max over ranks",
-                    "api": "crystalformer_b200.serving.PipelinedPredictor, 3 batches in flight"},
+                    "api": f"crystalformer_b200.serving.PipelinedPredictor, {e2e_depth} batches in flight on {e2e_streams} compute stream(s)"},
             "gpu_launches": None if launches is None else launches * args.steps,
             "gpu_launches_per_step": launches, "kernels_per_step": kernel_names,
             "parity": parity, "roofline": roofline, "lattice_sum_microbench": micro, "cpu_baseline": cpu,

@@ -198,6 +198,8 @@ class Latticeformer(nn.Module):
         desc = None if gather is None else gather.next_descriptor()
         with torch.cuda.device(dev):
             stream = torch.cuda.current_stream(dev)
+            if slot is not None and slot[2]:
+                stream.wait_event(slot[1])  # (a no-op in effect unless the workspace was last used on another stream)
             _lib.call("cf_model_forward", ctypes.c_void_p(torch.cuda.current_blas_handle()),
                       feats.data_ptr(), feats.shape[1], pos.data_ptr(), trans.data_ptr(), sizes.data_ptr(), n_atoms, B,
                       n_edges, max_atoms, plan["emb"].data_ptr(), None if emb_packed is None else emb_packed.data_ptr(),

@@ -28,10 +28,13 @@ import torch
 
 class PipelinedPredictor:
     def __init__(self, model: torch.nn.Module, depth: int = 3, device: Optional[torch.device] = None, post=None,
-                 gather=None):
+                 gather=None, streams: int = 1):
         """``post``: optional callable applied to the model output on the device before it is copied to the host
         (e.g. an all-gather of the ranks' outputs).  ``gather``: a ``sharding.PeerGather`` handed to the model, which
-        then returns the outputs of every rank's crystals."""
+        then returns the outputs of every rank's crystals.  ``streams``: compute streams the batches alternate between
+        (1 = the stream current at ``submit``).  With two, the kernels of consecutive, independent batches run side by
+        side and fill each other's idle issue slots (they are latency-bound), at the price of a longer latency per
+        batch; not combined with ``gather``, whose steps must run in the same order on every rank."""
         if depth < 1:
             raise ValueError("depth must be at least 1")
         self.model = model
@@ -41,7 +44,10 @@ class PipelinedPredictor:
         self.depth = depth
         self.post = post
         self.gather = gather
+        if streams < 1 or (streams > 1 and gather is not None):
+            raise ValueError("streams must be at least 1, and 1 with a peer gather")
         self.copy_stream = torch.cuda.Stream(self.device)
+        self.compute_streams = [torch.cuda.Stream(self.device) for _ in range(streams)] if streams > 1 else None
         self._inflight: Deque[Tuple[int, torch.cuda.Event, torch.Tensor, Optional[torch.Tensor]]] = deque()
         # per slot of the ring: device input buffers, an event "the forward that read them has run", the pinned output
         # buffer and (with a peer gather) a pinned copy of the gather's status word
@@ -82,7 +88,8 @@ class PipelinedPredictor:
         n_atoms, n_edges = int(sizes_np.sum()), int(np.dot(sizes_np, sizes_np))
         max_atoms = int(sizes_np.max()) if sizes_np.size else 1
         slot = self._next % self.depth
-        compute = torch.cuda.current_stream(self.device)
+        caller = torch.cuda.current_stream(self.device)
+        compute = caller if self.compute_streams is None else self.compute_streams[self._next % len(self.compute_streams)]
         dev = self._device_inputs(slot, batch)
         with torch.cuda.stream(self.copy_stream):
             if self._in_free[slot] is not None:
@@ -93,7 +100,7 @@ class PipelinedPredictor:
             dev.sizes.copy_(batch.sizes, non_blocking=True)
             self._copied[slot].record(self.copy_stream)
         compute.wait_event(self._copied[slot])
-        with torch.no_grad():
+        with torch.no_grad(), torch.cuda.stream(compute):
             counts = (n_atoms, n_edges, max_atoms)
             if self._plan is not None:
                 y = self.model._forward_native(dev, counts, self.gather, self._plan, inputs_ready=self._copied[slot])
@@ -108,13 +115,14 @@ class PipelinedPredictor:
         out = self._out_ring[slot]
         if out is None or out.shape != y.shape:
             out = self._out_ring[slot] = torch.empty(y.shape, dtype=y.dtype).pin_memory()
-        out.copy_(y, non_blocking=True)
         status = None
-        if self.gather is not None:
-            status = self._status_ring[slot]
-            if status is None:
-                status = self._status_ring[slot] = torch.zeros(1, dtype=torch.int32).pin_memory()
-            status.copy_(self.gather.status, non_blocking=True)
+        with torch.cuda.stream(compute):
+            out.copy_(y, non_blocking=True)
+            if self.gather is not None:
+                status = self._status_ring[slot]
+                if status is None:
+                    status = self._status_ring[slot] = torch.zeros(1, dtype=torch.int32).pin_memory()
+                status.copy_(self.gather.status, non_blocking=True)
         done = self._done[slot]
         done.record(compute)
         ticket = self._next

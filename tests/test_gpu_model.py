@@ -177,18 +177,20 @@ def test_sharded_batches_give_identical_outputs(golden_model):
     assert rel_err(b.cpu().numpy(), full[[1, 5, 3]].cpu().numpy()) < 1e-5
 
 
-def test_pipelined_predictor_equals_direct_calls(golden_model):
-    """Batches streamed through PipelinedPredictor (copies on a second stream, several batches in flight, results in
-    pinned ring buffers) give exactly what model(batch) gives, in submission order."""
+@pytest.mark.parametrize("depth,streams,count", [(2, 1, 5), (4, 3, 14)])
+def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, count):
+    """Batches streamed through PipelinedPredictor (copies on a second stream, several batches in flight - on one compute
+    stream or alternating between three -, early preparation beside the previous batches, results in pinned ring
+    buffers) give exactly what model(batch) gives, in submission order."""
     from crystalformer_b200.serving import PipelinedPredictor
     model = build(golden_model).eval()
-    batches = [make_crystals(40 + s, 5 + s, uniform_atoms(1, 8), length_range=(3.0, 10.0)) for s in range(5)]
+    batches = [make_crystals(40 + s, 5 + (3 * s) % 7, uniform_atoms(1, 8), length_range=(3.0, 10.0)) for s in range(count)]
     host = [types.SimpleNamespace(x=torch.from_numpy(b.x).pin_memory(), pos=torch.from_numpy(b.pos).pin_memory(),
                                   trans_vec=torch.from_numpy(b.trans_vec).pin_memory(),
                                   sizes=torch.from_numpy(b.sizes).pin_memory()) for b in batches]
     with torch.no_grad():
         direct = [model(types.SimpleNamespace(**{k: v.cuda() for k, v in vars(h).items()})).cpu() for h in host]
-    runner = PipelinedPredictor(model, depth=2)
+    runner = PipelinedPredictor(model, depth=depth, streams=streams)
     got, tickets = [], []
     for h in host:
         if runner.pending() == runner.depth:
