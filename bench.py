@@ -197,7 +197,9 @@ class StepTimer:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def one_round(self, step, steps, drain=None):
+    def one_round(self, step, steps, drain=None, finish=None):
+        """finish: called after the last step, before the round's end is recorded (work the steps left on other streams
+        is made to count)."""
         torch = self.torch
         spans = []
         host_t0 = time.perf_counter()
@@ -209,26 +211,30 @@ class StepTimer:
             e.record()
             spans.append((s, e))
         host_issue = time.perf_counter() - host_t0  # the host is done issuing; the device may still be busy
+        if finish:
+            finish()
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
         if drain:
             drain()
         self.barrier()
         span = sum(s.elapsed_time(e) for s, e in spans)
-        wall = spans[0][0].elapsed_time(spans[-1][1]) - (steps - 1) * self.flush_ms
+        wall = spans[0][0].elapsed_time(end) - (steps - 1) * self.flush_ms
         return {"span_ms": span, "wall_ms": max(wall, span), "host_issue_ms": host_issue * 1e3}
 
-    def run(self, step, steps, warmup, drain=None, target_ms=1000.0, max_rounds=200):
+    def run(self, step, steps, warmup, drain=None, target_ms=1000.0, max_rounds=200, finish=None):
         """Returns (ms per step, max over ranks; this rank's diagnostics)."""
         for _ in range(warmup):
             step()
         if drain:
             drain()
         self.barrier()
-        first = self.one_round(step, steps, drain)
+        first = self.one_round(step, steps, drain, finish)
         first_max = self.max_over_ranks(first["wall_ms"])
         rounds = int(min(max_rounds, max(1, math.ceil(target_ms / max(first_max, 1e-3)))))
         done, total_max = [first], first_max
         for _ in range(rounds - 1):
-            r = self.one_round(step, steps, drain)
+            r = self.one_round(step, steps, drain, finish)
             done.append(r)
             total_max += self.max_over_ranks(r["wall_ms"])
         n = len(done) * steps
@@ -301,7 +307,8 @@ def run_b200(args):
 
     # N > 1: the pooling + head kernel of every rank stores its outputs into every rank's gather buffer over NVLink
     # and a small kernel waits for all ranks (sharding.PeerGather); no collective library on the data path.
-    peers = PeerGather(shards, model.mlp[-1].out_features, device) if world > 1 else None
+    # (overlap: a step's collect, where a rank waits for the others, runs on its own stream beside the next steps)
+    peers = PeerGather(shards, model.mlp[-1].out_features, device, slots=8, overlap=True) if world > 1 else None
     extra = {} if peers is None else {"gather": peers}
 
     ready = torch.cuda.Event()
@@ -316,9 +323,9 @@ def run_b200(args):
     d2h_bytes = (global_batch.num_crystals if world > 1 else mine.num_crystals) * 4
 
     from crystalformer_b200.serving import PipelinedPredictor
-    # one GPU: four batches in flight alternating between three compute streams (the kernels of independent batches fill
-    # each other's idle issue slots); with a peer gather the steps must run in one order on every rank: one stream
-    e2e_depth, e2e_streams = (4, 3) if peers is None else (3, 1)
+    # four batches in flight alternating between three compute streams (the kernels of independent batches fill each
+    # other's idle issue slots)
+    e2e_depth, e2e_streams = 4, 3
     runner = PipelinedPredictor(model, depth=e2e_depth, device=device, gather=peers, streams=e2e_streams)
     pending = []
 
@@ -338,7 +345,8 @@ def run_b200(args):
     if sampler:
         time.sleep(0.3)  # let nvidia-smi start sampling
     t_begin = time.time()
-    ms_step, diag_resident = timer.run(step_resident, args.steps, args.warmup)
+    finish = None if peers is None else peers.wait_ready  # the last step's collect belongs to the round
+    ms_step, diag_resident = timer.run(step_resident, args.steps, args.warmup, finish=finish)
     t_end = time.time()
     clocks = sampler.stop(t_begin, t_end) if sampler else None
     if peers is not None:
@@ -346,7 +354,7 @@ def run_b200(args):
     # the attention calls are timed in a round of their own, with the same flushes: the event pairs the library records
     # around them sit between the kernels of a step and cost the step a few tens of microseconds
     model.encoder.attention_event_log = native_log
-    timer.one_round(step_resident, args.steps)
+    timer.one_round(step_resident, args.steps, finish=finish)
     model.encoder.attention_event_log = None
     op_ms = sum(s.elapsed_time(e) for s, e in native_log)
     op_calls = len(native_log)
@@ -386,6 +394,7 @@ def run_b200(args):
         with torch.no_grad():
             y_local = model(resident, counts=(n_atoms, n_edges, max_atoms))
             y_peer = model(resident, counts=(n_atoms, n_edges, max_atoms), gather=peers)
+        peers.wait_ready()
         y_nccl = gather_outputs(y_local, shards)
         peers.check()
         gather_check = "ok" if torch.equal(y_peer, y_nccl) else "MISMATCH"
@@ -589,16 +598,17 @@ def strong_scaling_case(name, rank, world, device, timer):
     mine = cb.select(shards[rank])
     part = to_device_batch(mine, device)
     counts = (mine.num_atoms, mine.num_edges, int(mine.sizes.max()) if mine.num_crystals else 1)
-    peers = PeerGather(shards, model.mlp[-1].out_features, device)
+    peers = PeerGather(shards, model.mlp[-1].out_features, device, slots=8, overlap=True)
 
     def step():
         with torch.no_grad():
             return model(part, counts=counts, gather=peers)
 
-    ms, _ = timer.run(step, 10, 3, target_ms=150.0, max_rounds=10)
+    ms, _ = timer.run(step, 10, 3, target_ms=150.0, max_rounds=10, finish=peers.wait_ready)
     peers.check()
     with torch.no_grad():
         y_all = model(part, counts=counts, gather=peers)
+    peers.wait_ready()
     peers.check()
     # the unsplit batch on one GPU (rank 0 alone; the others wait)
     single = torch.zeros(1, dtype=torch.float64, device=device)

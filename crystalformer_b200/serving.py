@@ -44,8 +44,8 @@ class PipelinedPredictor:
         self.depth = depth
         self.post = post
         self.gather = gather
-        if streams < 1 or (streams > 1 and gather is not None):
-            raise ValueError("streams must be at least 1, and 1 with a peer gather")
+        if streams < 1 or (streams > 1 and gather is not None and not getattr(gather, "overlap", False)):
+            raise ValueError("streams must be at least 1, and 1 with a peer gather that does not overlap its collects")
         self.copy_stream = torch.cuda.Stream(self.device)
         self.compute_streams = [torch.cuda.Stream(self.device) for _ in range(streams)] if streams > 1 else None
         self._inflight: Deque[Tuple[int, torch.cuda.Event, torch.Tensor, Optional[torch.Tensor]]] = deque()
@@ -116,7 +116,10 @@ class PipelinedPredictor:
         if out is None or out.shape != y.shape:
             out = self._out_ring[slot] = torch.empty(y.shape, dtype=y.dtype).pin_memory()
         status = None
-        with torch.cuda.stream(compute):
+        # the outputs go to the host from the stream they become valid on: the compute stream, or the stream of an
+        # overlapping peer gather's collects
+        last = compute if (self.gather is None or not self.gather.overlap) else self.gather.collect_stream
+        with torch.cuda.stream(last):
             out.copy_(y, non_blocking=True)
             if self.gather is not None:
                 status = self._status_ring[slot]
@@ -124,7 +127,7 @@ class PipelinedPredictor:
                     status = self._status_ring[slot] = torch.zeros(1, dtype=torch.int32).pin_memory()
                 status.copy_(self.gather.status, non_blocking=True)
         done = self._done[slot]
-        done.record(compute)
+        done.record(last)
         ticket = self._next
         self._inflight.append((ticket, done, out, status))
         self._next += 1

@@ -106,10 +106,17 @@ class PeerGather:
     ``model`` stores its outputs straight from the pooling + head kernel into every rank's buffer; ``store`` does the
     same for outputs that exist already.  Every rank must run the same sequence of gathers.  ``check()`` (a device
     synchronisation) raises if a collect gave up waiting for a rank.
+
+    ``overlap=True``: the collect of a step - the only place where a rank waits for the others - runs on a stream of
+    its own instead of the stream of the forward, so a rank that is ahead starts its next batches while the last rows
+    of the step arrive.  ``collect()`` then returns a tensor that is valid on ``collect_stream`` once ``ready`` has
+    fired: consume it there, or call ``wait_ready()`` to make the current stream wait.  A rank runs at most
+    ``slots // 2`` steps ahead of its own collects (the store of step t waits for the collect of step t - slots // 2),
+    which is what keeps a slot from being overwritten before every rank has read it.
     """
 
     def __init__(self, shards: List[List[int]], targets: int, device, group=None, slots: int = 4,
-                 timeout_s: float = 5.0):
+                 timeout_s: float = 5.0, overlap: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -142,12 +149,22 @@ class PeerGather:
                     self._bases.append(mapped.value)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.step = 0
+        self.overlap = bool(overlap)
+        self.collect_stream = torch.cuda.Stream(self.device) if self.overlap else None
+        self.ready: Optional[torch.cuda.Event] = None
+        self._collected = [None] * self.slots  # per slot: the event after the collect that last read it
+        self._lag = max(1, self.slots // 2)
         if self.world > 1:
             dist.barrier(group=group)  # every buffer is mapped everywhere before the first store
 
     def next_descriptor(self) -> _lib.PeerGatherDescriptor:
-        """Advances to the next step and returns its descriptor (for ``cf_model_forward`` / ``store``)."""
+        """Advances to the next step and returns its descriptor (for ``cf_model_forward`` / ``store``).  With
+        ``overlap`` the current stream is first made to wait for the collect of step - slots // 2."""
         self.step += 1
+        if self.overlap and self.step > self._lag:
+            done = self._collected[(self.step - self._lag) % self.slots]
+            if done is not None:
+                torch.cuda.current_stream(self.device).wait_event(done)
         at = (self.step % self.slots) * self._slot_bytes
         return peer_descriptor(self.world, self.rank, self.rows_per_rank, self.step, [b + at for b in self._bases])
 
@@ -166,13 +183,34 @@ class PeerGather:
         order of the unsharded batch."""
         if self.step == 0:
             raise RuntimeError("collect() before the first store")
-        out = torch.empty((self.total_rows, self.targets), dtype=torch.float32, device=self.device)
         at = self._own + (self.step % self.slots) * self._slot_bytes
-        with torch.cuda.device(self.device):
+        if not self.overlap:
+            out = torch.empty((self.total_rows, self.targets), dtype=torch.float32, device=self.device)
+            with torch.cuda.device(self.device):
+                _lib.call("cf_peer_gather_collect", at, self.step & 0xFFFFFFFF, self.index.data_ptr(), self.total_rows,
+                          self.targets, self.rows_per_rank, out.data_ptr(), self.status.data_ptr(), self.timeout_s,
+                          torch.cuda.current_stream(self.device).cuda_stream)
+            return out
+        slot = self.step % self.slots
+        stored = torch.cuda.Event()
+        stored.record(torch.cuda.current_stream(self.device))  # this rank's stores of the step have been issued
+        with torch.cuda.device(self.device), torch.cuda.stream(self.collect_stream):
+            self.collect_stream.wait_event(stored)
+            out = torch.empty((self.total_rows, self.targets), dtype=torch.float32, device=self.device)
             _lib.call("cf_peer_gather_collect", at, self.step & 0xFFFFFFFF, self.index.data_ptr(), self.total_rows,
                       self.targets, self.rows_per_rank, out.data_ptr(), self.status.data_ptr(), self.timeout_s,
-                      torch.cuda.current_stream(self.device).cuda_stream)
+                      self.collect_stream.cuda_stream)
+            done = self._collected[slot]
+            if done is None:
+                done = self._collected[slot] = torch.cuda.Event()
+            done.record(self.collect_stream)
+        self.ready = done
         return out
+
+    def wait_ready(self) -> None:
+        """``overlap``: makes the current stream wait for the most recent collect."""
+        if self.ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.ready)
 
     def check(self) -> None:
         code = int(self.status.item())

@@ -67,20 +67,22 @@ def test_collect_gives_up_on_rows_that_nothing_stores():
     assert float((out[:rows] + 1).sum().item()) == 2.0 * rows  # the device still answers
 
 
-def test_model_forward_with_a_gather_of_one_rank(golden_model):
+@pytest.mark.parametrize("overlap", [False, True])
+def test_model_forward_with_a_gather_of_one_rank(golden_model, overlap):
     """world = 1 through the public classes: the pooling + head kernel stores into the (own) gather buffer and the
-    collect puts the rows into the order of the unsharded batch."""
+    collect puts the rows into the order of the unsharded batch; also with the collects on a stream of their own."""
     from test_gpu_model import batch_of, build
     from crystalformer_b200.sharding import PeerGather
     model = build(golden_model).eval()
     batch = batch_of(golden_model)
     B = batch.sizes.shape[0]
     order = list(np.random.default_rng(0).permutation(B))  # local crystal c is crystal order[c] of the "unsharded" batch
-    gather = PeerGather([[int(g) for g in order]], model.mlp[-1].out_features, torch.device("cuda"))
+    gather = PeerGather([[int(g) for g in order]], model.mlp[-1].out_features, torch.device("cuda"), overlap=overlap)
     with torch.no_grad():
         y = model(batch)
-        for _ in range(3):  # several steps: slots are reused
+        for _ in range(7):  # several steps: slots are reused
             y_all = model(batch, gather=gather)
+            gather.wait_ready()
             gather.check()
             expect = torch.empty_like(y)
             expect[torch.as_tensor(order).cuda()] = y
@@ -107,19 +109,29 @@ shards = lpt_assign(cb.sizes, world)
 mine = cb.select(shards[rank])
 t = lambda a: torch.from_numpy(a).to(dev)
 batch = types.SimpleNamespace(x=t(mine.x), pos=t(mine.pos), trans_vec=t(mine.trans_vec), sizes=t(mine.sizes))
-gather = PeerGather(shards, model.mlp[-1].out_features, dev, timeout_s=10.0)
 ok = True
-with torch.no_grad():
-    for step in range(4):
+for overlap in (False, True):
+    gather = PeerGather(shards, model.mlp[-1].out_features, dev, timeout_s=10.0, slots=8 if overlap else 4, overlap=overlap)
+    with torch.no_grad():
         y = model(batch)
         want = gather_outputs(y, shards)
-        got = model(batch, gather=gather)
-        ok = ok and bool(torch.equal(got, want))
-        if step == 1:  # outputs that exist already
-            gather.store(y)
-            ok = ok and bool(torch.equal(gather.collect(), want))
-gather.check()
-gather.close()
+        outs = []
+        for step in range(12 if overlap else 4):
+            got = model(batch, gather=gather)
+            if overlap:
+                outs.append(got)  # compared after the loop: the rank runs ahead of its collects
+            else:
+                ok = ok and bool(torch.equal(got, want))
+            if step == 1:  # outputs that exist already
+                gather.store(y)
+                got2 = gather.collect()
+                gather.wait_ready()
+                ok = ok and bool(torch.equal(got2, want))
+        gather.wait_ready()
+        torch.cuda.synchronize()
+        ok = ok and all(bool(torch.equal(o, want)) for o in outs)
+    gather.check()
+    gather.close()
 flag = torch.tensor([1 if ok else 0], device=dev)
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 if rank == 0:
