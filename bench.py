@@ -271,7 +271,7 @@ def run_b200(args):
     import torch
     import torch.distributed as dist
     from crystalformer_b200 import ops
-    from crystalformer_b200.sharding import PeerGather, gather_outputs, lpt_assign, shard_balance
+    from crystalformer_b200.sharding import PeerGather, crystal_cost, gather_outputs, lpt_assign, shard_balance
     from crystalformer_b200.synthetic import make_config
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -289,7 +289,10 @@ def run_b200(args):
 
     wl = WORKLOADS[args.workload]
     global_batch = make_config(wl["config"], num_crystals=wl["crystals"] * world)
-    shards = lpt_assign(global_batch.sizes, world)
+    # the reference's greedy split, with the row scheduler's cost (n^2 x the terms per edge, which depend on the cell
+    # volume) in place of n^2 as the weight: shards of equal n^2 differ by several percent in lattice-sum terms
+    cost = crystal_cost(global_batch.sizes, global_batch.trans_vec)
+    shards = lpt_assign(global_batch.sizes, world, weights=cost)
     mine = global_batch.select(shards[rank])
     n_atoms, n_edges, max_atoms = mine.num_atoms, mine.num_edges, int(mine.sizes.max())
 
@@ -440,8 +443,8 @@ def run_b200(args):
                        "l2": "flushed between timed steps (256 MB write between the per-step event pairs)",
                        "timing": "rounds of `steps` steps issued back to back; device wall clock of a round minus the "
                                  "flushes inside it; rounds repeated until about 1 s of device time, averaged; max over ranks",
-                       "parallelism": f"dp{world} (LPT on n^2, outputs gathered by peer stores)",
-                       "shard_balance": shard_balance(global_batch.sizes, shards)},
+                       "parallelism": f"dp{world} (greedy LPT split on the row-cost weight, outputs gathered by peer stores)",
+                       "shard_balance": shard_balance(global_batch.sizes, shards, cost)},
             "per_rank": {"resident": every},
             "e2e": {"value": e2e_value, "unit": "crystals/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "timed_steps": e2e_steps,
@@ -586,7 +589,7 @@ def strong_scaling_case(name, rank, world, device, timer):
     models/latticeformer.py:243-252), outputs gathered by peer stores; rank 0 also times the unsplit batch alone."""
     import torch
     import torch.distributed as dist
-    from crystalformer_b200.sharding import PeerGather, lpt_assign, shard_balance
+    from crystalformer_b200.sharding import PeerGather, crystal_cost, lpt_assign, shard_balance
     from crystalformer_b200.synthetic import make_config
     wl = WORKLOADS[name]
     cb = make_config(wl["config"])
@@ -594,7 +597,8 @@ def strong_scaling_case(name, rank, world, device, timer):
     model = model.to(device)
     whole = to_device_batch(cb, device)
     fix_gauss_scale(model, whole)  # (every rank computes the same statistics from the same whole batch)
-    shards = lpt_assign(cb.sizes, world)
+    cost = crystal_cost(cb.sizes, cb.trans_vec)
+    shards = lpt_assign(cb.sizes, world, weights=cost)
     mine = cb.select(shards[rank])
     part = to_device_batch(mine, device)
     counts = (mine.num_atoms, mine.num_edges, int(mine.sizes.max()) if mine.num_crystals else 1)
@@ -632,6 +636,7 @@ def strong_scaling_case(name, rank, world, device, timer):
     return {"crystals": cb.num_crystals, "ms_per_step": ms, "crystals_per_s": cb.num_crystals / (ms * 1e-3),
             "ms_per_step_n1": float(single.item()), "speedup_vs_n1": float(single.item()) / ms,
             "edges_max_over_mean": shard_balance(cb.sizes, shards)["edges_max_over_mean"],
+            "cost_max_over_mean": shard_balance(cb.sizes, shards, cost)["cost_max_over_mean"],
             "largest_crystal_edges_over_mean_shard": float(int(cb.sizes.max()) ** 2 / (sum(edges) / world)),
             "sharded_equals_unsharded": ok}
 

@@ -11,7 +11,7 @@ import torch
 
 import oracle
 from conftest import rel_err
-from crystalformer_b200.sharding import gather_outputs, lpt_assign, shard_balance
+from crystalformer_b200.sharding import crystal_cost, gather_outputs, lpt_assign, shard_balance
 from crystalformer_b200.synthetic import CrystalBatch, make_config, make_crystals, uniform_atoms
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -46,6 +46,12 @@ def test_lpt_assignment_follows_the_reference_rule():
     for n in (2, 4, 8):
         bal = shard_balance(cb.sizes, lpt_assign(cb.sizes, n))
         assert bal["edges_max_over_mean"] < 1.01
+        # the same greedy rule on a weight that also knows the cell volumes: every crystal placed once, weights balanced
+        cost = crystal_cost(cb.sizes, cb.trans_vec)
+        by_cost = lpt_assign(cb.sizes, n, weights=cost)
+        assert sorted(sum(by_cost, [])) == list(range(cb.num_crystals))
+        assert shard_balance(cb.sizes, by_cost, cost)["cost_max_over_mean"] < 1.01
+    assert lpt_assign(sizes, 3, weights=[s * s for s in sizes]) == shards
 
 
 def test_empty_and_single_shard_gather():
