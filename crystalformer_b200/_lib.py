@@ -47,6 +47,7 @@ SIGNATURES = {
     "cf_row_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
     "cf_infinite_attn_fwd_sorted": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                                     I32, P, P, P, P],
+    "cf_serve_submit": [P, P, P, P, P, P, I64, I64, I64, I64, I32],
     "cf_row_cost": [P, P, I64, I64, F64, P, P],
     "cf_row_order": [P, P, I64, I64, F64, P, P],
     "cf_reci_phase": [P, P, P, P, I64, P, P],
@@ -65,6 +66,23 @@ class PeerGatherDescriptor(ctypes.Structure):
     """``cf_peer_gather`` of include/crystalformer_b200.h: one step of a peer gather as seen by one rank."""
     _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("rows_per_rank", c_int64),
                 ("step", ctypes.c_uint32), ("reserved", ctypes.c_uint32), ("cells", c_void_p * MAX_PEERS)]
+
+
+class ModelDesc(ctypes.Structure):
+    """``cf_model_desc`` of include/crystalformer_b200.h: the batch-independent arguments of cf_model_forward."""
+    _fields_ = [("feature_dim", c_int64), ("W_embed", c_void_p), ("W_embed_packed", c_void_p),
+                ("num_layers", ctypes.c_int32), ("lattice_range", ctypes.c_int32), ("minimum_range", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("weights", c_void_p), ("scalars", c_void_p), ("K", c_int64),
+                ("ff_dim", c_int64), ("wscale", c_double), ("cutoff_radius", c_double), ("W1", c_void_p), ("b1", c_void_p),
+                ("hidden", c_int64), ("W2", c_void_p), ("b2", c_void_p), ("targets", c_int64), ("order_reach", c_double)]
+
+
+class ServeSlot(ctypes.Structure):
+    """``cf_serve_slot``: the streams, events and buffers of one batch in flight."""
+    _fields_ = [("copy_stream", c_void_p), ("compute_stream", c_void_p), ("copied", c_void_p), ("inputs_free", c_void_p),
+                ("done", c_void_p), ("x", c_void_p), ("pos", c_void_p), ("trans", c_void_p), ("sizes", c_void_p),
+                ("workspace", c_void_p), ("y", c_void_p), ("y_host", c_void_p), ("max_atoms_total", c_int64),
+                ("max_crystals", c_int64), ("max_edges", c_int64)]
 
 
 class CrystalformerB200Error(RuntimeError):

@@ -150,6 +150,15 @@ class Latticeformer(nn.Module):
             sr = P.scale_real[0] if isinstance(P.scale_real, (list, tuple)) else P.scale_real
             dist_max = -dist_max * sr
         plan["hidden"], plan["targets"] = plan["w1"].shape[0], plan["w2"].shape[0]
+        if plan["emb_packed"] is not None:  # the description of the model for cf_serve_submit
+            plan["desc"] = _lib.ModelDesc(
+                feature_dim=plan["emb"].shape[1], W_embed=plan["emb"].data_ptr(), W_embed_packed=plan["emb_packed"].data_ptr(),
+                num_layers=len(enc.layers), lattice_range=int(P.lattice_range),
+                minimum_range=int(P.lattice_range) if P.minimum_range else 0, reserved=0,
+                weights=ctypes.cast(w["ptrs"], ctypes.c_void_p), scalars=ctypes.cast(w["scalars"], ctypes.c_void_p),
+                K=int(P.value_pe_dist_real), ff_dim=w["ff"], wscale=float(P.value_pe_width_scale), cutoff_radius=enc._cutoff(),
+                W1=plan["w1"].data_ptr(), b1=plan["b1"].data_ptr(), hidden=plan["hidden"], W2=plan["w2"].data_ptr(),
+                b2=plan["b2"].data_ptr(), targets=plan["targets"], order_reach=float(dist_max) + 1.0)
         plan["tail"] = (len(enc.layers), w["ptrs"], w["scalars"], int(P.value_pe_dist_real), w["ff"],
                         float(P.value_pe_width_scale), enc._cutoff(), int(P.lattice_range),
                         int(P.lattice_range) if P.minimum_range else 0, plan["w1"].data_ptr(), plan["b1"].data_ptr(),

@@ -397,6 +397,51 @@ int cf_model_forward(void *cublas_handle, const float *features, int64_t feature
                      void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
+ * One host call per batch of a streaming inference loop (no counterpart in the reference, whose demo and training
+ * scripts call the model batch by batch from a DataLoader): pinned host inputs -> device on a copy stream, the
+ * cf_model_forward of the batch on a compute stream with its preparation started as soon as the copy is done,
+ * outputs -> pinned host memory, and the events that order them.  Everything a batch in flight needs is a slot owned
+ * by the caller; nothing is allocated, kept or synchronised here.  Only the cuBLAS-free path (packed weights).
+ *   cf_model_desc : the batch-independent arguments of cf_model_forward (same meaning); the two HOST arrays must
+ *                   stay valid while calls are being made.
+ *   cf_serve_slot : streams and events as void* (cudaStream_t / cudaEvent_t); device buffers x (max_atoms_total x
+ *                   feature_dim), pos (max_atoms_total x 3), trans (max_crystals x 9) float32, sizes (max_crystals)
+ *                   int64, workspace (cf_model_workspace_bytes of the three maxima), y (max_crystals x targets);
+ *                   y_host: pinned, max_crystals x targets.  `copied` is recorded after the input copies,
+ *                   `inputs_free` after the forward, `done` after the output copy (the caller waits for it, e.g.
+ *                   cudaEventSynchronize, before reading y_host and before reusing the slot).
+ *   inputs_in_use : 0 for a slot's first batch; else the copy stream first waits for the slot's `inputs_free`.
+ * x_host .. sizes_host: HOST memory (pinned for the copies to be asynchronous) of the batch: one-hot species (N x
+ * feature_dim), positions, lattice rows, atoms per crystal; E = sum of sizes^2, max_atoms = largest size.
+ * ---------------------------------------------------------------------------------------------------------- */
+typedef struct cf_model_desc {
+    int64_t feature_dim;
+    const float *W_embed, *W_embed_packed;
+    int32_t num_layers, lattice_range, minimum_range, reserved;
+    const float *const *weights;
+    const double *scalars;
+    int64_t K, ff_dim;
+    double wscale, cutoff_radius;
+    const float *W1, *b1;
+    int64_t hidden;
+    const float *W2, *b2;
+    int64_t targets;
+    double order_reach;
+} cf_model_desc;
+typedef struct cf_serve_slot {
+    void *copy_stream, *compute_stream;
+    void *copied, *inputs_free, *done;
+    float *x, *pos, *trans;
+    int64_t *sizes;
+    void *workspace;
+    float *y, *y_host;
+    int64_t max_atoms_total, max_crystals, max_edges;
+} cf_serve_slot;
+int cf_serve_submit(const cf_model_desc *model, const cf_serve_slot *slot, const float *x_host, const float *pos_host,
+                    const float *trans_host, const int64_t *sizes_host, int64_t N, int64_t B, int64_t E,
+                    int64_t max_atoms, int inputs_in_use);
+
+/* ------------------------------------------------------------------------------------------------------------
  * Scheduling weight of every atom's row for the fused attention kernels (no counterpart in the reference, which
  * launches one thread per (atom, head) in index order): cost[i] = 1500 + n (1 + (4 pi / 3) reach^3 / |det trans|),
  * n the atom count of the atom's crystal; about the number of (key, translation) pairs within `reach` Angstrom.

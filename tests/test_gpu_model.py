@@ -177,8 +177,8 @@ def test_sharded_batches_give_identical_outputs(golden_model):
     assert rel_err(b.cpu().numpy(), full[[1, 5, 3]].cpu().numpy()) < 1e-5
 
 
-@pytest.mark.parametrize("depth,streams,count", [(2, 1, 5), (4, 3, 14)])
-def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, count):
+@pytest.mark.parametrize("depth,streams,count,one_call", [(2, 1, 5, True), (4, 3, 14, True), (3, 2, 7, False)])
+def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, count, one_call):
     """Batches streamed through PipelinedPredictor (copies on a second stream, several batches in flight - on one compute
     stream or alternating between three -, early preparation beside the previous batches, results in pinned ring
     buffers) give exactly what model(batch) gives, in submission order."""
@@ -190,7 +190,9 @@ def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, c
                                   sizes=torch.from_numpy(b.sizes).pin_memory()) for b in batches]
     with torch.no_grad():
         direct = [model(types.SimpleNamespace(**{k: v.cuda() for k, v in vars(h).items()})).cpu() for h in host]
-    runner = PipelinedPredictor(model, depth=depth, streams=streams)
+    # one_call: each submit is one call of cf_serve_submit (copies, forward and events issued by the library); otherwise
+    # the same steps are issued through torch (the path taken with a post-processing callable or a peer gather)
+    runner = PipelinedPredictor(model, depth=depth, streams=streams, post=None if one_call else (lambda y: y))
     got, tickets = [], []
     for h in host:
         if runner.pending() == runner.depth:
@@ -201,5 +203,16 @@ def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, c
     assert len(got) == len(direct)
     for y, ref in zip(got, direct):
         assert torch.equal(y, ref)
+    assert (runner._native[0] is not None) == one_call
     with pytest.raises(RuntimeError):
         runner.result(123)
+    if one_call:  # a batch larger than the slot's buffers is refused by the library, not written past their end
+        from crystalformer_b200 import _lib
+        import ctypes
+        st, h = runner._native[0], host[0]
+        st["c"].max_atoms_total = 1
+        with pytest.raises(_lib.CrystalformerB200Error) as e:
+            _lib.call("cf_serve_submit", ctypes.byref(runner._plan["desc"]), ctypes.byref(st["c"]), h.x.data_ptr(),
+                      h.pos.data_ptr(), h.trans_vec.data_ptr(), h.sizes.data_ptr(), int(h.x.shape[0]), int(h.sizes.shape[0]),
+                      int((h.sizes ** 2).sum()), int(h.sizes.max()), 1)
+        assert "exceeds the slot's buffers" in str(e.value)
