@@ -47,7 +47,7 @@ SIGNATURES = {
     "cf_row_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
     "cf_infinite_attn_fwd_sorted": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                                     I32, P, P, P, P],
-    "cf_serve_submit": [P, P, P, P, P, P, I64, I64, I64, I64, I32],
+    "cf_serve_submit": [P, P, P, P, P, P, I64, I64, I64, I64, I32, P],
     "cf_row_cost": [P, P, I64, I64, F64, P, P],
     "cf_row_order": [P, P, I64, I64, F64, P, P],
     "cf_reci_phase": [P, P, P, P, I64, P, P],
@@ -72,7 +72,7 @@ class ModelDesc(ctypes.Structure):
     """``cf_model_desc`` of include/crystalformer_b200.h: the batch-independent arguments of cf_model_forward."""
     _fields_ = [("feature_dim", c_int64), ("W_embed", c_void_p), ("W_embed_packed", c_void_p),
                 ("num_layers", ctypes.c_int32), ("lattice_range", ctypes.c_int32), ("minimum_range", ctypes.c_int32),
-                ("reserved", ctypes.c_int32), ("weights", c_void_p), ("scalars", c_void_p), ("K", c_int64),
+                ("dense_tile_rows", ctypes.c_int32), ("weights", c_void_p), ("scalars", c_void_p), ("K", c_int64),
                 ("ff_dim", c_int64), ("wscale", c_double), ("cutoff_radius", c_double), ("W1", c_void_p), ("b1", c_void_p),
                 ("hidden", c_int64), ("W2", c_void_p), ("b2", c_void_p), ("targets", c_int64), ("order_reach", c_double)]
 
@@ -83,6 +83,14 @@ class ServeSlot(ctypes.Structure):
                 ("done", c_void_p), ("x", c_void_p), ("pos", c_void_p), ("trans", c_void_p), ("sizes", c_void_p),
                 ("workspace", c_void_p), ("y", c_void_p), ("y_host", c_void_p), ("max_atoms_total", c_int64),
                 ("max_crystals", c_int64), ("max_edges", c_int64)]
+
+
+class ServeGather(ctypes.Structure):
+    """``cf_serve_gather``: the peer gather of one step of ``cf_serve_submit``."""
+    _fields_ = [("store", c_void_p), ("collect_stream", c_void_p), ("store_after", c_void_p), ("stored", c_void_p),
+                ("collected", c_void_p), ("own_cells", c_void_p), ("index", c_void_p), ("total_rows", c_int64),
+                ("y_all", c_void_p), ("y_all_host", c_void_p), ("status", c_void_p), ("status_host", c_void_p),
+                ("timeout_s", c_double)]
 
 
 class CrystalformerB200Error(RuntimeError):

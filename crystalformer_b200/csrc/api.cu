@@ -39,6 +39,12 @@ float weight_floor_log2()
     return f < -1e30 ? -1e30f : (float)f;
 }
 
+int &dense_tile_rows_choice()
+{
+    static thread_local int rows = 0;
+    return rows;
+}
+
 bool sorted_rows_enabled() { return g_sorted_rows.load() != 0; }
 
 bool chained_launches_enabled() { return g_chained.load() != 0; }

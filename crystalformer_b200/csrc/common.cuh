@@ -18,6 +18,12 @@ int fail(int code, const char *fmt, ...);
 int launch_status(const char *what);
 float weight_floor_log2();  // log2 of the weight below which a term is left out of the basis accumulation
 unsigned long long *row_stats_words();  // device words that the sorted row kernel adds its work counts to, or NULL
+int &dense_tile_rows_choice();  // this thread's row tile of the dense blocks: 0 = chosen per launch, 16, 32
+struct DenseTileRows {           // sets it for a scope
+    int saved;
+    explicit DenseTileRows(int rows) : saved(dense_tile_rows_choice()) { dense_tile_rows_choice() = rows; }
+    ~DenseTileRows() { dense_tile_rows_choice() = saved; }
+};
 bool sorted_rows_enabled();  // the one-call forwards may use row lists and the sorted row kernel (cf_set_sorted_rows)
 
 #define CF_REQUIRE(cond, code, ...) \

@@ -487,10 +487,13 @@ int launch_dense_block(const DenseArgs &p, cudaStream_t s)
     if (!p.tail && p.Wembed != nullptr && (p.features == nullptr || p.feature_dim < 1 || p.feature_dim > 128))
         return fail(CF_ERR_UNSUPPORTED, "dense block: embedding of %d features (1..128)", p.feature_dim);
     // 16-row tiles while they fit one wave of the SMs (more SMs busy), 32-row tiles beyond (half the weight traffic;
-    // a block is tensor-pipe bound either way, so what counts is the number of waves)
+    // a block is tensor-pipe bound either way, so what counts is the number of waves) - unless the caller chose:
+    // with several forwards side by side on the GPU the 32-row tiles' smaller total of SM time is worth more than
+    // the single forward's latency
     const long long tiles16 = (p.N + 15) / 16;
     const int sms = sm_count();
-    const bool small = tiles16 <= sms;
+    const int choice = dense_tile_rows_choice();
+    const bool small = choice == 16 || (choice != 32 && tiles16 <= sms);
     const size_t smem = sizeof(unsigned) * (4 * (small ? 16 : 32) * LDA + DB_WARPS * RING_WORDS +
                                             (KSPLIT > 1 ? 2 * 8 * 32 * 8 * (small ? 1 : 2) : 0));
     auto kernel = small ? dense_block_kernel<1> : dense_block_kernel<2>;

@@ -154,7 +154,7 @@ class Latticeformer(nn.Module):
             plan["desc"] = _lib.ModelDesc(
                 feature_dim=plan["emb"].shape[1], W_embed=plan["emb"].data_ptr(), W_embed_packed=plan["emb_packed"].data_ptr(),
                 num_layers=len(enc.layers), lattice_range=int(P.lattice_range),
-                minimum_range=int(P.lattice_range) if P.minimum_range else 0, reserved=0,
+                minimum_range=int(P.lattice_range) if P.minimum_range else 0, dense_tile_rows=0,
                 weights=ctypes.cast(w["ptrs"], ctypes.c_void_p), scalars=ctypes.cast(w["scalars"], ctypes.c_void_p),
                 K=int(P.value_pe_dist_real), ff_dim=w["ff"], wscale=float(P.value_pe_width_scale), cutoff_radius=enc._cutoff(),
                 W1=plan["w1"].data_ptr(), b1=plan["b1"].data_ptr(), hidden=plan["hidden"], W2=plan["w2"].data_ptr(),

@@ -31,13 +31,16 @@ from . import _lib
 
 class PipelinedPredictor:
     def __init__(self, model: torch.nn.Module, depth: int = 3, device: Optional[torch.device] = None, post=None,
-                 gather=None, streams: int = 1):
+                 gather=None, streams: int = 1, dense_tile_rows: Optional[int] = None):
         """``post``: optional callable applied to the model output on the device before it is copied to the host
         (e.g. an all-gather of the ranks' outputs).  ``gather``: a ``sharding.PeerGather`` handed to the model, which
         then returns the outputs of every rank's crystals.  ``streams``: compute streams the batches alternate between
         (1 = the stream current at ``submit``).  With two, the kernels of consecutive, independent batches run side by
         side and fill each other's idle issue slots (they are latency-bound), at the price of a longer latency per
-        batch; not combined with ``gather``, whose steps must run in the same order on every rank."""
+        batch; with a ``gather`` only if it overlaps its collects (its steps must otherwise run in one order on every
+        rank's one stream).  ``dense_tile_rows`` (16, 32 or 0 = chosen per launch; default 32 with several streams, else
+        0): the row tile of the fused dense blocks when batches are submitted through the library's one-call path:
+        32-row tiles take a little longer per forward and less SM time in total, which pays once streams overlap."""
         if depth < 1:
             raise ValueError("depth must be at least 1")
         self.model = model
@@ -45,6 +48,7 @@ class PipelinedPredictor:
         if self.device.type != "cuda":
             raise RuntimeError("PipelinedPredictor needs a CUDA model: crystalformer_b200 has no CPU path")
         self.depth = depth
+        self.dense_tile_rows = (32 if streams > 1 else 0) if dense_tile_rows is None else int(dense_tile_rows)
         self.post = post
         self.gather = gather
         if streams < 1 or (streams > 1 and gather is not None and not getattr(gather, "overlap", False)):
@@ -70,6 +74,8 @@ class PipelinedPredictor:
         native = getattr(self.model, "_native_ok", None)
         self._plan = self.model.native_plan(self.device) if (native is not None and not self.model.training
                                                              and native_ok_without_grad(self.model)) else None
+        if self._plan is not None and "desc" in self._plan:
+            self._plan["desc"].dense_tile_rows = self.dense_tile_rows
 
     def _device_inputs(self, slot: int, batch):
         """Device tensors of the slot with the batch's shapes (allocated once per shape, not per batch)."""
@@ -113,15 +119,23 @@ class PipelinedPredictor:
                            x=t["x"].data_ptr(), pos=t["pos"].data_ptr(), trans=t["trans"].data_ptr(), sizes=t["sizes"].data_ptr(),
                            workspace=t["work"].data_ptr(), y=t["y"].data_ptr(), y_host=t["y_host"].data_ptr(),
                            max_atoms_total=N, max_crystals=B, max_edges=E)
+        if self.gather is not None:
+            g = self.gather
+            t["y_all"] = torch.empty((g.total_rows, g.targets), dtype=torch.float32, device=dev)
+            t["y_all_host"] = torch.empty((g.total_rows, g.targets), dtype=torch.float32).pin_memory()
+            t["status_host"] = torch.zeros(1, dtype=torch.int32).pin_memory()
+            stored = torch.cuda.Event()
+            stored.record(compute)
+            events.append(stored)
         st = self._native[slot] = dict(c=c, tensors=t, events=events, used=False)
         return st
 
     def _native_applies(self, batch) -> bool:
         """One C call per batch (``cf_serve_submit``) when the model runs its one-call forward with the embedding folded
-        into the first block, nothing is applied to the outputs on the device, and the inputs are host tensors of
-        the types the kernels read."""
+        into the first block, nothing but a peer gather is applied to the outputs on the device, and the inputs are
+        host tensors of the types the kernels read."""
         plan = self._plan
-        if plan is None or "desc" not in plan or self.post is not None or self.gather is not None:
+        if plan is None or "desc" not in plan or self.post is not None:
             return False
         if getattr(self.model.encoder, "attention_event_log", None) is not None:
             return False  # (per-layer timing events are handed over by the framework-level path)
@@ -142,14 +156,23 @@ class PipelinedPredictor:
         if n_atoms > 0 and self._native_applies(batch):
             n_crystals = int(sizes_np.size)
             st = self._native_slot(slot, n_atoms, n_crystals, n_edges, compute)
+            t = st["tensors"]
+            gather = None
+            if self.gather is not None:
+                if n_crystals != self.gather.local_rows:
+                    raise ValueError(f"the peer gather expects {self.gather.local_rows} crystals per batch of this rank")
+                gather = self.gather.serve_step(compute, t["y_all"], t["y_all_host"], t["status_host"], st["events"][3])
             with torch.cuda.device(self.device):
                 _lib.call("cf_serve_submit", ctypes.byref(self._plan["desc"]), ctypes.byref(st["c"]), batch.x.data_ptr(),
                           batch.pos.data_ptr(), batch.trans_vec.data_ptr(), batch.sizes.data_ptr(), n_atoms, n_crystals,
-                          n_edges, max_atoms, 1 if st["used"] else 0)
+                          n_edges, max_atoms, 1 if st["used"] else 0, None if gather is None else ctypes.byref(gather))
             st["used"] = True
             st["batch"] = batch  # the copies read the host tensors after this call returns
             ticket = self._next
-            self._inflight.append((ticket, st["events"][2], st["tensors"]["y_host"][:n_crystals], None))
+            if gather is None:
+                self._inflight.append((ticket, st["events"][2], t["y_host"][:n_crystals], None))
+            else:
+                self._inflight.append((ticket, st["events"][2], t["y_all_host"], t["status_host"]))
             self._next += 1
             return ticket
         dev = self._device_inputs(slot, batch)

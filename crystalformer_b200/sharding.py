@@ -188,6 +188,33 @@ class PeerGather:
         at = (self.step % self.slots) * self._slot_bytes
         return peer_descriptor(self.world, self.rank, self.rows_per_rank, self.step, [b + at for b in self._bases])
 
+    def serve_step(self, compute_stream, y_all: torch.Tensor, y_all_host: torch.Tensor, status_host: torch.Tensor,
+                   stored: torch.cuda.Event) -> _lib.ServeGather:
+        """Advances to the next step and describes it for ``cf_serve_submit``, which then issues what
+        ``next_descriptor`` (the wait for the collect of step - slots // 2), the model's stores and ``collect`` issue:
+        the collect on ``collect_stream`` (``overlap``) or on ``compute_stream``, its outputs in ``y_all`` and, with
+        the status word, in the two pinned host tensors.  ``stored``: an event of the caller's, recorded by the call."""
+        self.step += 1
+        after = None
+        if self.overlap and self.step > self._lag:
+            after = self._collected[(self.step - self._lag) % self.slots]
+        slot = self.step % self.slots
+        at = slot * self._slot_bytes
+        self._serve_desc = peer_descriptor(self.world, self.rank, self.rows_per_rank, self.step, [b + at for b in self._bases])
+        collect_stream = self.collect_stream if self.overlap else compute_stream
+        done = self._collected[slot]
+        if done is None:
+            done = self._collected[slot] = torch.cuda.Event()
+            done.record(collect_stream)  # (an event has a handle once it has been recorded)
+        if self.overlap:
+            self.ready = done
+        return _lib.ServeGather(
+            store=ctypes.addressof(self._serve_desc), collect_stream=collect_stream.cuda_stream,
+            store_after=None if after is None else after.cuda_event, stored=stored.cuda_event, collected=done.cuda_event,
+            own_cells=self._own + at, index=self.index.data_ptr(), total_rows=self.total_rows, y_all=y_all.data_ptr(),
+            y_all_host=y_all_host.data_ptr(), status=self.status.data_ptr(), status_host=status_host.data_ptr(),
+            timeout_s=self.timeout_s)
+
     def store(self, y: torch.Tensor) -> None:
         """Opens the next step with outputs that exist already: (local crystals, targets) on this rank's device."""
         y = y.detach().float().contiguous()

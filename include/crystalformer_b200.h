@@ -411,13 +411,25 @@ int cf_model_forward(void *cublas_handle, const float *features, int64_t feature
  *                   `inputs_free` after the forward, `done` after the output copy (the caller waits for it, e.g.
  *                   cudaEventSynchronize, before reading y_host and before reusing the slot).
  *   inputs_in_use : 0 for a slot's first batch; else the copy stream first waits for the slot's `inputs_free`.
+ *   gather        : null, or the peer gather of the step (one process per GPU, each with its shard of the batch):
+ *                   `store` is the step's descriptor for cf_model_forward; the compute stream first waits for
+ *                   `store_after` (if not null: the event after the collect that last read the slot the step
+ *                   stores to); `stored` is recorded after the forward; the collect (cf_peer_gather_collect with
+ *                   `own_cells`, `index`, `total_rows`, `status`, `timeout_s`) runs on `collect_stream` after
+ *                   `stored`, writes y_all (total_rows x targets) and is followed by `collected`; y_all and the
+ *                   status word then go to y_all_host / status_host (pinned) and the slot's `done` is recorded on
+ *                   the collect stream.  The slot's y / y_host are not copied in that case.
+ *   cf_model_desc.dense_tile_rows : 0 = the dense blocks choose their row tile themselves (16 rows while that fills
+ *                   one wave of SMs: shortest latency of a single forward); 32 = 32-row tiles (fewer, longer blocks
+ *                   that read the weights half as often: more forwards per second when several streams keep the GPU
+ *                   full); 16 = always 16.
  * x_host .. sizes_host: HOST memory (pinned for the copies to be asynchronous) of the batch: one-hot species (N x
  * feature_dim), positions, lattice rows, atoms per crystal; E = sum of sizes^2, max_atoms = largest size.
  * ---------------------------------------------------------------------------------------------------------- */
 typedef struct cf_model_desc {
     int64_t feature_dim;
     const float *W_embed, *W_embed_packed;
-    int32_t num_layers, lattice_range, minimum_range, reserved;
+    int32_t num_layers, lattice_range, minimum_range, dense_tile_rows;
     const float *const *weights;
     const double *scalars;
     int64_t K, ff_dim;
@@ -437,9 +449,20 @@ typedef struct cf_serve_slot {
     float *y, *y_host;
     int64_t max_atoms_total, max_crystals, max_edges;
 } cf_serve_slot;
+typedef struct cf_serve_gather {
+    const cf_peer_gather *store;
+    void *collect_stream;
+    void *store_after, *stored, *collected;
+    const uint64_t *own_cells;
+    const int64_t *index;
+    int64_t total_rows;
+    float *y_all, *y_all_host;
+    int32_t *status, *status_host;
+    double timeout_s;
+} cf_serve_gather;
 int cf_serve_submit(const cf_model_desc *model, const cf_serve_slot *slot, const float *x_host, const float *pos_host,
                     const float *trans_host, const int64_t *sizes_host, int64_t N, int64_t B, int64_t E,
-                    int64_t max_atoms, int inputs_in_use);
+                    int64_t max_atoms, int inputs_in_use, const cf_serve_gather *gather);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Scheduling weight of every atom's row for the fused attention kernels (no counterpart in the reference, which

@@ -214,5 +214,5 @@ def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, c
         with pytest.raises(_lib.CrystalformerB200Error) as e:
             _lib.call("cf_serve_submit", ctypes.byref(runner._plan["desc"]), ctypes.byref(st["c"]), h.x.data_ptr(),
                       h.pos.data_ptr(), h.trans_vec.data_ptr(), h.sizes.data_ptr(), int(h.x.shape[0]), int(h.sizes.shape[0]),
-                      int((h.sizes ** 2).sum()), int(h.sizes.max()), 1)
+                      int((h.sizes ** 2).sum()), int(h.sizes.max()), 1, None)
         assert "exceeds the slot's buffers" in str(e.value)

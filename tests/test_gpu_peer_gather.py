@@ -90,6 +90,42 @@ def test_model_forward_with_a_gather_of_one_rank(golden_model, overlap):
     gather.close()
 
 
+@pytest.mark.parametrize("overlap,streams", [(False, 1), (True, 3)])
+def test_predictor_with_a_gather_of_one_rank(golden_model, overlap, streams):
+    """Host batches through PipelinedPredictor with a peer gather (world = 1): each submit is one library call that
+    copies the inputs, runs the forward, collects the gathered rows and copies them and the status word to the host."""
+    import types
+    from test_gpu_model import build
+    from crystalformer_b200.serving import PipelinedPredictor
+    from crystalformer_b200.sharding import PeerGather
+    from crystalformer_b200.synthetic import make_crystals, uniform_atoms
+    model = build(golden_model).eval()
+    B = 9
+    batches = [make_crystals(70 + s, B, uniform_atoms(1, 8), length_range=(3.0, 10.0)) for s in range(11)]
+    host = [types.SimpleNamespace(x=torch.from_numpy(b.x).pin_memory(), pos=torch.from_numpy(b.pos).pin_memory(),
+                                  trans_vec=torch.from_numpy(b.trans_vec).pin_memory(),
+                                  sizes=torch.from_numpy(b.sizes).pin_memory()) for b in batches]
+    order = [int(g) for g in np.random.default_rng(1).permutation(B)]
+    with torch.no_grad():
+        direct = [model(types.SimpleNamespace(**{k: v.cuda() for k, v in vars(h).items()})).cpu() for h in host]
+    gather = PeerGather([order], model.mlp[-1].out_features, torch.device("cuda"), slots=8, overlap=overlap)
+    runner = PipelinedPredictor(model, depth=4, streams=streams, gather=gather)
+    got, tickets = [], []
+    for h in host:
+        if runner.pending() == runner.depth:
+            got.append(runner.result(tickets.pop(0)).clone())
+        tickets.append(runner.submit(h))
+    while tickets:
+        got.append(runner.result(tickets.pop(0)).clone())
+    assert runner._native[0] is not None  # the one-call path was taken
+    for y_all, y in zip(got, direct):
+        expect = torch.empty_like(y)
+        expect[torch.as_tensor(order)] = y
+        assert torch.equal(y_all, expect)
+    gather.check()
+    gather.close()
+
+
 _CHILD = r"""
 import json, os, sys, types
 sys.path.insert(0, os.environ["CF_REPO"])
@@ -109,6 +145,15 @@ shards = lpt_assign(cb.sizes, world)
 mine = cb.select(shards[rank])
 t = lambda a: torch.from_numpy(a).to(dev)
 batch = types.SimpleNamespace(x=t(mine.x), pos=t(mine.pos), trans_vec=t(mine.trans_vec), sizes=t(mine.sizes))
+# one training-mode forward fixes the Gaussian-width statistics (rank 0's, sent to all), so that the model runs its
+# one-call inference path and is the same on every rank
+model.train()
+with torch.no_grad():
+    model(batch)
+model.eval()
+for name, buf in model.named_buffers():
+    if name.endswith("gauss_scale"):
+        dist.broadcast(buf, src=0)
 ok = True
 for overlap in (False, True):
     gather = PeerGather(shards, model.mlp[-1].out_features, dev, timeout_s=10.0, slots=8 if overlap else 4, overlap=overlap)
@@ -132,10 +177,29 @@ for overlap in (False, True):
         ok = ok and all(bool(torch.equal(o, want)) for o in outs)
     gather.check()
     gather.close()
-flag = torch.tensor([1 if ok else 0], device=dev)
+# host batches through the pipelined predictor: one library call per batch does copies, forward, collect and read-back
+from crystalformer_b200.serving import PipelinedPredictor
+pin = lambda a: torch.from_numpy(a).pin_memory()
+hostb = types.SimpleNamespace(x=pin(mine.x), pos=pin(mine.pos), trans_vec=pin(mine.trans_vec), sizes=pin(mine.sizes))
+gather = PeerGather(shards, model.mlp[-1].out_features, dev, timeout_s=10.0, slots=8, overlap=True)
+runner = PipelinedPredictor(model, depth=4, streams=3, gather=gather, dense_tile_rows=0)
+tickets, outs = [], []
+for step in range(13):
+    if runner.pending() == runner.depth:
+        outs.append(runner.result(tickets.pop(0)).clone())
+    tickets.append(runner.submit(hostb))
+while tickets:
+    outs.append(runner.result(tickets.pop(0)).clone())
+one_call = runner._native[0] is not None
+served = len(outs) == 13 and all(bool(torch.equal(o, want.cpu())) for o in outs)
+if not served:
+    print("rank", rank, "served outputs differ:", [float((o - want.cpu()).abs().max()) for o in outs], file=sys.stderr)
+gather.check()
+gather.close()
+flag = torch.tensor([int(ok), int(one_call), int(served)], device=dev)
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 if rank == 0:
-    print(json.dumps({"ok": int(flag.item())}))
+    print(json.dumps(dict(zip(("model", "one_call", "served"), flag.tolist()))))
 dist.destroy_process_group()
 """
 
@@ -149,4 +213,4 @@ def test_two_ranks_on_two_gpus(tmp_path):
            "127.0.0.1", "--master-port", "29641", str(script)]
     proc = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
-    assert json.loads(proc.stdout.strip().splitlines()[-1]) == {"ok": 1}
+    assert json.loads(proc.stdout.strip().splitlines()[-1]) == {"model": 1, "one_call": 1, "served": 1}
