@@ -8,17 +8,18 @@ namespace {
 
 constexpr int RL_THREADS = 256;
 constexpr int RL_WARPS = RL_THREADS / 32;
-constexpr int RL_BUCKETS = 512;
+constexpr int RL_BUCKETS = 2 * RL_THREADS;  // (the scan below takes two buckets per thread)
 constexpr int RL_MAX_TRANSLATIONS = 4096;  // boxes beyond this are not listed
 constexpr size_t RL_SMEM = sizeof(unsigned long long) * 2 * ROW_LIST_CAP + sizeof(int) * (2 * RL_BUCKETS + 8);
 
-// One thread block per row.  Lanes run over the translations of the box that contains every head's box (32 per
-// pass), the warps over (pass, quarter of the row's keys) units, so that lanes are busy whatever the number of keys;
-// terms within `window` of their edge's nearest image are appended to a shared-memory buffer (one atomic per warp and
-// step) as 64-bit items (d2 bits << 32 | key).  The items are then sorted: distributed over RL_BUCKETS buckets that
-// are equally spaced in d^3 (terms are about uniform in volume, so buckets hold a handful of items each), and placed
-// inside their bucket by counting the smaller items of the same bucket.  The 64-bit items are distinct except for
-// exact duplicates, so the result does not depend on the order in which the atomics arrived.
+// One thread block per row.  Every key's candidate translations (a bounding box of the ball that holds its listed
+// terms) are walked one per thread and step; terms within `window` of their edge's nearest image are appended to a
+// shared-memory buffer (one atomic per warp and step) as 64-bit items (d2 bits << 32 | key).  The items are then
+// sorted: distributed over RL_BUCKETS buckets that are equally spaced in d^3 (terms are about uniform in volume, so
+// buckets hold a handful of items each), and placed inside their bucket by counting the smaller items of the same
+// bucket.  The 64-bit items are distinct except for exact duplicates, so the result does not depend on the order in
+// which the atomics arrived.  Four warps per row: most of a row's cost is per thread (set-up, scans, barriers), not
+// per item.
 __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowListBuild p)
 {
     extern __shared__ __align__(16) unsigned long long rl_smem[];
@@ -29,6 +30,9 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
     __shared__ int dmin_s[ROW_LIST_MAX_KEYS];
     __shared__ float4 key_s[ROW_LIST_MAX_KEYS];                // relative position of every key, .w = its threshold
     __shared__ int cnt_s;
+    __shared__ int4 kbox_s[ROW_LIST_MAX_KEYS];                 // first translation of every key's box, its widths w3 | w2 << 8
+    __shared__ int kpre_s[ROW_LIST_MAX_KEYS + 1];              // translations in the boxes of the keys before
+    __shared__ float d2max_s;
     __shared__ long long base_s;
     const int tid = threadIdx.x, lane = tid & 31, wr = tid >> 5;
     const unsigned lt = (1u << lane) - 1u;
@@ -76,39 +80,88 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
             }
         }
         __syncthreads();
-        float d2_max = 1.0f;  // no listed term is farther (the same value in every thread)
+        // ---- the walk.  A key's listed terms lie in the ball |r + n1 t1 + n2 t2 + n3 t3|^2 <= threshold, a small part of
+        //      the box of the cut-off rule: with b_i the reciprocal rows (b_i . t_j = delta_ij), (r + n T) . b_i =
+        //      s_i + n_i and |x . b_i| <= |x| |b_i| bound every digit,
+        //          | n_i + s_i | <= rho |b_i|,      s_i = r . b_i,  rho = sqrt(threshold).
+        //      The first warp computes every key's bounding box, clipped to the rule's box (one key per lane; the
+        //      bounds are widened a little beyond any rounding, the test on d2 below decides membership, so the listed
+        //      set is that of a walk of the whole box), and the running sum of the boxes' sizes; then all threads walk
+        //      the concatenation of the boxes, one translation per thread and step, finding their key by bisection.
+        if (fits && wr == 0) {
+            const float c1x = cell.t2y * cell.t3z - cell.t2z * cell.t3y, c1y = cell.t2z * cell.t3x - cell.t2x * cell.t3z,
+                        c1z = cell.t2x * cell.t3y - cell.t2y * cell.t3x;
+            const float c2x = cell.t3y * cell.t1z - cell.t3z * cell.t1y, c2y = cell.t3z * cell.t1x - cell.t3x * cell.t1z,
+                        c2z = cell.t3x * cell.t1y - cell.t3y * cell.t1x;
+            const float c3x = cell.t1y * cell.t2z - cell.t1z * cell.t2y, c3y = cell.t1z * cell.t2x - cell.t1x * cell.t2z,
+                        c3z = cell.t1x * cell.t2y - cell.t1y * cell.t2x;
+            const float det = cell.t1x * c1x + cell.t1y * c1y + cell.t1z * c1z;
+            const bool prune = fabsf(det) > 1e-12f;  // (a flat cell keeps the whole box)
+            const float idet = prune ? 1.0f / det : 0.0f;
+            int lo1 = -R1, hi1 = R1, lo2 = -R2, hi2 = R2, lo3 = -R3, hi3 = R3;
+            const float4 r = lane < n ? key_s[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (prune) {
+                const float rho = sqrtf(fmaxf(r.w, 0.f)) * 1.0001f;
+                const float m1 = rho * sqrtf(c1x * c1x + c1y * c1y + c1z * c1z) * fabsf(idet) + 1e-3f;
+                const float m2 = rho * sqrtf(c2x * c2x + c2y * c2y + c2z * c2z) * fabsf(idet) + 1e-3f;
+                const float m3 = rho * sqrtf(c3x * c3x + c3y * c3y + c3z * c3z) * fabsf(idet) + 1e-3f;
+                const float s1 = (r.x * c1x + r.y * c1y + r.z * c1z) * idet, s2 = (r.x * c2x + r.y * c2y + r.z * c2z) * idet,
+                            s3 = (r.x * c3x + r.y * c3y + r.z * c3z) * idet;
+                // (clamped as floats first: the conversions then see small values only)
+                lo1 = (int)ceilf(fmaxf(-m1 - s1, (float)-R1)); hi1 = (int)floorf(fminf(m1 - s1, (float)R1));
+                lo2 = (int)ceilf(fmaxf(-m2 - s2, (float)-R2)); hi2 = (int)floorf(fminf(m2 - s2, (float)R2));
+                lo3 = (int)ceilf(fmaxf(-m3 - s3, (float)-R3)); hi3 = (int)floorf(fminf(m3 - s3, (float)R3));
+            }
+            const int w1 = max(hi1 - lo1 + 1, 0), w2 = max(hi2 - lo2 + 1, 0), w3 = max(hi3 - lo3 + 1, 0);
+            const int count = lane < n ? w1 * w2 * w3 : 0;
+            int incl = count;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(FULL, incl, o);
+                if (lane >= o) incl += up;
+            }
+            kpre_s[lane + 1] = incl;
+            if (lane == 0) kpre_s[0] = 0;
+            kbox_s[lane] = make_int4(lo1, lo2, lo3, max(w3, 1) | (max(w2, 1) << 8));
+            const float top = warp_max(lane < n ? r.w : 1.0f);
+            if (lane == 0) d2max_s = fmaxf(top, 1.0f);
+        }
+        __syncthreads();
+        const float d2_max = fits ? d2max_s : 1.0f;  // no listed term is farther (the same value in every thread)
         if (fits) {
-            for (int j = 0; j < n; ++j) d2_max = fmaxf(d2_max, key_s[j].w);
-            // ---- the walk: unit u = (pass of 32 translations, quarter of the keys); r + n1 t1 + n2 t2 + n3 t3 is
-            //      contracted like the reference's expression
-            const int units = 4 * ((T + 31) >> 5);
-            const float inv_s3 = __frcp_rn((float)S3), inv_s2 = __frcp_rn((float)S2);
-            for (int u = wr; u < units; u += RL_WARPS) {
-                const int tr = 32 * (u >> 2) + lane;
-                const bool in_box = tr < T;
-                // digits of tr in the mixed radix (S1, S2, S3): quotients by a rounded-down product with the reciprocal
-                // (exact for these small integers: tr < 2^12, S <= 65)
-                const int i12 = __float2int_rd(((float)tr + 0.5f) * inv_s3), i3 = tr - i12 * S3;
-                const int i1 = __float2int_rd(((float)i12 + 0.5f) * inv_s2), i2 = i12 - i1 * S2;
-                const int n1 = i1 - R1, n2 = i2 - R2, n3 = i3 - R3;
+            const int cand = kpre_s[n];
+            for (int f0 = 0; f0 < cand; f0 += RL_THREADS) {  // (block-uniform bounds: the ballots below are safe)
+                const int f = f0 + tid;
+                const bool valid = f < cand;
+                int j = 0;
+#pragma unroll
+                for (int step = 16; step >= 1; step >>= 1)
+                    if (j + step < n && kpre_s[j + step] <= f) j += step;  // the last key whose boxes start at or before f
+                const int4 kb = kbox_s[j];
+                const float4 r = key_s[j];
+                const int w3 = kb.w & 255, w2 = kb.w >> 8;
+                const int tr = valid ? f - kpre_s[j] : 0;
+                // digits of tr in the mixed radix (w1, w2, w3): quotients by a rounded-down product with the reciprocal
+                // (exact for these small integers: tr < 2^13, w <= 65)
+                const int i12 = __float2int_rd(((float)tr + 0.5f) * __frcp_rn((float)w3)), i3 = tr - i12 * w3;
+                const int i1 = __float2int_rd(((float)i12 + 0.5f) * __frcp_rn((float)w2)), i2 = i12 - i1 * w2;
+                const int n1 = kb.x + i1, n2 = kb.y + i2, n3 = kb.z + i3;
                 const float f1 = (float)n1, f2 = (float)n2, f3 = (float)n3;
-                const int key123 = (abs(n1) << 8) | (abs(n2) << 16) | (abs(n3) << 24);
-                for (int j = u & 3; j < n; j += 4) {
-                    const float4 r = key_s[j];
-                    const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
-                    const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
-                    const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
-                    const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
-                    const bool keep = in_box && d2 <= r.w;
-                    const unsigned mask = __ballot_sync(FULL, keep);
-                    if (mask == 0u) continue;
-                    int base = 0;
-                    if (lane == 0) base = atomicAdd(&cnt_s, __popc(mask));
-                    base = __shfl_sync(FULL, base, 0);
-                    if (keep) {
-                        const int at = base + __popc(mask & lt);
-                        if (at < ROW_LIST_CAP) ent[at] = ((unsigned long long)__float_as_uint(d2) << 32) | (unsigned)(key123 | j);
-                    }
+                // r + n1 t1 + n2 t2 + n3 t3, contracted like the reference's expression
+                const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
+                const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
+                const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
+                const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                const bool keep = valid && d2 <= r.w;
+                const unsigned mask = __ballot_sync(FULL, keep);
+                if (mask == 0u) continue;
+                int base = 0;
+                if (lane == 0) base = atomicAdd(&cnt_s, __popc(mask));
+                base = __shfl_sync(FULL, base, 0);
+                if (keep) {
+                    const int at = base + __popc(mask & lt);
+                    const int key123 = (abs(n1) << 8) | (abs(n2) << 16) | (abs(n3) << 24);
+                    if (at < ROW_LIST_CAP) ent[at] = ((unsigned long long)__float_as_uint(d2) << 32) | (unsigned)(key123 | j);
                 }
             }
         }
