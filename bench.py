@@ -311,7 +311,7 @@ def run_b200(args):
     # N > 1: the pooling + head kernel of every rank stores its outputs into every rank's gather buffer over NVLink
     # and a small kernel waits for all ranks (sharding.PeerGather); no collective library on the data path.
     # (overlap: a step's collect, where a rank waits for the others, runs on its own stream beside the next steps)
-    peers = PeerGather(shards, model.mlp[-1].out_features, device, slots=8, overlap=True) if world > 1 else None
+    peers = PeerGather(shards, model.mlp[-1].out_features, device, slots=12, overlap=True) if world > 1 else None
     extra = {} if peers is None else {"gather": peers}
 
     ready = torch.cuda.Event()
@@ -326,15 +326,15 @@ def run_b200(args):
     d2h_bytes = (global_batch.num_crystals if world > 1 else mine.num_crystals) * 4
 
     from crystalformer_b200.serving import PipelinedPredictor
-    # four batches in flight alternating between three compute streams (the kernels of independent batches fill each
-    # other's idle issue slots)
-    e2e_depth, e2e_streams = 4, 3
+    # six batches in flight alternating between four compute streams (the kernels of independent batches fill each
+    # other's idle issue slots); every submit is one call of the library (cf_serve_submit)
+    e2e_depth, e2e_streams = 6, 4
     runner = PipelinedPredictor(model, depth=e2e_depth, device=device, gather=peers, streams=e2e_streams)
     pending = []
 
     def step_e2e():
         """One batch through the public serving API: pinned host inputs -> device -> forward -> outputs in pinned host
-        memory.  Up to three batches are in flight; the host blocks only when it collects the oldest result."""
+        memory.  Several batches are in flight; the host blocks only when it collects the oldest result."""
         pending.append(runner.submit(pinned))
         if len(pending) == runner.depth:
             runner.result(pending.pop(0))
@@ -386,6 +386,14 @@ def run_b200(args):
     ms_e2e = e2e_wall * 1e3 / e2e_steps
     if peers is not None:
         peers.check()
+    # one more batch through the serving pipeline, compared with the forward of the device-resident copy: the timed
+    # loop delivered the outputs of the model, not of a shortened path
+    y_served = runner.result(runner.submit(pinned)).clone()
+    with torch.no_grad():
+        y_direct = model(resident, counts=(n_atoms, n_edges, max_atoms), **({} if peers is None else {"gather": peers}))
+    if peers is not None:
+        peers.wait_ready()
+    e2e_equal = bool(torch.equal(y_served, y_direct.cpu()))
 
     total_crystals = global_batch.num_crystals
     value = total_crystals / (ms_step * 1e-3)
@@ -450,6 +458,7 @@ def run_b200(args):
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "timed_steps": e2e_steps,
                     "host_issue_ms_per_step": e2e_issue * 1e3 / e2e_steps,
                     "clock": "host wall clock (perf_counter) from the first submit to the last result, max over ranks",
+                    "outputs_equal_direct_forward": e2e_equal,
                     "api": f"crystalformer_b200.serving.PipelinedPredictor, {e2e_depth} batches in flight on {e2e_streams} compute stream(s)"},
             "gpu_launches": None if launches is None else launches * args.steps,
             "gpu_launches_per_step": launches, "kernels_per_step": kernel_names,

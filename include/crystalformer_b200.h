@@ -12,7 +12,8 @@
  *     device memory and synchronise the device (set-up calls, never on the data path),
  *   - returns CF_OK or a negative CF_ERR_* code and never throws; cf_last_error() gives the message of the last
  *     failure on the calling thread.
- * State kept by the library: the two process-wide tuning values (cf_set_weight_floor_log2, cf_set_sorted_rows), a
+ * State kept by the library: the process-wide switches (cf_set_weight_floor_log2, cf_set_sorted_rows,
+ * cf_set_chained_launches, cf_set_row_stats), a
  * side stream and two events per (host thread, device) created by the first cf_encoder_forward / cf_model_forward,
  * the 8 MiB scratch array of cf_lattice_sum_bwd_static, and a pool of row tickets per device: 64 single counters
  * handed round-robin to the cf_infinite_attn_fwd[_listed] calls with K > 0 and 8 blocks of 16 handed round-robin to the
