@@ -10,12 +10,21 @@
 // few thousand rows.  Here a thread block owns a tile of 16 MT atom rows and carries it through all four
 // products; only x', q, k, v and a are written.
 //
-// Arithmetic: fp32 accuracy on the tensor cores by the three-product TF32 split,
-//     a b ~ a_hi b_hi + a_lo b_hi + a_hi b_lo,   a_hi = tf32(a), a_lo = tf32(a - a_hi)      (relative error ~2^-21),
-// with warp-level mma.m16n8k8 (a 16-row tile per instruction fits the ragged, few-thousand-row batches; the
-// 64/128-row tiles of the block-level tensor instructions would leave most SMs idle at these sizes).  Weights are
-// pre-split and stored in fragment order by the host (pack order documented at DensePacked below), so a B fragment is
-// one 16-byte load per lane; activations are split when they are written to shared memory.
+// Arithmetic: fp32-level accuracy on the tensor cores by splitting both operands, a = a_hi + a_lo with a_hi = tf32(a)
+// (so |a_lo| <= 2^-11 |a|), and summing
+//     a b ~ a_hi b_hi  +  ( a_lo b_hi + a_hi b_lo ),
+// the first product in TF32 (exact products of 11-bit mantissas, fp32 accumulation), the bracket - 2^-11 of the
+// result - in bfloat16 with fp32 accumulation as ONE 16-deep product: its A operand interleaves (a_lo, a_hi) along k
+// and its B operand (b_hi, b_lo), so that a k step of 8 costs two tensor instructions (m16n8k8 TF32 + m16n8k16 BF16)
+// instead of the three of an all-TF32 split; every legacy MMA shape issues at the same rate on this GPU (0.46 per
+// clock and SM, measured), so that is a third less tensor time.  Error per term: 2^-22 (a_lo b_lo dropped) + about
+// 2^-20 (bfloat16 rounding of the bracket's operands), i.e. 1e-6 relative, the level of an fp32 dot product of this
+// length.  Warp-level mma (a 16-row tile per instruction) fits the ragged, few-thousand-row batches; the 64/128-row
+// tiles of the block-level tensor instructions would leave most SMs idle at these sizes.  Weights are pre-split and
+// stored in fragment order by the host (pack order documented at DensePacked), so a B fragment is one 16-byte load
+// per lane; activations are split when they are written to shared memory: the `hi` tile holds TF32 words, the `lo`
+// tile the words { lower half: bf16(a_lo), upper half: bf16(a_hi) }, which ldmatrix delivers as the A fragment of the
+// 16-deep bfloat16 product with the same addresses as the TF32 fragment of the hi tile.
 #include "common.cuh"
 #include "dense_block.cuh"
 
@@ -47,6 +56,21 @@ __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const unsigned *ro
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(addr));
+}
+
+// the word of the correction operand: lower half bf16(lo), upper half bf16(hi)
+__device__ __forceinline__ unsigned corr_word(float hi, float lo)
+{
+    unsigned r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ void mma_bf16_k16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ void mma_tf32(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1)
@@ -158,15 +182,15 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
     // 32-bit elements are exactly the a0..a3 of the m16n8k8 A fragment: rows 0-7 / 8-15 of the m tile, words 0-3 / 4-7
     // of the k step.  Lane l supplies the address of row l%8 of matrix l/8.
     const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8, lcol = (lane >> 4) * 4;
-    // the three partial products go to separate accumulators: three independent dependency chains per tile instead of
-    // one of triple length
-    float lo1[MT][2][4], lo2[MT][2][4];
+    // the correction product goes to an accumulator of its own: two independent dependency chains per tile, and the
+    // small terms are summed among themselves before they meet the large ones
+    float corr[MT][2][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) lo1[mt][nt][u] = lo2[mt][nt][u] = 0.f;
+            for (int u = 0; u < 4; ++u) corr[mt][nt][u] = 0.f;
     constexpr int G = MT == 1 ? 4 : 2;  // k steps fetched and issued together: loads of all G before the first MMA
     const int k_first = ws.kh * KSTEPS;
 #pragma unroll 1
@@ -187,11 +211,10 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const unsigned bh0 = __float_as_uint(b[i][nt].x), bh1 = __float_as_uint(b[i][nt].y);
-                const unsigned bl0 = __float_as_uint(b[i][nt].z), bl1 = __float_as_uint(b[i][nt].w);
+                const unsigned bc0 = __float_as_uint(b[i][nt].z), bc1 = __float_as_uint(b[i][nt].w);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    mma_tf32(lo1[mt][nt], al[i][mt], bh0, bh1);
-                    mma_tf32(lo2[mt][nt], ah[i][mt], bl0, bl1);
+                    mma_bf16_k16(corr[mt][nt], al[i][mt], bc0, bc1);
                     mma_tf32(acc[mt][nt], ah[i][mt], bh0, bh1);
                 }
             }
@@ -201,7 +224,7 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) acc[mt][nt][u] += lo1[mt][nt][u] + lo2[mt][nt][u];
+            for (int u = 0; u < 4; ++u) acc[mt][nt][u] += corr[mt][nt][u];
 }
 
 // Writes this lane's accumulator entries of a 128-wide product (columns 16 warp + 8 nt + 2 t + {0,1}) into an operand tile.
@@ -218,7 +241,7 @@ __device__ __forceinline__ void store_split(unsigned *a_hi, unsigned *a_lo, cons
                 const int row = 16 * mt + g + (u >= 2 ? 8 : 0), col = 16 * warp + 8 * nt + 2 * t + (u & 1);
                 const unsigned hi = tf32_hi(v[mt][nt][u]);
                 a_hi[row * LDA + col] = hi;
-                a_lo[row * LDA + col] = tf32_hi(v[mt][nt][u] - __uint_as_float(hi));
+                a_lo[row * LDA + col] = corr_word(__uint_as_float(hi), v[mt][nt][u] - __uint_as_float(hi));
             }
 }
 
@@ -300,7 +323,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                 for (int u = 0; u < 4; ++u) {
                     const unsigned hi = tf32_hi(vv[u]);
                     a1_hi[r * LDA + 4 * c4 + u] = hi;
-                    a1_lo[r * LDA + 4 * c4 + u] = tf32_hi(vv[u] - __uint_as_float(hi));
+                    a1_lo[r * LDA + 4 * c4 + u] = corr_word(__uint_as_float(hi), vv[u] - __uint_as_float(hi));
                 }
             }
             // ---- y = x + bo + attn Wo^T
@@ -380,7 +403,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                 if (row0 + r < p.N && col < p.feature_dim) v = p.features[(row0 + r) * p.feature_dim + col];
                 const unsigned hi = tf32_hi(v);
                 a1_hi[r * LDA + col] = hi;
-                a1_lo[r * LDA + col] = tf32_hi(v - __uint_as_float(hi));
+                a1_lo[r * LDA + col] = corr_word(__uint_as_float(hi), v - __uint_as_float(hi));
             }
             zero(xo);
             __syncthreads();

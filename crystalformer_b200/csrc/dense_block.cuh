@@ -5,9 +5,11 @@
 namespace cf {
 
 // Packed weights (DensePacked order): a Linear weight W (out x in, row-major) is stored as float4 fragments
-//   P[(nt * (in/8) + ks) * 32 + lane] = { hi(W[n][k]), hi(W[n][k+4]), lo(W[n][k]), lo(W[n][k+4]) },
-//   n = 8 nt + lane/4,  k = 8 ks + lane%4,  hi(w) = w rounded to TF32 (10-bit mantissa, ties away), lo(w) = hi(w - hi(w)),
-// i.e. the B fragment of mma.m16n8k8 (and its low-order correction) for column tile nt and k step ks.
+//   P[(nt * (in/8) + ks) * 32 + lane] = { hi(W[n][k]), hi(W[n][k+4]), c(W[n][k]), c(W[n][k+4]) },
+//   n = 8 nt + lane/4,  k = 8 ks + lane%4,  hi(w) = w rounded to TF32 (10-bit mantissa, ties away),
+//   c(w) = the 32-bit word { lower half: bfloat16(hi(w)), upper half: bfloat16(w - hi(w)) },
+// i.e. the B fragment of mma.m16n8k8 (TF32) for column tile nt and k step ks, and the B fragment of the 16-deep
+// bfloat16 correction product of the same k step (whose A operand interleaves the activations' (lo, hi) halves).
 struct DenseArgs {
     long long N;
     int tail, head, ff;

@@ -36,20 +36,28 @@ def _tf32(x: Tensor) -> Tensor:
     return ((bits + 0x1000) & ~0x1FFF).view(torch.float32)
 
 
+def _bf16_pair(low: Tensor, high: Tensor) -> Tensor:
+    """float32-typed words whose lower / upper 16 bits are ``low`` / ``high`` rounded to bfloat16 (nearest even)."""
+    lo_bits = low.to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+    hi_bits = high.to(torch.bfloat16).view(torch.int16).to(torch.int32) << 16
+    return (hi_bits | lo_bits).view(torch.float32)
+
+
 def pack_dense_weight(W: Tensor) -> Tensor:
     """A Linear weight (out, in) in the fragment order of the fused dense kernel: float4 entries
-    [(nt * in/8 + ks) * 32 + lane] = (hi W[n,k], hi W[n,k+4], lo W[n,k], lo W[n,k+4]) with n = 8 nt + lane // 4,
-    k = 8 ks + lane % 4, hi = TF32 rounding, lo = hi(w - hi(w)).  Returned flat."""
+    [(nt * in/8 + ks) * 32 + lane] = (hi W[n,k], hi W[n,k+4], c W[n,k], c W[n,k+4]) with n = 8 nt + lane // 4,
+    k = 8 ks + lane % 4, hi = TF32 rounding and c(w) the word {lower half: bf16(hi(w)), upper half: bf16(w - hi(w))},
+    the operands of the kernel's main (TF32) and correction (bfloat16, 16-deep) products.  Returned flat."""
     out_f, in_f = W.shape
     assert out_f % 8 == 0 and in_f % 8 == 0
-    W = W.detach().float()
+    W = W.detach().float().contiguous()
     hi = _tf32(W)
-    lo = _tf32(W - hi)
+    corr = _bf16_pair(hi, W - hi)
 
     def frag(M):  # (out, in) -> (nt, ks, g, t, half)
         return M.view(out_f // 8, 8, in_f // 8, 2, 4).permute(0, 2, 1, 4, 3)
 
-    return torch.cat((frag(hi), frag(lo)), dim=-1).contiguous().reshape(-1)
+    return torch.cat((frag(hi), frag(corr)), dim=-1).contiguous().reshape(-1)
 
 
 class BatchGeometry:

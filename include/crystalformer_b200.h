@@ -314,10 +314,11 @@ int cf_infinite_attn_fwd_sorted(const float *q, const float *k, const float *v, 
  *             linear2.weight (128,ff), linear2.bias (128), packed (optional)
  *             packed: NULL, or Wqkv, out_proj.weight, linear1.weight, linear2.weight concatenated in the fragment
  *             order of the fused dense kernel: a weight W (out,in) as float4 entries
- *             [(nt * in/8 + ks) * 32 + lane] = (hi W[n,k], hi W[n,k+4], lo W[n,k], lo W[n,k+4]), n = 8 nt + lane/4,
- *             k = 8 ks + lane%4, hi = rounding to TF32 (ties away), lo = hi(w - hi(w)).  When every layer has it and
- *             ff_dim is a multiple of 128, the four products and the element-wise steps of a layer boundary run as ONE
- *             tensor-core kernel with three-product TF32 splitting (fp32-level accuracy) instead of cuBLAS SGEMMs.
+ *             [(nt * in/8 + ks) * 32 + lane] = (hi W[n,k], hi W[n,k+4], c W[n,k], c W[n,k+4]), n = 8 nt + lane/4,
+ *             k = 8 ks + lane%4, hi = rounding to TF32 (ties away), c(w) = the 32-bit word { lower half:
+ *             bfloat16(hi(w)), upper half: bfloat16(w - hi(w)) }.  When every layer has it and ff_dim is a multiple
+ *             of 128, the four products and the element-wise steps of a layer boundary run as ONE tensor-core kernel
+ *             (TF32 main product + bfloat16 correction product: fp32-level accuracy) instead of cuBLAS SGEMMs.
  *   scalars : HOST array of num_layers x 6 doubles: gauss_scale, gauss_shift, -0.5/scale_real^2, elu beta,
  *             gauss_lb_real, dist_max
  *   x       : (N,128) atom features, updated in place

@@ -132,7 +132,7 @@ def test_one_call_model_forward_on_more_than_1024_crystals(golden_model):
 
 @pytest.mark.parametrize("atoms", [(1, 7), (20, 45)])
 def test_fused_dense_block_equals_the_sgemm_path(golden_model, atoms):
-    """The tensor-core dense block (three-product TF32 splitting) against the same forward with cuBLAS SGEMMs: fp32-level
+    """The tensor-core dense block (TF32 product + bfloat16 correction product) against the same forward with cuBLAS SGEMMs: fp32-level
     agreement, on a batch smaller than one 16-row tile wave and on one with several tiles per block row range."""
     from crystalformer_b200.model import Latticeformer, default_params
     torch.manual_seed(3)
