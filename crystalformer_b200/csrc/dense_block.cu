@@ -25,6 +25,7 @@
 // per lane; activations are split when they are written to shared memory: the `hi` tile holds TF32 words, the `lo`
 // tile the words { lower half: bf16(a_lo), upper half: bf16(a_hi) }, which ldmatrix delivers as the A fragment of the
 // 16-deep bfloat16 product with the same addresses as the TF32 fragment of the hi tile.
+#include <type_traits>
 #include "common.cuh"
 #include "dense_block.cuh"
 
@@ -50,12 +51,26 @@ __device__ __forceinline__ unsigned tf32_hi(float x)
     return r;
 }
 
-__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const unsigned *row)
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+// ldmatrix from the 32-bit shared address `addr` + a compile-time byte offset (no address arithmetic at run time)
+template <int OFFSET>
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr)
 {
-    const unsigned addr = (unsigned)__cvta_generic_to_shared(row);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4+%5];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
+                 : "r"(addr), "n"(OFFSET));
+}
+
+// f(integral_constant<int, I>) for I = FIRST .. LAST - 1: loops whose index must be a compile-time constant (immediate
+// operands of the inline assembly)
+template <int FIRST, int LAST, typename F>
+__device__ __forceinline__ void static_for(F &&f)
+{
+    if constexpr (FIRST < LAST) {
+        f(std::integral_constant<int, FIRST>{});
+        static_for<FIRST + 1, LAST>(f);
+    }
 }
 
 // the word of the correction operand: lower half bf16(lo), upper half bf16(hi)
@@ -84,104 +99,83 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const unsigned (&a)[4], 
 // A warp consumes its B fragments in an order that is fixed in advance: panel after panel (a panel = the 16 k steps of
 // one 128-deep product for the warp's two column tiles), the same sequence for every row tile.  The packed layout
 // makes a fragment lane-private (a lane reads back exactly the 16 bytes it fetched), so each warp runs its own
-// cp.async ring, DEPTH items (k steps) ahead, across product, barrier and tile boundaries alike, with no block-level
-// synchronisation: weights stream from L2 continuously while the tensor cores work.
-constexpr int DEPTH = 8;                  // k steps in flight per warp, 1 KB each
+// cp.async ring with no block-level synchronisation: weights stream from L2 continuously, across product, barrier
+// and tile boundaries alike, while the tensor cores work.  The ring holds exactly one product (DEPTH = KSTEPS slots
+// of two 512-byte fragments), so slot s always carries k step s of a product: every shared-memory address of the
+// inner loop is a compile-time offset from one register.  The k steps are consumed in groups of G; right after a
+// group's fragments have been read into registers its slots are refilled with the same k steps of the NEXT product
+// (one commit per group), so the stream runs one product ahead.
+constexpr int DEPTH = KSTEPS;             // slots per warp, 1 KB each
 constexpr int RING_WORDS = DEPTH * 2 * 32 * 4;
 
 struct Panel {
-    const float4 *base;   // fragments of the warp's first column tile at k step 0
-    size_t tile_stride;   // float4 between the warp's two column tiles
+    const float4 *base;   // fragments of column pair cp's first column tile at k step 0
+    size_t tile_stride;   // float4 between the pair's two column tiles
 };
 
-struct WeightStream {
-    float4 *ring;         // this warp's [DEPTH][2][32] float4
-    int lane;
-    int panels;           // panels per row tile
-    long long produced, consumed, limit;  // items; limit = tiles of this block x panels x KSTEPS
-    struct { const float4 *Wo, *W1, *W2, *Wqkv, *Wembed; int ff, tail; } d;
-    int warp;             // column pair (0..7)
-    int kh;               // k half
-    int p_panel, p_ks;    // producer position within the row tile's sequence
-    Panel cur;            // the producer's current panel
+struct StreamPlan {
+    const float4 *Wo, *W1, *W2, *Wqkv, *Wembed;
+    int ff, tail, panels;
 
-    __device__ __forceinline__ Panel panel(int idx) const
+    __device__ __forceinline__ Panel panel(int idx, int cp) const
     {
-        const int chunks = d.ff / 128;
+        const int chunks = ff / 128;
         Panel r;
-        if (d.Wembed != nullptr && idx == 0) {  // the embedding comes first (never together with a tail)
-            r.base = d.Wembed + (size_t)(2 * warp) * 16 * 32;
+        if (Wembed != nullptr && idx == 0) {  // the embedding comes first (never together with a tail)
+            r.base = Wembed + (size_t)(2 * cp) * 16 * 32;
             r.tile_stride = 16 * 32;
-        } else if (d.tail && idx == 0) {
-            r.base = d.Wo + (size_t)(2 * warp) * 16 * 32;
+        } else if (tail && idx == 0) {
+            r.base = Wo + (size_t)(2 * cp) * 16 * 32;
             r.tile_stride = 16 * 32;
-        } else if (d.tail && idx <= 2 * chunks) {
+        } else if (tail && idx <= 2 * chunks) {
             const int ch = (idx - 1) >> 1;
-            if ((idx - 1) & 1) {  // W2, k steps 16 ch .. 16 ch + 15 of column tiles 2 warp, 2 warp + 1
-                r.base = d.W2 + ((size_t)(2 * warp) * (d.ff / 8) + 16 * ch) * 32;
-                r.tile_stride = (size_t)(d.ff / 8) * 32;
+            if ((idx - 1) & 1) {  // W2, k steps 16 ch .. 16 ch + 15 of column tiles 2 cp, 2 cp + 1
+                r.base = W2 + ((size_t)(2 * cp) * (ff / 8) + 16 * ch) * 32;
+                r.tile_stride = (size_t)(ff / 8) * 32;
             } else {              // W1, column tiles of the chunk's hidden units
-                r.base = d.W1 + (size_t)(16 * ch + 2 * warp) * 16 * 32;
+                r.base = W1 + (size_t)(16 * ch + 2 * cp) * 16 * 32;
                 r.tile_stride = 16 * 32;
             }
-        } else {                  // Wqkv, group 0..2 of the warp's 48 output columns
-            const int grp = idx - (d.tail ? 1 + 2 * chunks : 0) - (d.Wembed != nullptr ? 1 : 0);
-            r.base = d.Wqkv + (size_t)((48 * warp + 16 * grp) / 8) * 16 * 32;
+        } else {                  // Wqkv, group 0..2 of the pair's 48 output columns
+            const int grp = idx - (tail ? 1 + 2 * chunks : 0) - (Wembed != nullptr ? 1 : 0);
+            r.base = Wqkv + (size_t)((48 * cp + 16 * grp) / 8) * 16 * 32;
             r.tile_stride = 16 * 32;
         }
         return r;
     }
-    __device__ __forceinline__ void produce()
-    {
-        if (produced < limit) {
-            float4 *dst = ring + (size_t)(produced & (DEPTH - 1)) * 64 + lane;
-            const float4 *src = cur.base + (size_t)(kh * KSTEPS + p_ks) * 32 + lane;
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                const unsigned saddr = (unsigned)__cvta_generic_to_shared(dst + 32 * nt);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(src + nt * cur.tile_stride));
-            }
-            if (++p_ks == KSTEPS) {  // next panel of the sequence (wrapping to the next row tile's first)
-                p_ks = 0;
-                if (++p_panel == panels) p_panel = 0;
-                cur = panel(p_panel);
-            }
-        }
-        asm volatile("cp.async.commit_group;");  // always commit, so that the group count stays in step
-        ++produced;
-    }
-    __device__ __forceinline__ void start()
-    {
-        p_panel = p_ks = 0;
-        cur = panel(0);
-        for (int i = 0; i < DEPTH; ++i) produce();
-    }
-    // the next G items' fragments (b[i][nt]); refills the slots they free
-    template <int G>
-    __device__ __forceinline__ void consume(float4 (&b)[G][2])
-    {
-        asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - G) : "memory");
-#pragma unroll
-        for (int i = 0; i < G; ++i) {
-            const float4 *src = ring + (size_t)((consumed + i) & (DEPTH - 1)) * 64 + lane;
-            b[i][0] = src[0];
-            b[i][1] = src[32];
-        }
-        consumed += G;
-#pragma unroll
-        for (int i = 0; i < G; ++i) produce();
-    }
 };
 
-// acc[mt][nt] += A (rows of the tile x 128, split in shared memory) . B (the next panel of the weight stream).
-template <int MT>
-__device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsigned *__restrict__ a_hi,
-                                            const unsigned *__restrict__ a_lo, WeightStream &ws, int lane)
+// 16 bytes global -> shared (this lane's part of a fragment), OFFSET bytes into the warp's ring
+template <int OFFSET>
+__device__ __forceinline__ void cp_async_16(unsigned ring, const float4 *src)
 {
-    // ldmatrix hands a lane the 32-bit words (row lane/4, word lane%4) of four 8-row x 16-byte matrices, which for
-    // 32-bit elements are exactly the a0..a3 of the m16n8k8 A fragment: rows 0-7 / 8-15 of the m tile, words 0-3 / 4-7
-    // of the k step.  Lane l supplies the address of row l%8 of matrix l/8.
-    const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8, lcol = (lane >> 4) * 4;
+    asm volatile("cp.async.cg.shared.global [%0+%1], [%2], 16;" ::"r"(ring), "n"(OFFSET), "l"(src));
+}
+
+// Requests k steps FIRST .. FIRST + COUNT - 1 of a product whose fragments for this lane start at src0 / src1 (the
+// warp's two column tiles) into their slots, as one group; with src0 == nullptr only the (empty) group is committed,
+// so that the group count stays in step.
+template <int FIRST, int COUNT>
+__device__ __forceinline__ void request_steps(unsigned ring, const float4 *src0, const float4 *src1)
+{
+    if (src0 != nullptr) {
+        static_for<FIRST, FIRST + COUNT>([&](auto step) {
+            constexpr int S = decltype(step)::value;
+            cp_async_16<S * 1024>(ring, src0 + S * 32);
+            cp_async_16<S * 1024 + 512>(ring, src1 + S * 32);
+        });
+    }
+    asm volatile("cp.async.commit_group;");
+}
+
+// acc[mt][nt] += A (rows of the tile x 128, split in shared memory) . B (the product whose fragments are in the ring).
+// a_hi / a_lo: shared addresses of this lane's ldmatrix row at the warp's first k step; frag: this lane's fragment of
+// the warp's first column tile in slot 0 of its ring (ring: the same as a shared address); next0 / next1: this lane's
+// fragments of the next product (null after the block's last one), requested into the slots as they are read.
+template <int MT>
+__device__ __forceinline__ void product_128(float (&acc)[MT][2][4], unsigned a_hi, unsigned a_lo, const float4 *frag,
+                                            unsigned ring, const float4 *next0, const float4 *next1)
+{
     // the correction product goes to an accumulator of its own: two independent dependency chains per tile, and the
     // small terms are summed among themselves before they meet the large ones
     float corr[MT][2][4];
@@ -191,21 +185,32 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int u = 0; u < 4; ++u) corr[mt][nt][u] = 0.f;
-    constexpr int G = MT == 1 ? 4 : 2;  // k steps fetched and issued together: loads of all G before the first MMA
-    const int k_first = ws.kh * KSTEPS;
-#pragma unroll 1
-    for (int ks0 = 0; ks0 < KSTEPS; ks0 += G) {
+    constexpr int G = MT == 1 ? 4 : 2;     // k steps fetched and issued together: loads of all G before the first MMA
+    constexpr int GROUPS = KSTEPS / G;     // cp.async groups per product
+    static_for<0, GROUPS>([&](auto group) {
+        constexpr int KS0 = decltype(group)::value * G;
+        // this group's fragments were requested one product ago; GROUPS - 1 younger groups may still be in flight
+        asm volatile("cp.async.wait_group %0;" ::"n"(GROUPS - 1) : "memory");
         float4 b[G][2];
-        ws.template consume<G>(b);
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            b[i][0] = frag[(KS0 + i) * 64];
+            b[i][1] = frag[(KS0 + i) * 64 + 32];
+        }
+        request_steps<KS0, G>(ring, next0, next1);
+        // ldmatrix hands a lane the 32-bit words (row lane/4, word lane%4) of four 8-row x 16-byte matrices, which for
+        // 32-bit elements are exactly the a0..a3 of the m16n8k8 A fragment: rows 0-7 / 8-15 of the m tile, words 0-3 /
+        // 4-7 of the k step (and, read as 16-bit elements, the A fragment of the 16-deep product of the lo tile).
+        // Lane l supplies the address of row l%8 of matrix l/8.
         unsigned ah[G][MT][4], al[G][MT][4];
-#pragma unroll
-        for (int i = 0; i < G; ++i)
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const int off = (16 * mt + lrow) * LDA + 8 * (k_first + ks0 + i) + lcol;
-                ldmatrix_x4(ah[i][mt], a_hi + off);
-                ldmatrix_x4(al[i][mt], a_lo + off);
-            }
+        static_for<0, G>([&](auto step) {
+            constexpr int I = decltype(step)::value;
+            static_for<0, MT>([&](auto mtile) {
+                constexpr int M = decltype(mtile)::value;
+                ldmatrix_x4<4 * (16 * M * LDA + 8 * (KS0 + I))>(ah[I][M], a_hi);
+                ldmatrix_x4<4 * (16 * M * LDA + 8 * (KS0 + I))>(al[I][M], a_lo);
+            });
+        });
 #pragma unroll
         for (int i = 0; i < G; ++i)
 #pragma unroll
@@ -218,7 +223,7 @@ __device__ __forceinline__ void product_128(float (&acc)[MT][2][4], const unsign
                     mma_tf32(acc[mt][nt], ah[i][mt], bh0, bh1);
                 }
             }
-    }
+    });
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -260,13 +265,38 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
 
     const long long tiles = (p.N + ROWS - 1) / ROWS;
     const long long my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    WeightStream ws;
-    ws.ring = reinterpret_cast<float4 *>(a2_lo + ROWS * LDA) + (size_t)(tid >> 5) * DEPTH * 64;
-    ws.lane = lane;
-    ws.warp = warp;
-    ws.kh = kh;
-    // exchange buffers for the halves of a product: [2][8 column pairs][32 lanes][8 MT floats]
-    float *xch = reinterpret_cast<float *>(ws.ring - (size_t)(tid >> 5) * DEPTH * 64 + (size_t)DB_WARPS * DEPTH * 64);
+    // shared memory after the operand tiles: the warps' rings (16 x 8 KB) and the exchange buffers for the halves of a
+    // product ([2][8 column pairs][32 lanes][8 MT floats])
+    const int wid = tid >> 5;  // = 8 kh + warp
+    float4 *rings = reinterpret_cast<float4 *>(a2_lo + ROWS * LDA);
+    float *xch = reinterpret_cast<float *>(rings + (size_t)DB_WARPS * DEPTH * 64);
+    const float4 *frag = rings + (size_t)wid * DEPTH * 64 + lane;   // this lane's 16 bytes of slot 0, first column tile
+    const unsigned ring = smem_u32(frag);
+    StreamPlan plan;
+    plan.Wo = p.Wo; plan.W1 = p.W1; plan.W2 = p.W2; plan.Wqkv = p.Wqkv; plan.ff = p.ff; plan.tail = p.tail;
+    plan.Wembed = p.tail ? nullptr : p.Wembed;
+    plan.panels = (p.tail ? 1 + 2 * (p.ff / 128) : 0) + (p.head ? 3 : 0) + (plan.Wembed != nullptr ? 1 : 0);
+    const long long total_products = my_tiles * plan.panels;
+    long long products = 0;  // products done by this block
+    int next_panel = plan.panels > 1 ? 1 : 0;  // panel of product `products + 1` within the row tile's sequence
+    // this lane's fragments of the k steps of this warp's half of a panel, for its two column tiles
+    auto panel_src = [&](int idx, const float4 *&src0, const float4 *&src1) {
+        const Panel pn = plan.panel(idx, warp);
+        src0 = pn.base + (size_t)(kh * KSTEPS) * 32 + lane;
+        src1 = src0 + pn.tile_stride;
+    };
+    // this lane's ldmatrix row of the operand tiles at the warp's first k step
+    const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8, lcol = (lane >> 4) * 4;
+    const unsigned lane_off = 4u * (unsigned)(lrow * LDA + 8 * kh * KSTEPS + lcol);
+    const unsigned a1h = smem_u32(a1_hi) + lane_off, a1l = smem_u32(a1_lo) + lane_off;
+    const unsigned a2h = smem_u32(a2_hi) + lane_off, a2l = smem_u32(a2_lo) + lane_off;
+    auto product = [&](float (&acc)[MT][2][4], unsigned a_hi, unsigned a_lo) {
+        const float4 *next0 = nullptr, *next1 = nullptr;
+        if (products + 1 < total_products) panel_src(next_panel, next0, next1);
+        product_128<MT>(acc, a_hi, a_lo, frag, ring, next0, next1);
+        ++products;
+        if (++next_panel == plan.panels) next_panel = 0;
+    };
     int xsel = 0;
     // acc <- acc(kh = 0) + acc(kh = 1), valid in the owner warps afterwards; contains one block barrier
     auto combine = [&](float (&acc)[MT][2][4]) {
@@ -299,13 +329,13 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
 #pragma unroll
                 for (int u = 0; u < 4; ++u) acc[mt][nt][u] = 0.f;
     };
-    ws.d.Wo = p.Wo; ws.d.W1 = p.W1; ws.d.W2 = p.W2; ws.d.Wqkv = p.Wqkv; ws.d.ff = p.ff; ws.d.tail = p.tail;
-    ws.d.Wembed = p.tail ? nullptr : p.Wembed;
-    ws.panels = (p.tail ? 1 + 2 * (p.ff / 128) : 0) + (p.head ? 3 : 0) + (ws.d.Wembed != nullptr ? 1 : 0);
-    ws.produced = ws.consumed = 0;
-    ws.limit = my_tiles * ws.panels * KSTEPS;
     grid_launch_dependents();
-    ws.start();               // weights are constants: their stream starts while the previous kernel drains
+    {   // weights are constants: the stream of the first product starts while the previous kernel drains
+        constexpr int G = MT == 1 ? 4 : 2;
+        const float4 *src0 = nullptr, *src1 = nullptr;
+        if (total_products > 0) panel_src(0, src0, src1);
+        static_for<0, KSTEPS / G>([&](auto group) { request_steps<decltype(group)::value * G, G>(ring, src0, src1); });
+    }
     grid_dependency_wait();   // activations of the previous kernel (attention output, x) from here on
 
     for (long long tile = blockIdx.x; tile * ROWS < p.N; tile += gridDim.x) {
@@ -344,7 +374,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                 }
             if (!owner) zero(xo);
             __syncthreads();
-            product_128<MT>(xo, a1_hi, a1_lo, ws, lane);
+            product(xo, a1h, a1l);
             combine(xo);      // (its barrier: every warp has read attn)
             if (KSPLIT == 1) __syncthreads();
             if (owner) store_split<MT>(a1_hi, a1_lo, xo, warp, lane);
@@ -369,7 +399,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                     for (int mt = 0; mt < MT; ++mt) { h[mt][nt][0] = b1.x; h[mt][nt][1] = b1.y; h[mt][nt][2] = b1.x; h[mt][nt][3] = b1.y; }
                 }
                 if (!owner) zero(h);
-                product_128<MT>(h, a1_hi, a1_lo, ws, lane);  // W1, the chunk's hidden units
+                product(h, a1h, a1l);  // W1, the chunk's hidden units
                 combine(h);       // (its barrier: the previous chunk's readers are done with operand 2)
                 if (KSPLIT == 1) __syncthreads();
 #pragma unroll
@@ -380,7 +410,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                         for (int u = 0; u < 4; ++u) h[mt][nt][u] = fmaxf(h[mt][nt][u], 0.f);
                 if (owner) store_split<MT>(a2_hi, a2_lo, h, warp, lane);
                 __syncthreads();
-                product_128<MT>(xo, a2_hi, a2_lo, ws, lane);  // W2, the chunk's k steps
+                product(xo, a2h, a2l);  // W2, the chunk's k steps
             }
             combine(xo);
             // ---- write x'
@@ -395,7 +425,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                             *reinterpret_cast<float2 *>(p.x + row * 128 + 16 * warp + 8 * nt + 2 * t) =
                                 make_float2(xo[mt][nt][2 * half], xo[mt][nt][2 * half + 1]);
                     }
-        } else if (ws.d.Wembed != nullptr) {
+        } else if (plan.Wembed != nullptr) {
             // ---- x = features W_embed^T: operand 1 <- the tile's feature rows, zero beyond feature_dim
             for (int idx = tid; idx < ROWS * 128; idx += DB_THREADS) {
                 const int r = idx >> 7, col = idx & 127;
@@ -407,7 +437,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
             }
             zero(xo);
             __syncthreads();
-            product_128<MT>(xo, a1_hi, a1_lo, ws, lane);
+            product(xo, a1h, a1l);
             combine(xo);
             if (KSPLIT == 1) __syncthreads();
 #pragma unroll
@@ -453,7 +483,7 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
                 for (int mt = 0; mt < MT; ++mt) { acc[mt][nt][0] = bq.x; acc[mt][nt][1] = bq.y; acc[mt][nt][2] = bq.x; acc[mt][nt][3] = bq.y; }
             }
             if (!owner) zero(acc);
-            product_128<MT>(acc, a1_hi, a1_lo, ws, lane);
+            product(acc, a1h, a1l);
             combine(acc);
             if (!owner) continue;  // (warp-uniform; the epilogue below has no block barrier)
             const int which = col0 >> 7;           // 0 q, 1 k, 2 v (warp-uniform)
