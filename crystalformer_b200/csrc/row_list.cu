@@ -13,7 +13,7 @@ constexpr int RL_MAX_TRANSLATIONS = 4096;  // boxes beyond this are not listed
 constexpr size_t RL_SMEM = sizeof(unsigned long long) * 2 * ROW_LIST_CAP + sizeof(int) * (2 * RL_BUCKETS + 8);
 
 // One thread block per row.  Every key's candidate translations (a bounding box of the ball that holds its listed
-// terms) are walked one per thread and step; terms within `window` of their edge's nearest image are appended to a
+// terms) are walked by a warp, one per lane and step; terms within `window` of their edge's nearest image are appended to a
 // shared-memory buffer (one atomic per warp and step) as 64-bit items (d2 bits << 32 | key).  The items are then
 // sorted: distributed over RL_BUCKETS buckets that are equally spaced in d^3 (terms are about uniform in volume, so
 // buckets hold a handful of items each), and placed inside their bucket by counting the smaller items of the same
@@ -86,8 +86,8 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
         //          | n_i + s_i | <= rho |b_i|,      s_i = r . b_i,  rho = sqrt(threshold).
         //      The first warp computes every key's bounding box, clipped to the rule's box (one key per lane; the
         //      bounds are widened a little beyond any rounding, the test on d2 below decides membership, so the listed
-        //      set is that of a walk of the whole box), and the running sum of the boxes' sizes; then all threads walk
-        //      the concatenation of the boxes, one translation per thread and step, finding their key by bisection.
+        //      set is that of a walk of the whole box), and the running sum of the boxes' sizes; then the warps take
+        //      the keys in turn, lanes over the translations of a key's box.
         if (fits && wr == 0) {
             const float c1x = cell.t2y * cell.t3z - cell.t2z * cell.t3y, c1y = cell.t2z * cell.t3x - cell.t2x * cell.t3z,
                         c1z = cell.t2x * cell.t3y - cell.t2y * cell.t3x;
@@ -129,39 +129,37 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
         __syncthreads();
         const float d2_max = fits ? d2max_s : 1.0f;  // no listed term is farther (the same value in every thread)
         if (fits) {
-            const int cand = kpre_s[n];
-            for (int f0 = 0; f0 < cand; f0 += RL_THREADS) {  // (block-uniform bounds: the ballots below are safe)
-                const int f = f0 + tid;
-                const bool valid = f < cand;
-                int j = 0;
-#pragma unroll
-                for (int step = 16; step >= 1; step >>= 1)
-                    if (j + step < n && kpre_s[j + step] <= f) j += step;  // the last key whose boxes start at or before f
+            // a warp takes a key at a time, its lanes the translations of the key's box (32 per pass)
+            for (int j = wr; j < n; j += RL_WARPS) {
                 const int4 kb = kbox_s[j];
                 const float4 r = key_s[j];
+                const int count = kpre_s[j + 1] - kpre_s[j];
                 const int w3 = kb.w & 255, w2 = kb.w >> 8;
-                const int tr = valid ? f - kpre_s[j] : 0;
-                // digits of tr in the mixed radix (w1, w2, w3): quotients by a rounded-down product with the reciprocal
-                // (exact for these small integers: tr < 2^13, w <= 65)
-                const int i12 = __float2int_rd(((float)tr + 0.5f) * __frcp_rn((float)w3)), i3 = tr - i12 * w3;
-                const int i1 = __float2int_rd(((float)i12 + 0.5f) * __frcp_rn((float)w2)), i2 = i12 - i1 * w2;
-                const int n1 = kb.x + i1, n2 = kb.y + i2, n3 = kb.z + i3;
-                const float f1 = (float)n1, f2 = (float)n2, f3 = (float)n3;
-                // r + n1 t1 + n2 t2 + n3 t3, contracted like the reference's expression
-                const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
-                const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
-                const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
-                const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
-                const bool keep = valid && d2 <= r.w;
-                const unsigned mask = __ballot_sync(FULL, keep);
-                if (mask == 0u) continue;
-                int base = 0;
-                if (lane == 0) base = atomicAdd(&cnt_s, __popc(mask));
-                base = __shfl_sync(FULL, base, 0);
-                if (keep) {
-                    const int at = base + __popc(mask & lt);
-                    const int key123 = (abs(n1) << 8) | (abs(n2) << 16) | (abs(n3) << 24);
-                    if (at < ROW_LIST_CAP) ent[at] = ((unsigned long long)__float_as_uint(d2) << 32) | (unsigned)(key123 | j);
+                const float inv_w3 = __frcp_rn((float)w3), inv_w2 = __frcp_rn((float)w2);
+                for (int tr0 = 0; tr0 < count; tr0 += 32) {  // (warp-uniform bounds: the ballots below are safe)
+                    const int tr = tr0 + lane;
+                    // digits of tr in the mixed radix (w1, w2, w3): quotients by a rounded-down product with the
+                    // reciprocal (exact for these small integers: tr < 2^13, w <= 65)
+                    const int i12 = __float2int_rd(((float)tr + 0.5f) * inv_w3), i3 = tr - i12 * w3;
+                    const int i1 = __float2int_rd(((float)i12 + 0.5f) * inv_w2), i2 = i12 - i1 * w2;
+                    const int n1 = kb.x + i1, n2 = kb.y + i2, n3 = kb.z + i3;
+                    const float f1 = (float)n1, f2 = (float)n2, f3 = (float)n3;
+                    // r + n1 t1 + n2 t2 + n3 t3, contracted like the reference's expression
+                    const float dx = fmaf(cell.t3x, f3, fmaf(cell.t2x, f2, fmaf(cell.t1x, f1, r.x)));
+                    const float dy = fmaf(cell.t3y, f3, fmaf(cell.t2y, f2, fmaf(cell.t1y, f1, r.y)));
+                    const float dz = fmaf(cell.t3z, f3, fmaf(cell.t2z, f2, fmaf(cell.t1z, f1, r.z)));
+                    const float d2 = fmaf(dz, dz, fmaf(dy, dy, dx * dx));
+                    const bool keep = tr < count && d2 <= r.w;
+                    const unsigned mask = __ballot_sync(FULL, keep);
+                    if (mask == 0u) continue;
+                    int base = 0;
+                    if (lane == 0) base = atomicAdd(&cnt_s, __popc(mask));
+                    base = __shfl_sync(FULL, base, 0);
+                    if (keep) {
+                        const int at = base + __popc(mask & lt);
+                        const int key123 = (abs(n1) << 8) | (abs(n2) << 16) | (abs(n3) << 24);
+                        if (at < ROW_LIST_CAP) ent[at] = ((unsigned long long)__float_as_uint(d2) << 32) | (unsigned)(key123 | j);
+                    }
                 }
             }
         }
