@@ -288,7 +288,14 @@ def run_b200(args):
     torch.backends.cudnn.allow_tf32 = False
 
     wl = WORKLOADS[args.workload]
-    global_batch = make_config(wl["config"], num_crystals=wl["crystals"] * world)
+    # weak scaling = the work per GPU does not change with N: the global batch of N ranks is N copies of the workload's
+    # batch (an independent draw of N x 128 crystals would give every rank a different amount of work than the N = 1
+    # run has: the 128 crystals of cfg0 are 17 % lighter in lattice-sum terms than the mean of the distribution), which
+    # the greedy split below deals out one copy per rank.  Sharding of heterogeneous fixed batches is what `strong`
+    # measures.
+    import numpy as np
+    one = make_config(wl["config"], num_crystals=wl["crystals"])
+    global_batch = one if world == 1 else one.select(np.tile(np.arange(one.num_crystals), world))
     # the reference's greedy split, with the row scheduler's cost (n^2 x the terms per edge, which depend on the cell
     # volume) in place of n^2 as the weight: shards of equal n^2 differ by several percent in lattice-sum terms
     cost = crystal_cost(global_batch.sizes, global_batch.trans_vec)
@@ -452,6 +459,8 @@ def run_b200(args):
                        "timing": "rounds of `steps` steps issued back to back; device wall clock of a round minus the "
                                  "flushes inside it; rounds repeated until about 1 s of device time, averaged; max over ranks",
                        "parallelism": f"dp{world} (greedy LPT split on the row-cost weight, outputs gathered by peer stores)",
+                       "global_batch_is": "the workload's batch" if world == 1 else
+                                          f"{world} copies of the workload's batch (work per GPU = the one-GPU run's)",
                        "shard_balance": shard_balance(global_batch.sizes, shards, cost)},
             "per_rank": {"resident": every},
             "e2e": {"value": e2e_value, "unit": "crystals/s", "ms_per_step": ms_e2e,
@@ -862,12 +871,12 @@ def run_reference(args):
     torch.set_num_threads(os.cpu_count())
     wl = WORKLOADS[args.workload]
     world = args.gpus
-    cb = make_config(wl["config"], num_crystals=wl["crystals"] * world)
+    cb = make_config(wl["config"], num_crystals=wl["crystals"])  # (the other arm's global batch is N copies of it)
     model, params = make_model(wl["layers"], wl["K"])  # CPU module: a container of the seed-0 weights, never run
     state = {k: v.detach().cpu() for k, v in model.state_dict().items()}
     use_ref = _oracle.have_ref()
-    # a step = the batch of one GPU of the other arm (for N > 1 the first 1/N of the global batch)
-    sample = cb if world == 1 else cb.select(range(wl["crystals"]))
+    # a step = the batch of one GPU of the other arm
+    sample = cb
     t0 = time.time()
     forward_cpu(state, params, sample.select(range(min(8, sample.num_crystals))), use_ref=use_ref)  # warm-up (page-in, OpenMP pool)
     t0 = time.time()
