@@ -369,27 +369,30 @@ def run_b200(args):
     op_ms = sum(s.elapsed_time(e) for s, e in native_log)
     op_calls = len(native_log)
 
-    # ---- e2e: host wall clock around the serving pipeline, no flush; repeated until about a second has been timed
+    # ---- e2e: host wall clock around the serving pipeline, no flush: one uninterrupted stream of batches, a multiple of
+    #      `steps` long enough for about a second (a first round of `steps` batches sets the length), from the first
+    #      submit to the last result
     for _ in range(args.warmup):
         step_e2e()
     drain()
     timer.barrier()
-    e2e_steps, e2e_wall, e2e_issue = 0, 0.0, 0.0
-    while e2e_wall < 1.0 and e2e_steps < 200 * args.steps:
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            step_e2e()
-        t1 = time.perf_counter()
-        drain()
-        torch.cuda.synchronize()
-        t2 = time.perf_counter()
-        if world > 1:
-            dist.barrier()
-        e2e_wall += timer.max_over_ranks(t2 - t0)
-        e2e_issue += t1 - t0
-        e2e_steps += args.steps
-        if world > 1:  # every rank must run the same number of rounds
-            e2e_wall = timer.max_over_ranks(e2e_wall)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    drain()
+    torch.cuda.synchronize()
+    first_round = timer.max_over_ranks(time.perf_counter() - t0)  # (the same on every rank: all run the same length)
+    e2e_steps = args.steps * int(max(1, min(200, math.ceil(1.0 / max(first_round, 1e-6)))))
+    timer.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    t1 = time.perf_counter()
+    drain()
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    e2e_wall = timer.max_over_ranks(t2 - t0)
+    e2e_issue = t1 - t0
     ms_e2e = e2e_wall * 1e3 / e2e_steps
     if peers is not None:
         peers.check()
@@ -466,7 +469,8 @@ def run_b200(args):
             "e2e": {"value": e2e_value, "unit": "crystals/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "timed_steps": e2e_steps,
                     "host_issue_ms_per_step": e2e_issue * 1e3 / e2e_steps,
-                    "clock": "host wall clock (perf_counter) from the first submit to the last result, max over ranks",
+                    "clock": "host wall clock (perf_counter) from the first submit to the last result of one uninterrupted "
+                             "stream of timed_steps batches (pipeline fill and drain inside the clock), max over ranks",
                     "outputs_equal_direct_forward": e2e_equal,
                     "api": f"crystalformer_b200.serving.PipelinedPredictor, {e2e_depth} batches in flight on {e2e_streams} compute stream(s)"},
             "gpu_launches": None if launches is None else launches * args.steps,
