@@ -318,7 +318,7 @@ def run_b200(args):
     # N > 1: the pooling + head kernel of every rank stores its outputs into every rank's gather buffer over NVLink
     # and a small kernel waits for all ranks (sharding.PeerGather); no collective library on the data path.
     # (overlap: a step's collect, where a rank waits for the others, runs on its own stream beside the next steps)
-    peers = PeerGather(shards, model.mlp[-1].out_features, device, slots=12, overlap=True) if world > 1 else None
+    peers = PeerGather(shards, model.mlp[-1].out_features, device, slots=20, overlap=True) if world > 1 else None
     extra = {} if peers is None else {"gather": peers}
 
     ready = torch.cuda.Event()
@@ -333,9 +333,10 @@ def run_b200(args):
     d2h_bytes = (global_batch.num_crystals if world > 1 else mine.num_crystals) * 4
 
     from crystalformer_b200.serving import PipelinedPredictor
-    # six batches in flight alternating between four compute streams (the kernels of independent batches fill each
-    # other's idle issue slots); every submit is one call of the library (cf_serve_submit)
-    e2e_depth, e2e_streams = 6, 4
+    # ten batches in flight alternating between six compute streams (the kernels of independent batches fill each
+    # other's idle issue slots: measured 0.255 / 0.216 / 0.210 / 0.209 ms per batch with 2 / 4 / 6 / 8 streams); every
+    # submit is one call of the library (cf_serve_submit)
+    e2e_depth, e2e_streams = 10, 6
     runner = PipelinedPredictor(model, depth=e2e_depth, device=device, gather=peers, streams=e2e_streams)
     pending = []
 
