@@ -437,7 +437,6 @@ def run_b200(args):
         roofline = attention_roofline(ops, device, model, step_resident, wl, n_atoms, n_edges, max_atoms, op_ms, op_calls,
                                       ms_step, sm_mhz * 1e6)
         micro = lattice_microbench(ops, device, roofline["peaks"])
-        launches, kernel_names = count_kernel_launches(step_resident)
         cpu = parity = None
         if world == 1 and not args.no_cpu_baseline:
             with torch.no_grad():
@@ -451,6 +450,9 @@ def run_b200(args):
             workloads = {"cfg2": extra_workload("cfg2", device, timer, not args.no_cpu_baseline),
                          "cfg4": extra_workload("cfg4", device, timer, not args.no_cpu_baseline),
                          "cfg3_train": train_step_case(ops, device, 256)}
+        # the kernels of one forward, counted from the profiler's CUDA activity records: last of all, because the
+        # profiler's instrumentation stays attached to the process and slows later launches on the host side
+        launches, kernel_names = count_kernel_launches(step_resident)
         result = {
             "metric": metric_name(wl["layers"]),
             "value": value, "unit": "crystals/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -761,8 +763,11 @@ def train_step_case(ops, device, crystals=None):
     raw = ops.infinite_attn_fwd, ops.infinite_attn_bwd
     ops.infinite_attn_fwd, ops.infinite_attn_bwd = wrap(raw[0], "fwd"), wrap(raw[1], "bwd")
 
+    weights = [w for w in model.parameters() if w.requires_grad]
+
     def step():
-        model.zero_grad(set_to_none=True)
+        for w in weights:  # (what zero_grad(set_to_none=True) does, without walking the module tree every step)
+            w.grad = None
         loss = (model(batch, counts=counts) - target).abs().mean()
         loss.backward()
         return loss
@@ -771,7 +776,6 @@ def train_step_case(ops, device, crystals=None):
         for _ in range(5):
             step()
         torch.cuda.synchronize()
-        on["v"] = True
         reps = 20
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
@@ -781,6 +785,12 @@ def train_step_case(ops, device, crystals=None):
         e.record()
         host = time.perf_counter() - t0
         torch.cuda.synchronize()
+        # the attention operators are timed in three more steps: their event pairs cost the host time that the timed
+        # steps, which the host's issue rate bounds, should not pay
+        on["v"] = True
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
     finally:
         ops.infinite_attn_fwd, ops.infinite_attn_bwd = raw
     ms = s.elapsed_time(e) / reps
@@ -789,7 +799,7 @@ def train_step_case(ops, device, crystals=None):
             "atoms": cb.num_atoms, "edges": cb.num_edges,
             "ms_per_step": ms, "crystals_per_s": cb.num_crystals / (ms * 1e-3), "host_issue_ms": host * 1e3 / reps,
             "attention_fwd_us": per["fwd"] * 1e3, "attention_bwd_us": per["bwd"] * 1e3,
-            "attention_calls_per_step": len(events["fwd"]) // reps, "loss": float(loss.item()),
+            "attention_calls_per_step": len(events["fwd"]) // 3, "loss": float(loss.item()),
             "timing": "20 steps back to back between one CUDA-event pair (no L2 flush: the step's working set of "
                       "activations exceeds what survives between uses anyway)",
             "note": "term lists built once per step inside the first forward call; the rest of the step is torch autograd"}
