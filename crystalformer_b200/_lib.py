@@ -47,7 +47,7 @@ SIGNATURES = {
     "cf_row_list_build": [P, P, P, P, P, P, P, I64, I64, I64, F64, I32, I32, F64, P, P],
     "cf_infinite_attn_fwd_sorted": [P, P, P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, I64, F64, F64, P, F64, I32,
                                     I32, P, P, P, P],
-    "cf_serve_submit": [P, P, P, P, P, P, I64, I64, I64, I64, I32, P],
+    "cf_serve_submit": [P, P, P, P, P, P, I64, I64, I64, I64, I32, P, P],
     "cf_row_cost": [P, P, I64, I64, F64, P, P],
     "cf_row_order": [P, P, I64, I64, F64, P, P],
     "cf_reci_phase": [P, P, P, P, I64, P, P],
@@ -82,7 +82,7 @@ class ServeSlot(ctypes.Structure):
     _fields_ = [("copy_stream", c_void_p), ("compute_stream", c_void_p), ("copied", c_void_p), ("inputs_free", c_void_p),
                 ("done", c_void_p), ("x", c_void_p), ("pos", c_void_p), ("trans", c_void_p), ("sizes", c_void_p),
                 ("workspace", c_void_p), ("y", c_void_p), ("y_host", c_void_p), ("max_atoms_total", c_int64),
-                ("max_crystals", c_int64), ("max_edges", c_int64)]
+                ("max_crystals", c_int64), ("max_edges", c_int64), ("species", c_void_p)]
 
 
 class ServeGather(ctypes.Structure):

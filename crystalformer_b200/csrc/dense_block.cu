@@ -430,7 +430,9 @@ __global__ void __launch_bounds__(DB_THREADS) dense_block_kernel(const DenseArgs
             for (int idx = tid; idx < ROWS * 128; idx += DB_THREADS) {
                 const int r = idx >> 7, col = idx & 127;
                 float v = 0.f;
-                if (row0 + r < p.N && col < p.feature_dim) v = p.features[(row0 + r) * p.feature_dim + col];
+                if (row0 + r < p.N && col < p.feature_dim)
+                    v = p.features != nullptr ? p.features[(row0 + r) * p.feature_dim + col]
+                                              : (p.species[row0 + r] == (long long)col ? 1.0f : 0.0f);
                 const unsigned hi = tf32_hi(v);
                 a1_hi[r * LDA + col] = hi;
                 a1_lo[r * LDA + col] = corr_word(__uint_as_float(hi), v - __uint_as_float(hi));
@@ -537,7 +539,7 @@ int launch_dense_block(const DenseArgs &p, cudaStream_t s)
     if (p.N == 0) return CF_OK;
     if (p.tail && (p.ff <= 0 || p.ff % 128 != 0))
         return fail(CF_ERR_UNSUPPORTED, "dense block: ff_dim=%d must be a positive multiple of 128", p.ff);
-    if (!p.tail && p.Wembed != nullptr && (p.features == nullptr || p.feature_dim < 1 || p.feature_dim > 128))
+    if (!p.tail && p.Wembed != nullptr && ((p.features == nullptr && p.species == nullptr) || p.feature_dim < 1 || p.feature_dim > 128))
         return fail(CF_ERR_UNSUPPORTED, "dense block: embedding of %d features (1..128)", p.feature_dim);
     // 16-row tiles while they fit one wave of the SMs (more SMs busy), 32-row tiles beyond (half the weight traffic;
     // a block is tensor-pipe bound either way, so what counts is the number of waves) - unless the caller chose:

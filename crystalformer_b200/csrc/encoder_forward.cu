@@ -284,7 +284,7 @@ int cf::encoder_forward_impl(void *cublas_handle, int num_layers, const float *c
         d.N = N; d.ff = ff; d.x = x; d.q = q; d.k = k; d.v = v; d.a = a; d.attn = attn;
         head_of(d, 0);
         d.chained = 0;  // (first kernel of the forward on this stream: nothing to chain to)
-        if (embed != nullptr) { d.features = embed->features; d.feature_dim = embed->feature_dim; d.Wembed = embed->packed; }
+        if (embed != nullptr) { d.features = embed->features; d.species = embed->species; d.feature_dim = embed->feature_dim; d.Wembed = embed->packed; }
         rc = launch_dense_block(d, s);
         if (forked) cudaStreamWaitEvent(s, side_stream().join, 0);
         for (int l = 0; l < num_layers && rc == CF_OK; ++l) {

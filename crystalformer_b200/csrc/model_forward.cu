@@ -120,16 +120,20 @@ extern "C" int64_t cf_model_workspace_bytes(int64_t N, int64_t B, int64_t E, int
     return (int64_t)cf::carve(nullptr, N, B, E, ff_dim).bytes;
 }
 
-extern "C" int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
-                                const float *trans, const int64_t *sizes, int64_t N, int64_t B, int64_t E,
-                                int64_t max_atoms, const float *W_embed, const float *W_embed_packed, int num_layers,
-                                const float *const *weights, const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
-                                int lattice_range, int minimum_range, const float *W1, const float *b1, int64_t hidden,
-                                const float *W2, const float *b2, int64_t targets, double order_reach, void *workspace,
-                                float *y, void *const *attn_events, const cf_peer_gather *gather, void *inputs_ready,
-                                void *slot_free, void *stream)
+namespace cf {
+
+// cf_model_forward with the species of the atoms given either as feature rows (`features`, the reference's interface)
+// or as indices (`species`: the embedding of atom i is column species[i] of W_embed, i.e. what a one-hot feature row
+// gives; only with packed weights, where the first dense block builds the one-hot rows in shared memory).
+int model_forward_impl(void *cublas_handle, const float *features, const int64_t *species, int64_t feature_dim, const float *pos,
+                       const float *trans, const int64_t *sizes, int64_t N, int64_t B, int64_t E,
+                       int64_t max_atoms, const float *W_embed, const float *W_embed_packed, int num_layers,
+                       const float *const *weights, const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                       int lattice_range, int minimum_range, const float *W1, const float *b1, int64_t hidden,
+                       const float *W2, const float *b2, int64_t targets, double order_reach, void *workspace,
+                       float *y, void *const *attn_events, const cf_peer_gather *gather, void *inputs_ready,
+                       void *slot_free, void *stream)
 {
-    using namespace cf;
     CF_REQUIRE(N >= 0 && B >= 0 && E >= 0 && feature_dim > 0, CF_ERR_INVALID, "cf_model_forward: bad size");
     if (gather != nullptr) {
         const int grc = validate_peer_gather(gather, B, "cf_model_forward");
@@ -140,12 +144,13 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
                (long long)targets, HEAD_MAX_HIDDEN);
     CF_REQUIRE(N < (1ll << 31) / 512, CF_ERR_RANGE, "cf_model_forward: N=%lld too large for 32-bit GEMM sizes", (long long)N);
     if (B == 0) return CF_OK;
-    CF_REQUIRE(features && pos && trans && sizes && W_embed && W1 && b1 && W2 && b2 && workspace && y, CF_ERR_INVALID,
+    CF_REQUIRE((features || species) && pos && trans && sizes && W_embed && W1 && b1 && W2 && b2 && workspace && y, CF_ERR_INVALID,
                "cf_model_forward: null pointer");
     // With packed weights everywhere the whole forward runs in this library's kernels and cuBLAS is not touched.
     const bool embed_fused = W_embed_packed != nullptr && feature_dim <= MODEL_DIM && num_layers > 0 && N > 0 &&
                              dense_path_available(num_layers, weights, ff_dim);
     CF_REQUIRE(embed_fused || cublas_handle, CF_ERR_INVALID, "cf_model_forward: null cuBLAS handle");
+    CF_REQUIRE(embed_fused || features, CF_ERR_UNSUPPORTED, "cf_model_forward: species indices need the packed weights");
     cudaStream_t s = as_stream(stream);
     Scratch w = carve(workspace, N, B, E, ff_dim);
 
@@ -169,7 +174,7 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
         const cublasStatus_t st = linear(bl, handle, features, W_embed, w.x, (int)N, (int)feature_dim, MODEL_DIM, 0.0f);
         if (st != CUBLAS_STATUS_SUCCESS) return fail(CF_ERR_CUDA, "cf_model_forward: cuBLAS SGEMM failed with status %d", (int)st);
     }
-    const EmbedStage embed{features, (int)feature_dim, reinterpret_cast<const float4 *>(W_embed_packed)};
+    const EmbedStage embed{features, species, (int)feature_dim, reinterpret_cast<const float4 *>(W_embed_packed)};
     rc = encoder_forward_impl(cublas_handle, num_layers, weights, scalars, w.x, w.pos_ij, trans,
                               cutoff_radius != 0.0 ? w.rvlen : nullptr, w.batch, w.edges, w.row_start, N, B, E, max_atoms, K,
                               ff_dim, wscale, cutoff_radius, lattice_range, minimum_range, w.encoder, order, attn_events,
@@ -183,4 +188,22 @@ extern "C" int cf_model_forward(void *cublas_handle, const float *features, int6
         launch_chained(pool_head_kernel<false>, dim3((unsigned)B), dim3(HEAD_THREADS), 0, s, chained, (const float *)w.x,
                        (const int64_t *)w.atom_start, W1, b1, W2, b2, (int)hidden, (int)targets, y, cf_peer_gather{});
     return launch_status("cf_model_forward");
+}
+
+}  // namespace cf
+
+extern "C" int cf_model_forward(void *cublas_handle, const float *features, int64_t feature_dim, const float *pos,
+                                const float *trans, const int64_t *sizes, int64_t N, int64_t B, int64_t E,
+                                int64_t max_atoms, const float *W_embed, const float *W_embed_packed, int num_layers,
+                                const float *const *weights, const double *scalars, int64_t K, int64_t ff_dim, double wscale, double cutoff_radius,
+                                int lattice_range, int minimum_range, const float *W1, const float *b1, int64_t hidden,
+                                const float *W2, const float *b2, int64_t targets, double order_reach, void *workspace,
+                                float *y, void *const *attn_events, const cf_peer_gather *gather, void *inputs_ready,
+                                void *slot_free, void *stream)
+{
+    CF_REQUIRE(features != nullptr || B == 0, CF_ERR_INVALID, "cf_model_forward: null pointer");
+    return cf::model_forward_impl(cublas_handle, features, nullptr, feature_dim, pos, trans, sizes, N, B, E, max_atoms, W_embed,
+                                  W_embed_packed, num_layers, weights, scalars, K, ff_dim, wscale, cutoff_radius, lattice_range,
+                                  minimum_range, W1, b1, hidden, W2, b2, targets, order_reach, workspace, y, attn_events, gather,
+                                  inputs_ready, slot_free, stream);
 }

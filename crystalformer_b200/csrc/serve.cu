@@ -7,11 +7,12 @@
 // The function keeps no state and owns nothing: streams, events and every buffer are the caller's (cf_serve_slot), so
 // one caller can keep several batches in flight (one slot each) and alternate between compute streams.
 #include "common.cuh"
+#include "dense_block.cuh"
 
 extern "C" int cf_serve_submit(const cf_model_desc *model, const cf_serve_slot *slot, const float *x_host,
                                const float *pos_host, const float *trans_host, const int64_t *sizes_host, int64_t N,
                                int64_t B, int64_t E, int64_t max_atoms, int inputs_in_use,
-                               const cf_serve_gather *gather)
+                               const cf_serve_gather *gather, const int64_t *species_host)
 {
     using namespace cf;
     CF_REQUIRE(model != nullptr && slot != nullptr, CF_ERR_INVALID, "cf_serve_submit: null description");
@@ -27,7 +28,8 @@ extern "C" int cf_serve_submit(const cf_model_desc *model, const cf_serve_slot *
         CF_REQUIRE(gather->store && gather->stored && gather->collected && gather->own_cells && gather->index &&
                        gather->y_all && gather->y_all_host && gather->status && gather->status_host && gather->total_rows >= 0,
                    CF_ERR_INVALID, "cf_serve_submit: incomplete gather");
-    CF_REQUIRE(x_host && pos_host && trans_host && sizes_host, CF_ERR_INVALID, "cf_serve_submit: null input");
+    CF_REQUIRE((x_host || species_host) && pos_host && trans_host && sizes_host, CF_ERR_INVALID, "cf_serve_submit: null input");
+    CF_REQUIRE(x_host || slot->species, CF_ERR_INVALID, "cf_serve_submit: species indices given, but the slot has no buffer for them");
     // (a null stream handle is the default stream: valid for either role, though copies then do not overlap compute)
     CF_REQUIRE(slot->copied && slot->inputs_free && slot->done && slot->x && slot->pos && slot->trans && slot->sizes &&
                    slot->workspace && slot->y && slot->y_host,
@@ -38,7 +40,8 @@ extern "C" int cf_serve_submit(const cf_model_desc *model, const cf_serve_slot *
     bool ok = true;
     // the forward that last read the slot's input buffers has run
     if (inputs_in_use) ok = ok && cudaStreamWaitEvent(copy, inputs_free, 0) == cudaSuccess;
-    if (N > 0) ok = ok && cudaMemcpyAsync(slot->x, x_host, sizeof(float) * (size_t)N * (size_t)model->feature_dim, cudaMemcpyHostToDevice, copy) == cudaSuccess;
+    if (N > 0 && x_host) ok = ok && cudaMemcpyAsync(slot->x, x_host, sizeof(float) * (size_t)N * (size_t)model->feature_dim, cudaMemcpyHostToDevice, copy) == cudaSuccess;
+    if (N > 0 && !x_host) ok = ok && cudaMemcpyAsync(slot->species, species_host, sizeof(int64_t) * (size_t)N, cudaMemcpyHostToDevice, copy) == cudaSuccess;
     if (N > 0) ok = ok && cudaMemcpyAsync(slot->pos, pos_host, sizeof(float) * 3 * (size_t)N, cudaMemcpyHostToDevice, copy) == cudaSuccess;
     if (B > 0) ok = ok && cudaMemcpyAsync(slot->trans, trans_host, sizeof(float) * 9 * (size_t)B, cudaMemcpyHostToDevice, copy) == cudaSuccess;
     if (B > 0) ok = ok && cudaMemcpyAsync(slot->sizes, sizes_host, sizeof(int64_t) * (size_t)B, cudaMemcpyHostToDevice, copy) == cudaSuccess;
@@ -51,7 +54,7 @@ extern "C" int cf_serve_submit(const cf_model_desc *model, const cf_serve_slot *
         ok = ok && cudaStreamWaitEvent(compute, reinterpret_cast<cudaEvent_t>(gather->store_after), 0) == cudaSuccess;
     if (!ok) return launch_status("cf_serve_submit: wait for the gather slot");
     DenseTileRows tile_rows(model->dense_tile_rows);  // for the launches of this call, on this thread
-    const int rc = cf_model_forward(nullptr, slot->x, model->feature_dim, slot->pos, slot->trans, slot->sizes, N, B, E,
+    const int rc = model_forward_impl(nullptr, x_host ? slot->x : nullptr, x_host ? nullptr : slot->species, model->feature_dim, slot->pos, slot->trans, slot->sizes, N, B, E,
                                     max_atoms, model->W_embed, model->W_embed_packed, model->num_layers, model->weights,
                                     model->scalars, model->K, model->ff_dim, model->wscale, model->cutoff_radius,
                                     model->lattice_range, model->minimum_range, model->W1, model->b1, model->hidden,

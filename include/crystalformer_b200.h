@@ -421,6 +421,10 @@ int cf_model_forward(void *cublas_handle, const float *features, int64_t feature
  *                   `stored`, writes y_all (total_rows x targets) and is followed by `collected`; y_all and the
  *                   status word then go to y_all_host / status_host (pinned) and the slot's `done` is recorded on
  *                   the collect stream.  The slot's y / y_host are not copied in that case.
+ *   species_host  : with x_host == NULL: HOST array of N indices below feature_dim (the atoms' species, i.e. the
+ *                   position of the 1 in a one-hot feature row): 8 N bytes are copied instead of 4 N feature_dim, into
+ *                   the slot's `species` buffer (max_atoms_total int64, may be NULL in slots that never take indices),
+ *                   and the first dense block builds the one-hot rows in shared memory; same outputs, bit for bit.
  *   cf_model_desc.dense_tile_rows : 0 = the dense blocks choose their row tile themselves (16 rows while that fills
  *                   one wave of SMs: shortest latency of a single forward); 32 = 32-row tiles (fewer, longer blocks
  *                   that read the weights half as often: more forwards per second when several streams keep the GPU
@@ -450,6 +454,7 @@ typedef struct cf_serve_slot {
     void *workspace;
     float *y, *y_host;
     int64_t max_atoms_total, max_crystals, max_edges;
+    int64_t *species;
 } cf_serve_slot;
 typedef struct cf_serve_gather {
     const cf_peer_gather *store;
@@ -464,7 +469,7 @@ typedef struct cf_serve_gather {
 } cf_serve_gather;
 int cf_serve_submit(const cf_model_desc *model, const cf_serve_slot *slot, const float *x_host, const float *pos_host,
                     const float *trans_host, const int64_t *sizes_host, int64_t N, int64_t B, int64_t E,
-                    int64_t max_atoms, int inputs_in_use, const cf_serve_gather *gather);
+                    int64_t max_atoms, int inputs_in_use, const cf_serve_gather *gather, const int64_t *species_host);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Scheduling weight of every atom's row for the fused attention kernels (no counterpart in the reference, which

@@ -204,6 +204,11 @@ def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, c
     for y, ref in zip(got, direct):
         assert torch.equal(y, ref)
     assert (runner._native[0] is not None) == one_call
+    if one_call:  # the same batches with species indices instead of one-hot rows: the same bits
+        for h, ref in zip(host[:depth], direct):
+            assert bool(((h.x.sum(1) == 1) & (h.x.max(1).values == 1)).all())  # (the synthetic rows are one-hot)
+            hz = types.SimpleNamespace(z=h.x.argmax(1).contiguous().pin_memory(), pos=h.pos, trans_vec=h.trans_vec, sizes=h.sizes)
+            assert torch.equal(runner.result(runner.submit(hz)), ref)
     with pytest.raises(RuntimeError):
         runner.result(123)
     if one_call:  # a batch larger than the slot's buffers is refused by the library, not written past their end
@@ -214,5 +219,5 @@ def test_pipelined_predictor_equals_direct_calls(golden_model, depth, streams, c
         with pytest.raises(_lib.CrystalformerB200Error) as e:
             _lib.call("cf_serve_submit", ctypes.byref(runner._plan["desc"]), ctypes.byref(st["c"]), h.x.data_ptr(),
                       h.pos.data_ptr(), h.trans_vec.data_ptr(), h.sizes.data_ptr(), int(h.x.shape[0]), int(h.sizes.shape[0]),
-                      int((h.sizes ** 2).sum()), int(h.sizes.max()), 1, None)
+                      int((h.sizes ** 2).sum()), int(h.sizes.max()), 1, None, None)
         assert "exceeds the slot's buffers" in str(e.value)
