@@ -61,7 +61,8 @@ struct RowArgs {
     long long N;
     int max_atoms;
     int keep_logit;  // 0: inference, the logits are not written back
-    int phi_in_row;  // 1: no phi kernel ran; rows (all of at most 32 keys) sum phi from their term lists themselves
+    int phi_in_row;  // 1: no phi kernel ran; rows of at most 32 keys with a basis sum phi from their term lists
+                     // themselves, all others (left-over rows of the sorted path) enumerate it edge by edge
     BoxRule rule;
     BasisParams basis;
 };
@@ -95,8 +96,11 @@ __device__ __noinline__ void edge_phi_enumerated(const BoxRule rule, const float
 // ROW_WARPS = 1: one warp per atom, four atoms per thread block (small crystals: a row is a few thousand terms and
 //                its cost is dominated by the latency of its phases, so four rows progress independently per block
 //                and only warp-level synchronisation is needed).
-template <int K, int ROW_WARPS>
-__global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)) infinite_attn_rows_kernel(const RowArgs p)
+// ENUM_PHI: the kernel for left-over rows of the sorted path that neither a phi kernel nor term lists serve (no basis,
+// or more than 32 keys): phi of every edge is enumerated inside the row (a variant of its own, so that the ordinary
+// instantiations carry none of its code or registers).
+template <int K, int ROW_WARPS, bool ENUM_PHI = false>
+__global__ void __launch_bounds__(THREADS, ENUM_PHI ? 2 : (K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4))) infinite_attn_rows_kernel(const RowArgs p)
 {
     extern __shared__ __align__(16) float smem_all[];
     constexpr int GROUPS = WARPS / ROW_WARPS;        // row groups per block
@@ -283,8 +287,14 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
                         rx = __fsub_rn(pp[0], pi[0]); ry = __fsub_rn(pp[1], pi[1]); rz = __fsub_rn(pp[2], pi[2]);
                     }
                 }
-                // phi: left in shared memory by the phase above, or in the logit array by the phi kernel
-                const float *src = (phi_here ? part + 8 * lane : logit_io + (e0 + lane) * HEADS) + h0;
+                // phi: left in shared memory by the phase above, or in the logit array by the phi kernel, or - a left-over
+                // row without a basis, for which neither ran - enumerated here
+                __align__(16) float enumerated[8];
+                const bool phi_enum = ENUM_PHI && p.phi_in_row != 0 && !phi_here;
+                if (phi_enum)
+                    edge_phi_enumerated(p.rule, p.a + i * HEADS, p.rvlen ? p.rvlen + 3 * c : nullptr, p.tvecs + 9 * c,
+                                        p.pos_ij + 3 * (e0 + lane), p.basis.floor_log2, enumerated);
+                const float *src = (phi_enum ? enumerated : phi_here ? part + 8 * lane : logit_io + (e0 + lane) * HEADS) + h0;
                 if (HPW == 8) {
                     const float4 v0 = reinterpret_cast<const float4 *>(src)[0], v1 = reinterpret_cast<const float4 *>(src)[1];
                     phi[0] = v0.x; phi[1] = v0.y; phi[2] = v0.z; phi[3] = v0.w;
@@ -386,8 +396,15 @@ __global__ void __launch_bounds__(THREADS, K == 0 ? 6 : (ROW_WARPS == 1 ? 3 : 4)
             for (int j = rt; j < n; j += RT) {
                 const float4 *kp = reinterpret_cast<const float4 *>(kmat + (a0 + j) * HEADS * HEAD_DIM);
                 float4 *lp = reinterpret_cast<float4 *>(logit_io + (e0 + j) * HEADS);  // phi was left here by the phi kernel
-                const float4 ph0 = lp[0], ph1 = lp[1];
-                const float phi[8] = {ph0.x, ph0.y, ph0.z, ph0.w, ph1.x, ph1.y, ph1.z, ph1.w};
+                float phi[8];
+                if (ENUM_PHI && p.phi_in_row != 0) {  // (a left-over row: no phi kernel ran)
+                    edge_phi_enumerated(p.rule, p.a + i * HEADS, p.rvlen ? p.rvlen + 3 * c : nullptr, p.tvecs + 9 * c,
+                                        p.pos_ij + 3 * (e0 + j), p.basis.floor_log2, phi);
+                } else {
+                    const float4 ph0 = lp[0], ph1 = lp[1];
+                    phi[0] = ph0.x; phi[1] = ph0.y; phi[2] = ph0.z; phi[3] = ph0.w;
+                    phi[4] = ph1.x; phi[5] = ph1.y; phi[6] = ph1.z; phi[7] = ph1.w;
+                }
                 float lg[8];
 #pragma unroll
                 for (int h = 0; h < HEADS; ++h) {
@@ -789,7 +806,12 @@ int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s
     const int groups = WARPS / row_warps;
     const size_t smem = sizeof(float) * groups * row_group_floats(max_atoms, K > 0, row_warps);
     void (*kernel)(const RowArgs);
-    if (K > 0)
+    // left-over rows of the sorted path without a basis, or of more than 32 keys: phi enumerated inside the row
+    const bool enum_phi = p.phi_in_row != 0 && (K == 0 || max_atoms > 32);
+    if (enum_phi)
+        kernel = K > 0 ? infinite_attn_rows_kernel<64, 4, true>
+                       : (row_warps == 1 ? infinite_attn_rows_kernel<0, 1, true> : infinite_attn_rows_kernel<0, 4, true>);
+    else if (K > 0)
         kernel = row_warps == 1 ? infinite_attn_rows_kernel<64, 1> : infinite_attn_rows_kernel<64, 4>;
     else
         kernel = row_warps == 1 ? infinite_attn_rows_kernel<0, 1> : infinite_attn_rows_kernel<0, 4>;
@@ -800,9 +822,9 @@ int launch_rows(const RowArgs &p, int64_t K, long long grid_rows, cudaStream_t s
                         smem, max_atoms);
         }
     }
-    static thread_local size_t cached_smem[4] = {0, 0, 0, 0};
-    static thread_local int cached_occ[4] = {0, 0, 0, 0};
-    const int slot = (K > 0 ? 2 : 0) + (row_warps == 1 ? 0 : 1);
+    static thread_local size_t cached_smem[8] = {};
+    static thread_local int cached_occ[8] = {};
+    const int slot = (K > 0 ? 2 : 0) + (row_warps == 1 ? 0 : 1) + (enum_phi ? 4 : 0);
     if (cached_occ[slot] == 0 || cached_smem[slot] != smem) {
         int occ = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, THREADS, smem) != cudaSuccess || occ <= 0) occ = 1;
@@ -822,7 +844,8 @@ int launch_leftover_rows(const float *q, const float *k, const float *v, const f
                          const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
                          const int64_t *row_start, int64_t N, int64_t E, int64_t max_atoms, double dist_max,
                          double wscale, const float *W, double cutoff_radius, int lattice_range, int minimum_range,
-                         float *out, float *lse, const int *rows, const unsigned *count, unsigned *ticket, cudaStream_t s)
+                         float *out, float *lse, const int *rows, const unsigned *count, unsigned *ticket, int64_t K,
+                         cudaStream_t s)
 {
     RowArgs p{};
     p.q = q; p.k = k; p.v = v; p.a = a; p.pos_ij = pos_ij; p.tvecs = tvecs; p.rvlen = rvlen; p.W = W;
@@ -832,9 +855,9 @@ int launch_leftover_rows(const float *q, const float *k, const float *v, const f
     p.phi_in_row = 1;  // no list: every edge's phi is enumerated inside the row kernel
     p.ticket = ticket;
     p.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
-    p.basis = make_basis_params(64, dist_max, wscale, weight_floor_log2());
+    p.basis = make_basis_params(K, dist_max, wscale, weight_floor_log2());
     // left-over rows are rare: a grid of one block per SM draws them through the ticket
-    return launch_rows(p, 64, (long long)sm_count() * (max_atoms <= 12 ? WARPS : 1), s, true);
+    return launch_rows(p, K, (long long)sm_count() * (max_atoms <= 12 ? WARPS : 1), s, true);
 }
 }  // namespace cf
 

@@ -1,4 +1,4 @@
-// Fused infinitely connected attention, forward, for batches of small crystals (at most 32 atoms per cell): one warp
+// Fused infinitely connected attention, forward, for batches of small crystals (at most 64 atoms per cell): one warp
 // per atom row (the four warps of a block share a row whose list is long), the row's terms read from its
 // distance-sorted row list (row_list.cuh), every sum over terms done as tensor-core products.
 //
@@ -21,7 +21,9 @@
 // the sweep ends at the first chunk whose entries are below the weight floor for every head.
 //
 // Rows without a list, rows of more than 16 NT keys and rows where a head's sum comes out empty are appended to the
-// left-over list and processed by the enumerating row kernel (infinite_attn_fwd.cu) afterwards.
+// left-over list and processed by the enumerating row kernel (infinite_attn_fwd.cu) afterwards.  Without a radial
+// basis (K = 0: PSI = false) the histogram, its tiles and the projection W drop out; the rest is the same (the
+// one-call forwards do not use that variant: there the enumerating kernel with term lists is faster).
 #include "lattice_core.cuh"
 #include "row_list.cuh"
 
@@ -30,7 +32,6 @@ namespace {
 
 constexpr int SR_THREADS = 128;
 constexpr int SR_WARPS = SR_THREADS / 32;
-constexpr int CJ_LD = 33;     // leading dimension of the per-(head, key) tables
 constexpr int PSI_LD = 68;    // leading dimension of the histogram tile (heads x 64 bins): 4-bank shift per head
 constexpr int RING_SLOTS = 3; // groups of eight chunks staged per warp
 constexpr int CHANNELS = HEADS * HEAD_DIM;
@@ -95,12 +96,14 @@ __device__ __forceinline__ float warp_max_heads(const float (&v)[8], int lane)
     return r;
 }
 
-// Shared memory of one thread block.
+// Shared memory of one thread block (NT key tiles of 16; PSI: with the radial basis).
+template <int NT, bool PSI>
 struct SortedSmem {
-    float wt[64 * CHANNELS];              // W transposed: wt[k][channel], staged once per block
+    static constexpr int CJ_LD = 16 * NT + 1;  // leading dimension of the per-(head, key) tables (odd: no bank conflicts)
+    float wt[PSI ? 64 * CHANNELS : 4];    // W transposed: wt[k][channel], staged once per block
     float cj[SR_WARPS][8 * CJ_LD];        // s_h[j] per (head, key); a block working on one row uses table 0
     float pj[SR_WARPS][8 * CJ_LD];        // P_h[j]
-    float psi[SR_WARPS][8 * PSI_LD];      // Psi_h[k]
+    float psi[SR_WARPS][PSI ? 8 * PSI_LD : 4];  // Psi_h[k]
     float2 ring[SR_WARPS][RING_SLOTS][64];  // list entries, 8 chunks (512 bytes) per slot
     long long next_task;
 };
@@ -109,9 +112,10 @@ struct SortedSmem {
 // COOP = true: the four warps of the block share the row - the keys of the q.k table, then the row's chunks dealt
 // round-robin, every warp with its own accumulators; the partial histograms meet in shared memory and every thread
 // finishes one output channel.  Returns false if the row must be left over.
-template <int NT, bool COOP>
-__device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &sm, const int4 r0, const int4 r1, int warp, int lane)
+template <int NT, bool COOP, bool PSI>
+__device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem<NT, PSI> &sm, const int4 r0, const int4 r1, int warp, int lane)
 {
+    constexpr int CJ_LD = SortedSmem<NT, PSI>::CJ_LD;
     const int g = lane >> 2, t = lane & 3;
     auto sync = [&]() {
         if (COOP) __syncthreads(); else __syncwarp();
@@ -145,6 +149,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
     const float4 a_hi = __ldg(reinterpret_cast<const float4 *>(p.a + (size_t)i * HEADS) + 1);
     const float4 q4 = __ldg(reinterpret_cast<const float4 *>(p.q + (size_t)i * CHANNELS) + lane);
     const float dm = lane < n ? __ldg(p.dmin + e0 + lane) : 0.f;
+    const float dm2 = (NT > 2 && lane + 32 < n) ? __ldg(p.dmin + e0 + lane + 32) : 0.f;  // keys 32 .. 63
     float rvl[3] = {0.f, 0.f, 0.f};
     if (p.rvlen) { rvl[0] = __ldg(p.rvlen + 3 * c); rvl[1] = __ldg(p.rvlen + 3 * c + 1); rvl[2] = __ldg(p.rvlen + 3 * c + 2); }
 
@@ -188,6 +193,11 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
             const float s = lane < n ? cj[h * CJ_LD + lane] : -INFINITY;
             s8[h] = s;
             m8[h] = fmaf(a8[h] * LOG2E, dm, s);
+            if (NT > 2) {  // (a lane looks after keys lane and lane + 32)
+                const float s2 = lane + 32 < n ? cj[h * CJ_LD + lane + 32] : -INFINITY;
+                s8[h] = fmaxf(s8[h], s2);
+                m8[h] = fmaxf(m8[h], fmaf(a8[h] * LOG2E, dm2, s2));
+            }
         }
         M_g = warp_max_heads(m8, lane);
         slack_g = warp_max_heads(s8, lane) - M_g;
@@ -233,7 +243,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
                 w = (row_key_in_box(keyv[u], boxor) && (u < 2 || two)) ? w : 0.f;
                 split_tf32(w, w_hi[u], w_lo[u]);
                 dj[u] = j - g;
-                x[u] = d2v[u] * rsqrt_fast(fmaxf(d2v[u], 1e-35f)) * p.bin_scale;  // basis coordinate of the term
+                if (PSI) x[u] = d2v[u] * rsqrt_fast(fmaxf(d2v[u], 1e-35f)) * p.bin_scale;  // basis coordinate of the term
             }
             // P^T tiles: one-hot of the terms' keys (rows g, g + 8 of tile u are keys 16 u + g, 16 u + g + 8)
 #pragma unroll
@@ -249,6 +259,8 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
                 mma_tf32(accP[u], o[4], o[5], o[6], o[7], w_hi[2], w_hi[3]);
                 mma_tf32(accP[u], o[4], o[5], o[6], o[7], w_lo[2], w_lo[3]);
             }
+            swept += two ? 2 : 1;
+            if (PSI) {
             // the bin tiles the two chunks can reach
             const float x_first = __shfl_sync(FULL, x[0], 0), x_last = __shfl_sync(FULL, x[3], 3);
             const float b_lo = fmaf(x_first, p.inv_bin_step, -1.0f - p.tile_reach);
@@ -256,7 +268,6 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
             const int m_lo = max(0, __float2int_rd(b_lo * 0.0625f));
             const int m_hi = b_hi < 0.0f ? -1 : min(3, __float2int_rd(b_hi * 0.0625f));  // (beyond the last bin: only phi needs the terms)
             const float uu[4] = {x[0] - ucg, x[1] - ucg, x[2] - ucg, x[3] - ucg};
-            swept += two ? 2 : 1;
             tiles_done += max(m_hi - m_lo + 1, 0) * (two ? 2 : 1);
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
@@ -276,6 +287,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
                 mma_tf32(accPsi[m], lo[4], lo[5], lo[6], lo[7], w_hi[2], w_hi[3]);
                 mma_tf32(accPsi[m], hi[4], hi[5], hi[6], hi[7], w_lo[2], w_lo[3]);
             }
+            }
         }
         __syncwarp();  // every lane is done with the slot before a later fetch overwrites it
         if (++ring_slot == RING_SLOTS) ring_slot = 0;
@@ -290,7 +302,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
     // ---- accumulators -> shared memory (C fragment: rows g, g + 8; columns = heads 2 t, 2 t + 1)
     __syncwarp();
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
+    for (int m = 0; m < (PSI ? 4 : 0); ++m) {
         psi[(2 * t) * PSI_LD + 16 * m + g] = accPsi[m][0];
         psi[(2 * t + 1) * PSI_LD + 16 * m + g] = accPsi[m][1];
         psi[(2 * t) * PSI_LD + 16 * m + g + 8] = accPsi[m][2];
@@ -307,7 +319,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
     if (COOP) {
         // ---- the four partial tables are added in a fixed order; one output channel per thread
         const int tid = 32 * warp + lane;
-        for (int idx = tid; idx < 8 * PSI_LD; idx += SR_THREADS)
+        for (int idx = tid; idx < (PSI ? 8 * PSI_LD : 0); idx += SR_THREADS)
             sm.psi[0][idx] = (sm.psi[0][idx] + sm.psi[1][idx]) + (sm.psi[2][idx] + sm.psi[3][idx]);
         for (int idx = tid; idx < 8 * CJ_LD; idx += SR_THREADS)
             sm.pj[0][idx] = (sm.pj[0][idx] + sm.pj[1][idx]) + (sm.pj[2][idx] + sm.pj[3][idx]);
@@ -332,7 +344,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
         const float *ps = sm.psi[0] + h * PSI_LD;
         float o0 = 0.f, o1 = 0.f;
 #pragma unroll 8
-        for (int k4 = 0; k4 < 64; k4 += 4) {
+        for (int k4 = 0; k4 < (PSI ? 64 : 0); k4 += 4) {
             const float4 pv = *reinterpret_cast<const float4 *>(ps + k4);
             o0 = fmaf(sm.wt[(k4 + 0) * CHANNELS + tid], pv.x, o0);
             o1 = fmaf(sm.wt[(k4 + 1) * CHANNELS + tid], pv.y, o1);
@@ -368,7 +380,7 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
         const float *ps = psi + g * PSI_LD;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-        for (int k4 = 0; k4 < 64; k4 += 4) {
+        for (int k4 = 0; k4 < (PSI ? 64 : 0); k4 += 4) {
             const float4 pv = *reinterpret_cast<const float4 *>(ps + k4);
             const float pk[4] = {pv.x, pv.y, pv.z, pv.w};
 #pragma unroll
@@ -391,16 +403,16 @@ __device__ __forceinline__ bool sorted_row(const SortedRowArgs &p, SortedSmem &s
 // takes rows of the second list on its own, again the first by position and the rest through a ticket.  Which warps
 // compute a row has no influence on which terms are summed, and the choice between the two organisations depends on
 // the row's list alone, so results are repeatable bit for bit.
-template <int NT>
-__global__ void __launch_bounds__(SR_THREADS, 4) infinite_attn_sorted_rows_kernel(const SortedRowArgs p)
+template <int NT, bool PSI>
+__global__ void __launch_bounds__(SR_THREADS, NT > 2 ? 3 : 4) infinite_attn_sorted_rows_kernel(const SortedRowArgs p)
 {
     extern __shared__ __align__(16) unsigned char sorted_smem_raw[];
-    SortedSmem &sm = *reinterpret_cast<SortedSmem *>(sorted_smem_raw);
+    SortedSmem<NT, PSI> &sm = *reinterpret_cast<SortedSmem<NT, PSI> *>(sorted_smem_raw);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     grid_launch_dependents();
     // W (8,16,64) -> wt[k][channel]: thread = channel, 256 contiguous bytes read, 64 conflict-free stores (W is a
     // constant: in a chained launch this runs while the kernel before this one drains)
-    {
+    if (PSI) {
         const float4 *src = reinterpret_cast<const float4 *>(p.W + (size_t)tid * 64);
 #pragma unroll 4
         for (int k4 = 0; k4 < 16; ++k4) {
@@ -421,7 +433,7 @@ __global__ void __launch_bounds__(SR_THREADS, 4) infinite_attn_sorted_rows_kerne
         if (tid == 0) drawn = atomicAdd(p.sched, 1u);  // (needed only after the row)
         const int slot = __ldg(p.tasks + task);
         const int4 r0 = __ldg(p.rowdir + 2 * (long long)slot), r1 = __ldg(p.rowdir + 2 * (long long)slot + 1);
-        if (!sorted_row<NT, true>(p, sm, r0, r1, warp, lane) && tid == 0) p.leftover[atomicAdd(p.sched + 1, 1u)] = r0.x;
+        if (!sorted_row<NT, true, PSI>(p, sm, r0, r1, warp, lane) && tid == 0) p.leftover[atomicAdd(p.sched + 1, 1u)] = r0.x;
         if (tid == 0) sm.next_task = (long long)gridDim.x + drawn;
         __syncthreads();
         task = sm.next_task;
@@ -435,7 +447,7 @@ __global__ void __launch_bounds__(SR_THREADS, 4) infinite_attn_sorted_rows_kerne
         if (lane == 0) drawn = atomicAdd(p.sched + 3, 1u);
         const int slot = __ldg(p.tasks + p.N + task);
         const int4 r0 = __ldg(p.rowdir + 2 * (long long)slot), r1 = __ldg(p.rowdir + 2 * (long long)slot + 1);
-        if (!sorted_row<NT, false>(p, sm, r0, r1, warp, lane) && lane == 0) p.leftover[atomicAdd(p.sched + 1, 1u)] = r0.x;
+        if (!sorted_row<NT, false, PSI>(p, sm, r0, r1, warp, lane) && lane == 0) p.leftover[atomicAdd(p.sched + 1, 1u)] = r0.x;
         task = first_wave + __shfl_sync(FULL, drawn, 0);
     }
 }
@@ -451,7 +463,7 @@ int launch_sorted_rows(const SortedRowLaunch &l, cudaStream_t s)
     p.tasks = l.view.tasks; p.task_count = l.view.task_count;
     p.sched = l.sched; p.leftover = l.view.leftover;
     p.out = l.out; p.lse = l.lse; p.N = l.N; p.rule = l.rule;
-    const BasisParams bp = make_basis_params(64, l.dist_max, l.wscale, weight_floor_log2());
+    const BasisParams bp = make_basis_params(64, l.dist_max > 0 ? l.dist_max : 1.0, l.wscale > 0 ? l.wscale : 1.0, weight_floor_log2());
     p.bin_step = bp.bin_step; p.bin_scale = bp.bin_scale; p.inv_bin_step = 1.0f / bp.bin_step;
     // a basis value exp2(-(step * bins)^2) is below the weight floor beyond sqrt(-floor) / step bins (floor clipped to
     // [2^-126, 2^-24]: with the floor switched off the whole float range is kept)
@@ -459,21 +471,32 @@ int launch_sorted_rows(const SortedRowLaunch &l, cudaStream_t s)
     p.tile_reach = sqrtf(fl) / bp.bin_step;
     p.floor_log2 = weight_floor_log2();
     p.stats = row_stats_words();
-    auto kernel = l.max_atoms <= 16 ? infinite_attn_sorted_rows_kernel<1> : infinite_attn_sorted_rows_kernel<2>;
-    static thread_local bool configured[64][2] = {};
+    // key tiles: 1, 2 or 4 (16, 32, 64 keys); with or without the radial basis
+    const int variant = (l.max_atoms <= 16 ? 0 : l.max_atoms <= 32 ? 1 : 2) + (l.K > 0 ? 0 : 3);
+    void (*kernel)(const SortedRowArgs) = nullptr;
+    size_t smem = 0;
+    switch (variant) {
+    case 0: kernel = infinite_attn_sorted_rows_kernel<1, true>; smem = sizeof(SortedSmem<1, true>); break;
+    case 1: kernel = infinite_attn_sorted_rows_kernel<2, true>; smem = sizeof(SortedSmem<2, true>); break;
+    case 2: kernel = infinite_attn_sorted_rows_kernel<4, true>; smem = sizeof(SortedSmem<4, true>); break;
+    case 3: kernel = infinite_attn_sorted_rows_kernel<1, false>; smem = sizeof(SortedSmem<1, false>); break;
+    case 4: kernel = infinite_attn_sorted_rows_kernel<2, false>; smem = sizeof(SortedSmem<2, false>); break;
+    default: kernel = infinite_attn_sorted_rows_kernel<4, false>; smem = sizeof(SortedSmem<4, false>); break;
+    }
+    static thread_local bool configured[64][6] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    bool &done = configured[dev & 63][l.max_atoms <= 16 ? 0 : 1];
+    bool &done = configured[dev & 63][variant];
     if (!done) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortedSmem)) != cudaSuccess) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
-            return fail(CF_ERR_CUDA, "sorted row kernel: %zu bytes of shared memory not available", sizeof(SortedSmem));
+            return fail(CF_ERR_CUDA, "sorted row kernel: %zu bytes of shared memory not available", smem);
         }
         done = true;
     }
-    const long long cap = (long long)sm_count() * 4;
+    const long long cap = (long long)sm_count() * (l.max_atoms > 32 ? 3 : 4);
     const unsigned blocks = (unsigned)(l.N < cap ? l.N : cap);
-    launch_chained(kernel, dim3(blocks), dim3(SR_THREADS), sizeof(SortedSmem), s, l.chained, p);
+    launch_chained(kernel, dim3(blocks), dim3(SR_THREADS), smem, s, l.chained, p);
     return launch_status("infinite_attn_sorted_rows_kernel");
 }
 
@@ -484,7 +507,8 @@ int launch_leftover_rows(const float *q, const float *k, const float *v, const f
                          const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
                          const int64_t *row_start, int64_t N, int64_t E, int64_t max_atoms, double dist_max,
                          double wscale, const float *W, double cutoff_radius, int lattice_range, int minimum_range,
-                         float *out, float *lse, const int *rows, const unsigned *count, unsigned *ticket, cudaStream_t s);
+                         float *out, float *lse, const int *rows, const unsigned *count, unsigned *ticket, int64_t K,
+                         cudaStream_t s);
 
 // One attention call over a batch's row lists: the sorted row kernel, then the enumerating row kernel for whatever it
 // left over (normally nothing: that launch then finds a zero count and returns).  sched_slot: which of the
@@ -494,21 +518,21 @@ int sorted_attn_impl(const float *q, const float *k, const float *v, const float
                      const float *tvecs, const float *rvlen, const int64_t *batch, const int64_t *edges,
                      const int64_t *row_start, int64_t N, int64_t E, int64_t max_atoms, double dist_max, double wscale,
                      const float *W, double cutoff_radius, int lattice_range, int minimum_range, float *out, float *lse,
-                     const RowListView &view, int sched_slot, bool zeroed, cudaStream_t s)
+                     const RowListView &view, int sched_slot, bool zeroed, int64_t K, cudaStream_t s)
 {
     // (chained launches only when no memset sits between this call's kernels and the one before them)
     unsigned *sched = view.sched + 4 * sched_slot;
     if (!zeroed && cudaMemsetAsync(sched, 0, 4 * sizeof(unsigned), s) != cudaSuccess) return launch_status("row scheduling block");
     SortedRowLaunch l{};
     l.q = q; l.k = k; l.v = v; l.a = a; l.rvlen = cutoff_radius != 0.0 ? rvlen : nullptr; l.W = W;
-    l.view = view; l.sched = sched; l.out = out; l.lse = lse; l.N = N; l.max_atoms = (int)max_atoms;
+    l.view = view; l.sched = sched; l.out = out; l.lse = lse; l.N = N; l.max_atoms = (int)max_atoms; l.K = (int)K;
     l.rule = BoxRule{(float)cutoff_radius, lattice_range, minimum_range};
     l.dist_max = dist_max; l.wscale = wscale;
     l.chained = zeroed;
     int rc = launch_sorted_rows(l, s);
     if (rc != CF_OK) return rc;
     return launch_leftover_rows(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, N, E, max_atoms, dist_max, wscale,
-                                W, cutoff_radius, lattice_range, minimum_range, out, lse, view.leftover, sched + 1, sched + 2, s);
+                                W, cutoff_radius, lattice_range, minimum_range, out, lse, view.leftover, sched + 1, sched + 2, K, s);
 }
 }  // namespace cf
 
@@ -522,18 +546,18 @@ extern "C" int cf_infinite_attn_fwd_sorted(const float *q, const float *k, const
 {
     using namespace cf;
     CF_REQUIRE(N >= 0 && E >= 0 && B >= 0, CF_ERR_INVALID, "cf_infinite_attn_fwd_sorted: negative size");
-    CF_REQUIRE(H == HEADS && D == HEAD_DIM && K == 64, CF_ERR_UNSUPPORTED,
-               "cf_infinite_attn_fwd_sorted: H=%lld D=%lld K=%lld, only H=8 D=16 K=64 is compiled", (long long)H, (long long)D, (long long)K);
+    CF_REQUIRE(H == HEADS && D == HEAD_DIM && (K == 64 || K == 0), CF_ERR_UNSUPPORTED,
+               "cf_infinite_attn_fwd_sorted: H=%lld D=%lld K=%lld, only H=8 D=16 K in {0, 64} is compiled", (long long)H, (long long)D, (long long)K);
     CF_REQUIRE(max_atoms >= 1 && max_atoms <= ROW_LIST_MAX_KEYS, CF_ERR_RANGE,
                "cf_infinite_attn_fwd_sorted: max_atoms=%lld outside [1,%d]", (long long)max_atoms, ROW_LIST_MAX_KEYS);
     CF_REQUIRE(lattice_range >= 0 && lattice_range <= CF_MAX_RANGE && minimum_range >= 0, CF_ERR_RANGE,
                "cf_infinite_attn_fwd_sorted: lattice_range %d outside [0,%d]", lattice_range, CF_MAX_RANGE);
     if (N == 0) return CF_OK;
-    CF_REQUIRE(q && k && v && a && pos_ij && tvecs && batch && edges && row_start && W && out && lse && row_lists, CF_ERR_INVALID,
-               "cf_infinite_attn_fwd_sorted: null pointer");
-    CF_REQUIRE(dist_max > 0 && wscale > 0, CF_ERR_INVALID, "cf_infinite_attn_fwd_sorted: dist_max and wscale must be positive");
+    CF_REQUIRE(q && k && v && a && pos_ij && tvecs && batch && edges && row_start && (W || K == 0) && out && lse && row_lists,
+               CF_ERR_INVALID, "cf_infinite_attn_fwd_sorted: null pointer");
+    CF_REQUIRE(K == 0 || (dist_max > 0 && wscale > 0), CF_ERR_INVALID, "cf_infinite_attn_fwd_sorted: dist_max and wscale must be positive");
     const RowListView view = row_list_carve(row_lists, N, E);
     return sorted_attn_impl(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, N, E, max_atoms, dist_max, wscale, W,
-                            cutoff_radius, lattice_range, minimum_range, out, lse, view, ROW_SCHED_SLOTS - 1, false,
+                            cutoff_radius, lattice_range, minimum_range, out, lse, view, ROW_SCHED_SLOTS - 1, false, K,
                             as_stream(stream));
 }

@@ -31,8 +31,8 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
     __shared__ float4 key_s[ROW_LIST_MAX_KEYS];                // relative position of every key, .w = its threshold
     __shared__ int cnt_s;
     __shared__ int4 kbox_s[ROW_LIST_MAX_KEYS];                 // first translation of every key's box, its widths w3 | w2 << 8
-    __shared__ int kpre_s[ROW_LIST_MAX_KEYS + 1];              // translations in the boxes of the keys before
-    __shared__ float d2max_s;
+    __shared__ int kcnt_s[ROW_LIST_MAX_KEYS];                  // translations in every key's box
+    __shared__ float d2max_s[ROW_LIST_MAX_KEYS / 32];          // largest threshold among every 32 keys
     __shared__ long long base_s;
     const int tid = threadIdx.x, lane = tid & 31, wr = tid >> 5;
     const unsigned lt = (1u << lane) - 1u;
@@ -84,11 +84,12 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
         //      the box of the cut-off rule: with b_i the reciprocal rows (b_i . t_j = delta_ij), (r + n T) . b_i =
         //      s_i + n_i and |x . b_i| <= |x| |b_i| bound every digit,
         //          | n_i + s_i | <= rho |b_i|,      s_i = r . b_i,  rho = sqrt(threshold).
-        //      The first warp computes every key's bounding box, clipped to the rule's box (one key per lane; the
+        //      The first warps compute every key's bounding box, clipped to the rule's box (one key per lane; the
         //      bounds are widened a little beyond any rounding, the test on d2 below decides membership, so the listed
-        //      set is that of a walk of the whole box), and the running sum of the boxes' sizes; then the warps take
-        //      the keys in turn, lanes over the translations of a key's box.
-        if (fits && wr == 0) {
+        //      set is that of a walk of the whole box); then the warps take the keys in turn, lanes over the
+        //      translations of a key's box.
+        if (fits && wr < ROW_LIST_MAX_KEYS / 32) {
+            const int key = 32 * wr + lane;
             const float c1x = cell.t2y * cell.t3z - cell.t2z * cell.t3y, c1y = cell.t2z * cell.t3x - cell.t2x * cell.t3z,
                         c1z = cell.t2x * cell.t3y - cell.t2y * cell.t3x;
             const float c2x = cell.t3y * cell.t1z - cell.t3z * cell.t1y, c2y = cell.t3z * cell.t1x - cell.t3x * cell.t1z,
@@ -99,7 +100,7 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
             const bool prune = fabsf(det) > 1e-12f;  // (a flat cell keeps the whole box)
             const float idet = prune ? 1.0f / det : 0.0f;
             int lo1 = -R1, hi1 = R1, lo2 = -R2, hi2 = R2, lo3 = -R3, hi3 = R3;
-            const float4 r = lane < n ? key_s[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 r = key < n ? key_s[key] : make_float4(0.f, 0.f, 0.f, 0.f);
             if (prune) {
                 const float rho = sqrtf(fmaxf(r.w, 0.f)) * 1.0001f;
                 const float m1 = rho * sqrtf(c1x * c1x + c1y * c1y + c1z * c1z) * fabsf(idet) + 1e-3f;
@@ -113,27 +114,23 @@ __global__ void __launch_bounds__(RL_THREADS) row_list_build_kernel(const RowLis
                 lo3 = (int)ceilf(fmaxf(-m3 - s3, (float)-R3)); hi3 = (int)floorf(fminf(m3 - s3, (float)R3));
             }
             const int w1 = max(hi1 - lo1 + 1, 0), w2 = max(hi2 - lo2 + 1, 0), w3 = max(hi3 - lo3 + 1, 0);
-            const int count = lane < n ? w1 * w2 * w3 : 0;
-            int incl = count;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int up = __shfl_up_sync(FULL, incl, o);
-                if (lane >= o) incl += up;
-            }
-            kpre_s[lane + 1] = incl;
-            if (lane == 0) kpre_s[0] = 0;
-            kbox_s[lane] = make_int4(lo1, lo2, lo3, max(w3, 1) | (max(w2, 1) << 8));
-            const float top = warp_max(lane < n ? r.w : 1.0f);
-            if (lane == 0) d2max_s = fmaxf(top, 1.0f);
+            kcnt_s[key] = key < n ? w1 * w2 * w3 : 0;
+            kbox_s[key] = make_int4(lo1, lo2, lo3, max(w3, 1) | (max(w2, 1) << 8));
+            const float top = warp_max(key < n ? r.w : 1.0f);
+            if (lane == 0) d2max_s[wr] = fmaxf(top, 1.0f);
         }
         __syncthreads();
-        const float d2_max = fits ? d2max_s : 1.0f;  // no listed term is farther (the same value in every thread)
+        float d2_max = 1.0f;  // no listed term is farther (the same value in every thread)
+        if (fits) {
+#pragma unroll
+            for (int u = 0; u < ROW_LIST_MAX_KEYS / 32; ++u) d2_max = fmaxf(d2_max, d2max_s[u]);
+        }
         if (fits) {
             // a warp takes a key at a time, its lanes the translations of the key's box (32 per pass)
             for (int j = wr; j < n; j += RL_WARPS) {
                 const int4 kb = kbox_s[j];
                 const float4 r = key_s[j];
-                const int count = kpre_s[j + 1] - kpre_s[j];
+                const int count = kcnt_s[j];
                 const int w3 = kb.w & 255, w2 = kb.w >> 8;
                 const float inv_w3 = __frcp_rn((float)w3), inv_w2 = __frcp_rn((float)w2);
                 for (int tr0 = 0; tr0 < count; tr0 += 32) {  // (warp-uniform bounds: the ballots below are safe)

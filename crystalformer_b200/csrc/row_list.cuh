@@ -34,7 +34,7 @@
 
 namespace cf {
 
-constexpr int ROW_LIST_MAX_KEYS = 32;   // crystals of at most this many atoms
+constexpr int ROW_LIST_MAX_KEYS = 64;   // crystals of at most this many atoms
 constexpr int ROW_LIST_CAP = 4096;      // entries of one row (sorted in shared memory by the build)
 constexpr int ROW_SCHED_SLOTS = 16;     // attention calls per build that find a zeroed scheduling block
 constexpr int ROW_PAD_KEY = 0x7f7f7f00; // |n| bytes of 127: outside every box (CF_MAX_RANGE = 32)
@@ -85,6 +85,7 @@ struct SortedRowLaunch {
     float *out, *lse;
     long long N;
     int max_atoms;
+    int K;         // 64: with the radial basis and its projection W; 0: without
     BoxRule rule;
     double dist_max, wscale;
     bool chained;  // launch as a chained kernel (common.cuh)

@@ -252,7 +252,7 @@ def term_list_build(pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, cu
 
 def row_list_build(pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, cutoff_radius, lattice_range,
                    minimum_range, a_widest, row_order=None):
-    """Row lists of a batch of crystals of at most 32 atoms (see cf_row_list_build): the workspace tensor to hand to
+    """Row lists of a batch of crystals of at most 64 atoms (see cf_row_list_build): the workspace tensor to hand to
     ``infinite_attn_fwd_sorted`` for every layer of the batch."""
     dev = pos_ij.device
     pos_ij, tvecs, rvlen = (_want(t, torch.float32, n, dev) for t, n in ((pos_ij, "pos_ij"), (tvecs, "tvecs"), (rvlen, "rvlen")))
@@ -270,7 +270,7 @@ def row_list_build(pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, cut
 
 def infinite_attn_fwd_sorted(q, k, v, a, pos_ij, tvecs, rvlen, batch, edges, row_start, max_atoms, K, dist_max, wscale,
                              W, cutoff_radius, lattice_range, minimum_range, row_lists):
-    """Fused attention forward over a batch's row lists (inference; crystals of at most 32 atoms, K = 64).
+    """Fused attention forward over a batch's row lists (inference; crystals of at most 64 atoms, K = 64 or 0).
     Returns (out (N,H,D), lse (N,H))."""
     dev = q.device
     q, k, v, a, tvecs = (_want(t, torch.float32, n, dev) for t, n in

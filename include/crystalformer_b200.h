@@ -66,7 +66,7 @@ void cf_set_weight_floor_log2(double log2_floor);
 double cf_get_weight_floor_log2(void);
 
 /* Whether cf_encoder_forward / cf_model_forward may take the row-list path (cf_row_list_build +
- * cf_infinite_attn_fwd_sorted, below) for batches whose crystals have at most 32 atoms; 1 by default, 0 keeps the
+ * cf_infinite_attn_fwd_sorted, below) for batches whose crystals have at most 64 atoms; 1 by default, 0 keeps the
  * term-list kernels for every batch.  Process-wide, read at launch time. */
 void cf_set_sorted_rows(int enabled);
 int cf_get_sorted_rows(void);
@@ -272,7 +272,9 @@ int cf_infinite_attn_bwd_listed(const float *q, const float *k, const float *v, 
                                 void *stream);
 
 /* ------------------------------------------------------------------------------------------------------------
- * Row lists and the tensor-core row kernel for batches of small crystals (max_atoms <= 32, K = 64, inference).
+ * Row lists and the tensor-core row kernel for batches of small crystals (max_atoms <= 64; K = 64, or K = 0: no
+ * radial basis, W may be NULL; inference).  The one-call forwards use them for K = 64 (without a basis the
+ * enumerating kernel with term lists is the faster one).
  * Same function as cf_infinite_attn_fwd (real_enc_proj_fwd + fused_dpa_fwd of the reference,
  * models/kernels/real_enc_proj_fwd.cu:63-169, models/kernels/fused_dpa_fwd_v3.cu), other organisation:
  * cf_row_list_build stores, per ATOM ROW, all (key, translation) terms within the term-list window of their edge's
@@ -282,8 +284,8 @@ int cf_infinite_attn_bwd_listed(const float *q, const float *k, const float *v, 
  * as mma.m16n8k8 products (TF32 operands split into high and low parts: fp32-level accuracy).  The sweep stops at the
  * first eight entries that are below the weight floor for every head of this layer.  Rows that do not fit the
  * workspace (more than 4096 entries, or the pool is full) and rows where a head's box misses every listed term are
- * processed by the enumerating kernel of cf_infinite_attn_fwd inside the same call: results do not depend on the
- * capacities.  No logits are written (inference); lse (N,H) is.
+ * processed by the enumerating kernel of cf_infinite_attn_fwd inside the same call (rows without a basis or of more
+ * than 32 keys enumerate phi edge by edge there: slow, and rare): results do not depend on the capacities.  No logits are written (inference); lse (N,H) is.
  *   workspace: cf_row_list_workspace_bytes(N, E) bytes, 16-byte aligned, built with the weight floor in force at the
  *   time; it also holds the row counters of the calls that use it, so calls sharing a workspace must be ordered
  *   (one stream), and every build allows any number of calls.

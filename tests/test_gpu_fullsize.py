@@ -226,14 +226,16 @@ def test_listed_backward_against_the_float64_oracle_at_cfg3_size(ops):
         assert rel_err(got[rows].cpu().numpy(), want) < TOL, name
 
 
-def test_one_call_model_forward_of_the_bench_configuration_against_the_cpu_model():
+@pytest.mark.parametrize("config,crystals", [("cfg0", 24), ("cfg3", 20)])
+def test_one_call_model_forward_of_the_bench_configuration_against_the_cpu_model(config, crystals):
     """The path the benchmark times - cf_model_forward: embedding inside the first dense block, row lists, the sorted
     row kernel, the fused dense blocks, pooling + head - on the 4-layer, ff 512, K = 64 model over 24 crystals of the
-    headline configuration, against the CPU restatement of the reference model with the same state_dict."""
+    headline configuration (at most 30 atoms: two key tiles) and 20 of the training configuration (up to 40 atoms: four
+    key tiles), against the CPU restatement of the reference model with the same state_dict."""
     import types
     import bench
     from oracle.model_cpu import forward_cpu
-    cb = make_config("cfg0", num_crystals=24)
+    cb = make_config(config, num_crystals=crystals)
     model, params = bench.make_model(4, 64)
     model = model.cuda()
     batch = bench.to_device_batch(cb, torch.device("cuda"))

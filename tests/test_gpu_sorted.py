@@ -115,6 +115,58 @@ def test_sorted_rows_against_oracle_chain(ops, cutoff, minimum, nmax, floor):
         assert no_list == 0
 
 
+@pytest.mark.parametrize("nmax,Kb,cutoff,lengths", [(48, 64, -3.5, (4.0, 11.0)), (60, 64, -3.5, (4.0, 11.0)),
+                                                    (64, 64, 0.0, (4.0, 11.0)), (20, 0, -3.5, (4.0, 11.0)),
+                                                    (40, 0, -3.5, (4.0, 11.0)), (60, 0, 0.0, (4.0, 11.0)),
+                                                    (56, 64, -3.5, (2.5, 4.5)), (56, 0, -3.5, (2.5, 4.5)),
+                                                    (24, 0, -3.5, (2.5, 3.5))])
+def test_sorted_rows_up_to_64_keys_and_without_basis(ops, nmax, Kb, cutoff, lengths):
+    """Crystals of up to 64 atoms (four key tiles; a lane looks after two keys) and the variant without a radial basis
+    (K = 0: no histogram, no projection), against the float64 oracle chain and the enumerating kernel.  The cases with
+    cells of a few Angstrom have rows of more than 4096 entries, which are left over to the enumerating row kernel
+    inside the same call (it enumerates phi edge by edge there: neither a phi kernel nor term lists serve those rows)."""
+    cb = make_crystals(73, 8, uniform_atoms(max(1, nmax // 2), nmax), length_range=lengths)
+    prep = prepare(ops, cb)
+    N = cb.num_atoms
+    rng = np.random.default_rng(73)
+    sig = 1.4 * (0.6 + 0.9 * rng.random((N, H)))
+    a = (-0.5 / sig ** 2).astype(np.float32)
+    a_widest = float(-0.5 / (1.4 * 1.5) ** 2)
+    W = (rng.standard_normal((H, D, 64)) * 0.1).astype(np.float32) if Kb else None
+    q = (rng.standard_normal((N, H, D)) * 0.5).astype(np.float32)
+    k, v = (rng.standard_normal((N, H, D)).astype(np.float32) for _ in range(2))
+    tv, max_atoms = dev(cb.trans_vec), int(cb.sizes.max())
+    assert max_atoms > 32 or Kb == 0
+    lists = ops.row_list_build(prep["pos_ij"], tv, prep["rvlen"], prep["batch"], prep["edges"], prep["row_start"], max_atoms,
+                               cutoff, 2, 2, a_widest)
+    run = lambda: ops.infinite_attn_fwd_sorted(dev(q), dev(k), dev(v), dev(a), prep["pos_ij"], tv, prep["rvlen"], prep["batch"],
+                                               prep["edges"], prep["row_start"], max_atoms, Kb, DIST_MAX, WSCALE,
+                                               None if W is None else dev(W), cutoff, 2, 2, lists)
+    out, lse = run()
+    again, lse2 = run()
+    assert torch.equal(out, again) and torch.equal(lse, lse2)
+    plain = ops.infinite_attn_fwd(dev(q), dev(k), dev(v), dev(a), prep["pos_ij"], tv, prep["rvlen"], prep["batch"],
+                                  prep["edges"], prep["row_start"], max_atoms, Kb, DIST_MAX, WSCALE,
+                                  None if W is None else dev(W), cutoff, 2, 2)
+    assert rel_err(out.cpu().numpy(), plain[0].cpu().numpy()) < 2e-5
+    edges = oracle.edge_index(cb.sizes)
+    pos_ij, _, _, rvlen = oracle.geometry(cb.pos, cb.trans_vec, edges)
+    z, psiW = oracle.lattice_sum_fwd(a, pos_ij, cb.trans_vec, cb.batch, edges, Kb, DIST_MAX, WSCALE,
+                                     W=None if W is None else W[None], rvlen=rvlen, cutoff_radius=cutoff, minimum_range=2,
+                                     precision="f64")
+    prob, ref = oracle.fused_attn_fwd(q, k, v, z, psiW if Kb else None, edges, precision="f64")
+    assert rel_err(out.cpu().numpy(), ref) < TOL
+    logit = np.einsum("ehd,ehd->eh", q[edges[0]].astype(np.float64), k[edges[1]].astype(np.float64)) + z
+    ref_lse = np.full((N, H), -np.inf)
+    np.logaddexp.at(ref_lse, edges[0], logit)
+    assert np.abs(lse.cpu().numpy() - ref_lse).max() < 1e-4 * max(1.0, np.abs(ref_lse).max())
+    # rows computed by the enumerating kernel: those without a list (more than 4096 entries)
+    rowdir, _, sched, *_ = carve(lists, N, cb.num_edges)
+    no_list = int((rowdir[:, 4] < 0).sum())
+    assert int(sched[15, 1]) >= no_list
+    assert (no_list > 0) == (lengths[1] < 5.0)
+
+
 def test_row_lists_are_sorted_and_complete(ops):
     """Structure of the lists: every row's entries ascend in d2, keys are the row's keys, the per-edge minimum is the
     smallest listed d2 of the edge, and the entries of a row are exactly the entries of its edges' term lists."""
