@@ -97,6 +97,17 @@ def term_lists_for(edges: Tensor, pos_ij: Tensor, tvecs: Tensor, rvlen: Optional
     return hit[0], hit[1]
 
 
+_HEAD_INDEX = {}
+
+
+def _head_index(H: int, device) -> Tensor:
+    """arange(H) on the device, made once."""
+    key = (H, device)
+    if key not in _HEAD_INDEX:
+        _HEAD_INDEX[key] = torch.arange(H, device=device)
+    return _HEAD_INDEX[key]
+
+
 class InfiniteAttentionFunction(torch.autograd.Function):
     """out_i = sum_j softmax_j(q_i.k_j + phi_ij) (v_j + W psi_ij), phi/psi recomputed in forward and backward.
 
@@ -136,8 +147,34 @@ class InfiniteAttentionFunction(torch.autograd.Function):
             # atoms (eight times the flops of the per-head products, and a fraction of their time at these sizes)
             N, H, D = gout.shape
             full = gout.reshape(N, H * D).t() @ psi_row.reshape(N, H * K)
-            gW = torch.stack([full[h * D:(h + 1) * D, h * K:(h + 1) * K] for h in range(H)]).reshape(ctx.w_shape)
+            heads = _head_index(H, full.device)
+            gW = full.view(H, D, H, K)[heads, :, heads, :].reshape(ctx.w_shape)  # (one gather instead of H slices)
         return (gq, gk, gv, ga, gW) + (None,) * 15
+
+
+class EluWidthFunction(torch.autograd.Function):
+    """a = c ((1 - lb) elu(t) + 1),  t = (q . w + shift) scale beta / (1 - lb)  per (atom, head): the default pipeline from
+    the projected query to the Gaussian parameter (…attention_cuda.py:647-722 with positive_func "elu", gauss_state "q",
+    normalize_gauss) as ONE autograd node.  Same arithmetic, in the same order, as the operation-by-operation code of
+    ``_widths``; a training step records and replays eight operations per layer less."""
+
+    @staticmethod
+    def forward(ctx, q, w, scale, shift, beta, lb, c):
+        alpha = (q * w).sum(dim=-1)
+        t = ((alpha + shift) * scale) * (beta / (1.0 - lb))
+        e = F.elu(t)
+        ctx.save_for_backward(q, w, e, scale)
+        ctx.factor = c * beta  # da/dalpha = c beta scale elu'(t)
+        return ((1.0 - lb) * e + 1.0) * c
+
+    @staticmethod
+    def backward(ctx, ga):
+        q, w, e, scale = ctx.saved_tensors
+        # elu'(t) = 1 for t > 0, exp(t) = elu(t) + 1 otherwise
+        galpha = ga * (torch.clamp(e, max=0.0) + 1.0) * (scale * ctx.factor)
+        gq = galpha.unsqueeze(-1) * w if ctx.needs_input_grad[0] else None
+        gw = torch.einsum("nh,nhd->hd", galpha, q).reshape(w.shape) if ctx.needs_input_grad[1] else None
+        return gq, gw, None, None, None, None, None
 
 
 def positive_function(name: str):
@@ -257,6 +294,12 @@ class CrystalformerMultiheadAttentionCUDA(Module):
         P = self.params
         N, H, Dq = q.shape
         w = self.lattice_pos_weights
+        if P.gauss_state.startswith("q") and P.normalize_gauss and self._scale_known and P.domain == "real" \
+                and P.positive_func.startswith("elu") and torch.is_grad_enabled():
+            # training with the default pipeline: one autograd node
+            beta = float(P.positive_func.split("=")[1]) if "=" in P.positive_func else 1.0
+            return EluWidthFunction.apply(q, w.reshape(1, H, Dq), self.gauss_scale[0], self.gauss_scale[1], beta,
+                                          float(P.gauss_lb_real), -0.5 * P.scale_real ** -2)
         if P.gauss_state.startswith("q"):
             # q_h . w_h per (atom, head): an element-wise product and a 16-term sum (the reference writes it as a batched
             # matrix product, ...attention_cuda.py:647, which launches a GEMM per head for a dot product)

@@ -113,3 +113,25 @@ def test_a_rank_that_leaves_makes_the_others_fail_not_hang(tmp_path):
     outs = run_ranks(tmp_path, 2, extra_env={"FAIL_RANK": "1"}, timeout=90)
     assert outs[1][0] == 3
     assert outs[0][0] != 0 and "GATHER_OK" not in outs[0][1]
+
+
+def test_elu_width_function_equals_the_recorded_operations():
+    """The one-node width pipeline of the attention module (training, default parameters) against the same arithmetic
+    recorded operation by operation: equal values, equal gradients (float64, CPU)."""
+    import torch
+    import torch.nn.functional as F
+    from crystalformer_b200.attention import EluWidthFunction
+    torch.manual_seed(0)
+    N, H, D = 37, 8, 16
+    q = torch.randn(N, H, D, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(1, H, D, dtype=torch.float64, requires_grad=True)
+    scale, shift = torch.tensor(0.7, dtype=torch.float64), torch.tensor(-0.2, dtype=torch.float64)
+    beta, lb, c = 0.1, 0.5, -0.5 / 1.4 ** 2
+    a = EluWidthFunction.apply(q, w, scale, shift, beta, lb, c)
+    ga = torch.randn(N, H, dtype=torch.float64)
+    gq, gw = torch.autograd.grad(a, (q, w), ga)
+    alpha = ((q * w).sum(-1) + shift) * scale
+    ref = ((1.0 - lb) * F.elu(alpha * (beta / (1.0 - lb))) + 1.0) * c
+    rq, rw = torch.autograd.grad(ref, (q, w), ga)
+    assert torch.equal(a, ref)
+    assert torch.allclose(gq, rq, rtol=1e-12, atol=1e-14) and torch.allclose(gw, rw, rtol=1e-12, atol=1e-14)
