@@ -57,7 +57,9 @@ int cf_version(void);
  * failing call on the same thread. */
 const char *cf_last_error(void);
 
-/* Terms of a lattice sum whose weight is below 2^log2_floor of the sum's largest term for every head are left out:
+/* An approximation, not a bit-neutral skip: terms of a lattice sum whose weight is below 2^log2_floor of the sum's
+ * largest term for every head are left out (and the backward contracts the radial basis over the 20 bins around a
+ * term only):
  * in phi relative to the nearest image, in the radial-basis accumulation relative to the normalised total (in the
  * fused attention: relative to the whole row's soft-max total).  Default -30: such a term is below 1/64 ulp of a
  * float32 sum (measured change of the attention output 6e-8 relative, against 4e-9 at -40); pass -1000 to
