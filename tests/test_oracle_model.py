@@ -135,3 +135,23 @@ def test_elu_width_function_equals_the_recorded_operations():
     rq, rw = torch.autograd.grad(ref, (q, w), ga)
     assert torch.equal(a, ref)
     assert torch.allclose(gq, rq, rtol=1e-12, atol=1e-14) and torch.allclose(gw, rw, rtol=1e-12, atol=1e-14)
+
+
+def test_copies_of_a_batch_are_dealt_one_per_rank():
+    """The weak-scaling batch of the benchmark: N copies of the one-GPU batch.  The greedy split on the row cost (which
+    differs from crystal to crystal) gives every rank exactly one copy of every crystal; on n^2, where different crystals
+    tie, every rank still gets the same multiset of sizes.  Either way the work per rank is the one-GPU work."""
+    import numpy as np
+    from crystalformer_b200.sharding import crystal_cost, lpt_assign
+    from crystalformer_b200.synthetic import make_config
+    one = make_config("cfg0", num_crystals=32)
+    for world in (2, 4, 8):
+        tiled = one.select(np.tile(np.arange(one.num_crystals), world))
+        for weights in (None, crystal_cost(tiled.sizes, tiled.trans_vec)):
+            shards = lpt_assign(tiled.sizes, world, weights=weights)
+            assert sorted(i for s in shards for i in s) == list(range(tiled.num_crystals))
+            for s in shards:
+                if weights is None:
+                    assert sorted(tiled.sizes[list(s)].tolist()) == sorted(one.sizes.tolist())
+                else:
+                    assert sorted(int(i) % one.num_crystals for i in s) == list(range(one.num_crystals))
